@@ -1,0 +1,138 @@
+/*
+ * spingalett_b200_kernels.h -- the thin C shim between the C23 host library
+ * and the hand-written sm_100a kernels.
+ *
+ * Everything here is `extern "C"`, takes plain pointers and sizes, and runs on
+ * the CUDA device that is current on the calling thread.  Device pointers are
+ * marked "dev".  Every function returns 0 on success or a negative SPGK_E_*
+ * code; spgk_error_string() describes the last failure on the calling thread.
+ * None of these functions has a CPU implementation: with no CUDA device they
+ * fail.
+ *
+ * Each compute entry point names the reference routine (pka-human/Spingalett,
+ * path:line) whose work it does on the GPU.
+ */
+#pragma once
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef SPGK_API
+#  define SPGK_API __attribute__((visibility("default")))
+#endif
+
+#define SPGK_OK            0
+#define SPGK_E_CUDA       -1   /* a CUDA runtime/driver call failed            */
+#define SPGK_E_ARG        -2   /* argument outside what the kernel supports   */
+#define SPGK_E_NOMEM      -3   /* device or pinned-host allocation failed     */
+#define SPGK_E_TIMEOUT    -4   /* a bounded device-side wait gave up          */
+#define SPGK_E_UNSUPPORTED -5  /* shape/format not handled by this fast path  */
+
+/* One dense layer as the kernels see it.  `w` is the weight matrix exactly as
+ * Serialize.c stores it (row-major [out][in], packing running across rows),
+ * WITHOUT the leading abs-max float of the integer formats; that scalar
+ * arrives pre-divided in w_scale (abs_max/127, /7, /1; 1.0 for float
+ * formats), so value = q * w_scale (reference Serialize.c:222-294). */
+typedef struct {
+    const void  *w;          /* dev, 256-byte aligned                        */
+    const float *bias;       /* dev, fp32 [out], already dequantised          */
+    float        w_scale;
+    uint32_t     in;
+    uint32_t     out;
+    int32_t      precision;  /* PrecisionMode: 0 f32, 1 f16, 2 bf16, 3 i8, 4 i4, 5 i2 */
+    int32_t      act;        /* ActivationFunction                            */
+} spgk_layer;
+
+/* 16-bit operand flavour used on the tensor-core paths. */
+#define SPGK_T_F16   0
+#define SPGK_T_BF16  1
+
+SPGK_API const char *spgk_error_string(void);
+
+/* ---- device plumbing ---------------------------------------------------- */
+SPGK_API int spgk_device_count(int *count);
+SPGK_API int spgk_set_device(int device);
+SPGK_API int spgk_get_device(int *device);
+/* compute capability major*10+minor and SM count of the current device */
+SPGK_API int spgk_device_info(int *cc, int *sm_count, size_t *total_mem);
+SPGK_API int spgk_malloc(void **dev, size_t bytes);
+SPGK_API int spgk_free(void *dev);
+SPGK_API int spgk_host_alloc(void **host, size_t bytes);     /* pinned */
+SPGK_API int spgk_host_free(void *host);
+SPGK_API int spgk_memcpy_h2d(void *dev, const void *host, size_t bytes, void *stream);
+SPGK_API int spgk_memcpy_d2h(void *host, const void *dev, size_t bytes, void *stream);
+SPGK_API int spgk_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream);
+SPGK_API int spgk_memset(void *dev, int value, size_t bytes, void *stream);
+SPGK_API int spgk_stream_sync(void *stream);
+/* 1 if ptr is device (or managed) memory, 0 if host, <0 on error */
+SPGK_API int spgk_is_device_pointer(const void *ptr);
+/* number of kernel launches made through this shim by the calling process */
+SPGK_API uint64_t spgk_launch_count(void);
+
+/* ---- K0: general layer, fp32 SIMT ---------------------------------------
+ * y[n][j] = act(bias[j] + w_scale * sum_k q[j][k] * x[n][k]) for any
+ * precision and any shape (odd widths, packed rows starting mid-byte).
+ * x: dev fp32 [N][in] (row stride ldx floats), y: dev fp32 [N][out] (ldy).
+ * ACT_SOFTMAX is NOT applied here (use spgk_softmax_rows afterwards).
+ * Does the work of forward()'s layer step, reference Network.c:218-247. */
+SPGK_API int spgk_layer_simt(const spgk_layer *L, const float *x, uint32_t ldx,
+                             float *y, uint32_t ldy, uint32_t N, void *stream);
+
+/* ---- softmax over rows, in place ----------------------------------------
+ * Reference Activation.c:5-21 per row: max from -FLT_MAX, expf(x-max), scale
+ * by 1/sum only if sum > 0.  width <= 65535. */
+SPGK_API int spgk_softmax_rows(float *y, uint32_t ldy, uint32_t N, uint32_t width, void *stream);
+
+/* ---- split fp32 activations into 16-bit terms ----------------------------
+ * dst holds `parts` planes of [N][ld16] 16-bit values (plane stride
+ * plane_elems): plane 0 = round(x), plane 1 = round(x - plane0), ...
+ * Columns in..ld16 are zero-filled.  type = SPGK_T_F16 / SPGK_T_BF16. */
+SPGK_API int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in,
+                          void *dst, uint32_t ld16, uint64_t plane_elems,
+                          int parts, int type, void *stream);
+
+/* ---- K1: small-batch fused dequant-GEMV ----------------------------------
+ * Whole layer for 1 <= N <= SPGK_GEMV_MAX_BATCH rows: streams the packed
+ * weights once with 128-bit loads, dequantises in registers, multiplies on
+ * the warp-level tensor path against a two/three-term bf16 split of x,
+ * reduces across warps, applies bias + activation.  Memory-bound by design.
+ * Needs 16-byte aligned packed rows (returns SPGK_E_UNSUPPORTED otherwise).
+ * scratch: dev, at least spgk_gemv_scratch_bytes(L, N) bytes.
+ * Does forward()'s layer step, reference Network.c:218-247 / SIMD.c:190-240. */
+#define SPGK_GEMV_MAX_BATCH 16
+SPGK_API size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N);
+SPGK_API int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx,
+                             float *y, uint32_t ldy, uint32_t N,
+                             void *scratch, void *stream);
+
+/* ---- K2: large-batch tcgen05 GEMM layer ----------------------------------
+ * C[N][out] = act(bias + w_scale * A[N][in] * W^T) with the accumulator in
+ * tensor memory.  A is the 16-bit split produced by spgk_split16 or by the
+ * previous layer's epilogue (`a_parts` planes, row stride lda elements, plane
+ * stride a_plane elements).  W is read in its stored precision: 16-bit files
+ * go from global to shared memory by TMA, the other precisions are
+ * dequantised into the shared-memory operand tile by converter warps.
+ * Output: if out16 != NULL, `out_parts` 16-bit planes for the next layer
+ * (row stride ldo16, plane stride o_plane; padding columns zeroed); if
+ * out32 != NULL, fp32 [N][ldo32].  When softmax_fused != 0 the activation is
+ * ACT_SOFTMAX and out <= the kernel's N tile, so the row softmax is applied in
+ * the epilogue; otherwise softmax layers need spgk_softmax_rows afterwards.
+ * status: dev int32[4] scratch the kernel reports bounded-wait failures in.
+ * Does batch_forward()'s layer step, reference Training.c:318-343. */
+SPGK_API int spgk_layer_gemm_tc(const spgk_layer *L,
+                                const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int a_type,
+                                void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
+                                float *out32, uint32_t ldo32,
+                                uint32_t N, int softmax_fused, int32_t *status, void *stream);
+/* 1 if spgk_layer_gemm_tc can take this layer (alignment/format rules). */
+SPGK_API int spgk_gemm_tc_supported(const spgk_layer *L);
+/* widest softmax the GEMM epilogue can fuse */
+SPGK_API uint32_t spgk_gemm_tc_softmax_max(void);
+
+#ifdef __cplusplus
+}
+#endif

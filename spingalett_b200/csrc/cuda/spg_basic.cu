@@ -1,0 +1,233 @@
+// spg_basic.cu -- device plumbing of the C shim, the general SIMT layer kernel
+// (any precision, any shape), the row softmax and the 16-bit activation split.
+#include "spg_common.cuh"
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+static thread_local char g_err[512] = "no error";
+static std::atomic<uint64_t> g_launches{0};
+
+void spgk_set_error(const char *what, const char *detail)
+{
+    snprintf(g_err, sizeof g_err, "%s: %s", what ? what : "?", detail ? detail : "?");
+}
+void spgk_count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int spgk_check_launch(const char *kernel_name)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { spgk_set_error(kernel_name, cudaGetErrorString(e)); return SPGK_E_CUDA; }
+    spgk_count_launch();
+    return SPGK_OK;
+}
+
+extern "C" {
+
+const char *spgk_error_string(void) { return g_err; }
+uint64_t spgk_launch_count(void) { return g_launches.load(); }
+
+int spgk_device_count(int *count)
+{
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) { *count = 0; spgk_set_error("cudaGetDeviceCount", cudaGetErrorString(e)); return SPGK_E_CUDA; }
+    *count = n;
+    return SPGK_OK;
+}
+int spgk_set_device(int device) { SPGK_CUDA(cudaSetDevice(device)); return SPGK_OK; }
+int spgk_get_device(int *device) { SPGK_CUDA(cudaGetDevice(device)); return SPGK_OK; }
+int spgk_device_info(int *cc, int *sm_count, size_t *total_mem)
+{
+    int dev = 0;
+    SPGK_CUDA(cudaGetDevice(&dev));
+    cudaDeviceProp p;
+    SPGK_CUDA(cudaGetDeviceProperties(&p, dev));
+    if (cc) *cc = p.major * 10 + p.minor;
+    if (sm_count) *sm_count = p.multiProcessorCount;
+    if (total_mem) *total_mem = p.totalGlobalMem;
+    return SPGK_OK;
+}
+int spgk_malloc(void **dev, size_t bytes)
+{
+    *dev = nullptr;
+    SPGK_CUDA(cudaMalloc(dev, bytes ? bytes : 256));
+    return SPGK_OK;
+}
+int spgk_free(void *dev) { if (dev) SPGK_CUDA(cudaFree(dev)); return SPGK_OK; }
+int spgk_host_alloc(void **host, size_t bytes)
+{
+    *host = nullptr;
+    SPGK_CUDA(cudaHostAlloc(host, bytes ? bytes : 64, cudaHostAllocDefault));
+    return SPGK_OK;
+}
+int spgk_host_free(void *host) { if (host) SPGK_CUDA(cudaFreeHost(host)); return SPGK_OK; }
+int spgk_memcpy_h2d(void *dev, const void *host, size_t bytes, void *stream)
+{
+    SPGK_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return SPGK_OK;
+}
+int spgk_memcpy_d2h(void *host, const void *dev, size_t bytes, void *stream)
+{
+    SPGK_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return SPGK_OK;
+}
+int spgk_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream)
+{
+    SPGK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return SPGK_OK;
+}
+int spgk_memset(void *dev, int value, size_t bytes, void *stream)
+{
+    SPGK_CUDA(cudaMemsetAsync(dev, value, bytes, (cudaStream_t)stream));
+    return SPGK_OK;
+}
+int spgk_stream_sync(void *stream) { SPGK_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); return SPGK_OK; }
+int spgk_is_device_pointer(const void *ptr)
+{
+    cudaPointerAttributes a;
+    cudaError_t e = cudaPointerGetAttributes(&a, ptr);
+    if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+    return (a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged) ? 1 : 0;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// K0: general layer.  One warp per output neuron j and tile of up to NB batch
+// rows; lanes stride over k.  Every stored element is decoded individually, so
+// rows of packed formats may start in the middle of a byte.
+// ---------------------------------------------------------------------------
+template <int NB>
+__global__ void __launch_bounds__(256)
+spg_layer_simt_kernel(const void *__restrict__ w, const float *__restrict__ bias, float w_scale,
+                      uint32_t in, uint32_t out, int precision, int act,
+                      const float *__restrict__ x, uint32_t ldx, float *__restrict__ y, uint32_t ldy, uint32_t N)
+{
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t j = blockIdx.x * 8u + warp;
+    const uint32_t n0 = blockIdx.y * NB;
+    if (j >= out) return;
+    float acc[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+    const uint64_t row0 = (uint64_t)j * in;
+    for (uint32_t k = lane; k < in; k += 32u) {
+        float q = spg_decode_elem(w, row0 + k, precision);
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            uint32_t n = n0 + b;
+            float xv = n < N ? x[(uint64_t)n * ldx + k] : 0.0f;
+            acc[b] = fmaf(q, xv, acc[b]);
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < NB; b++) acc[b] = spg_warp_sum(acc[b]);
+    if (lane == 0) {
+        float bj = bias ? bias[j] : 0.0f;
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            uint32_t n = n0 + b;
+            if (n < N) y[(uint64_t)n * ldy + j] = spg_activate(fmaf(acc[b], w_scale, bj), act);
+        }
+    }
+}
+
+// Row softmax, one warp per row (Activation.c:5-21).
+__global__ void __launch_bounds__(256)
+spg_softmax_rows_kernel(float *__restrict__ y, uint32_t ldy, uint32_t N, uint32_t width)
+{
+    const uint32_t row = blockIdx.x * 8u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (row >= N) return;
+    float *r = y + (uint64_t)row * ldy;
+    float mx = -FLT_MAX;
+    for (uint32_t i = lane; i < width; i += 32u) { float v = r[i]; if (v > mx) mx = v; }
+    mx = spg_warp_max(mx);
+    float sum = 0.0f;
+    for (uint32_t i = lane; i < width; i += 32u) { float e = expf(r[i] - mx); r[i] = e; sum += e; }
+    sum = spg_warp_sum(sum);
+    if (sum > 0.0f) {
+        float inv = 1.0f / sum;
+        for (uint32_t i = lane; i < width; i += 32u) r[i] *= inv;
+    }
+}
+
+// fp32 -> `parts` 16-bit planes (term p = round(x - sum of earlier terms)).
+template <typename T16>
+__device__ __forceinline__ T16 spg_to16(float v);
+template <> __device__ __forceinline__ __half spg_to16<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 spg_to16<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <typename T16>
+__device__ __forceinline__ float spg_from16(T16 v);
+template <> __device__ __forceinline__ float spg_from16<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float spg_from16<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T16>
+__global__ void __launch_bounds__(256)
+spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t in,
+                   T16 *__restrict__ dst, uint32_t ld16, uint64_t plane_elems, int parts)
+{
+    const uint64_t total = (uint64_t)N * ld16;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint32_t n = (uint32_t)(i / ld16), k = (uint32_t)(i % ld16);
+        float v = k < in ? x[(uint64_t)n * ldx + k] : 0.0f;
+        for (int p = 0; p < parts; p++) {
+            T16 h = spg_to16<T16>(v);
+            dst[(uint64_t)p * plane_elems + i] = h;
+            v -= spg_from16<T16>(h);
+        }
+    }
+}
+
+extern "C" {
+
+int spgk_layer_simt(const spgk_layer *L, const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N, void *stream)
+{
+    if (!L || !x || !y || !L->w || L->in == 0 || L->out == 0 || (unsigned)L->precision >= SPG_P_COUNT) {
+        spgk_set_error("spgk_layer_simt", "bad argument");
+        return SPGK_E_ARG;
+    }
+    if (N == 0) return SPGK_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 block(256);
+    uint32_t gx = (L->out + 7u) / 8u;
+    int act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
+    // gridDim.y is limited to 65535: walk the batch in slabs
+    const uint32_t NB = N >= 8 ? 8 : (N >= 4 ? 4 : (N >= 2 ? 2 : 1));
+    const uint32_t slab = 65535u * NB;
+    for (uint32_t n0 = 0; n0 < N; n0 += slab) {
+        uint32_t n = N - n0 < slab ? N - n0 : slab;
+        dim3 grid(gx, (n + NB - 1) / NB);
+        const float *xs = x + (uint64_t)n0 * ldx;
+        float *ys = y + (uint64_t)n0 * ldy;
+#define SPG_LAUNCH_SIMT(NBV) spg_layer_simt_kernel<NBV><<<grid, block, 0, s>>>(L->w, L->bias, L->w_scale, L->in, L->out, L->precision, act, xs, ldx, ys, ldy, n)
+        if (NB == 8) SPG_LAUNCH_SIMT(8); else if (NB == 4) SPG_LAUNCH_SIMT(4); else if (NB == 2) SPG_LAUNCH_SIMT(2); else SPG_LAUNCH_SIMT(1);
+#undef SPG_LAUNCH_SIMT
+        int rc = spgk_check_launch("spg_layer_simt_kernel");
+        if (rc) return rc;
+    }
+    return SPGK_OK;
+}
+
+int spgk_softmax_rows(float *y, uint32_t ldy, uint32_t N, uint32_t width, void *stream)
+{
+    if (!y || width == 0 || width > 65535u) { spgk_set_error("spgk_softmax_rows", "bad argument"); return SPGK_E_ARG; }
+    if (N == 0) return SPGK_OK;
+    spg_softmax_rows_kernel<<<(N + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(y, ldy, N, width);
+    return spgk_check_launch("spg_softmax_rows_kernel");
+}
+
+int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in, void *dst, uint32_t ld16,
+                 uint64_t plane_elems, int parts, int type, void *stream)
+{
+    if (!x || !dst || parts < 1 || parts > 3 || ld16 < in) { spgk_set_error("spgk_split16", "bad argument"); return SPGK_E_ARG; }
+    if (N == 0) return SPGK_OK;
+    uint64_t total = (uint64_t)N * ld16;
+    uint32_t blocks = (uint32_t)((total + 255) / 256 < 148ull * 16 ? (total + 255) / 256 : 148ull * 16);
+    if (type == SPGK_T_F16)
+        spg_split16_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts);
+    else
+        spg_split16_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts);
+    return spgk_check_launch("spg_split16_kernel");
+}
+
+}  // extern "C"

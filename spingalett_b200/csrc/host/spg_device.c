@@ -1,0 +1,357 @@
+/* Device residency of a network and the orchestration of the layer chain.
+ *
+ * The weights go to the GPU exactly as stored (packed INT8/INT4/INT2, FP16,
+ * BF16 or FP32 images, one 256-byte aligned allocation per matrix); biases go
+ * as fp32.  Two chains exist: the small-batch chain (fused dequant-GEMV per
+ * layer, fp32 activations) and the large-batch chain (tcgen05 GEMM per layer,
+ * 16-bit activations between layers).  Shapes a fast kernel does not take run
+ * on the general SIMT kernel -- still on the GPU; nothing here computes on
+ * the CPU. */
+#include "spg_internal.h"
+#include <stdlib.h>
+#include <string.h>
+
+int spg_map_kernel_error(int rc, const char *where)
+{
+    if (rc == SPGK_OK) return SPINGALETT_OK;
+    int code = rc == SPGK_E_NOMEM ? SPINGALETT_ERR_ALLOC
+             : (rc == SPGK_E_ARG || rc == SPGK_E_UNSUPPORTED) ? SPINGALETT_ERR_INVALID
+             : SPINGALETT_ERR_DEVICE;
+    spg_set_errorf(code, "%s: %s", where, spgk_error_string());
+    spg_log(LOG_ERROR, "%s: %s", where, spgk_error_string());
+    return code;
+}
+
+static _Thread_local int t_device = -1;     /* device chosen with spingalett_set_device */
+
+int spingalett_set_device(int device)
+{
+    int rc = spg_map_kernel_error(spgk_set_device(device), "set_device");
+    if (rc == SPINGALETT_OK) t_device = device;
+    return rc;
+}
+
+int spingalett_get_device_count(void)
+{
+    int n = 0;
+    if (spgk_device_count(&n) != SPGK_OK) return 0;
+    return n;
+}
+
+void spingalett_set_stream(NeuralNetwork *net, void *cuda_stream)
+{
+    if (net) spg_priv(net)->stream = cuda_stream;
+}
+
+void spg_dev_invalidate(spg_net *n) { if (n->dev_ready) spg_dev_release(n); }
+
+static int bind_device(spg_net *n)
+{
+    if (n->device < 0) {
+        int count = 0;
+        if (spgk_device_count(&count) != SPGK_OK || count <= 0) {
+            spg_set_error(SPINGALETT_ERR_DEVICE, "no CUDA device available (this library has no CPU compute path)");
+            spg_log(LOG_ERROR, "no CUDA device available");
+            return SPINGALETT_ERR_DEVICE;
+        }
+        int cur = 0;
+        if (t_device >= 0) cur = t_device;
+        else if (spgk_get_device(&cur) != SPGK_OK) cur = 0;
+        n->device = cur;
+    }
+    return spg_map_kernel_error(spgk_set_device(n->device), "bind device");
+}
+
+void spg_dev_release(spg_net *n)
+{
+    if (n->device >= 0) spgk_set_device(n->device);
+    for (uint32_t l = 0; l < n->dev_layers; l++) {
+        if (n->d_w) spgk_free(n->d_w[l]);
+        if (n->d_bias) spgk_free(n->d_bias[l]);
+    }
+    free(n->d_w); free(n->d_bias); free(n->klayers);
+    n->d_w = NULL; n->d_bias = NULL; n->klayers = NULL; n->dev_layers = 0;
+    spgk_free(n->d_small); n->d_small = NULL; n->small_cap = 0;
+    spgk_free(n->d_gemv_scratch); n->d_gemv_scratch = NULL; n->gemv_scratch_bytes = 0;
+    spgk_free(n->d_in32); n->d_in32 = NULL; n->in32_bytes = 0;
+    spgk_free(n->d_out32); n->d_out32 = NULL; n->out32_bytes = 0;
+    for (int i = 0; i < 2; i++) {
+        spgk_free(n->d_act16[i]); n->d_act16[i] = NULL;
+        spgk_free(n->d_act32[i]); n->d_act32[i] = NULL;
+    }
+    n->act16_bytes = 0; n->act32_bytes = 0;
+    spgk_free(n->d_status); n->d_status = NULL;
+    n->dev_ready = false;
+}
+
+int spg_dev_ensure(spg_net *n)
+{
+    if (n->dev_ready) return spg_map_kernel_error(spgk_set_device(n->device), "bind device");
+    NeuralNetwork *p = &n->pub;
+    if (p->layers < 2) { spg_set_error(SPINGALETT_ERR_INVALID, "network has no weight layer"); return SPINGALETT_ERR_INVALID; }
+    int rc = bind_device(n);
+    if (rc) return rc;
+    uint32_t wl = p->layers - 1;
+    n->d_w = calloc(wl, sizeof *n->d_w);
+    n->d_bias = calloc(wl, sizeof *n->d_bias);
+    n->klayers = calloc(wl, sizeof *n->klayers);
+    if (!n->d_w || !n->d_bias || !n->klayers) {
+        spg_set_error(SPINGALETT_ERR_ALLOC, "device descriptor allocation failed");
+        free(n->d_w); free(n->d_bias); free(n->klayers);
+        n->d_w = NULL; n->d_bias = NULL; n->klayers = NULL;
+        return SPINGALETT_ERR_ALLOC;
+    }
+    n->dev_layers = wl;
+    const bool packed = n->payload_layers == wl && n->payload_w;
+    for (uint32_t l = 0; l < wl; l++) {
+        uint32_t in = p->topology[l], out = p->topology[l + 1];
+        const void *src;
+        size_t bytes;
+        float scale = 1.0f;
+        PrecisionMode prec;
+        if (packed) {
+            src = n->payload_w[l]; bytes = n->payload_w_bytes[l]; prec = n->store_precision;
+            if (prec >= PRECISION_INT8) {
+                float amax = n->amax_w[l];
+                scale = amax > 0.0f ? amax / spg_precision_q(prec) : 0.0f;     /* Serialize.c:232 */
+            }
+        } else {
+            src = p->weights + p->weight_offsets[l]; bytes = (size_t)in * out * sizeof(float); prec = PRECISION_FLOAT32;
+        }
+        /* slack so that whole-vector loads at the tail of the last row stay inside the allocation */
+        if ((rc = spg_map_kernel_error(spgk_malloc(&n->d_w[l], bytes + 256), "weight allocation"))) goto fail;
+        if ((rc = spg_map_kernel_error(spgk_memset((char *)n->d_w[l] + bytes, 0, 256, n->stream), "weight tail clear"))) goto fail;
+        if ((rc = spg_map_kernel_error(spgk_memcpy_h2d(n->d_w[l], src, bytes, n->stream), "weight upload"))) goto fail;
+        void *db = NULL;
+        if ((rc = spg_map_kernel_error(spgk_malloc(&db, (size_t)out * sizeof(float)), "bias allocation"))) goto fail;
+        n->d_bias[l] = db;
+        if ((rc = spg_map_kernel_error(spgk_memcpy_h2d(db, p->biases + p->bias_offsets[l], (size_t)out * sizeof(float), n->stream), "bias upload"))) goto fail;
+        n->klayers[l] = (spgk_layer){ .w = n->d_w[l], .bias = n->d_bias[l], .w_scale = scale, .in = in, .out = out,
+                                      .precision = (int32_t)prec, .act = (int32_t)p->act_func[l] };
+    }
+    void *st = NULL;
+    if ((rc = spg_map_kernel_error(spgk_malloc(&st, 64), "status allocation"))) goto fail;
+    n->d_status = st;
+    if ((rc = spg_map_kernel_error(spgk_memset(st, 0, 64, n->stream), "status clear"))) goto fail;
+    if ((rc = spg_map_kernel_error(spgk_stream_sync(n->stream), "upload sync"))) goto fail;
+    n->dev_ready = true;
+    return SPINGALETT_OK;
+fail:
+    spg_dev_release(n);
+    return rc;
+}
+
+int spingalett_sync_weights(NeuralNetwork *net)
+{
+    if (!net) { spg_set_error(SPINGALETT_ERR_INVALID, "sync_weights: net is NULL"); return SPINGALETT_ERR_INVALID; }
+    spg_net *n = spg_priv(net);
+    spg_dev_invalidate(n);
+    spg_net_drop_payload(n);            /* the host fp32 arrays are now the truth */
+    return SPINGALETT_OK;
+}
+
+/* grow-only device buffer */
+static int reserve(void **buf, size_t *have, size_t need, const char *what)
+{
+    if (*have >= need && *buf) return SPINGALETT_OK;
+    spgk_free(*buf); *buf = NULL; *have = 0;
+    int rc = spg_map_kernel_error(spgk_malloc(buf, need), what);
+    if (rc == SPINGALETT_OK) *have = need;
+    return rc;
+}
+
+/* ------------------------------------------------------------------------ */
+/* small-batch chain                                                         */
+/* ------------------------------------------------------------------------ */
+
+static int small_reserve(spg_net *n, uint32_t N)
+{
+    NeuralNetwork *p = &n->pub;
+    if (n->small_cap < N || !n->d_small) {
+        spgk_free(n->d_small); n->d_small = NULL; n->small_cap = 0;
+        void *b = NULL;
+        int rc = spg_map_kernel_error(spgk_malloc(&b, (size_t)N * p->total_neurons * sizeof(float)), "small-batch workspace");
+        if (rc) return rc;
+        n->d_small = b; n->small_cap = N;
+    }
+    size_t need = 0;
+    for (uint32_t l = 0; l < n->dev_layers; l++) {
+        size_t s = spgk_gemv_scratch_bytes(&n->klayers[l], N);
+        if (s > need) need = s;
+    }
+    if (need) return reserve(&n->d_gemv_scratch, &n->gemv_scratch_bytes, need, "gemv scratch");
+    return SPINGALETT_OK;
+}
+
+/* Runs N <= SPGK_GEMV_MAX_BATCH rows.  d_x == NULL means the caller already
+ * placed the input rows in slot 0 of the workspace (after this function
+ * reserved it through a first call with N rows -- see forward()). */
+int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N, float **d_last)
+{
+    NeuralNetwork *p = &n->pub;
+    int rc = small_reserve(n, N);
+    if (rc) return rc;
+    if (!d_last) return SPINGALETT_OK;          /* reservation only */
+    const float *x = d_x ? d_x : n->d_small;
+    uint32_t xld = d_x ? ldx : p->topology[0];
+    const char *path = "gemv";
+    for (uint32_t l = 0; l < n->dev_layers; l++) {
+        const spgk_layer *L = &n->klayers[l];
+        float *y = n->d_small + (size_t)N * p->neuron_offsets[l + 1];
+        int k = spgk_layer_gemv(L, x, xld, y, L->out, N, n->d_gemv_scratch, n->stream);
+        if (k == SPGK_E_UNSUPPORTED) {
+            path = "simt";
+            k = spgk_layer_simt(L, x, xld, y, L->out, N, n->stream);
+        }
+        if ((rc = spg_map_kernel_error(k, "layer (small batch)"))) return rc;
+        if (L->act == ACT_SOFTMAX && (rc = spg_map_kernel_error(spgk_softmax_rows(y, L->out, N, L->out, n->stream), "softmax"))) return rc;
+        x = y; xld = L->out;
+    }
+    spg_note_path(path);
+    *d_last = n->d_small + (size_t)N * p->neuron_offsets[p->layers - 1];
+    return SPINGALETT_OK;
+}
+
+/* ------------------------------------------------------------------------ */
+/* large-batch chain                                                         */
+/* ------------------------------------------------------------------------ */
+
+static uint32_t round8(uint32_t v) { return (v + 7u) & ~7u; }
+
+static int large_simt(spg_net *n, const float *d_x, uint32_t N, float *d_out)
+{
+    NeuralNetwork *p = &n->pub;
+    uint32_t maxw = 0;
+    for (uint32_t l = 1; l < p->layers; l++) if (p->topology[l] > maxw) maxw = p->topology[l];
+    size_t need = (size_t)N * maxw * sizeof(float);
+    if (n->act32_bytes < need) {
+        for (int i = 0; i < 2; i++) { spgk_free(n->d_act32[i]); n->d_act32[i] = NULL; }
+        n->act32_bytes = 0;
+        for (int i = 0; i < 2; i++) {
+            void *b = NULL;
+            int rc = spg_map_kernel_error(spgk_malloc(&b, need), "fp32 activation workspace");
+            if (rc) return rc;
+            n->d_act32[i] = b;
+        }
+        n->act32_bytes = need;
+    }
+    const float *x = d_x;
+    uint32_t xld = p->topology[0];
+    for (uint32_t l = 0; l < n->dev_layers; l++) {
+        const spgk_layer *L = &n->klayers[l];
+        bool last = l + 1 == n->dev_layers;
+        float *y = last ? d_out : n->d_act32[l & 1];
+        int rc = spg_map_kernel_error(spgk_layer_simt(L, x, xld, y, L->out, N, n->stream), "layer (simt)");
+        if (rc) return rc;
+        if (L->act == ACT_SOFTMAX && (rc = spg_map_kernel_error(spgk_softmax_rows(y, L->out, N, L->out, n->stream), "softmax"))) return rc;
+        x = y; xld = L->out;
+    }
+    spg_note_path("simt");
+    return SPINGALETT_OK;
+}
+
+int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out)
+{
+    NeuralNetwork *p = &n->pub;
+    bool tc = true;
+    for (uint32_t l = 0; l < n->dev_layers; l++) tc = tc && spgk_gemm_tc_supported(&n->klayers[l]);
+    if (!tc) return large_simt(n, d_x, N, d_out);
+
+    const bool exact = spingalett_get_math_mode() == SPINGALETT_MATH_EXACT;
+    const int prec = n->klayers[0].precision;
+    /* 16-bit flavour: the file's own 16-bit type when it has one (exact
+     * weights); otherwise fp16 for the one-term mode (11 significant bits) and
+     * bf16 for the two-term mode (fp32 range, 16 bits over two terms). */
+    const int type = prec == PRECISION_FP16 ? SPGK_T_F16 : prec == PRECISION_BFLOAT16 ? SPGK_T_BF16
+                   : exact ? SPGK_T_BF16 : SPGK_T_F16;
+    const int parts = exact ? 2 : 1;
+    uint32_t maxld = 0;
+    for (uint32_t l = 0; l + 1 < p->layers; l++) if (round8(p->topology[l]) > maxld) maxld = round8(p->topology[l]);
+    const uint64_t plane = (uint64_t)N * maxld;
+    size_t need = (size_t)plane * 2u * (size_t)parts;
+    if (n->act16_bytes < need) {
+        for (int i = 0; i < 2; i++) { spgk_free(n->d_act16[i]); n->d_act16[i] = NULL; }
+        n->act16_bytes = 0;
+        for (int i = 0; i < 2; i++) {
+            int rc = spg_map_kernel_error(spgk_malloc(&n->d_act16[i], need), "16-bit activation workspace");
+            if (rc) return rc;
+        }
+        n->act16_bytes = need;
+    }
+    int rc = spg_map_kernel_error(spgk_split16(d_x, p->topology[0], N, p->topology[0], n->d_act16[0],
+                                               round8(p->topology[0]), plane, parts, type, n->stream), "input split");
+    if (rc) return rc;
+    for (uint32_t l = 0; l < n->dev_layers; l++) {
+        const spgk_layer *L = &n->klayers[l];
+        bool last = l + 1 == n->dev_layers;
+        bool fuse_sm = L->act == ACT_SOFTMAX && L->out <= spgk_gemm_tc_softmax_max();
+        void *o16 = last ? NULL : n->d_act16[(l + 1) & 1];
+        float *o32 = last ? d_out : NULL;
+        if (!last && L->act == ACT_SOFTMAX && !fuse_sm) {
+            /* a wide softmax in the middle of the chain: finish it in fp32 and re-split */
+            return large_simt(n, d_x, N, d_out);
+        }
+        rc = spg_map_kernel_error(spgk_layer_gemm_tc(L, n->d_act16[l & 1], round8(L->in), plane, parts, type,
+                                                     o16, round8(L->out), plane, parts, o32, L->out,
+                                                     N, fuse_sm ? 1 : 0, n->d_status, n->stream), "layer (tcgen05)");
+        if (rc) return rc;
+        if (last && L->act == ACT_SOFTMAX && !fuse_sm &&
+            (rc = spg_map_kernel_error(spgk_softmax_rows(d_out, L->out, N, L->out, n->stream), "softmax"))) return rc;
+    }
+    spg_note_path("tcgen05");
+    return SPINGALETT_OK;
+}
+
+/* ------------------------------------------------------------------------ */
+/* batched inference entry point                                             */
+/* ------------------------------------------------------------------------ */
+
+float *forward_batch_struct_arguments(ForwardBatchArgs a)
+{
+    NeuralNetwork *p = a.net;
+    if (!p || !a.inputs) { spg_set_error(SPINGALETT_ERR_INVALID, "forward_batch: net or inputs is NULL"); return NULL; }
+    if (p->layers < 2) { spg_set_error(SPINGALETT_ERR_INVALID, "Network must have at least 2 layers for forward pass"); return NULL; }
+    spg_net *n = spg_priv(p);
+    const uint32_t N = a.sample_count;
+    const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1];
+    if (spg_dev_ensure(n) != SPINGALETT_OK) return NULL;
+    const size_t in_bytes = (size_t)N * in0 * sizeof(float), out_bytes = (size_t)N * outw * sizeof(float);
+
+    float *result = a.outputs;
+    const bool out_dev = a.outputs && spgk_is_device_pointer(a.outputs) == 1;
+    if (!a.outputs) {
+        if (n->h_out_bytes < out_bytes || !n->h_out) {
+            spgk_host_free(n->h_out); n->h_out = NULL; n->h_out_bytes = 0;
+            void *h = NULL;
+            if (spg_map_kernel_error(spgk_host_alloc(&h, out_bytes), "forward_batch: output buffer")) return NULL;
+            n->h_out = h; n->h_out_bytes = out_bytes;
+        }
+        result = n->h_out;
+    }
+    if (N == 0) return result;
+
+    const float *d_x = a.inputs;
+    if (spgk_is_device_pointer(a.inputs) != 1) {
+        if (reserve((void **)&n->d_in32, &n->in32_bytes, in_bytes, "forward_batch: input staging")) return NULL;
+        if (spg_map_kernel_error(spgk_memcpy_h2d(n->d_in32, a.inputs, in_bytes, n->stream), "forward_batch: input copy")) return NULL;
+        d_x = n->d_in32;
+    }
+
+    if (N <= SPGK_GEMV_MAX_BATCH) {
+        float *d_last = NULL;
+        if (spg_dev_forward_small(n, d_x, in0, N, &d_last)) return NULL;
+        int k = out_dev ? spgk_memcpy_d2d(result, d_last, out_bytes, n->stream)
+                        : spgk_memcpy_d2h(result, d_last, out_bytes, n->stream);
+        if (spg_map_kernel_error(k, "forward_batch: output copy")) return NULL;
+    } else {
+        float *d_out = result;
+        if (!out_dev) {
+            if (reserve((void **)&n->d_out32, &n->out32_bytes, out_bytes, "forward_batch: output staging")) return NULL;
+            d_out = n->d_out32;
+        }
+        if (spg_dev_forward_large(n, d_x, N, d_out)) return NULL;
+        if (!out_dev && spg_map_kernel_error(spgk_memcpy_d2h(result, d_out, out_bytes, n->stream), "forward_batch: output copy")) return NULL;
+    }
+    if (spg_map_kernel_error(spgk_stream_sync(n->stream), "forward_batch: sync")) return NULL;
+    return result;
+}
