@@ -1,0 +1,126 @@
+"""GPU parity: the CUDA library against the CPU oracle and the reference-made
+golden outputs, through the C ABI (forward / forward_batch)."""
+import json
+
+import numpy as np
+import pytest
+
+import nets
+from conftest import PRECS, golden
+
+pytestmark = pytest.mark.gpu
+META = json.load(open(golden("golden.json")))
+NETS = list(META["nets"].keys())
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu(has_gpu):
+    assert has_gpu, "no CUDA device: the GPU tests cannot run (there is no CPU path to fall back to)"
+
+
+@pytest.mark.parametrize("name", NETS)
+@pytest.mark.parametrize("prec", PRECS)
+def test_forward_single_sample_golden(spg, oracle, name, prec):
+    """forward() on the GPU reproduces the reference's own outputs for its own files."""
+    net = spg.Network.load(golden(f"{name}.{prec}.nn"))
+    x = np.load(golden(f"{name}.inputs.npy"))
+    ref = np.load(golden(f"{name}.{prec}.outputs.npy"))
+    onet = oracle.OracleNet.from_file(golden(f"{name}.{prec}.nn"))
+    for i, xi in enumerate(x):
+        y = net.forward(xi)
+        assert np.allclose(y, ref[i], rtol=1e-4, atol=2e-5), (name, prec, i, np.abs(y - ref[i]).max())
+    # net->neurons holds every layer's activations of the last sample (Network.c:216-250)
+    import ctypes as C
+    acts = np.empty(sum(onet.topology), np.float32)
+    oracle.Oracle.lib().spgo_forward_batch_acts(onet.h, x[-1].ctypes.data_as(C.POINTER(C.c_float)), 1,
+                                                acts.ctypes.data_as(C.POINTER(C.c_float)))
+    got = np.ctypeslib.as_array(net.c.neurons, shape=(net.c.total_neurons,))
+    assert np.allclose(got, acts, rtol=1e-4, atol=2e-5)
+    net.free()
+
+
+@pytest.mark.parametrize("name", NETS)
+@pytest.mark.parametrize("prec", PRECS)
+@pytest.mark.parametrize("n", [1, 2, 7, 8, 9, 16, 17, 127, 129, 256])
+def test_forward_batch_small_nets(spg, oracle, name, prec, n):
+    """Odd shapes (packed rows starting mid-byte, widths 15/9/7/5) at ragged batch sizes."""
+    net = spg.Network.load(golden(f"{name}.{prec}.nn"))
+    onet = oracle.OracleNet.from_file(golden(f"{name}.{prec}.nn"))
+    x = (nets.uniform_inputs(n, onet.topology[0], seed=n) * 2 - 0.5).astype(np.float32)
+    want = onet.forward_batch(x)
+    # guard words around the output buffer catch out-of-bounds writes
+    width = onet.topology[-1]
+    buf = np.full(n * width + 64, 777.0, np.float32)
+    out = buf[32:32 + n * width].reshape(n, width)
+    net.forward_batch(x, out)
+    assert np.all(buf[:32] == 777.0) and np.all(buf[-32:] == 777.0)
+    assert np.allclose(out, want, rtol=2e-3, atol=2e-4), (spg.last_path(), np.abs(out - want).max())
+    net.free()
+
+
+def test_empty_batch_and_bad_arguments(spg):
+    net = spg.Network.load(golden("small.fp32.nn"))
+    out = net.forward_batch(np.zeros((0, 20), np.float32))
+    assert out.shape == (0, 10)
+    r = spg.lib().forward_batch_struct_arguments(spg.abi.ForwardBatchArgs(None, None, 0, None))
+    assert not r and spg.lib().spingalett_last_error_code() == spg.abi.ERR_INVALID
+    spg.lib().spingalett_clear_error()
+    net.free()
+
+
+def test_library_owned_output_and_device_pointers(spg, oracle):
+    import torch
+    net = spg.Network.load(golden("wide8.int8.nn"))
+    onet = oracle.OracleNet.from_file(golden("wide8.int8.nn"))
+    x = nets.uniform_inputs(300, 64, seed=5)
+    want = onet.forward_batch(x)
+    import ctypes as C
+    r = spg.lib().forward_batch_struct_arguments(spg.abi.ForwardBatchArgs(net._h, x.ctypes.data, 300, None))
+    got = np.ctypeslib.as_array(C.cast(r, C.POINTER(C.c_float)), shape=(300, 24)).copy()
+    assert np.allclose(got, want, rtol=2e-3, atol=2e-4)
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.full((300, 24), -5.0, device="cuda")
+    torch.cuda.synchronize()
+    net.forward_batch_ptr(xd.data_ptr(), 300, yd.data_ptr())
+    assert np.allclose(yd.cpu().numpy(), want, rtol=2e-3, atol=2e-4)
+    net.free()
+
+
+def test_weights_edited_on_host_are_picked_up_after_sync(spg, oracle):
+    net = spg.Network.load(golden("small.int4.nn"))
+    x = nets.uniform_inputs(4, 20, seed=1)
+    before = net.forward_batch(x)
+    net.weights[:] *= 0.5
+    net.sync_weights()
+    after = net.forward_batch(x)
+    onet = oracle.OracleNet.from_arrays(net.topology, net.acts, net.weights, net.biases)
+    assert np.allclose(after, onet.forward_batch(x), rtol=1e-4, atol=2e-5)
+    assert not np.allclose(after, before)
+    net.free()
+
+
+@pytest.mark.parametrize("prec", PRECS)
+@pytest.mark.parametrize("n", [1, 256, 65536])
+def test_config_mlp_784_512_1000_10(spg, oracle, tmp_path_factory, prec, n):
+    """README-shaped MLP, He-init from the reference's seeded generator, every stored
+    precision, batch 1 / 256 / 65536.  Criteria: >= 99.9 % argmax agreement and max-abs
+    softmax error <= 2e-3 (float files) / 5e-3 (integer files) against the oracle
+    run on the identically dequantised weights."""
+    p = PRECS.index(prec)
+    d = tmp_path_factory.getbasetemp()
+    path = nets.make_net_file(spg, str(d / f"A_{prec}.nn"), nets.A_TOPO, nets.A_ACTS, p, seed=1234, reference_rng=True)
+    net = spg.Network.load(path)
+    onet = oracle.OracleNet.from_file(path)
+    x = nets.uniform_inputs(n, 784, seed=4321)
+    got = net.forward_batch(x)
+    # the oracle checks up to 4096 rows (seconds of CPU); full-size properties cover the rest
+    rows = np.arange(n) if n <= 4096 else np.random.default_rng(3).choice(n, 4096, replace=False)
+    want = onet.forward_batch(x[rows])
+    agree, err = nets.parity(got[rows], want)
+    assert agree >= 0.999 and err <= nets.tolerance(p), (spg.last_path(), agree, err)
+    assert np.all(np.isfinite(got)) and np.allclose(got.sum(1), 1.0, atol=1e-4)
+    if n > 4096:
+        # rows are independent: a row computed inside the big batch equals the same row computed in a small one
+        again = net.forward_batch(x[rows[:512]])
+        assert np.abs(again - got[rows[:512]]).max() <= nets.tolerance(p)
+    net.free()
