@@ -1,0 +1,314 @@
+#!/usr/bin/env python3
+"""Benchmark of the batched MLP forward path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--dtype int8] [--batch 65536] [--math exact|fast] [--all-dtypes]
+
+One "step" is one forward pass of the 784-512-1000-10 MLP (weights stored in
+the chosen .nn precision, INT8 by default) over one batch of 65536 synthetic
+U[0,1) rows per GPU.  Ranks are independent (weights replicated, rows sharded,
+no collective), so scaling is weak: `value` is all ranks' rows per second.
+
+  value     device-resident throughput: inputs and outputs in HBM, K steps timed
+            with CUDA events on the launching stream, max over ranks
+  e2e       the same call with HOST (pinned) buffers: H2D of the batch and D2H
+            of the result inside the timed region
+  roofline  the tcgen05 GEMM kernel: algorithmic FLOPs of the launches in the
+            timed region / their summed device time (event pairs recorded by
+            the library around each launch), against the measured bf16 peak
+  cpu_baseline  the reference's own CPU forward (built from its sources into
+            oracle/_ref) or, if that is absent, the C restatement in oracle/,
+            timed on this host's cores on a bounded sample of the same batch
+
+`--impl reference` runs only that CPU arm and prints the same JSON shape.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+TOPO = [784, 512, 1000, 10]
+FLOP_PER_SAMPLE = 2 * (784 * 512 + 512 * 1000 + 1000 * 10)       # 1 846 816
+METRIC = "mlp_forward_samples_per_sec"
+PRECS = ["fp32", "fp16", "bf16", "int8", "int4", "int2"]
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--dtype", default="int8", choices=PRECS)
+    ap.add_argument("--batch", type=int, default=65536)
+    ap.add_argument("--math", default="exact", choices=["exact", "fast"])
+    ap.add_argument("--all-dtypes", action="store_true", help="also report every stored precision (fewer steps each)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.rows = []
+        self._stop = threading.Event()
+        self._t = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[1]) for r in self.rows)
+        reasons = set()
+        for r in self.rows:
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.rows[0][2]), "reasons": sorted(reasons),
+                "samples": len(self.rows)}
+
+
+def make_net_file(spg, dtype, tmpdir):
+    import nets
+    return nets.make_net_file(spg, os.path.join(tmpdir, f"mlp_{dtype}.nn"), nets.A_TOPO, nets.A_ACTS,
+                              spg.abi.PRECISION_NAMES[dtype], seed=1234, reference_rng=True)
+
+
+def cpu_arm(path, x, steps, warmup, sample_rows):
+    """Times the reference's CPU forward (or the oracle port) on `sample_rows` rows per step."""
+    from oracle import Oracle, OracleNet, Reference
+    xs = np.ascontiguousarray(x[:sample_rows])
+    cores = os.cpu_count() or 1
+    if Reference.available():
+        R = Reference
+        lib = R.lib()
+        lib.spingalett_set_num_threads(cores)
+        net = R.load(path)
+        blas = bool(lib.refh_has_blas())
+        if blas:
+            lib.refh_blas_threads(cores)
+            lib.spingalett_set_compute_mode(2)      # COMPUTE_OPENBLAS
+            ws = lib.refh_ws_create(net, sample_rows)
+            run = lambda: lib.refh_ws_forward(net, ws, xs.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), sample_rows)
+            how = "reference batch_forward (OpenBLAS sgemm + its own bias/activation/softmax passes)"
+        else:
+            lib.spingalett_set_compute_mode(1)      # COMPUTE_OPENMP
+            run = lambda: R.forward_batch(net, xs)
+            how = "reference forward() per sample (OpenMP)"
+        kind = "reference"
+    else:
+        net = OracleNet.from_file(path)
+        run = lambda: net.forward_batch(xs)
+        kind, how = "port", "oracle C restatement, OpenMP over rows"
+        cores = Oracle.threads()
+    for _ in range(max(1, warmup)):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = time.perf_counter() - t0
+    return {"value": sample_rows * steps / dt, "unit": "samples/s", "cores": cores, "kind": kind,
+            "sample": f"{sample_rows} rows x {steps} steps of the same batch; {how}", "ms_per_step": dt / steps * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import spingalett_b200 as spg          # only to write the .nn file the reference then loads itself
+    spg.lib().spingalett_set_verbose(False)
+    import nets
+    tmpdir = tempfile.mkdtemp(prefix="spg_bench_")
+    path = make_net_file(spg, args.dtype, tmpdir)
+    x = nets.uniform_inputs(args.batch, TOPO[0], seed=4321)
+    r = cpu_arm(path, x, args.steps, args.warmup, args.batch)
+    line = {"metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": {"workload": f"MLP 784-512-1000-10, {args.dtype} .nn file (dequantised to fp32 at load), batch {args.batch}",
+                       "batch_per_gpu": args.batch},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def measure(spg, net, torch, x_dev, y_dev, x_pin, y_pin, batch, steps, warmup, dist, local_rank):
+    """Returns (device ms/step, e2e ms/step, kernel ms, kernel launches, launches, clocks)."""
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(max(3, warmup)):
+        net.forward_batch_ptr(x_dev.data_ptr(), batch, y_dev.data_ptr())
+    net.synchronize()
+    net.profile(True)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clk:
+        l0 = spg.kernel_launches()
+        start.record()
+        for _ in range(steps):
+            net.forward_batch_ptr(x_dev.data_ptr(), batch, y_dev.data_ptr())
+        stop.record()
+        barrier()
+        launches = spg.kernel_launches() - l0
+    net.synchronize()
+    dev_ms = reduce_max(start.elapsed_time(stop)) / steps
+    k_ms, k_cnt = net.profile_read()
+    net.profile(False)
+
+    # end to end: pinned host buffers through the public call, copies inside the timed region
+    for _ in range(2):
+        net.forward_batch_ptr(x_pin.data_ptr(), batch, y_pin.data_ptr())
+    barrier()
+    e2e_steps = max(3, steps // 4)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        net.forward_batch_ptr(x_pin.data_ptr(), batch, y_pin.data_ptr())      # returns with the result on the host
+    torch.cuda.synchronize()
+    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3) / e2e_steps
+    return dev_ms, e2e_ms, k_ms, k_cnt, launches, clk.summary()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+
+    import spingalett_b200 as spg
+    import nets
+    lib = spg.lib()
+    lib.spingalett_set_verbose(False)
+    assert lib.spingalett_set_device(local_rank) == 0
+    spg.set_math_mode(spg.abi.MATH_EXACT if args.math == "exact" else spg.abi.MATH_FAST)
+    pk = peaks()
+    tmpdir = tempfile.mkdtemp(prefix=f"spg_bench_r{rank}_")
+    batch = args.batch
+
+    x = nets.uniform_inputs(batch, TOPO[0], seed=4321 + rank)
+    x_dev = torch.from_numpy(x).cuda()
+    y_dev = torch.empty((batch, TOPO[-1]), dtype=torch.float32, device="cuda")
+    x_pin = torch.from_numpy(x).pin_memory()
+    y_pin = torch.empty((batch, TOPO[-1]), dtype=torch.float32).pin_memory()
+
+    def run_dtype(dtype, steps, warmup):
+        path = make_net_file(spg, dtype, tmpdir)
+        net = spg.Network.load(path)
+        net.set_stream(torch.cuda.current_stream().cuda_stream)
+        res = measure(spg, net, torch, x_dev, y_dev, x_pin, y_pin, batch, steps, warmup, dist, local_rank)
+        path_taken = spg.last_path()
+        net.free()
+        return path, res, path_taken
+
+    path, (dev_ms, e2e_ms, k_ms, k_cnt, launches, clocks), path_taken = run_dtype(args.dtype, args.steps, args.warmup)
+    value = batch * world / (dev_ms * 1e-3)
+    e2e_value = batch * world / (e2e_ms * 1e-3)
+    passes = 2 if args.math == "exact" else 1
+    line = {
+        "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16xf16->f32" if args.math == "fast" else "bf16(hi+lo)xbf16->f32", "data": "synthetic",
+        "config": {"workload": f"MLP 784-512-1000-10 forward, weights stored {args.dtype} (.nn), batch {batch} per GPU, U[0,1) fp32 inputs",
+                   "batch_per_gpu": batch, "math_mode": args.math, "path": path_taken,
+                   "l2": "inputs (205 MB per batch) and activations exceed the 126 MB L2; no explicit flush",
+                   "sharding": "rows across ranks, weights replicated, no collective"},
+        "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": batch * TOPO[0] * 4, "d2h_bytes_per_step": batch * TOPO[-1] * 4},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if k_cnt:
+        flops = FLOP_PER_SAMPLE * batch * args.steps            # algorithmic: 2*N*sum(in*out), one term per product
+        achieved = flops / (k_ms * 1e-3) / 1e12
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "gemm_tc_traffic.json")
+        if os.path.exists(tpath):
+            traffic = json.load(open(tpath)).get(f"{args.dtype}_{args.math}_{batch}")
+        line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                            "frac": achieved / pk["bf16_tflops"], "traffic": traffic,
+                            "kernel": "spg_gemm_tc_kernel", "launches": int(k_cnt), "kernel_ms_per_step": k_ms / args.steps,
+                            "peak_source": pk["source"] + " burst bf16", "tensor_passes_per_product": passes,
+                            "executed_frac": achieved * passes / pk["bf16_tflops"]}
+    if args.all_dtypes:
+        per = {}
+        for dt in PRECS:
+            _, (d_ms, e_ms, km, kc, _, _), _ = run_dtype(dt, max(5, args.steps // 2), 3)
+            per[dt] = {"value": batch * world / (d_ms * 1e-3), "e2e": batch * world / (e_ms * 1e-3),
+                       "kernel_tflops": (FLOP_PER_SAMPLE * batch * max(5, args.steps // 2) / (km * 1e-3) / 1e12) if kc else None}
+        line["per_dtype"] = per
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sample = min(batch, 16384)
+        cb = cpu_arm(path, x, 3, 1, sample)
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

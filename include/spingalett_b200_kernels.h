@@ -73,6 +73,12 @@ SPGK_API int spgk_is_device_pointer(const void *ptr);
 /* number of kernel launches made through this shim by the calling process */
 SPGK_API uint64_t spgk_launch_count(void);
 
+/* CUDA events for timing on the launching stream */
+SPGK_API int spgk_event_create(void **event);
+SPGK_API int spgk_event_destroy(void *event);
+SPGK_API int spgk_event_record(void *event, void *stream);
+SPGK_API int spgk_event_elapsed_ms(void *start, void *stop, float *ms);
+
 /* ---- K0: general layer, fp32 SIMT ---------------------------------------
  * y[n][j] = act(bias[j] + w_scale * sum_k q[j][k] * x[n][k]) for any
  * precision and any shape (odd widths, packed rows starting mid-byte).
@@ -111,27 +117,40 @@ SPGK_API int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx,
 
 /* ---- K2: large-batch tcgen05 GEMM layer ----------------------------------
  * C[N][out] = act(bias + w_scale * A[N][in] * W^T) with the accumulator in
- * tensor memory.  A is the 16-bit split produced by spgk_split16 or by the
- * previous layer's epilogue (`a_parts` planes, row stride lda elements, plane
- * stride a_plane elements).  W is read in its stored precision: 16-bit files
- * go from global to shared memory by TMA, the other precisions are
- * dequantised into the shared-memory operand tile by converter warps.
- * Output: if out16 != NULL, `out_parts` 16-bit planes for the next layer
- * (row stride ldo16, plane stride o_plane; padding columns zeroed); if
- * out32 != NULL, fp32 [N][ldo32].  When softmax_fused != 0 the activation is
- * ACT_SOFTMAX and out <= the kernel's N tile, so the row softmax is applied in
- * the epilogue; otherwise softmax layers need spgk_softmax_rows afterwards.
- * status: dev int32[4] scratch the kernel reports bounded-wait failures in.
+ * tensor memory; both operands reach shared memory by TMA (no multicast).
+ *
+ * A is the 16-bit split produced by spgk_split16 or by the previous layer's
+ * epilogue (`a_parts` planes, row stride lda elements, plane stride a_plane).
+ * W is a 16-bit K-major operand [out][ldw] in `w_parts` planes: for FP16/BF16
+ * files with 16-byte aligned rows it is the stored payload itself
+ * (spgk_weights16_direct() == 1, ldw = in); every other precision or shape is
+ * first expanded by spgk_dequant16 into scratch of spgk_weights16_bytes()
+ * bytes (integers are exact in one plane; the per-array scale is applied in
+ * the epilogue).  Passes run hi*hi, then lo*hi and hi*lo when a second plane
+ * exists, all into the same fp32 accumulator.  The two operands may use
+ * different 16-bit flavours (w_type16 for W, type16 for A and the output).
+ *
+ * Output: if out16 != NULL, `out_parts` 16-bit planes for the next layer (row
+ * stride ldo16, a multiple of 8; plane stride o_plane); if out32 != NULL, fp32
+ * [N][ldo32].  softmax_fused != 0 applies the row softmax in the epilogue
+ * (needs out <= spgk_gemm_tc_softmax_max() and out32); otherwise a softmax
+ * layer needs spgk_softmax_rows afterwards.
+ * status: dev int32 the kernel reports a bounded wait that gave up in; read it
+ * with spgk_gemm_tc_status() (which synchronises the stream).
  * Does batch_forward()'s layer step, reference Training.c:318-343. */
+SPGK_API int spgk_gemm_tc_supported(const spgk_layer *L);
+SPGK_API uint32_t spgk_gemm_tc_softmax_max(void);
+SPGK_API int spgk_weights16_direct(const spgk_layer *L, int type16);
+SPGK_API size_t spgk_weights16_bytes(const spgk_layer *L, int parts);
+SPGK_API int spgk_dequant16(const spgk_layer *L, void *dst, uint32_t ldw, uint64_t plane, int parts,
+                            int type16, void *stream);
 SPGK_API int spgk_layer_gemm_tc(const spgk_layer *L,
-                                const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int a_type,
+                                const void *w16, uint32_t ldw, uint64_t w_plane, int w_parts, int w_type16,
+                                const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
                                 void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
                                 float *out32, uint32_t ldo32,
                                 uint32_t N, int softmax_fused, int32_t *status, void *stream);
-/* 1 if spgk_layer_gemm_tc can take this layer (alignment/format rules). */
-SPGK_API int spgk_gemm_tc_supported(const spgk_layer *L);
-/* widest softmax the GEMM epilogue can fuse */
-SPGK_API uint32_t spgk_gemm_tc_softmax_max(void);
+SPGK_API int spgk_gemm_tc_status(int32_t *status, void *stream);
 
 #ifdef __cplusplus
 }

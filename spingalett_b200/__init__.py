@@ -135,6 +135,19 @@ class Network:
         if lib().spingalett_sync_weights(self._h) != 0:
             _check()
 
+    def synchronize(self):
+        if lib().spingalett_synchronize(self._h) != 0:
+            _check()
+
+    def profile(self, enable=True):
+        lib().spingalett_profile(self._h, enable)
+
+    def profile_read(self):
+        """(summed device milliseconds of the timed layer kernels, how many kernels) since the last read"""
+        ms, cnt = C.c_double(0), C.c_uint64(0)
+        lib().spingalett_profile_read(self._h, C.byref(ms), C.byref(cnt))
+        return ms.value, cnt.value
+
     def set_stream(self, stream_handle):
         lib().spingalett_set_stream(self._h, C.c_void_p(stream_handle))
 

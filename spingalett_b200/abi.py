@@ -138,6 +138,7 @@ EXTENSION_SYMBOLS = [
     "forward_batch_struct_arguments", "spingalett_set_math_mode", "spingalett_get_math_mode",
     "spingalett_set_device", "spingalett_get_device_count", "spingalett_set_stream", "spingalett_sync_weights",
     "spingalett_seed", "spingalett_kernel_launches", "spingalett_last_path",
+    "spingalett_profile", "spingalett_profile_read", "spingalett_synchronize",
 ]
 
 
@@ -158,4 +159,10 @@ def bind_extensions(lib):
     lib.spingalett_seed.restype = None
     lib.spingalett_kernel_launches.restype = C.c_uint64
     lib.spingalett_last_path.restype = C.c_char_p
+    lib.spingalett_synchronize.argtypes = [NetP]
+    lib.spingalett_synchronize.restype = C.c_int
+    lib.spingalett_profile.argtypes = [NetP, C.c_bool]
+    lib.spingalett_profile.restype = None
+    lib.spingalett_profile_read.argtypes = [NetP, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
+    lib.spingalett_profile_read.restype = None
     return lib

@@ -82,6 +82,16 @@ int spgk_memset(void *dev, int value, size_t bytes, void *stream)
     return SPGK_OK;
 }
 int spgk_stream_sync(void *stream) { SPGK_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); return SPGK_OK; }
+int spgk_event_create(void **event)
+{
+    cudaEvent_t e;
+    SPGK_CUDA(cudaEventCreate(&e));
+    *event = e;
+    return SPGK_OK;
+}
+int spgk_event_destroy(void *event) { if (event) SPGK_CUDA(cudaEventDestroy((cudaEvent_t)event)); return SPGK_OK; }
+int spgk_event_record(void *event, void *stream) { SPGK_CUDA(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream)); return SPGK_OK; }
+int spgk_event_elapsed_ms(void *start, void *stop, float *ms) { SPGK_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop)); return SPGK_OK; }
 int spgk_is_device_pointer(const void *ptr)
 {
     cudaPointerAttributes a;

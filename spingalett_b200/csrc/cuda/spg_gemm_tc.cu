@@ -1,8 +1,638 @@
-// placeholder: replaced by the tcgen05 GEMM
+// spg_gemm_tc.cu -- large-batch dense layer on the 5th-generation tensor cores.
+//
+//   C[M][N] = act(bias + scale * sum over passes  A_pa[M][K] * W_pw[N][K]^T)
+//
+// Both operands are 16-bit and K-major (activations row-major [rows][K], weights
+// row-major [out][in] exactly as Spingalett lays them out), so a tile of either
+// is a stack of 128-byte rows: TMA (cp.async.bulk.tensor, 128-byte swizzle, no
+// multicast) brings [128 x 64] A tiles and [BN x 64] W tiles into shared memory,
+// one elected thread issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) with the
+// fp32 accumulator in tensor memory, and eight epilogue warps read it back with
+// tcgen05.ld, apply scale, bias, activation (optionally the row softmax) and
+// write either the 16-bit operand planes of the next layer or the final fp32
+// output.  The kernel is persistent (one CTA per SM walks a tile list) and the
+// accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the CTA records a
+// code in `status`, raises a shared abort flag that all roles poll, drains, frees
+// its tensor memory and returns; the launcher turns that into SPGK_E_TIMEOUT.
 #include "spg_common.cuh"
-extern "C" {
-int spgk_gemm_tc_supported(const spgk_layer *) { return 0; }
-uint32_t spgk_gemm_tc_softmax_max(void) { return 0; }
-int spgk_layer_gemm_tc(const spgk_layer *, const void *, uint32_t, uint64_t, int, int, void *, uint32_t, uint64_t, int,
-                       float *, uint32_t, uint32_t, int, int32_t *, void *) { return SPGK_E_UNSUPPORTED; }
+#include <cuda.h>
+#include <cstdio>
+#include <mutex>
+#include <type_traits>
+
+namespace {
+
+constexpr uint32_t BM = 128;            // rows of C per tile (UMMA M)
+constexpr uint32_t BK = 64;             // K elements per stage: 64 * 2 B = one 128-byte swizzle row
+constexpr uint32_t UMMA_K = 16;
+constexpr uint32_t A_TILE_BYTES = BM * BK * 2;
+constexpr uint32_t EPI_WARPS = 8;       // two warps per TMEM lane quadrant, each taking half of the tile's columns
+constexpr uint32_t NUM_THREADS = 64 + 32 * EPI_WARPS;   // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2.. epilogue
+constexpr uint32_t WAIT_LIMIT = 1u << 23;
+constexpr uint32_t MAX_PASSES = 4;
+constexpr uint32_t SOFTMAX_FUSE_MAX = 256;
+
+struct GemmParams {
+    uint32_t M, N, K;
+    uint32_t BN, stages, kblocks;
+    uint32_t npass;
+    uint32_t pass_a[MAX_PASSES], pass_w[MAX_PASSES];
+    uint32_t m_tiles, n_tiles, group_m;
+    uint32_t idesc;
+    float scale;
+    const float *bias;
+    int act;
+    int softmax;
+    void *out16; uint32_t ldo16; uint64_t o_plane; int out_parts; int type16;
+    float *out32; uint32_t ldo32;
+    int32_t *status;
+};
+
+// ---- raw PTX wrappers -------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait.  Returns false when the abort flag is up or the bound was hit
+// (in which case it raises the flag and records `code`).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *status, int code)
+{
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled shared-memory operand descriptor: rows of 128
+// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), tile base
+// 1024-byte aligned; version 1; layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address
+    d |= (uint64_t)1u << 16;                           // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024u >> 4) << 32;                 // stride byte offset
+    d |= (uint64_t)1u << 46;                           // descriptor version
+    d |= (uint64_t)2u << 61;                           // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void tile_coords(const GemmParams &p, uint32_t t, uint32_t &m_tile, uint32_t &n_tile)
+{
+    // Tiles are walked in bands of group_m row-tiles, row-tile fastest inside a band,
+    // so CTAs running at the same time share W tiles and a small set of A tiles in L2.
+    const uint32_t band = p.group_m * p.n_tiles;
+    const uint32_t g = t / band, r = t % band;
+    const uint32_t rows_here = min(p.group_m, p.m_tiles - g * p.group_m);
+    m_tile = g * p.group_m + r % rows_here;
+    n_tile = r / rows_here;
+}
+
+template <typename T16> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b)
+{
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b)
+{
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <typename T16> __device__ __forceinline__ float round16(float a);
+template <> __device__ __forceinline__ float round16<__half>(float a) { return __half2float(__float2half_rn(a)); }
+template <> __device__ __forceinline__ float round16<__nv_bfloat16>(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
+
+// store 16 consecutive activations of one row as 16-bit planes (hi [, lo])
+template <typename T16>
+__device__ __forceinline__ void store16(const GemmParams &p, uint32_t row, uint32_t col0, const float (&v)[16])
+{
+    T16 *base = reinterpret_cast<T16 *>(p.out16) + (uint64_t)row * p.ldo16 + col0;
+#pragma unroll
+    for (int g = 0; g < 2; g++) {
+        if (col0 + 8u * g >= p.ldo16) break;                    // ldo16 is a multiple of 8
+        uint4 hi;
+        hi.x = pack2<T16>(v[8 * g + 0], v[8 * g + 1]); hi.y = pack2<T16>(v[8 * g + 2], v[8 * g + 3]);
+        hi.z = pack2<T16>(v[8 * g + 4], v[8 * g + 5]); hi.w = pack2<T16>(v[8 * g + 6], v[8 * g + 7]);
+        *reinterpret_cast<uint4 *>(base + 8 * g) = hi;
+        if (p.out_parts > 1) {
+            float r[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) r[i] = v[8 * g + i] - round16<T16>(v[8 * g + i]);
+            uint4 lo;
+            lo.x = pack2<T16>(r[0], r[1]); lo.y = pack2<T16>(r[2], r[3]);
+            lo.z = pack2<T16>(r[4], r[5]); lo.w = pack2<T16>(r[6], r[7]);
+            *reinterpret_cast<uint4 *>(base + p.o_plane + 8 * g) = lo;
+        }
+    }
+}
+
+// 16 accumulator columns of one row -> scale, bias, activation.  `full` says all 16 columns exist.
+template <int ACT>
+__device__ __forceinline__ void finish16(const GemmParams &p, const uint32_t (&r)[16], uint32_t col0, bool full, float (&v)[16])
+{
+    if (full) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col0 + i));   // same address in every lane
+            v[i + 0] = spg_activate(fmaf(__uint_as_float(r[i + 0]), p.scale, b.x), ACT);
+            v[i + 1] = spg_activate(fmaf(__uint_as_float(r[i + 1]), p.scale, b.y), ACT);
+            v[i + 2] = spg_activate(fmaf(__uint_as_float(r[i + 2]), p.scale, b.z), ACT);
+            v[i + 3] = spg_activate(fmaf(__uint_as_float(r[i + 3]), p.scale, b.w), ACT);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const float b = col0 + i < p.N ? p.bias[col0 + i] : 0.0f;
+            v[i] = spg_activate(fmaf(__uint_as_float(r[i]), p.scale, b), ACT);
+        }
+    }
+}
+
+__device__ __forceinline__ void write16(const GemmParams &p, uint32_t row, uint32_t col0, const float (&v)[16])
+{
+    if (p.out16) {
+        if (p.type16 == SPGK_T_F16) store16<__half>(p, row, col0, v);
+        else store16<__nv_bfloat16>(p, row, col0, v);
+    }
+    if (p.out32) {
+        float *o = p.out32 + (uint64_t)row * p.ldo32 + col0;
+        if ((p.ldo32 & 3u) == 0 && col0 + 16 <= p.N) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4 *>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) if (col0 + i < p.N) o[i] = v[i];
+        }
+    }
+}
+
+// Epilogue role.  Warp w reads TMEM lanes 32*(w%4).. (its quadrant) and, of the tile's BN columns,
+// the half selected by (w-2)/4; each thread therefore owns one row of C and walks its columns in
+// chunks of 32 (two tcgen05.ld in flight per wait).
+template <int ACT>
+__device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
+                                              volatile int *abort_flag, uint32_t warp, uint32_t lane)
+{
+    const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    const uint32_t span = p.BN >= 32 ? p.BN / 2 : p.BN;            // columns per warp
+    const uint32_t c_begin = p.BN >= 32 ? half * span : 0;
+    const bool idle = p.BN < 32 && half == 1;                      // a 16-wide tile has work for one warp per quadrant
+    const bool vec_bias = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
+    uint32_t tcount = 0;
+    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, tcount++) {
+        uint32_t mt, nt;
+        tile_coords(p, t, mt, nt);
+        const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, p.status, 4)) break;
+        tc_fence_after();
+        const uint32_t row = mt * BM + q * 32u + lane;
+        const uint32_t n0 = nt * p.BN;
+        const uint32_t taddr = tmem_base + acc * p.BN + ((q * 32u) << 16);
+        const bool row_ok = row < p.M;
+        if (!idle) {
+            for (uint32_t c0 = c_begin; c0 < c_begin + span; c0 += 32) {
+                if (n0 + c0 >= p.N) break;                         // only zero-filled W rows beyond N
+                const bool second = c0 + 16 < c_begin + span && n0 + c0 + 16 < p.N;
+                uint32_t r0[16], r1[16];
+                tmem_ld16(taddr + c0, r0);
+                if (second) tmem_ld16(taddr + c0 + 16, r1);
+                tmem_ld_wait();
+                float v[16];
+                finish16<ACT>(p, r0, n0 + c0, vec_bias && n0 + c0 + 16 <= p.N, v);
+                if (row_ok) write16(p, row, n0 + c0, v);
+                if (second) {
+                    finish16<ACT>(p, r1, n0 + c0 + 16, vec_bias && n0 + c0 + 32 <= p.N, v);
+                    if (row_ok) write16(p, row, n0 + c0 + 16, v);
+                }
+            }
+        }
+        tc_fence_before();
+        mbar_arrive(tempty0 + 8 * acc);                            // every epilogue thread hands the accumulator back
+    }
+}
+
+// Fused row softmax (reference Activation.c:5-21): the whole row (N <= BN) sits in one TMEM lane, so
+// one thread per row sweeps it three times: running max from -FLT_MAX, sum of expf(v - max), then
+// expf(v - max) / sum written out (the division happens only when the sum is positive).
+__device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
+                                                 volatile int *abort_flag, uint32_t warp, uint32_t lane)
+{
+    const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    uint32_t tcount = 0;
+    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, tcount++) {
+        uint32_t mt, nt;
+        tile_coords(p, t, mt, nt);
+        const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, p.status, 4)) break;
+        tc_fence_after();
+        if (half == 0) {
+            const uint32_t row = mt * BM + q * 32u + lane;
+            const uint32_t taddr = tmem_base + acc * p.BN + ((q * 32u) << 16);
+            float mx = -FLT_MAX, sum = 0.0f;
+            for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    if (c0 + i < p.N) { const float v = fmaf(__uint_as_float(r[i]), p.scale, p.bias[c0 + i]); if (v > mx) mx = v; }
+            }
+            for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    if (c0 + i < p.N) sum += expf(fmaf(__uint_as_float(r[i]), p.scale, p.bias[c0 + i]) - mx);
+            }
+            const float inv = sum > 0.0f ? 1.0f / sum : 1.0f;
+            for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        if (c0 + i < p.N)
+                            p.out32[(uint64_t)row * p.ldo32 + c0 + i] =
+                                expf(fmaf(__uint_as_float(r[i]), p.scale, p.bias[c0 + i]) - mx) * inv;
+                }
+            }
+        }
+        tc_fence_before();
+        mbar_arrive(tempty0 + 8 * acc);
+    }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment of the operand tiles (required by the 128-byte swizzle atoms)
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (base - raw);
+
+    const uint32_t b_tile_bytes = p.BN * BK * 2;
+    const uint32_t a_off = 0, b_off = p.stages * A_TILE_BYTES;
+    const uint32_t bar_off = b_off + p.stages * b_tile_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + bar_off);
+    // barrier table: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
+    const uint32_t full0 = base + bar_off, empty0 = full0 + 8 * p.stages;
+    const uint32_t tfull0 = empty0 + 8 * p.stages, tempty0 = tfull0 + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t tmem_cols = 2 * p.BN < 32 ? 32 : 2 * p.BN;       // power of two: BN in {16,32,64,128,256}
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (uint32_t a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 32 * EPI_WARPS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    const uint32_t iters_per_tile = p.npass * p.kblocks;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool alive = true;
+            for (uint32_t t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+                uint32_t mt, nt;
+                tile_coords(p, t, mt, nt);
+                for (uint32_t ps = 0; ps < p.npass && alive; ps++) {
+                    for (uint32_t kb = 0; kb < p.kblocks; kb++, it++) {
+                        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
+                        mbar_arrive_expect_tx(full0 + 8 * s, A_TILE_BYTES + b_tile_bytes);
+                        tma_load_3d(base + a_off + s * A_TILE_BYTES, &map_a, full0 + 8 * s,
+                                    (int)(kb * BK), (int)(mt * BM), (int)p.pass_a[ps]);
+                        tma_load_3d(base + b_off + s * b_tile_bytes, &map_w, full0 + 8 * s,
+                                    (int)(kb * BK), (int)(nt * p.BN), (int)p.pass_w[ps]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool alive = true;
+            for (uint32_t t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, tcount++) {
+                const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1u, abort_flag, p.status, 2)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * p.BN;
+                for (uint32_t i = 0; i < iters_per_tile; i++, it++) {
+                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint64_t da = make_smem_desc(base + a_off + s * A_TILE_BYTES);
+                    const uint64_t db = make_smem_desc(base + b_off + s * b_tile_bytes);
+#pragma unroll
+                    for (uint32_t k = 0; k < BK / UMMA_K; k++)
+                        umma_f16(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (i | k) ? 1u : 0u);   // +32 bytes per K step
+                    umma_commit(empty0 + 8 * s);          // frees the stage once these MMAs have read it
+                }
+                if (alive) umma_commit(tfull0 + 8 * acc);  // accumulator complete
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        // The activation is resolved once, outside every loop, so the per-element code is branch-free.
+        switch (p.softmax ? -1 : p.act) {
+            case -1:               epilogue_softmax(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case SPG_ACT_RELU:     epilogue_loop<SPG_ACT_RELU>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case SPG_ACT_LEAKY:    epilogue_loop<SPG_ACT_LEAKY>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case SPG_ACT_FOO52:    epilogue_loop<SPG_ACT_FOO52>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case SPG_ACT_TANH:     epilogue_loop<SPG_ACT_TANH>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case SPG_ACT_SIGMOID:  epilogue_loop<SPG_ACT_SIGMOID>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            default:               epilogue_loop<SPG_ACT_NONE>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+        }
+    }
+
+    // ------------------------------ common tail -----------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// 16-bit weight operand preparation: any stored precision -> `parts` planes of
+// [out][ldw] 16-bit values (plane 0 = round(q), plane 1 = round(q - plane 0)).
+// Integer formats are exact in one plane; the per-array scale stays outside.
+// ---------------------------------------------------------------------------------
+template <typename T16>
+__global__ void __launch_bounds__(256)
+spg_dequant16_kernel(const void *__restrict__ w, int precision, uint32_t in, uint32_t out,
+                     T16 *__restrict__ dst, uint32_t ldw, uint64_t plane, int parts)
+{
+    const uint64_t total = (uint64_t)out * ldw;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t j = (uint32_t)(i / ldw), k = (uint32_t)(i % ldw);
+        float v = k < in ? spg_decode_elem(w, (uint64_t)j * in + k, precision) : 0.0f;
+        for (int pt = 0; pt < parts; pt++) {
+            T16 h;
+            float back;
+            if constexpr (std::is_same<T16, __half>::value) { h = __float2half_rn(v); back = __half2float(h); }
+            else { h = __float2bfloat16_rn(v); back = __bfloat162float(h); }
+            dst[(uint64_t)pt * plane + i] = h;
+            v -= back;
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 3-D map over `parts` planes of a row-major [rows][ld] 16-bit matrix whose first K columns are valid.
+int make_map(CUtensorMap *map, const void *base, int type16, uint32_t K, uint32_t rows, uint32_t ld, uint64_t plane,
+             int parts, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { spgk_set_error("cuTensorMapEncodeTiled", "driver entry point not available"); return SPGK_E_CUDA; }
+    if (((uintptr_t)base & 15u) || (ld & 7u) || (parts > 1 && (plane & 7u))) {
+        spgk_set_error("tensor map", "operand is not 16-byte aligned");
+        return SPGK_E_ARG;
+    }
+    cuuint64_t dims[3] = { K, rows, (cuuint64_t)parts };
+    cuuint64_t plane_bytes = parts > 1 ? plane * 2 : (cuuint64_t)rows * ld * 2;
+    plane_bytes = (plane_bytes + 15) & ~(cuuint64_t)15;
+    cuuint64_t strides[2] = { (cuuint64_t)ld * 2, plane_bytes };
+    cuuint32_t box[3] = { BK, box_rows, 1 };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = fn(map, type16 == SPGK_T_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[64];
+        snprintf(msg, sizeof msg, "CUresult %d", (int)r);
+        spgk_set_error("cuTensorMapEncodeTiled", msg);
+        return SPGK_E_CUDA;
+    }
+    return SPGK_OK;
+}
+
+uint32_t pick_bn(uint32_t out)
+{
+    if (out > 128) return 256;
+    uint32_t bn = 16;
+    while (bn < out) bn <<= 1;
+    return bn;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t spgk_gemm_tc_softmax_max(void) { return SOFTMAX_FUSE_MAX; }
+
+int spgk_gemm_tc_supported(const spgk_layer *L)
+{
+    if (!L || L->in == 0 || L->out == 0) return 0;
+    static int cc = -1;
+    if (cc < 0) { int c = 0; if (spgk_device_info(&c, nullptr, nullptr) != SPGK_OK) return 0; cc = c; }
+    return cc == 100 ? 1 : 0;        // tcgen05 / TMEM exist on sm_100 only
+}
+
+int spgk_weights16_direct(const spgk_layer *L, int type16)
+{
+    if ((L->in & 7u) || ((uintptr_t)L->w & 15u)) return 0;
+    return (L->precision == SPG_P_F16 && type16 == SPGK_T_F16) || (L->precision == SPG_P_BF16 && type16 == SPGK_T_BF16);
+}
+
+size_t spgk_weights16_bytes(const spgk_layer *L, int parts)
+{
+    return (size_t)L->out * ((L->in + 7u) & ~7u) * 2u * (size_t)parts;
+}
+
+int spgk_dequant16(const spgk_layer *L, void *dst, uint32_t ldw, uint64_t plane, int parts, int type16, void *stream)
+{
+    if (!L || !dst || ldw < L->in || (ldw & 7u) || parts < 1 || parts > 2) { spgk_set_error("spgk_dequant16", "bad argument"); return SPGK_E_ARG; }
+    const uint64_t total = (uint64_t)L->out * ldw;
+    const uint32_t blocks = (uint32_t)((total + 255) / 256 < 148ull * 32 ? (total + 255) / 256 : 148ull * 32);
+    if (type16 == SPGK_T_F16)
+        spg_dequant16_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>(L->w, L->precision, L->in, L->out, (__half *)dst, ldw, plane, parts);
+    else
+        spg_dequant16_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>(L->w, L->precision, L->in, L->out, (__nv_bfloat16 *)dst, ldw, plane, parts);
+    return spgk_check_launch("spg_dequant16_kernel");
+}
+
+int spgk_layer_gemm_tc(const spgk_layer *L,
+                       const void *w16, uint32_t ldw, uint64_t w_plane, int w_parts, int w_type16,
+                       const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
+                       void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
+                       float *out32, uint32_t ldo32,
+                       uint32_t N, int softmax_fused, int32_t *status, void *stream)
+{
+    if (!L || !w16 || !a16 || !L->bias || (!out16 && !out32) || !status || a_parts < 1 || a_parts > 2 || w_parts < 1 || w_parts > 2 ||
+        (out16 && (ldo16 & 7u)) || (softmax_fused && (!out32 || L->out > SOFTMAX_FUSE_MAX))) {
+        spgk_set_error("spgk_layer_gemm_tc", "bad argument");
+        return SPGK_E_ARG;
+    }
+    if (N == 0) return SPGK_OK;
+    static int sm_count = 0;
+    static size_t smem_max = 0;
+    if (!sm_count) {
+        int dev = 0, sms = 0, optin = 0;
+        SPGK_CUDA(cudaGetDevice(&dev));
+        SPGK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        SPGK_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        SPGK_CUDA(cudaFuncSetAttribute(spg_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin));
+        smem_max = (size_t)optin;
+        sm_count = sms;
+    }
+    GemmParams p{};
+    p.M = N; p.N = L->out; p.K = L->in;
+    p.BN = softmax_fused ? pick_bn(L->out) : pick_bn(L->out);
+    p.kblocks = (L->in + BK - 1) / BK;
+    // passes: hi*hi first, then the correction terms (lo*hi, hi*lo); lo*lo is below fp32 resolution
+    p.npass = 0;
+    p.pass_a[p.npass] = 0; p.pass_w[p.npass] = 0; p.npass++;
+    if (a_parts > 1) { p.pass_a[p.npass] = 1; p.pass_w[p.npass] = 0; p.npass++; }
+    if (w_parts > 1) { p.pass_a[p.npass] = 0; p.pass_w[p.npass] = 1; p.npass++; }
+    const uint32_t stage_bytes = A_TILE_BYTES + p.BN * BK * 2;
+    const size_t fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 4) + 64;
+    uint32_t stages = (uint32_t)((smem_max - fixed) / stage_bytes);
+    if (stages > 8) stages = 8;
+    if (stages < 2) { spgk_set_error("spgk_layer_gemm_tc", "not enough shared memory"); return SPGK_E_UNSUPPORTED; }
+    p.stages = stages;
+    p.m_tiles = (N + BM - 1) / BM;
+    p.n_tiles = (L->out + p.BN - 1) / p.BN;
+    p.group_m = p.m_tiles < 16 ? p.m_tiles : 16;
+    p.idesc = (1u << 4) | ((uint32_t)type16 << 7) | ((uint32_t)w_type16 << 10) | ((p.BN >> 3) << 17) | ((BM >> 4) << 24);
+    p.scale = L->w_scale; p.bias = L->bias;
+    p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
+    p.softmax = softmax_fused ? 1 : 0;
+    if (softmax_fused && p.n_tiles != 1) { spgk_set_error("spgk_layer_gemm_tc", "softmax row does not fit one tile"); return SPGK_E_ARG; }
+    p.out16 = out16; p.ldo16 = ldo16; p.o_plane = o_plane; p.out_parts = out_parts; p.type16 = type16;
+    p.out32 = out32; p.ldo32 = ldo32;
+    p.status = status;
+
+    CUtensorMap map_a, map_w;
+    int rc = make_map(&map_a, a16, type16, L->in, N, lda, a_plane, a_parts, BM);
+    if (rc) return rc;
+    rc = make_map(&map_w, w16, w_type16, L->in, L->out, ldw, w_plane, w_parts, p.BN);
+    if (rc) return rc;
+
+    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
+    const size_t smem = 1024 + (size_t)stages * stage_bytes + 8 * (2 * stages + 4) + 64;
+    spg_gemm_tc_kernel<<<grid, NUM_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_w, p);
+    return spgk_check_launch("spg_gemm_tc_kernel");
+}
+
+// Reads back and clears the status word the GEMM kernels report bounded-wait
+// failures in (synchronises the stream).
+int spgk_gemm_tc_status(int32_t *status, void *stream)
+{
+    int32_t h = 0;
+    SPGK_CUDA(cudaMemcpyAsync(&h, status, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SPGK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (h != 0) {
+        char msg[96];
+        snprintf(msg, sizeof msg, "bounded wait %d gave up inside the tcgen05 GEMM", (int)h);
+        spgk_set_error("spg_gemm_tc_kernel", msg);
+        SPGK_CUDA(cudaMemsetAsync(status, 0, sizeof h, (cudaStream_t)stream));
+        return SPGK_E_TIMEOUT;
+    }
+    return SPGK_OK;
+}
+
+}  // extern "C"

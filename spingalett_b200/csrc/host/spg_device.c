@@ -81,6 +81,9 @@ void spg_dev_release(spg_net *n)
     }
     n->act16_bytes = 0; n->act32_bytes = 0;
     spgk_free(n->d_status); n->d_status = NULL;
+    spgk_free(n->d_w16); n->d_w16 = NULL; n->w16_bytes = 0;
+    for (uint32_t i = 0; i < n->prof_cap; i++) spgk_event_destroy(n->prof_ev[i]);
+    free(n->prof_ev); n->prof_ev = NULL; n->prof_cap = 0; n->prof_used = 0;
     n->dev_ready = false;
 }
 
@@ -141,6 +144,30 @@ fail:
     return rc;
 }
 
+static void prof_collect(spg_net *n);
+
+/* Wait for the net's stream, then surface a bounded-wait failure reported by a
+ * tensor-core kernel and fold the timing events in. */
+static int finish(spg_net *n)
+{
+    int rc;
+    if (n->status_pending) {
+        n->status_pending = false;
+        if ((rc = spg_map_kernel_error(spgk_gemm_tc_status(n->d_status, n->stream), "tcgen05 GEMM"))) return rc;
+    } else if ((rc = spg_map_kernel_error(spgk_stream_sync(n->stream), "stream sync"))) return rc;
+    prof_collect(n);
+    return SPINGALETT_OK;
+}
+
+int spingalett_synchronize(NeuralNetwork *net)
+{
+    if (!net) { spg_set_error(SPINGALETT_ERR_INVALID, "synchronize: net is NULL"); return SPINGALETT_ERR_INVALID; }
+    spg_net *n = spg_priv(net);
+    if (!n->dev_ready) return SPINGALETT_OK;
+    int rc = spg_map_kernel_error(spgk_set_device(n->device), "bind device");
+    return rc ? rc : finish(n);
+}
+
 int spingalett_sync_weights(NeuralNetwork *net)
 {
     if (!net) { spg_set_error(SPINGALETT_ERR_INVALID, "sync_weights: net is NULL"); return SPINGALETT_ERR_INVALID; }
@@ -148,6 +175,48 @@ int spingalett_sync_weights(NeuralNetwork *net)
     spg_dev_invalidate(n);
     spg_net_drop_payload(n);            /* the host fp32 arrays are now the truth */
     return SPINGALETT_OK;
+}
+
+/* ---- optional timing of the layer kernels -------------------------------- */
+void spingalett_profile(NeuralNetwork *net, bool enable)
+{
+    if (!net) return;
+    spg_net *n = spg_priv(net);
+    n->prof_on = enable;
+    n->prof_ms = 0.0; n->prof_launches = 0; n->prof_used = 0;
+}
+
+void spingalett_profile_read(NeuralNetwork *net, double *kernel_ms, uint64_t *launches)
+{
+    spg_net *n = spg_priv(net);
+    if (kernel_ms) *kernel_ms = n->prof_ms;
+    if (launches) *launches = n->prof_launches;
+    n->prof_ms = 0.0; n->prof_launches = 0;
+}
+
+static void prof_mark(spg_net *n)
+{
+    if (!n->prof_on) return;
+    if (n->prof_used == n->prof_cap) {
+        uint32_t cap = n->prof_cap ? n->prof_cap * 2 : 16;
+        void **ev = realloc(n->prof_ev, cap * sizeof *ev);
+        if (!ev) return;
+        for (uint32_t i = n->prof_cap; i < cap; i++) ev[i] = NULL;
+        n->prof_ev = ev; n->prof_cap = cap;
+    }
+    if (!n->prof_ev[n->prof_used] && spgk_event_create(&n->prof_ev[n->prof_used]) != SPGK_OK) return;
+    spgk_event_record(n->prof_ev[n->prof_used], n->stream);
+    n->prof_used++;
+}
+
+/* after the stream has been synchronised: add up the (start, stop) pairs */
+static void prof_collect(spg_net *n)
+{
+    for (uint32_t i = 0; i + 1 < n->prof_used; i += 2) {
+        float ms = 0.0f;
+        if (spgk_event_elapsed_ms(n->prof_ev[i], n->prof_ev[i + 1], &ms) == SPGK_OK) { n->prof_ms += ms; n->prof_launches++; }
+    }
+    n->prof_used = 0;
 }
 
 /* grow-only device buffer */
@@ -255,6 +324,7 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     NeuralNetwork *p = &n->pub;
     bool tc = true;
     for (uint32_t l = 0; l < n->dev_layers; l++) tc = tc && spgk_gemm_tc_supported(&n->klayers[l]);
+    for (uint32_t l = 0; l + 1 < n->dev_layers; l++) tc = tc && n->klayers[l].act != ACT_SOFTMAX;   /* softmax only as the last layer */
     if (!tc) return large_simt(n, d_x, N, d_out);
 
     const bool exact = spingalett_get_math_mode() == SPINGALETT_MATH_EXACT;
@@ -278,8 +348,19 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
         }
         n->act16_bytes = need;
     }
-    int rc = spg_map_kernel_error(spgk_split16(d_x, p->topology[0], N, p->topology[0], n->d_act16[0],
-                                               round8(p->topology[0]), plane, parts, type, n->stream), "input split");
+    /* scratch for the 16-bit weight operand of layers that are not stored as one */
+    size_t wneed = 0;
+    for (uint32_t l = 0; l < n->dev_layers; l++) {
+        const spgk_layer *L = &n->klayers[l];
+        if (!spgk_weights16_direct(L, type)) {
+            size_t b = spgk_weights16_bytes(L, (exact && L->precision == PRECISION_FLOAT32) ? 2 : 1);
+            if (b > wneed) wneed = b;
+        }
+    }
+    int rc;
+    if (wneed && (rc = reserve(&n->d_w16, &n->w16_bytes, wneed, "16-bit weight operand scratch"))) return rc;
+    rc = spg_map_kernel_error(spgk_split16(d_x, p->topology[0], N, p->topology[0], n->d_act16[0],
+                                           round8(p->topology[0]), plane, parts, type, n->stream), "input split");
     if (rc) return rc;
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
@@ -287,17 +368,28 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
         bool fuse_sm = L->act == ACT_SOFTMAX && L->out <= spgk_gemm_tc_softmax_max();
         void *o16 = last ? NULL : n->d_act16[(l + 1) & 1];
         float *o32 = last ? d_out : NULL;
-        if (!last && L->act == ACT_SOFTMAX && !fuse_sm) {
-            /* a wide softmax in the middle of the chain: finish it in fp32 and re-split */
-            return large_simt(n, d_x, N, d_out);
+        const void *w16 = L->w;
+        uint32_t ldw = L->in;
+        uint64_t w_plane = 0;
+        int w_parts = 1;
+        if (!spgk_weights16_direct(L, type)) {
+            w_parts = (exact && L->precision == PRECISION_FLOAT32) ? 2 : 1;
+            ldw = round8(L->in);
+            w_plane = (uint64_t)L->out * ldw;
+            w16 = n->d_w16;
+            if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16, ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
         }
-        rc = spg_map_kernel_error(spgk_layer_gemm_tc(L, n->d_act16[l & 1], round8(L->in), plane, parts, type,
+        prof_mark(n);
+        rc = spg_map_kernel_error(spgk_layer_gemm_tc(L, w16, ldw, w_plane, w_parts, type,
+                                                     n->d_act16[l & 1], round8(L->in), plane, parts, type,
                                                      o16, round8(L->out), plane, parts, o32, L->out,
-                                                     N, fuse_sm ? 1 : 0, n->d_status, n->stream), "layer (tcgen05)");
+                                                     N, (last && fuse_sm) ? 1 : 0, n->d_status, n->stream), "layer (tcgen05)");
+        prof_mark(n);
         if (rc) return rc;
         if (last && L->act == ACT_SOFTMAX && !fuse_sm &&
             (rc = spg_map_kernel_error(spgk_softmax_rows(d_out, L->out, N, L->out, n->stream), "softmax"))) return rc;
     }
+    n->status_pending = true;
     spg_note_path("tcgen05");
     return SPINGALETT_OK;
 }
@@ -331,7 +423,8 @@ float *forward_batch_struct_arguments(ForwardBatchArgs a)
     if (N == 0) return result;
 
     const float *d_x = a.inputs;
-    if (spgk_is_device_pointer(a.inputs) != 1) {
+    const bool in_dev = spgk_is_device_pointer(a.inputs) == 1;
+    if (!in_dev) {
         if (reserve((void **)&n->d_in32, &n->in32_bytes, in_bytes, "forward_batch: input staging")) return NULL;
         if (spg_map_kernel_error(spgk_memcpy_h2d(n->d_in32, a.inputs, in_bytes, n->stream), "forward_batch: input copy")) return NULL;
         d_x = n->d_in32;
@@ -352,6 +445,9 @@ float *forward_batch_struct_arguments(ForwardBatchArgs a)
         if (spg_dev_forward_large(n, d_x, N, d_out)) return NULL;
         if (!out_dev && spg_map_kernel_error(spgk_memcpy_d2h(result, d_out, out_bytes, n->stream), "forward_batch: output copy")) return NULL;
     }
-    if (spg_map_kernel_error(spgk_stream_sync(n->stream), "forward_batch: sync")) return NULL;
+    /* device-to-device calls are stream-ordered like any CUDA library call: the caller
+     * synchronises (spingalett_synchronize or its own stream sync); host buffers are
+     * complete on return */
+    if (!(in_dev && out_dev) && finish(n)) return NULL;
     return result;
 }

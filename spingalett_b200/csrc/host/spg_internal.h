@@ -52,10 +52,15 @@ typedef struct {
     float *d_out32; size_t out32_bytes;     /* fp32 outputs of the last layer */
     void  *d_act16[2]; size_t act16_bytes;  /* ping-pong 16-bit activation planes */
     float *d_act32[2]; size_t act32_bytes;  /* ping-pong fp32 activations (SIMT chain) */
-    int32_t *d_status;
+    int32_t *d_status; bool status_pending;
+    void *d_w16; size_t w16_bytes;         /* 16-bit weight operand of the layer in flight */
 
     float *h_out; size_t h_out_bytes;       /* library-owned pinned output buffer */
     float *h_stage; size_t h_stage_bytes;   /* pinned staging for forward() */
+
+    /* optional kernel timing (spingalett_profile): event pairs around the layer kernels */
+    bool prof_on; void **prof_ev; uint32_t prof_cap, prof_used;
+    double prof_ms; uint64_t prof_launches;
 
     /* training state on the device (created by the first train() call) */
     void *train;

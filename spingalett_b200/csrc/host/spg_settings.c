@@ -13,7 +13,7 @@ static _Atomic unsigned s_threads = 0;
 static _Atomic int      s_level = LOG_INFO;
 static _Atomic(LogCallback) s_cb = NULL;
 static _Atomic bool     s_verbose = true;
-static _Atomic int      s_math = SPINGALETT_MATH_FAST;
+static _Atomic int      s_math = SPINGALETT_MATH_EXACT;
 static _Atomic bool     s_mode_note_done = false;
 static _Thread_local const char *t_path = "none";
 

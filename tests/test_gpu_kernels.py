@@ -1,0 +1,139 @@
+"""Kernel-level GPU tests through the spgk_* shim: each hand-written kernel
+against a numpy restatement of the same arithmetic on the same operands."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def k(spg, has_gpu):
+    assert has_gpu, "no CUDA device"
+    lib = spg.lib()
+    vp = C.c_void_p
+    lib.spgk_error_string.restype = C.c_char_p
+    lib.spgk_split16.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_uint32, C.c_uint64, C.c_int, C.c_int, vp]
+    lib.spgk_dequant16.argtypes = [C.POINTER(spg.abi.KLayer), vp, C.c_uint32, C.c_uint64, C.c_int, C.c_int, vp]
+    lib.spgk_layer_gemm_tc.argtypes = [C.POINTER(spg.abi.KLayer), vp, C.c_uint32, C.c_uint64, C.c_int, C.c_int,
+                                       vp, C.c_uint32, C.c_uint64, C.c_int, C.c_int,
+                                       vp, C.c_uint32, C.c_uint64, C.c_int, vp, C.c_uint32,
+                                       C.c_uint32, C.c_int, vp, vp]
+    lib.spgk_gemm_tc_status.argtypes = [vp, vp]
+    lib.spgk_layer_simt.argtypes = [C.POINTER(spg.abi.KLayer), vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, vp]
+    lib.spgk_softmax_rows.argtypes = [vp, C.c_uint32, C.c_uint32, C.c_uint32, vp]
+    lib.spgk_layer_gemv.argtypes = [C.POINTER(spg.abi.KLayer), vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, vp, vp]
+    lib.spgk_gemv_scratch_bytes.argtypes = [C.POINTER(spg.abi.KLayer), C.c_uint32]
+    lib.spgk_gemv_scratch_bytes.restype = C.c_size_t
+    return lib
+
+
+def _round16(x, t):
+    import torch
+    dt = torch.float16 if t == 0 else torch.bfloat16
+    return torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(dt).float().numpy()
+
+
+ACT = {1: lambda v: np.maximum(v, 0), 6: lambda v: v, 3: lambda v: np.where(v > 0, v, 0.01 * v),
+       2: np.tanh, 0: lambda v: 1 / (1 + np.exp(-v)),
+       4: lambda v: np.where(v > 1, 1 + 0.01 * (v - 1), np.where(v < 0, 0.01 * v, v))}
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 16, 64), (256, 512, 784), (300, 1000, 512), (1000, 10, 1000),
+                                   (77, 33, 20), (129, 264, 136), (4096, 512, 784), (128, 256, 8192)])
+@pytest.mark.parametrize("t16", [0, 1])
+@pytest.mark.parametrize("parts", [1, 2])
+def test_gemm_tc_against_numpy(spg, k, M, N, K, t16, parts):
+    """tcgen05 GEMM + fused epilogue vs float64 matmul of the same rounded operands."""
+    import torch
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32) * 0.1
+    act = [1, 6, 3, 2, 0, 4][(M + N + K) % 6]
+    scale = 0.75
+    ld = (K + 7) & ~7
+    ldo = (N + 7) & ~7
+    dt = torch.float16 if t16 == 0 else torch.bfloat16
+    xd = torch.from_numpy(x).cuda()
+    a16 = torch.zeros((parts, M, ld), dtype=dt, device="cuda")
+    assert k.spgk_split16(xd.data_ptr(), K, M, K, a16.data_ptr(), ld, M * ld, parts, t16, None) == 0, k.spgk_error_string()
+    wd = torch.from_numpy(w).cuda()
+    bd = torch.from_numpy(bias).cuda()
+    L = spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), scale, K, N, 0, act)
+    w16 = torch.zeros((1, N, ld), dtype=dt, device="cuda")
+    assert k.spgk_dequant16(C.byref(L), w16.data_ptr(), ld, N * ld, 1, t16, None) == 0, k.spgk_error_string()
+    o16 = torch.full((parts, M, ldo), 7.0, dtype=dt, device="cuda")
+    o32 = torch.full((M + 1, N), -3.0, dtype=torch.float32, device="cuda")
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    rc = k.spgk_layer_gemm_tc(C.byref(L), w16.data_ptr(), ld, N * ld, 1, t16, a16.data_ptr(), ld, M * ld, parts, t16,
+                              o16.data_ptr(), ldo, M * ldo, parts, o32.data_ptr(), N, M, 0, status.data_ptr(), None)
+    assert rc == 0, k.spgk_error_string()
+    assert k.spgk_gemm_tc_status(status.data_ptr(), None) == 0, k.spgk_error_string()
+    # the operands the tensor cores saw
+    xs = a16.float().cpu().numpy()[:, :, :K].astype(np.float64).sum(0)
+    ws = w16.float().cpu().numpy()[0, :, :K].astype(np.float64)
+    want = ACT[act](xs @ ws.T * scale + bias)
+    got = o32.cpu().numpy()
+    assert np.all(got[M] == -3.0)                                   # guard row untouched
+    tol = 2e-5 * np.sqrt(K) + 1e-5
+    assert np.abs(got[:M] - want).max() <= tol * max(1.0, np.abs(want).max()), np.abs(got[:M] - want).max()
+    # 16-bit planes reassemble the fp32 result to the precision of the split
+    rec = o16.float().cpu().numpy()[:, :, :N].astype(np.float64).sum(0)
+    eps = (2.0 ** -11 if t16 == 0 else 2.0 ** -8) ** parts
+    assert np.abs(rec - got[:M]).max() <= 1.01 * eps * max(1.0, np.abs(got[:M]).max())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 10, 1000), (500, 256, 64), (130, 100, 200)])
+def test_gemm_tc_fused_softmax(spg, k, M, N, K):
+    import torch
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 2 / np.sqrt(K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    ld = (K + 7) & ~7
+    xd = torch.from_numpy(x).cuda()
+    a16 = torch.zeros((2, M, ld), dtype=torch.bfloat16, device="cuda")
+    assert k.spgk_split16(xd.data_ptr(), K, M, K, a16.data_ptr(), ld, M * ld, 2, 1, None) == 0
+    wd, bd = torch.from_numpy(w).cuda(), torch.from_numpy(bias).cuda()
+    L = spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), 1.0, K, N, 0, 5)
+    w16 = torch.zeros((2, N, ld), dtype=torch.bfloat16, device="cuda")
+    assert k.spgk_dequant16(C.byref(L), w16.data_ptr(), ld, N * ld, 2, 1, None) == 0
+    o32 = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    rc = k.spgk_layer_gemm_tc(C.byref(L), w16.data_ptr(), ld, N * ld, 2, 1, a16.data_ptr(), ld, M * ld, 2, 1,
+                              None, 0, 0, 1, o32.data_ptr(), N, M, 1, status.data_ptr(), None)
+    assert rc == 0, k.spgk_error_string()
+    assert k.spgk_gemm_tc_status(status.data_ptr(), None) == 0
+    z = x.astype(np.float64) @ w.astype(np.float64).T + bias
+    e = np.exp(z - z.max(1, keepdims=True))
+    want = e / e.sum(1, keepdims=True)
+    assert np.abs(o32.cpu().numpy() - want).max() < 2e-4
+
+
+@pytest.mark.parametrize("prec,bits", [(3, 8), (4, 4), (5, 2), (0, 32), (1, 16), (2, 16)])
+@pytest.mark.parametrize("out_in", [(33, 20), (9, 15), (7, 9), (256, 64)])
+def test_dequant16_every_precision(spg, k, oracle, prec, bits, out_in):
+    """Packed payload -> 16-bit operand planes reproduces the stored integers / floats."""
+    import torch
+    out, inn = out_in
+    rng = np.random.default_rng(out * 100 + inn)
+    vals = rng.standard_normal(out * inn).astype(np.float32)
+    raw = oracle.Oracle.encode(vals, prec)
+    dec = oracle.Oracle.decode(raw, out * inn, prec)
+    skip = 4 if prec >= 3 else 0
+    amax = np.frombuffer(raw[:4].tobytes(), np.float32)[0] if skip else 1.0
+    q = {3: 127.0, 4: 7.0, 5: 1.0}.get(prec, 1.0)
+    scale = amax / q if skip else 1.0
+    payload = torch.from_numpy(np.concatenate([raw[skip:], np.zeros(64, np.uint8)])).cuda()
+    L = spg.abi.KLayer(payload.data_ptr(), None, scale, inn, out, prec, 6)
+    ld = (inn + 7) & ~7
+    for t16, dt in ((0, torch.float16), (1, torch.bfloat16)):
+        w16 = torch.full((2, out, ld), 9.0, dtype=dt, device="cuda")
+        assert k.spgk_dequant16(C.byref(L), w16.data_ptr(), ld, out * ld, 2, t16, None) == 0
+        got = w16.float().cpu().numpy().astype(np.float64)
+        assert np.all(got[:, :, inn:] == 0)
+        rec = got[:, :, :inn].sum(0).reshape(-1) * scale
+        tol = 0 if prec >= 3 or (prec == 1 and t16 == 0) or (prec == 2 and t16 == 1) else 2.0 ** -15
+        assert np.abs(rec - dec.astype(np.float64)).max() <= (tol + 3e-7) * np.abs(dec).max()
