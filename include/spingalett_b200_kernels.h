@@ -152,6 +152,36 @@ SPGK_API int spgk_layer_gemm_tc(const spgk_layer *L,
                                 uint32_t N, int softmax_fused, int32_t *status, void *stream);
 SPGK_API int spgk_gemm_tc_status(int32_t *status, void *stream);
 
+/* ---- K2 without allocations ----------------------------------------------
+ * (No counterpart in the reference: it has no GPU code and no scratch memory.)
+ * The same layer as spgk_layer_gemm_tc, for callers that cannot allocate device
+ * memory: a server that handed all of HBM to its own arena at start-up, or a
+ * latency-critical loop that cannot take the device-wide synchronisation hidden
+ * in cudaMalloc/cudaFree.  The caller still passes the packed layer, the 16-bit
+ * activations and the output buffers; the scratch (the 16-bit weight operand
+ * expanded from the packed payload, and the kernel's status word) is a fixed
+ * array inside the library's device image.  Every GPU that loads the library
+ * holds that array until the process exits.
+ *   - Limit: the expanded weight operand, out * round_up(in, 8) * 2 bytes (twice
+ *     that for FP32 files with a_parts == 2), must fit
+ *     SPGK_NOALLOC_MAX_WEIGHT_BYTES; larger layers are refused with SPGK_E_ARG
+ *     and a message naming both sizes.  FP16/BF16 payloads that TMA can read in
+ *     place need no weight scratch at all.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents
+ *     (this function clears what has to start at zero), so two calls that
+ *     overlap on the GPU -- different streams, different host threads -- race.
+ *   - The call calls no cudaMalloc, cudaFree or allocating library routine, and
+ *     returns after the stream has finished the layer (it reads the status word
+ *     back): SPGK_OK, or SPGK_E_TIMEOUT if a bounded wait gave up. */
+#define SPGK_NOALLOC_MAX_WEIGHT_BYTES (8u << 20)
+SPGK_API int spgk_layer_gemm_tc_noalloc(const spgk_layer *L,
+                                        const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
+                                        void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
+                                        float *out32, uint32_t ldo32,
+                                        uint32_t N, int softmax_fused, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -635,4 +635,77 @@ int spgk_gemm_tc_status(int32_t *status, void *stream)
     return SPGK_OK;
 }
 
+// ---------------------------------------------------------------------------------
+// Allocation-free variant of the layer GEMM.
+//
+// Some callers must not allocate device memory at all: a serving process that gave
+// the whole of HBM to its own arena at start-up has nothing left for cudaMalloc to
+// hand out, and a latency-critical loop cannot afford the device-wide
+// synchronisation that cudaMalloc / cudaFree imply.  For them the scratch this layer
+// needs -- the 16-bit weight operand expanded from the packed payload, and the word
+// the kernel reports a bounded wait in -- lives in a fixed array inside the library's
+// device image.  Every GPU that loads the library carries that array until the
+// process exits, which is why its size is modest and fixed.
+// ---------------------------------------------------------------------------------
+constexpr size_t NOALLOC_HEAD_BYTES = 256;                               // status word, padded
+constexpr size_t NOALLOC_WEIGHT_BYTES = SPGK_NOALLOC_MAX_WEIGHT_BYTES;   // 16-bit weight operand
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_HEAD_BYTES + NOALLOC_WEIGHT_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static void *g_noalloc_dev_ptr[NOALLOC_MAX_DEVICES];      // device address of the array, per device
+static std::mutex g_noalloc_mutex;
+
+int spgk_layer_gemm_tc_noalloc(const spgk_layer *L,
+                               const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
+                               void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
+                               float *out32, uint32_t ldo32,
+                               uint32_t N, int softmax_fused, void *stream)
+{
+    if (!L || !L->w) { spgk_set_error("spgk_layer_gemm_tc_noalloc", "bad argument"); return SPGK_E_ARG; }
+    const bool direct = spgk_weights16_direct(L, type16) != 0;
+    const int w_parts = (!direct && L->precision == SPG_P_F32 && a_parts == 2) ? 2 : 1;
+    const size_t need = direct ? 0 : spgk_weights16_bytes(L, w_parts);
+    if (need > NOALLOC_WEIGHT_BYTES) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "layer needs %zu bytes of weight-operand scratch, the built-in array holds %zu "
+                 "(use spgk_layer_gemm_tc with caller-provided scratch)", need, (size_t)NOALLOC_WEIGHT_BYTES);
+        spgk_set_error("spgk_layer_gemm_tc_noalloc", msg);
+        return SPGK_E_ARG;
+    }
+    // Set-up, once per device and with that device current: in host code the array's name is only a
+    // stand-in, the address a kernel can use comes from cudaGetSymbolAddress.
+    int dev = 0;
+    SPGK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) { spgk_set_error("spgk_layer_gemm_tc_noalloc", "device index out of range"); return SPGK_E_ARG; }
+    void *base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_dev_ptr[dev]) {
+            void *p = nullptr;
+            SPGK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            g_noalloc_dev_ptr[dev] = p;
+        }
+        base = g_noalloc_dev_ptr[dev];
+    }
+    int32_t *status = reinterpret_cast<int32_t *>(base);
+    void *w16_scratch = static_cast<unsigned char *>(base) + NOALLOC_HEAD_BYTES;
+    // The array keeps whatever the previous call left: the status word must start at zero; the weight
+    // operand is rewritten in full (padding columns included) by the expansion below.
+    SPGK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), (cudaStream_t)stream));
+    const void *w16 = L->w;
+    uint32_t ldw = L->in;
+    uint64_t w_plane = 0;
+    if (!direct) {
+        ldw = (L->in + 7u) & ~7u;
+        w_plane = (uint64_t)L->out * ldw;
+        int rc = spgk_dequant16(L, w16_scratch, ldw, w_plane, w_parts, type16, stream);
+        if (rc) return rc;
+        w16 = w16_scratch;
+    }
+    int rc = spgk_layer_gemm_tc(L, w16, ldw, w_plane, w_parts, type16, a16, lda, a_plane, a_parts, type16,
+                                out16, ldo16, o_plane, out_parts, out32, ldo32, N, softmax_fused, status, stream);
+    if (rc) return rc;
+    return spgk_gemm_tc_status(status, stream);
+}
+
 }  // extern "C"
