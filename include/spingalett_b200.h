@@ -251,7 +251,9 @@ SPINGALETT_API float *forward_struct_arguments(ForwardArgs args);
 /* :230 -- training.  Supported on the GPU: MODE_ARRAY with
  * STRATEGY_FULL_BATCH or STRATEGY_SMALL_BATCH, OPTIMIZER_ADAM,
  * LOSS_CROSS_ENTROPY over a softmax or sigmoid output layer.  Other
- * combinations are rejected with ERR_INVALID (no CPU path exists here). */
+ * combinations (other optimizers, weight decay, gradient clipping, autosave, MSE)
+ * are rejected with ERR_INVALID (no CPU path exists here).  On return the host
+ * arrays of the net (weights, biases, grad_*, opt_*) hold the trained state. */
 SPINGALETT_API void train_struct_arguments(TrainArgs args);
 
 /* :233 -- write a .nn file in the requested precision; ".nn" is appended when
@@ -326,6 +328,18 @@ SPINGALETT_API int spingalett_sync_weights(NeuralNetwork *net);
 /* Seed the calling thread's weight-initialisation generator (the reference
  * keeps the equivalent hook private, Src/Spingalett.Random.c:18). */
 SPINGALETT_API void spingalett_seed(uint64_t seed);
+
+/* Data-parallel training, one process per GPU.  Rank 0 creates a 128-byte id
+ * (spingalett_dist_unique_id) and passes it to the other ranks over any host
+ * channel; every rank then calls spingalett_dist_init(rank, world, id).  From
+ * then on train() sums the flat gradient buffer [gW | gB] across ranks with one
+ * NCCL all-reduce per step and Adam divides by `world`, which keeps replicas
+ * bit-identical.  The reference has no multi-process mode; single-rank train()
+ * behaves like its batched trainer (Training.c:691-817). */
+SPINGALETT_API int spingalett_dist_unique_id(void *id128);
+SPINGALETT_API int spingalett_dist_init(int rank, int world, const void *id128);
+SPINGALETT_API void spingalett_dist_shutdown(void);
+SPINGALETT_API int spingalett_dist_world(void);
 
 /* Kernel timing for benchmarks: while enabled, the library brackets each
  * large-batch layer kernel with CUDA events on the net's stream;

@@ -104,12 +104,16 @@ SPGK_API int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in,
 /* ---- K1: small-batch fused dequant-GEMV ----------------------------------
  * Whole layer for 1 <= N <= SPGK_GEMV_MAX_BATCH rows: streams the packed
  * weights once with 128-bit loads, dequantises in registers, multiplies on
- * the warp-level tensor path against a two/three-term bf16 split of x,
- * reduces across warps, applies bias + activation.  Memory-bound by design.
- * Needs 16-byte aligned packed rows (returns SPGK_E_UNSUPPORTED otherwise).
- * scratch: dev, at least spgk_gemv_scratch_bytes(L, N) bytes.
+ * the warp-level tensor path against a two/three-term bf16 split of x (all
+ * products exact, fp32 accumulation), reduces the K splits, applies bias +
+ * activation (not softmax).  Memory-bound by design.
+ * Needs 16-byte aligned packed rows (in * bits % 128 == 0); returns
+ * SPGK_E_UNSUPPORTED otherwise so the caller can use spgk_layer_simt.
+ * scratch: dev, at least spgk_gemv_scratch_bytes(L, N) bytes, ZERO-FILLED before
+ * its first use (it starts with the kernel's ticket counters, which every call
+ * leaves at zero again).  Calls sharing a scratch buffer must not overlap.
  * Does forward()'s layer step, reference Network.c:218-247 / SIMD.c:190-240. */
-#define SPGK_GEMV_MAX_BATCH 16
+#define SPGK_GEMV_MAX_BATCH 8
 SPGK_API size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N);
 SPGK_API int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx,
                              float *y, uint32_t ldy, uint32_t N,
@@ -151,6 +155,40 @@ SPGK_API int spgk_layer_gemm_tc(const spgk_layer *L,
                                 float *out32, uint32_t ldo32,
                                 uint32_t N, int softmax_fused, int32_t *status, void *stream);
 SPGK_API int spgk_gemm_tc_status(int32_t *status, void *stream);
+
+/* ---- training step (fp32, as the reference) -------------------------------
+ * spgk_train_gemm modes:
+ *   0  C[M][N] = act(A[M][K] B[N][K]^T + bias[N])      forward, batch_forward (Training.c:327-343);
+ *                                                        ACT_SOFTMAX is left to spgk_softmax_rows
+ *   1  C[M][N] = (A[M][K] B[K][N]) * act'(aux[M][N])   delta back-propagation (Training.c:383-392);
+ *                                                        the derivative takes the activation OUTPUT
+ *   2  C[M][N] = alpha * A[K][M]^T B[K][N]             weight gradient (Training.c:405-411)
+ * spgk_ce_delta: delta = a - t (cross-entropy over softmax or sigmoid, Training.c:366-371); if
+ *   loss != NULL the batch's summed cross-entropy (SIMD.c:533-549) is added to *loss.
+ * spgk_col_sums: out[j] = scale * sum_rows d[row][j]   bias gradient (Training.c:413-417).
+ * spgk_gather_rows: dst[i] = src[idx[i]]                mini-batch assembly (Training.c:759-767).
+ * spgk_adam: one fused pass over a flat parameter buffer; g is scaled by gscale first
+ *   (1/ranks after a sum all-reduce); epsilon inside the square root (SIMD.c:279-328).
+ * spgk_nonfinite: sets *flag_dev to 1 if any element is NaN/Inf (Training.c:11-19). */
+SPGK_API int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint32_t ldb,
+                             float *C, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K, float alpha,
+                             const float *bias, const float *aux, uint32_t ldaux, int act, void *stream);
+SPGK_API int spgk_ce_delta(const float *a, const float *t, float *delta, uint64_t count, float *loss,
+                           int sigmoid_output, void *stream);
+SPGK_API int spgk_col_sums(const float *d, uint32_t rows, uint32_t cols, float scale, float *out, void *stream);
+SPGK_API int spgk_gather_rows(const float *src, const uint32_t *idx, float *dst, uint32_t rows, uint32_t width,
+                              void *stream);
+SPGK_API int spgk_adam(float *w, float *m, float *v, const float *g, uint64_t n, float lr, float b1, float b2,
+                       float mf, float vf, float eps, float gscale, void *stream);
+SPGK_API int spgk_nonfinite(const float *w, uint64_t n, int *flag_dev, void *stream);
+
+/* ---- gradient exchange: NCCL, loaded with dlopen at first use -----------------
+ * One communicator per process (one process per GPU).  Rank 0 makes a 128-byte id with
+ * spgk_nccl_unique_id and hands it to the other ranks by any host channel. */
+SPGK_API int spgk_nccl_unique_id(void *id128);
+SPGK_API int spgk_nccl_init(void **comm, int rank, int world, const void *id128);
+SPGK_API int spgk_nccl_allreduce_sum(void *comm, float *buf, uint64_t count, void *stream);
+SPGK_API int spgk_nccl_destroy(void *comm);
 
 /* ---- K2 without allocations ----------------------------------------------
  * (No counterpart in the reference: it has no GPU code and no scratch memory.)

@@ -135,6 +135,32 @@ class Network:
         if lib().spingalett_sync_weights(self._h) != 0:
             _check()
 
+    def train(self, inputs, targets, *, epochs=1, batch_size=0, strategy=abi.STRATEGY_SMALL_BATCH,
+              optimizer=abi.OPTIMIZER_ADAM, learning_rate=0.0, beta1=0.0, beta2=0.0, epsilon=0.0,
+              report_interval=0, reset_optimizer=False, nan_check_interval=0, callback=None, callback_interval=0):
+        """reference train(): MODE_ARRAY over host arrays [samples][in] / [samples][out]."""
+        x, t = _as_f32(inputs), _as_f32(targets)
+        args = abi.TrainArgs()
+        args.net = self._h
+        args.training_mode = abi.MODE_ARRAY if hasattr(abi, "MODE_ARRAY") else 0
+        args.training_strategy = strategy
+        args.optimizer_type = optimizer
+        args.inputs = x.ctypes.data
+        args.targets = t.ctypes.data
+        args.sample_count = x.shape[0]
+        args.batch_size = batch_size
+        args.epochs = epochs
+        args.learning_rate = learning_rate
+        args.beta1, args.beta2, args.epsilon = beta1, beta2, epsilon
+        args.report_interval = report_interval
+        args.reset_optimizer = reset_optimizer
+        args.nan_check_interval = nan_check_interval
+        if callback is not None:
+            args.callback = abi.TrainCallback(callback)
+            args.callback_interval = callback_interval
+        lib().train_struct_arguments(args)
+        _check()
+
     def synchronize(self):
         if lib().spingalett_synchronize(self._h) != 0:
             _check()
@@ -182,6 +208,13 @@ class Network:
             _check()
             raise SpingalettError(-1, "forward_batch returned NULL")
         return r
+
+
+def shard_rows(rows, world, rank):
+    """Contiguous share [lo, hi) of `rows` batch rows for `rank` of `world` (sizes differ by at most one)."""
+    base, extra = divmod(rows, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
 
 
 def set_math_mode(mode):

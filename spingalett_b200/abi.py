@@ -139,6 +139,7 @@ EXTENSION_SYMBOLS = [
     "spingalett_set_device", "spingalett_get_device_count", "spingalett_set_stream", "spingalett_sync_weights",
     "spingalett_seed", "spingalett_kernel_launches", "spingalett_last_path",
     "spingalett_profile", "spingalett_profile_read", "spingalett_synchronize",
+    "spingalett_dist_unique_id", "spingalett_dist_init", "spingalett_dist_shutdown", "spingalett_dist_world",
 ]
 
 
@@ -159,6 +160,12 @@ def bind_extensions(lib):
     lib.spingalett_seed.restype = None
     lib.spingalett_kernel_launches.restype = C.c_uint64
     lib.spingalett_last_path.restype = C.c_char_p
+    lib.spingalett_dist_unique_id.argtypes = [C.c_void_p]
+    lib.spingalett_dist_unique_id.restype = C.c_int
+    lib.spingalett_dist_init.argtypes = [C.c_int, C.c_int, C.c_void_p]
+    lib.spingalett_dist_init.restype = C.c_int
+    lib.spingalett_dist_shutdown.restype = None
+    lib.spingalett_dist_world.restype = C.c_int
     lib.spingalett_synchronize.argtypes = [NetP]
     lib.spingalett_synchronize.restype = C.c_int
     lib.spingalett_profile.argtypes = [NetP, C.c_bool]

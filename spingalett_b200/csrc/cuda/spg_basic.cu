@@ -171,19 +171,33 @@ __device__ __forceinline__ float spg_from16(T16 v);
 template <> __device__ __forceinline__ float spg_from16<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float spg_from16<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-template <typename T16>
+// One thread converts 8 consecutive columns of one row: two 128-bit loads (when the row is
+// 16-byte aligned) and one 128-bit store per plane.  ld16 is a multiple of 8.
+template <typename T16, bool VEC>
 __global__ void __launch_bounds__(256)
 spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t in,
                    T16 *__restrict__ dst, uint32_t ld16, uint64_t plane_elems, int parts)
 {
-    const uint64_t total = (uint64_t)N * ld16;
+    const uint32_t chunks = ld16 >> 3;
+    const uint64_t total = (uint64_t)N * chunks;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        uint32_t n = (uint32_t)(i / ld16), k = (uint32_t)(i % ld16);
-        float v = k < in ? x[(uint64_t)n * ldx + k] : 0.0f;
+        const uint32_t n = (uint32_t)(i / chunks), k0 = (uint32_t)(i % chunks) << 3;
+        const float *src = x + (uint64_t)n * ldx + k0;
+        float v[8];
+        if (VEC && k0 + 8 <= in) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = k0 + j < in ? src[j] : 0.0f;
+        }
+        T16 *out = dst + (uint64_t)n * ld16 + k0;
         for (int p = 0; p < parts; p++) {
-            T16 h = spg_to16<T16>(v);
-            dst[(uint64_t)p * plane_elems + i] = h;
-            v -= spg_from16<T16>(h);
+            union { uint4 q; T16 h[8]; } pk;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { pk.h[j] = spg_to16<T16>(v[j]); v[j] -= spg_from16<T16>(pk.h[j]); }
+            *reinterpret_cast<uint4 *>(out + (uint64_t)p * plane_elems) = pk.q;
         }
     }
 }
@@ -231,12 +245,18 @@ int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in, void *ds
 {
     if (!x || !dst || parts < 1 || parts > 3 || ld16 < in) { spgk_set_error("spgk_split16", "bad argument"); return SPGK_E_ARG; }
     if (N == 0) return SPGK_OK;
-    uint64_t total = (uint64_t)N * ld16;
-    uint32_t blocks = (uint32_t)((total + 255) / 256 < 148ull * 16 ? (total + 255) / 256 : 148ull * 16);
-    if (type == SPGK_T_F16)
-        spg_split16_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts);
-    else
-        spg_split16_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts);
+    if ((ld16 & 7u) || (plane_elems & 7u) || ((uintptr_t)dst & 15u)) { spgk_set_error("spgk_split16", "destination planes must be 16-byte aligned"); return SPGK_E_ARG; }
+    const uint64_t total = (uint64_t)N * (ld16 >> 3);
+    const uint32_t blocks = (uint32_t)((total + 255) / 256 < 148ull * 16 ? (total + 255) / 256 : 148ull * 16);
+    const bool vec = ((uintptr_t)x & 15u) == 0 && (ldx & 3u) == 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (type == SPGK_T_F16) {
+        if (vec) spg_split16_kernel<__half, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts);
+        else spg_split16_kernel<__half, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts);
+    } else {
+        if (vec) spg_split16_kernel<__nv_bfloat16, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts);
+        else spg_split16_kernel<__nv_bfloat16, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts);
+    }
     return spgk_check_launch("spg_split16_kernel");
 }
 

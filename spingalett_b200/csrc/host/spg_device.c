@@ -248,7 +248,12 @@ static int small_reserve(spg_net *n, uint32_t N)
         size_t s = spgk_gemv_scratch_bytes(&n->klayers[l], N);
         if (s > need) need = s;
     }
-    if (need) return reserve(&n->d_gemv_scratch, &n->gemv_scratch_bytes, need, "gemv scratch");
+    if (need && (n->gemv_scratch_bytes < need || !n->d_gemv_scratch)) {
+        int rc = reserve(&n->d_gemv_scratch, &n->gemv_scratch_bytes, need, "gemv scratch");
+        if (rc) return rc;
+        /* the kernel's ticket counters must start at zero; it leaves them at zero */
+        return spg_map_kernel_error(spgk_memset(n->d_gemv_scratch, 0, need, n->stream), "gemv scratch clear");
+    }
     return SPINGALETT_OK;
 }
 

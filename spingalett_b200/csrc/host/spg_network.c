@@ -19,18 +19,21 @@ static float *zeros_f32(uint64_t count)
     size_t bytes = (size_t)count * sizeof(float);
     bytes = (bytes + 63u) & ~(size_t)63u;
     if (bytes == 0) bytes = 64;
-    float *p = aligned_alloc(64, bytes);
-    if (p) memset(p, 0, bytes);
-    return p;
+    return calloc(1, bytes);
 }
 
-/* Replace *arr by a zero-extended copy holding new_count elements. */
+/* Grow *arr to new_count elements, new tail zero-filled.  realloc lets the allocator extend large
+ * blocks in place (mremap) instead of copying, which matters for nets with 1e8..1e9 weights. */
 static bool grow_f32(float **arr, uint64_t old_count, uint64_t new_count)
 {
-    float *p = zeros_f32(new_count);
+    if (!*arr) {
+        *arr = zeros_f32(new_count);
+        return *arr != NULL;
+    }
+    size_t bytes = (size_t)new_count * sizeof(float);
+    float *p = realloc(*arr, bytes ? bytes : 64);
     if (!p) return false;
-    if (*arr && old_count) memcpy(p, *arr, (size_t)old_count * sizeof(float));
-    free(*arr);
+    if (new_count > old_count) memset(p + old_count, 0, (size_t)(new_count - old_count) * sizeof(float));
     *arr = p;
     return true;
 }

@@ -1,0 +1,70 @@
+"""GPU parity on the two large benchmark configurations (seeded synthetic weights of the named
+shapes; the oracle checks a bounded number of rows, size-independent properties cover the rest).
+
+  W: 4096-8192-8192-8192-8192-4096(Tanh)-1000(Softmax), LeakyReLU hidden, "Xavier" weights stored BF16,
+     N(0,1) inputs, batch 16384 (oracle on 192 rows).
+  L: 8192-16384-16384-8192-1000(Softmax), FOO52 hidden, He weights stored INT4, N(0,1) inputs,
+     batch 1 / 8 (memory-bound dequant-GEMV) and 64 / 256 (tensor path).
+"""
+import numpy as np
+import pytest
+
+import nets
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def w_net(spg, oracle, has_gpu, tmp_path_factory):
+    assert has_gpu, "no CUDA device"
+    path = str(tmp_path_factory.mktemp("cfg") / "W_bf16.nn")
+    nets.make_net_file(spg, path, nets.W_TOPO, nets.W_ACTS, spg.abi.PRECISION_BFLOAT16, gain=1.0, seed=77)
+    net = spg.Network.load(path)
+    onet = oracle.OracleNet.from_file(path)
+    yield net, onet
+    net.free()
+
+
+@pytest.fixture(scope="module")
+def l_net(spg, oracle, has_gpu, tmp_path_factory):
+    assert has_gpu, "no CUDA device"
+    path = str(tmp_path_factory.mktemp("cfg") / "L_int4.nn")
+    nets.make_net_file(spg, path, nets.L_TOPO, nets.L_ACTS, spg.abi.PRECISION_INT4, gain=2.0, seed=78)
+    net = spg.Network.load(path)
+    onet = oracle.OracleNet.from_file(path)
+    yield net, onet
+    net.free()
+
+
+def test_wide_bf16_mlp_batch_16384(spg, w_net):
+    net, onet = w_net
+    n = 16384
+    x = nets.normal_inputs(n, nets.W_TOPO[0], seed=5)
+    spg.set_math_mode(spg.abi.MATH_EXACT)
+    got = net.forward_batch(x)
+    assert spg.last_path() == "tcgen05"
+    rows = np.random.default_rng(1).choice(n, 192, replace=False)
+    want = onet.forward_batch(x[rows])
+    agree, err = nets.parity(got[rows], want)
+    assert agree == 1.0 and err <= 2e-5, (agree, err)           # bar: 99.9 % / 2e-3
+    assert np.all(np.isfinite(got)) and np.allclose(got.sum(1), 1.0, atol=1e-4)
+    # rows are independent: the same rows in a small batch give the same result
+    again = net.forward_batch(x[rows])
+    assert np.abs(again - got[rows]).max() <= 2e-6
+
+
+@pytest.mark.parametrize("n", [1, 8, 64, 256])
+def test_large_int4_mlp_batch_sweep(spg, l_net, n):
+    net, onet = l_net
+    x = nets.normal_inputs(n, nets.L_TOPO[0], seed=100 + n)
+    spg.set_math_mode(spg.abi.MATH_EXACT)
+    got = net.forward_batch(x)
+    assert spg.last_path() == ("gemv" if n <= 8 else "tcgen05")
+    rows = np.arange(n) if n <= 64 else np.random.default_rng(2).choice(n, 64, replace=False)
+    want = onet.forward_batch(x[rows])
+    agree, err = nets.parity(got[rows], want)
+    assert agree == 1.0 and err <= 2e-5, (n, agree, err)        # bar: 99.9 % / 5e-3
+    assert np.allclose(got.sum(1), 1.0, atol=1e-4)
+    if n == 1:
+        one = net.forward(x[0])                                  # the reference's single-sample entry point
+        assert np.abs(one - want[0]).max() <= 2e-5

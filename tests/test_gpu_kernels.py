@@ -137,3 +137,49 @@ def test_dequant16_every_precision(spg, k, oracle, prec, bits, out_in):
         rec = got[:, :, :inn].sum(0).reshape(-1) * scale
         tol = 0 if prec >= 3 or (prec == 1 and t16 == 0) or (prec == 2 and t16 == 1) else 2.0 ** -15
         assert np.abs(rec - dec.astype(np.float64)).max() <= (tol + 3e-7) * np.abs(dec).max()
+
+
+@pytest.mark.parametrize("prec", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("out,inn,n", [(16, 256, 1), (100, 1024, 2), (1000, 8192, 3), (130, 512, 4), (257, 4096, 8),
+                                       (10, 1024, 1), (128, 16384, 5)])
+def test_gemv_against_float64(spg, k, oracle, prec, out, inn, n):
+    """Fused dequant-GEMV (all six stored precisions, K splits, ragged row blocks) vs a float64 product
+    of the decoded weights; the kernel's products are exact, so only fp32 summation error remains."""
+    import torch
+    rng = np.random.default_rng(out * 31 + inn + n)
+    vals = (rng.standard_normal(out * inn) / np.sqrt(inn)).astype(np.float32)
+    raw = oracle.Oracle.encode(vals, prec)
+    dec = oracle.Oracle.decode(raw, out * inn, prec).astype(np.float64).reshape(out, inn)
+    skip = 4 if prec >= 3 else 0
+    amax = float(np.frombuffer(raw[:4].tobytes(), np.float32)[0]) if skip else 1.0
+    scale = amax / {3: 127.0, 4: 7.0, 5: 1.0}[prec] if skip else 1.0
+    payload = torch.from_numpy(np.concatenate([raw[skip:], np.zeros(256, np.uint8)])).cuda()
+    bias = rng.standard_normal(out).astype(np.float32) * 0.1
+    bd = torch.from_numpy(bias).cuda()
+    act = [1, 6, 3, 2, 0, 4][(out + n) % 6]
+    L = spg.abi.KLayer(payload.data_ptr(), bd.data_ptr(), scale, inn, out, prec, act)
+    x = rng.standard_normal((n, inn)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.full((n + 1, out), -9.0, device="cuda")
+    nbytes = k.spgk_gemv_scratch_bytes(C.byref(L), n)
+    assert nbytes > 0
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    for rep in range(2):                      # the second call checks the ticket counters were left at zero
+        rc = k.spgk_layer_gemv(C.byref(L), xd.data_ptr(), inn, y.data_ptr(), out, n, scratch.data_ptr(), None)
+        assert rc == 0, k.spgk_error_string()
+        torch.cuda.synchronize()
+        want = ACT[act](x.astype(np.float64) @ dec.T + bias)
+        got = y.cpu().numpy()
+        assert np.all(got[n] == -9.0)
+        assert np.abs(got[:n] - want).max() <= 3e-6 * max(1.0, np.abs(want).max()) * np.sqrt(inn / 256), (rep, np.abs(got[:n] - want).max())
+
+
+def test_gemv_declines_unaligned_rows(spg, k):
+    import torch
+    payload = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    bias = torch.zeros(16, device="cuda")
+    L = spg.abi.KLayer(payload.data_ptr(), bias.data_ptr(), 1.0, 784, 16, 4, 1)      # 392-byte INT4 rows
+    assert k.spgk_gemv_scratch_bytes(C.byref(L), 1) == 0
+    x = torch.zeros(784, device="cuda")
+    y = torch.zeros(16, device="cuda")
+    assert k.spgk_layer_gemv(C.byref(L), x.data_ptr(), 784, y.data_ptr(), 16, 1, payload.data_ptr(), None) == -5

@@ -1,0 +1,149 @@
+"""GPU training step (cross-entropy + Adam) against the reference-made golden gradients / Adam
+trajectory and against the CPU oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import nets
+from conftest import golden
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu(has_gpu):
+    assert has_gpu, "no CUDA device"
+
+
+def _flat(c, wfield, bfield):
+    return np.concatenate([np.ctypeslib.as_array(getattr(c, wfield), shape=(c.total_weights,)),
+                           np.ctypeslib.as_array(getattr(c, bfield), shape=(c.total_biases,))]).copy()
+
+
+def test_one_full_batch_step_matches_reference_gradients(spg, oracle):
+    """net->grad_* after one train() step equal the reference's batch gradients (golden), and the
+    updated weights equal oracle gradients + oracle Adam."""
+    g = np.load(golden("train.npz"))
+    net = spg.Network.load(golden("train.fp32.nn"))
+    onet = oracle.OracleNet.from_file(golden("train.fp32.nn"))
+    w0 = np.concatenate([net.weights, net.biases]).copy()
+    net.train(g["x"], g["t"], epochs=1, strategy=spg.abi.STRATEGY_FULL_BATCH, learning_rate=1e-3)
+    grads = _flat(net.c, "grad_weights", "grad_biases")
+    ref = g["grads"]
+    assert np.linalg.norm(grads - ref) / np.linalg.norm(ref) <= 1e-5
+    assert net.c.time_step == 1
+    # first Adam step from zero state: factors as train() forms them (Training.c:480-482, :777-779)
+    w, m, v = w0.copy(), np.zeros_like(w0), np.zeros_like(w0)
+    fp = C.POINTER(C.c_float)
+    og = onet.gradients(g["x"], g["t"], 1.0 / g["x"].shape[0])
+    mf = np.float32(1.0) / (np.float32(1.0) - np.float32(0.9))
+    vf = np.float32(1.0) / (np.float32(1.0) - np.float32(0.999))
+    oracle.Oracle.lib().spgo_adam(w.ctypes.data_as(fp), m.ctypes.data_as(fp), v.ctypes.data_as(fp), og.ctypes.data_as(fp),
+                                  w.size, 1e-3, 0.9, 0.999, mf, vf, 1e-8)
+    got = np.concatenate([net.weights, net.biases])
+    # the first Adam step is lr*sign(g) wherever |g| >> sqrt(eps): compare where the gradient is not ~0
+    solid = np.abs(og) > 1e-6
+    assert np.abs(got - w)[solid].max() <= 2e-6
+    assert np.abs(_flat(net.c, "opt_m_weights", "opt_m_biases") - m).max() <= 1e-7
+    net.free()
+
+
+def test_adam_kernel_matches_reference_trajectory(spg):
+    import torch
+    g = np.load(golden("train.npz"))
+    lib = spg.lib()
+    lib.spgk_adam.argtypes = [C.c_void_p] * 4 + [C.c_uint64] + [C.c_float] * 7 + [C.c_void_p]
+    w = torch.from_numpy(g["adam_w0"].copy()).cuda()
+    m, v = torch.zeros_like(w), torch.zeros_like(w)
+    b1p = b2p = np.float32(1.0)
+    for step in range(10):
+        b1p = np.float32(b1p * np.float32(0.9))
+        b2p = np.float32(b2p * np.float32(0.999))
+        mf = np.float32(1.0) / (np.float32(1.0) - b1p)
+        vf = np.float32(1.0) / (np.float32(1.0) - b2p)
+        gs = torch.from_numpy(g["adam_g"][step].copy()).cuda()
+        assert lib.spgk_adam(w.data_ptr(), m.data_ptr(), v.data_ptr(), gs.data_ptr(), w.numel(),
+                             1e-3, 0.9, 0.999, float(mf), float(vf), 1e-8, 1.0, None) == 0
+        assert np.abs(w.cpu().numpy() - g["adam_w"][step]).max() <= 1e-6
+    assert np.abs(m.cpu().numpy() - g["adam_m"]).max() <= 1e-7 and np.abs(v.cpu().numpy() - g["adam_v"]).max() <= 1e-8
+
+
+def test_minibatch_training_reduces_loss_on_the_benchmark_mlp(spg, oracle):
+    """784-512-1000-10, He init, 256-row mini-batches, Adam lr 1e-3, uniform one-hot targets:
+    the cross-entropy reported through the callback falls, and the trained weights serve inference."""
+    net = spg.Network.build(nets.A_TOPO, nets.A_ACTS, spg.abi.WEIGHT_INITIALIZATION_HE, seed=5)
+    rng = np.random.default_rng(0)
+    n = 1024
+    x = rng.random((n, 784), dtype=np.float32)
+    t = np.zeros((n, 10), np.float32)
+    t[np.arange(n), rng.integers(0, 10, n)] = 1.0
+    errors = []
+    spg.lib().spingalett_seed(9)
+    net.train(x, t, epochs=30, batch_size=256, strategy=spg.abi.STRATEGY_SMALL_BATCH, learning_rate=1e-3,
+              callback=lambda h, epoch, err: errors.append(err) or False, callback_interval=1, nan_check_interval=10)
+    assert len(errors) == 30 and net.c.time_step == 30 * 4
+    assert errors[0] > 2.0 and errors[-1] < 0.5 * errors[0], errors
+    assert np.all(np.isfinite(net.weights))
+    # inference afterwards runs on the trained weights (device image refreshed) and matches the oracle on them
+    onet = oracle.OracleNet.from_arrays(net.topology, net.acts, net.weights, net.biases)
+    got = net.forward_batch(x[:64])
+    assert np.abs(got - onet.forward_batch(x[:64])).max() <= 2e-5
+    acc = np.mean(np.argmax(net.forward_batch(x), 1) == np.argmax(t, 1))
+    assert acc > 0.5
+    net.free()
+
+
+def test_sigmoid_output_and_ragged_last_batch(spg, oracle):
+    """Cross-entropy over a sigmoid output layer, batch size that does not divide the sample count."""
+    net = spg.Network.build([12, 9, 3], [spg.abi.ACT_FOO52, spg.abi.ACT_SIGMOID], spg.abi.WEIGHT_INITIALIZATION_HE, seed=4)
+    onet = oracle.OracleNet.from_arrays(net.topology, net.acts, net.weights, net.biases)
+    rng = np.random.default_rng(1)
+    x = rng.random((10, 12), dtype=np.float32)
+    t = (rng.random((10, 3)) > 0.5).astype(np.float32)
+    net.train(x, t, epochs=1, strategy=spg.abi.STRATEGY_FULL_BATCH, learning_rate=1e-2)
+    grads = _flat(net.c, "grad_weights", "grad_biases")
+    og = onet.gradients(x, t, 0.1)
+    assert np.linalg.norm(grads - og) / np.linalg.norm(og) <= 1e-5
+    net.train(x, t, epochs=2, batch_size=4, strategy=spg.abi.STRATEGY_SMALL_BATCH)      # batches of 4, 4, 2
+    assert net.c.time_step == 1 + 2 * 3
+    net.free()
+
+
+def test_unsupported_training_requests_are_refused(spg):
+    lib, a = spg.lib(), spg.abi
+    net = spg.Network.build([4, 3, 2], [a.ACT_RELU, a.ACT_SOFTMAX], a.WEIGHT_INITIALIZATION_HE, seed=1)
+    x = np.zeros((4, 4), np.float32)
+    t = np.zeros((4, 2), np.float32)
+    for kw in (dict(optimizer=a.OPTIMIZER_SGD), dict(strategy=a.STRATEGY_SAMPLE)):
+        with pytest.raises(spg.SpingalettError) as e:
+            net.train(x, t, epochs=1, **kw)
+        assert e.value.code == a.ERR_INVALID
+    with pytest.raises(spg.SpingalettError):
+        net.train(x, t, epochs=0)
+    mse = spg.Network.build([4, 2], [a.ACT_SIGMOID], a.WEIGHT_INITIALIZATION_HE, loss=a.LOSS_MSE, seed=1)
+    with pytest.raises(spg.SpingalettError):
+        mse.train(x, t, epochs=1, strategy=a.STRATEGY_FULL_BATCH)
+    hidden = spg.Network.build([4, 3, 2], [a.ACT_SOFTMAX, a.ACT_SOFTMAX], a.WEIGHT_INITIALIZATION_HE, seed=1)
+    with pytest.raises(spg.SpingalettError) as e:                                      # Training.c:620-626
+        hidden.train(x, t, epochs=1, strategy=a.STRATEGY_FULL_BATCH)
+    assert "hidden" in str(e.value)
+    for n in (net, mse, hidden):
+        n.free()
+
+
+def test_two_rank_data_parallel_step(spg, tmp_path):
+    """Two processes, one GPU each: the all-reduced gradient equals the gradient of the concatenated
+    batch and both replicas end bit-identical.  Needs two GPUs."""
+    if spg.lib().spingalett_get_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import os
+    import subprocess
+    import sys
+    worker = os.path.join(os.path.dirname(__file__), "dist_train_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29577", worker, str(tmp_path)],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "DIST_TRAIN_OK" in r.stdout
