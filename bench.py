@@ -40,6 +40,27 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 TOPO = [784, 512, 1000, 10]
 FLOP_PER_SAMPLE = 2 * (784 * 512 + 512 * 1000 + 1000 * 10)       # 1 846 816
+
+# name -> (topology, activation names, default dtype, default batch, weight gain, input distribution)
+WORKLOADS = {
+    "mlp":   ([784, 512, 1000, 10], "A", "int8", 65536, 2.0, "uniform"),
+    "wide":  ([4096, 8192, 8192, 8192, 8192, 4096, 1000], "W", "bf16", 16384, 1.0, "normal"),
+    "large": ([8192, 16384, 16384, 8192, 1000], "L", "int4", 1, 2.0, "normal"),
+}
+BITS = {"fp32": 32, "fp16": 16, "bf16": 16, "int8": 8, "int4": 4, "int2": 2}
+
+
+def flops_per_sample(topo):
+    return 2 * sum(a * b for a, b in zip(topo[:-1], topo[1:]))
+
+
+def algorithmic_bytes(topo, dtype, batch):
+    """Weights and biases once in their stored precision (+4-byte abs-max per integer array), input and output rows."""
+    bits, extra = BITS[dtype], (4 if dtype.startswith("int") else 0)
+    total = 0
+    for a, b in zip(topo[:-1], topo[1:]):
+        total += (a * b * bits + 7) // 8 + extra + (b * bits + 7) // 8 + extra
+    return total + batch * topo[0] * 4 + batch * topo[-1] * 4
 METRIC = "mlp_forward_samples_per_sec"
 PRECS = ["fp32", "fp16", "bf16", "int8", "int4", "int2"]
 
@@ -50,12 +71,16 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--dtype", default="int8", choices=PRECS)
-    ap.add_argument("--batch", type=int, default=65536)
+    ap.add_argument("--workload", default="mlp", choices=list(WORKLOADS), help="mlp = the benchmark line; wide/large = the other configurations")
+    ap.add_argument("--dtype", default=None, choices=PRECS)
+    ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--math", default="exact", choices=["exact", "fast"])
     ap.add_argument("--all-dtypes", action="store_true", help="also report every stored precision (fewer steps each)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    return ap.parse_args()
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    args.topo, args.dtype, args.batch = w[0], args.dtype or w[2], args.batch or w[3]
+    return args
 
 
 def peaks():
@@ -141,10 +166,19 @@ class ClockSampler:
                 "samples": len(sm), "source": "nvml" if self._nvml else "nvidia-smi"}
 
 
-def make_net_file(spg, dtype, tmpdir):
+def make_net_file(spg, dtype, tmpdir, workload="mlp"):
     import nets
-    return nets.make_net_file(spg, os.path.join(tmpdir, f"mlp_{dtype}.nn"), nets.A_TOPO, nets.A_ACTS,
-                              spg.abi.PRECISION_NAMES[dtype], seed=1234, reference_rng=True)
+    if workload == "mlp":
+        return nets.make_net_file(spg, os.path.join(tmpdir, f"mlp_{dtype}.nn"), nets.A_TOPO, nets.A_ACTS,
+                                  spg.abi.PRECISION_NAMES[dtype], seed=1234, reference_rng=True)
+    topo, acts = (nets.W_TOPO, nets.W_ACTS) if workload == "wide" else (nets.L_TOPO, nets.L_ACTS)
+    return nets.make_net_file(spg, os.path.join(tmpdir, f"{workload}_{dtype}.nn"), topo, acts,
+                              spg.abi.PRECISION_NAMES[dtype], gain=WORKLOADS[workload][4], seed=77)
+
+
+def make_inputs(workload, batch, width, seed):
+    import nets
+    return nets.uniform_inputs(batch, width, seed) if WORKLOADS[workload][5] == "uniform" else nets.normal_inputs(batch, width, seed)
 
 
 def cpu_arm(path, x, steps, warmup, sample_rows):
@@ -192,13 +226,13 @@ def run_reference(args):
     spg.lib().spingalett_set_verbose(False)
     import nets
     tmpdir = tempfile.mkdtemp(prefix="spg_bench_")
-    path = make_net_file(spg, args.dtype, tmpdir)
-    x = nets.uniform_inputs(args.batch, TOPO[0], seed=4321)
+    path = make_net_file(spg, args.dtype, tmpdir, args.workload)
+    x = make_inputs(args.workload, args.batch, args.topo[0], 4321)
     r = cpu_arm(path, x, args.steps, args.warmup, args.batch)
     line = {"metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": f"MLP 784-512-1000-10, {args.dtype} .nn file (dequantised to fp32 at load), batch {args.batch}",
+            "config": {"workload": f"MLP {'-'.join(map(str, args.topo))}, {args.dtype} .nn file (dequantised to fp32 at load), batch {args.batch}",
                        "batch_per_gpu": args.batch},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -278,14 +312,15 @@ def main():
     tmpdir = tempfile.mkdtemp(prefix=f"spg_bench_r{rank}_")
     batch = args.batch
 
-    x = nets.uniform_inputs(batch, TOPO[0], seed=4321 + rank)
+    topo = args.topo
+    x = make_inputs(args.workload, batch, topo[0], 4321 + rank)
     x_dev = torch.from_numpy(x).cuda()
-    y_dev = torch.empty((batch, TOPO[-1]), dtype=torch.float32, device="cuda")
+    y_dev = torch.empty((batch, topo[-1]), dtype=torch.float32, device="cuda")
     x_pin = torch.from_numpy(x).pin_memory()
-    y_pin = torch.empty((batch, TOPO[-1]), dtype=torch.float32).pin_memory()
+    y_pin = torch.empty((batch, topo[-1]), dtype=torch.float32).pin_memory()
 
     def run_dtype(dtype, steps, warmup):
-        path = make_net_file(spg, dtype, tmpdir)
+        path = make_net_file(spg, dtype, tmpdir, args.workload)
         net = spg.Network.load(path)
         net.set_stream(torch.cuda.current_stream().cuda_stream)
         res = measure(spg, net, torch, x_dev, y_dev, x_pin, y_pin, batch, steps, warmup, dist, local_rank)
@@ -301,36 +336,50 @@ def main():
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16xf16->f32" if args.math == "fast" else "bf16(hi+lo)xbf16->f32", "data": "synthetic",
-        "config": {"workload": f"MLP 784-512-1000-10 forward, weights stored {args.dtype} (.nn), batch {batch} per GPU, U[0,1) fp32 inputs",
+        "config": {"workload": f"MLP {'-'.join(map(str, topo))} forward, weights stored {args.dtype} (.nn), batch {batch} per GPU, "
+                               f"{'U[0,1)' if WORKLOADS[args.workload][5] == 'uniform' else 'N(0,1)'} fp32 inputs",
                    "batch_per_gpu": batch, "math_mode": args.math, "path": path_taken,
-                   "l2": "inputs (205 MB per batch) and activations exceed the 126 MB L2; no explicit flush",
+                   "l2": ("inputs (205 MB per batch) and activations exceed the 126 MB L2; no explicit flush" if args.workload == "mlp"
+                          else "the stored weights streamed every step (>= 136 MB) exceed the 126 MB L2; no explicit flush"),
                    "sharding": "rows across ranks, weights replicated, no collective"},
         "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": batch * TOPO[0] * 4, "d2h_bytes_per_step": batch * TOPO[-1] * 4},
+                "h2d_bytes_per_step": batch * topo[0] * 4, "d2h_bytes_per_step": batch * topo[-1] * 4},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
-    if k_cnt:
-        flops = FLOP_PER_SAMPLE * batch * args.steps            # algorithmic: 2*N*sum(in*out), one term per product
+    if k_cnt and path_taken == "tcgen05":
+        flops = flops_per_sample(topo) * batch * args.steps      # algorithmic: 2*N*sum(in*out), one term per product
         achieved = flops / (k_ms * 1e-3) / 1e12
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "gemm_tc_traffic.json")
         if os.path.exists(tpath):
-            traffic = json.load(open(tpath)).get(f"{args.dtype}_{args.math}_{batch}")
+            traffic = json.load(open(tpath)).get(f"{args.workload}_{args.dtype}_{args.math}_{batch}")
         line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                             "frac": achieved / pk["bf16_tflops"], "traffic": traffic,
                             "kernel": "spg_gemm_tc_kernel", "launches": int(k_cnt), "kernel_ms_per_step": k_ms / args.steps,
                             "peak_source": pk["source"] + " burst bf16", "tensor_passes_per_product": passes,
                             "executed_frac": achieved * passes / pk["bf16_tflops"]}
+    elif k_cnt:
+        nbytes = algorithmic_bytes(topo, args.dtype, batch)      # per step, all layers (one kernel launch per layer)
+        achieved = nbytes * args.steps / (k_ms * 1e-3) / 1e9
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "gemv_traffic.json")
+        if os.path.exists(tpath):
+            traffic = json.load(open(tpath)).get(f"{args.workload}_{args.dtype}_{batch}")
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                            "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "kernel": "spg_gemv_kernel",
+                            "launches": int(k_cnt), "kernel_ms_per_step": k_ms / args.steps,
+                            "algorithmic_bytes_per_step": nbytes, "peak_source": pk["source"] + " copy bandwidth",
+                            "whole_step_frac": nbytes / (dev_ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
     if args.all_dtypes:
         per = {}
         for dt in PRECS:
             _, (d_ms, e_ms, km, kc, _, _), _ = run_dtype(dt, max(5, args.steps // 2), 3)
             per[dt] = {"value": batch * world / (d_ms * 1e-3), "e2e": batch * world / (e_ms * 1e-3),
-                       "kernel_tflops": (FLOP_PER_SAMPLE * batch * max(5, args.steps // 2) / (km * 1e-3) / 1e12) if kc else None}
+                       "kernel_tflops": (flops_per_sample(topo) * batch * max(5, args.steps // 2) / (km * 1e-3) / 1e12) if kc else None}
         line["per_dtype"] = per
     if rank == 0 and world == 1 and not args.no_cpu:
-        sample = min(batch, 16384)
+        sample = min(batch, 16384 if args.workload == "mlp" else 64)
         cb = cpu_arm(path, x, 3, 1, sample)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if dist is not None:

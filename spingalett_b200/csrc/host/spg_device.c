@@ -145,6 +145,7 @@ fail:
 }
 
 static void prof_collect(spg_net *n);
+static void prof_mark(spg_net *n);
 
 /* Wait for the net's stream, then surface a bounded-wait failure reported by a
  * tensor-core kernel and fold the timing events in. */
@@ -272,8 +273,11 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
         float *y = n->d_small + (size_t)N * p->neuron_offsets[l + 1];
+        prof_mark(n);
         int k = spgk_layer_gemv(L, x, xld, y, L->out, N, n->d_gemv_scratch, n->stream);
+        prof_mark(n);
         if (k == SPGK_E_UNSUPPORTED) {
+            if (n->prof_used >= 2) n->prof_used -= 2;      /* nothing was launched between the two marks */
             path = "simt";
             k = spgk_layer_simt(L, x, xld, y, L->out, N, n->stream);
         }
