@@ -118,6 +118,21 @@ SPGK_API size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N);
 SPGK_API int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx,
                              float *y, uint32_t ldy, uint32_t N,
                              void *scratch, void *stream);
+/* Chained form for a run of layers.  The kernel consumes its input as bf16 terms
+ * laid out in the order its weight loads need them ("staged" input).
+ * staged_in : this layer's staged input, produced by the previous call; NULL makes
+ *             the call stage x itself (one small extra kernel).
+ * staged_out: if `next` is given, also eligible for this kernel and L is not a
+ *             softmax layer (spgk_gemv_chain_stages_next() == 1), the CTAs that
+ *             finish the layer write next's staged input here, so the following
+ *             call needs no staging kernel.  spgk_gemv_staged_bytes(width, N) bytes
+ *             for a layer whose `in` is `width`.
+ * y (fp32) is always written as well. */
+SPGK_API size_t spgk_gemv_staged_bytes(uint32_t width, uint32_t N);
+SPGK_API int spgk_gemv_chain_stages_next(const spgk_layer *L, const spgk_layer *next, uint32_t N);
+SPGK_API int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const void *staged_in, void *staged_out,
+                                   const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,
+                                   void *scratch, void *stream);
 
 /* ---- K2: large-batch tcgen05 GEMM layer ----------------------------------
  * C[N][out] = act(bias + w_scale * A[N][in] * W^T) with the accumulator in

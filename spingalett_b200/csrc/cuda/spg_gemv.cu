@@ -47,6 +47,9 @@ struct GemvParams {
     uint32_t kchunk, splits, row_blocks;
     uint32_t *tickets;                      // [row_blocks]
     float *partial;                         // [splits][row_blocks*128][8*T]
+    const uint4 *xin;                       // this layer's staged input (see staged_index)
+    __nv_bfloat16 *xout;                    // staged input of the next layer, written by the finishing CTAs (or NULL)
+    int next_prec; uint32_t next_kpad;      // precision of the next layer's weights; its K rounded up to a whole step
 };
 
 // elements covered by one 128-bit load, per stored precision
@@ -60,21 +63,56 @@ template <> struct Fmt<SPG_P_F32>  { static constexpr int EL = 4,  BITS = 32; };
 
 // Position of element e (0..EL-1 of a lane's 128-bit load) in fragment order: which 4-element
 // B block it belongs to and where inside the block [b0.lo, b0.hi, b1.lo, b1.hi].
-template <int PREC>
-__device__ __forceinline__ void frag_pos(uint32_t e, uint32_t &block, uint32_t &r)
+__device__ __forceinline__ void frag_pos(int prec, uint32_t e, uint32_t &block, uint32_t &r)
 {
-    if (PREC == SPG_P_I4) {            // word j = 8 nibbles; masks deliver pairs (i, i+4)
+    if (prec == SPG_P_I4) {            // word j = 8 nibbles; masks deliver pairs (i, i+4)
         const uint32_t j = e >> 3, i = e & 7u, low = i & 3u;
         block = 2 * j + (low >> 1); r = (low & 1u) * 2 + (i >> 2);
-    } else if (PREC == SPG_P_I2) {     // word j = 16 crumbs; masks deliver pairs (i, i+8)
+    } else if (prec == SPG_P_I2) {     // word j = 16 crumbs; masks deliver pairs (i, i+8)
         const uint32_t j = e >> 4, i = e & 15u, low = i & 7u;
         block = 4 * j + (low >> 1); r = (low & 1u) * 2 + (i >> 3);
-    } else if (PREC == SPG_P_I8) {     // word j = 4 bytes; masks deliver pairs (i, i+2)
+    } else if (prec == SPG_P_I8) {     // word j = 4 bytes; masks deliver pairs (i, i+2)
         const uint32_t j = e >> 2, i = e & 3u;
         block = j; r = (i & 1u) * 2 + (i >> 1);
     } else {                           // 16-bit and 32-bit floats keep their natural order
         block = e >> 2; r = e & 3u;
     }
+}
+
+__host__ __device__ inline uint32_t elems_per_load(int prec) { return 128u / spg_bits_per_elem(prec); }
+
+// Index (in bf16 units) of activation element k, column `col`, inside a staged-input buffer laid out as
+// [step][block][tile][t][8 columns][4]: the order in which the weight loads of a layer stored in
+// precision `prec` consume it.  T = column tiles of 8.
+__device__ __forceinline__ uint64_t staged_index(int prec, uint32_t T, uint32_t k, uint32_t col)
+{
+    const uint32_t el = elems_per_load(prec), ks = 4 * el, nb = el / 4;
+    const uint32_t step = k / ks, rem = k % ks, tt = rem / el, e = rem % el;
+    uint32_t block, r;
+    frag_pos(prec, e, block, r);
+    const uint64_t slot = ((((uint64_t)step * nb + block) * T + (col >> 3)) * 4 + tt) * 8 + (col & 7u);
+    return slot * 4 + r;
+}
+
+// Splits v into P bf16 terms (term i = round(v - earlier terms)) and stores them for columns n*P .. n*P+P-1.
+__device__ __forceinline__ void stage_value(__nv_bfloat16 *dst, int prec, uint32_t T, uint32_t k, uint32_t n, uint32_t P, float v)
+{
+    for (uint32_t q = 0; q < P; q++) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        dst[staged_index(prec, T, k, n * P + q)] = h;
+        v -= __bfloat162float(h);
+    }
+}
+
+// Stages a whole activation matrix x[N][in] (fp32) for a layer of precision `prec`: one thread per k.
+// Elements k in [in, kpad) are written as zero so that the last partial step multiplies by zero.
+__global__ void __launch_bounds__(256)
+spg_gemv_stage_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t P, uint32_t in, uint32_t kpad,
+                      int prec, uint32_t T, __nv_bfloat16 *__restrict__ dst)
+{
+    const uint32_t k = blockIdx.x * 256 + threadIdx.x;
+    if (k >= kpad) return;
+    for (uint32_t n = 0; n < N; n++) stage_value(dst, prec, T, k, n, P, k < in ? x[(uint64_t)n * ldx + k] : 0.0f);
 }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
@@ -126,27 +164,12 @@ spg_gemv_kernel(const GemvParams p)
 #pragma unroll
     for (int u = 0; u < U; u++) { ra[u] = load_row(row_a, u); rbw[u] = load_row(row_b, u); }
 
-    // ---- stage the activation chunk as bf16 terms in fragment order ----
+    // ---- copy this chunk of the staged input (already split into bf16 terms, in fragment order) ----
     {
-        __nv_bfloat16 *xh = reinterpret_cast<__nv_bfloat16 *>(xs);
-        const uint32_t span = steps * KS;
-        for (uint32_t idx = tid; idx < span * CPAD; idx += GEMV_THREADS) {
-            const uint32_t col = idx / span, kk = idx % span;
-            float term = 0.0f;
-            if (col < p.C) {
-                const uint32_t n = col / p.P, pi = col % p.P, k = k0 + kk;
-                float v = k < kend ? p.x[(uint64_t)n * p.ldx + k] : 0.0f;
-                for (uint32_t q = 0; q <= pi; q++) {           // term pi = round(x - earlier terms)
-                    term = __bfloat162float(__float2bfloat16_rn(v));
-                    v -= term;
-                }
-            }
-            const uint32_t step = kk / KS, rem = kk % KS, tt = rem / EL, e = rem % EL;
-            uint32_t block, r;
-            frag_pos<PREC>(e, block, r);
-            const uint32_t slot = (((step * NB + block) * T + (col >> 3)) * 4 + tt) * 8 + (col & 7u);
-            xh[slot * 4 + r] = __float2bfloat16_rn(term);
-        }
+        const uint32_t per_step = NB * T * 16;                 // 16-byte units per step
+        const uint4 *src = p.xin + (size_t)(k0 / KS) * per_step;
+        uint4 *dst = reinterpret_cast<uint4 *>(xs);
+        for (uint32_t i = tid; i < steps * per_step; i += GEMV_THREADS) dst[i] = __ldg(src + i);
     }
     __syncthreads();
 
@@ -289,12 +312,19 @@ spg_gemv_kernel(const GemvParams p)
             for (uint32_t q = p.P; q-- > 0;) part += __ldcg(src + q);      // smallest term first
             sum += part;
         }
-        p.y[(uint64_t)n * p.ldy + row] = spg_activate(fmaf(sum, p.scale, p.bias[row]), p.act);
+        const float yv = spg_activate(fmaf(sum, p.scale, p.bias[row]), p.act);
+        p.y[(uint64_t)n * p.ldy + row] = yv;
+        if (p.xout) stage_value(p.xout, p.next_prec, T, row, n, p.P, yv);
+    }
+    if (p.xout && rb == p.row_blocks - 1) {
+        // zero the tail of the next layer's last step (k in [out, next_kpad)), all columns
+        for (uint32_t idx = tid; idx < (p.next_kpad - p.out) * CPAD; idx += GEMV_THREADS)
+            p.xout[staged_index(p.next_prec, T, p.out + idx / CPAD, idx % CPAD)] = __float2bfloat16_rn(0.0f);
     }
     if (tid == 0) p.tickets[rb] = 0;                           // leave the counter ready for the next call
 }
 
-struct Plan { uint32_t P, C, T, kchunk, splits, row_blocks; size_t tickets_bytes, partial_bytes, smem; bool ok; };
+struct Plan { uint32_t P, C, T, kchunk, splits, row_blocks, kpad; size_t tickets_bytes, partial_bytes, staged_bytes, smem; bool ok; };
 
 int bits_of(int prec) { return (int)spg_bits_per_elem(prec); }
 
@@ -323,6 +353,8 @@ Plan make_plan(const spgk_layer *L, uint32_t N)
     pl.tickets_bytes = ((size_t)pl.row_blocks * 4 + 255) & ~(size_t)255;
     pl.partial_bytes = (size_t)pl.splits * pl.row_blocks * ROWS_PER_CTA * 8 * pl.T * sizeof(float);
     pl.smem = (size_t)((kchunk + ks - 1) / ks) * ks * 16 * pl.T;
+    pl.kpad = (L->in + ks - 1) / ks * ks;
+    pl.staged_bytes = ((size_t)pl.kpad * 16 * pl.T + 255) & ~(size_t)255;
     pl.ok = true;
     return pl;
 }
@@ -353,25 +385,50 @@ extern "C" {
 size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N)
 {
     Plan pl = make_plan(L, N);
-    return pl.ok ? pl.tickets_bytes + pl.partial_bytes : 0;
+    return pl.ok ? pl.tickets_bytes + pl.partial_bytes + pl.staged_bytes : 0;
 }
 
-int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,
-                    void *scratch, void *stream)
+size_t spgk_gemv_staged_bytes(uint32_t width, uint32_t N)
 {
-    if (!L || !x || !y || !L->w || !L->bias) { spgk_set_error("spgk_layer_gemv", "bad argument"); return SPGK_E_ARG; }
+    if (N == 0 || N > MAX_BATCH) return 0;
+    const uint32_t T = (N * (N <= 2 ? 3u : 2u) + 7) / 8;
+    return ((size_t)((width + 255u) & ~255u) * 16 * T + 255) & ~(size_t)255;
+}
+
+int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const void *staged_in, void *staged_out,
+                          const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N, void *scratch, void *stream)
+{
+    if (!L || !y || !L->w || !L->bias || (!x && !staged_in)) { spgk_set_error("spgk_layer_gemv", "bad argument"); return SPGK_E_ARG; }
     Plan pl = make_plan(L, N);
     if (!pl.ok) return SPGK_E_UNSUPPORTED;
     if (!scratch) { spgk_set_error("spgk_layer_gemv", "scratch is NULL"); return SPGK_E_ARG; }
+    cudaStream_t s = (cudaStream_t)stream;
     GemvParams p{};
     p.w = L->w; p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out;
     p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
     p.x = x; p.ldx = ldx; p.y = y; p.ldy = ldy;
     p.N = N; p.P = pl.P; p.C = pl.C;
     p.kchunk = pl.kchunk; p.splits = pl.splits; p.row_blocks = pl.row_blocks;
-    p.tickets = reinterpret_cast<uint32_t *>(scratch);
-    p.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + pl.tickets_bytes);
-    cudaStream_t s = (cudaStream_t)stream;
+    uint8_t *base = reinterpret_cast<uint8_t *>(scratch);
+    p.tickets = reinterpret_cast<uint32_t *>(base);
+    p.partial = reinterpret_cast<float *>(base + pl.tickets_bytes);
+    if (staged_in) {
+        p.xin = reinterpret_cast<const uint4 *>(staged_in);
+    } else {
+        // split x into bf16 terms in the order this layer's weight loads consume them
+        __nv_bfloat16 *own = reinterpret_cast<__nv_bfloat16 *>(base + pl.tickets_bytes + pl.partial_bytes);
+        spg_gemv_stage_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.kpad, L->precision, pl.T, own);
+        int rc = spgk_check_launch("spg_gemv_stage_kernel");
+        if (rc) return rc;
+        p.xin = reinterpret_cast<const uint4 *>(own);
+    }
+    // The finishing CTAs can stage the next layer's input directly, when that layer will also run here
+    // and this layer's output needs no further pass (softmax) first.
+    p.xout = nullptr; p.next_prec = 0; p.next_kpad = 0;
+    if (next && staged_out && L->act != SPG_ACT_SOFTMAX && next->in == L->out) {
+        Plan np = make_plan(next, N);
+        if (np.ok) { p.xout = reinterpret_cast<__nv_bfloat16 *>(staged_out); p.next_prec = next->precision; p.next_kpad = np.kpad; }
+    }
     switch (L->precision) {
         case SPG_P_I4:   return launch_t<SPG_P_I4>(p, pl, s);
         case SPG_P_I2:   return launch_t<SPG_P_I2>(p, pl, s);
@@ -380,6 +437,20 @@ int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx, float *y,
         case SPG_P_F16:  return launch_t<SPG_P_F16>(p, pl, s);
         default:         return launch_t<SPG_P_F32>(p, pl, s);
     }
+}
+
+// 1 if the call above staged (or would stage) `next`'s input: lets the caller know whether to pass it on
+int spgk_gemv_chain_stages_next(const spgk_layer *L, const spgk_layer *next, uint32_t N)
+{
+    if (!L || !next || L->act == SPG_ACT_SOFTMAX || next->in != L->out) return 0;
+    return make_plan(L, N).ok && make_plan(next, N).ok ? 1 : 0;
+}
+
+int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,
+                    void *scratch, void *stream)
+{
+    if (!x) { spgk_set_error("spgk_layer_gemv", "bad argument"); return SPGK_E_ARG; }
+    return spgk_layer_gemv_chain(L, nullptr, nullptr, nullptr, x, ldx, y, ldy, N, scratch, stream);
 }
 
 }  // extern "C"

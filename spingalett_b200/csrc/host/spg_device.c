@@ -73,6 +73,7 @@ void spg_dev_release(spg_net *n)
     n->d_w = NULL; n->d_bias = NULL; n->klayers = NULL; n->dev_layers = 0;
     spgk_free(n->d_small); n->d_small = NULL; n->small_cap = 0;
     spgk_free(n->d_gemv_scratch); n->d_gemv_scratch = NULL; n->gemv_scratch_bytes = 0;
+    for (int i = 0; i < 2; i++) { spgk_free(n->d_staged[i]); n->d_staged[i] = NULL; n->staged_bytes[i] = 0; }
     spgk_free(n->d_in32); n->d_in32 = NULL; n->in32_bytes = 0;
     spgk_free(n->d_out32); n->d_out32 = NULL; n->out32_bytes = 0;
     for (int i = 0; i < 2; i++) {
@@ -244,10 +245,16 @@ static int small_reserve(spg_net *n, uint32_t N)
         if (rc) return rc;
         n->d_small = b; n->small_cap = N;
     }
-    size_t need = 0;
+    size_t need = 0, staged = 0;
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         size_t s = spgk_gemv_scratch_bytes(&n->klayers[l], N);
         if (s > need) need = s;
+        s = spgk_gemv_staged_bytes(n->klayers[l].in, N);
+        if (s > staged) staged = s;
+    }
+    for (int i = 0; i < 2 && staged; i++) {
+        int rc = reserve(&n->d_staged[i], &n->staged_bytes[i], staged, "gemv staged input");
+        if (rc) return rc;
     }
     if (need && (n->gemv_scratch_bytes < need || !n->d_gemv_scratch)) {
         int rc = reserve(&n->d_gemv_scratch, &n->gemv_scratch_bytes, need, "gemv scratch");
@@ -270,12 +277,16 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
     const float *x = d_x ? d_x : n->d_small;
     uint32_t xld = d_x ? ldx : p->topology[0];
     const char *path = "gemv";
+    const void *staged = NULL;                       /* input of the layer in flight, already in the kernel's order */
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
+        const spgk_layer *next = l + 1 < n->dev_layers ? &n->klayers[l + 1] : NULL;
         float *y = n->d_small + (size_t)N * p->neuron_offsets[l + 1];
+        void *staged_out = n->d_staged[(l + 1) & 1];
         prof_mark(n);
-        int k = spgk_layer_gemv(L, x, xld, y, L->out, N, n->d_gemv_scratch, n->stream);
+        int k = spgk_layer_gemv_chain(L, next, staged, staged_out, x, xld, y, L->out, N, n->d_gemv_scratch, n->stream);
         prof_mark(n);
+        staged = (k == SPGK_OK && next && spgk_gemv_chain_stages_next(L, next, N)) ? staged_out : NULL;
         if (k == SPGK_E_UNSUPPORTED) {
             if (n->prof_used >= 2) n->prof_used -= 2;      /* nothing was launched between the two marks */
             path = "simt";

@@ -46,6 +46,7 @@ typedef struct {
      * small_cap rows, laid out layer after layer ([rows][width] each) */
     float *d_small; uint32_t small_cap;
     void *d_gemv_scratch; size_t gemv_scratch_bytes;
+    void *d_staged[2]; size_t staged_bytes[2];   /* ping-pong staged inputs of the GEMV chain */
 
     /* large-batch workspace */
     float *d_in32;  size_t in32_bytes;      /* staging for host inputs */
