@@ -107,11 +107,11 @@ SPGK_API int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in,
  * the warp-level tensor path against a two/three-term bf16 split of x (all
  * products exact, fp32 accumulation), reduces the K splits, applies bias +
  * activation (not softmax).  Memory-bound by design.
- * Needs 16-byte aligned packed rows (in * bits % 128 == 0); returns
- * SPGK_E_UNSUPPORTED otherwise so the caller can use spgk_layer_simt.
+ * Needs 16-byte aligned packed rows of at least 64 bytes (TMA boxes of the packed
+ * matrix); returns SPGK_E_UNSUPPORTED otherwise so the caller can use spgk_layer_simt.
  * scratch: dev, at least spgk_gemv_scratch_bytes(L, N) bytes, ZERO-FILLED before
- * its first use (it starts with the kernel's ticket counters, which every call
- * leaves at zero again).  Calls sharing a scratch buffer must not overlap.
+ * its first use (it starts with the status word a bounded wait that gave up is
+ * reported in; read it with spgk_gemv_status).  Calls sharing a scratch buffer must not overlap.
  * Does forward()'s layer step, reference Network.c:218-247 / SIMD.c:190-240. */
 #define SPGK_GEMV_MAX_BATCH 8
 SPGK_API size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N);
@@ -129,6 +129,8 @@ SPGK_API int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx,
  *             for a layer whose `in` is `width`.
  * y (fp32) is always written as well. */
 SPGK_API size_t spgk_gemv_staged_bytes(uint32_t width, uint32_t N);
+/* status word at the start of scratch: SPGK_E_TIMEOUT if a bounded wait inside the kernel gave up (synchronises) */
+SPGK_API int spgk_gemv_status(void *scratch, void *stream);
 SPGK_API int spgk_gemv_chain_stages_next(const spgk_layer *L, const spgk_layer *next, uint32_t N);
 SPGK_API int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const void *staged_in, void *staged_out,
                                    const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,

@@ -161,6 +161,38 @@ spg_softmax_rows_kernel(float *__restrict__ y, uint32_t ldy, uint32_t N, uint32_
     }
 }
 
+// Row softmax for a handful of rows: one 256-thread block per row, so a single wide row (batch 1,
+// width 1000) is not left to one warp.
+__global__ void __launch_bounds__(256)
+spg_softmax_block_kernel(float *__restrict__ y, uint32_t ldy, uint32_t width)
+{
+    __shared__ float red[8];
+    __shared__ float bcast;
+    float *r = y + (uint64_t)blockIdx.x * ldy;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    float mx = -FLT_MAX;
+    for (uint32_t i = tid; i < width; i += 256) { float v = r[i]; if (v > mx) mx = v; }
+    mx = spg_warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (tid == 0) { float m = red[0]; for (int q = 1; q < 8; q++) m = fmaxf(m, red[q]); bcast = m; }
+    __syncthreads();
+    mx = bcast;
+    float sum = 0.0f;
+    for (uint32_t i = tid; i < width; i += 256) { float e = expf(r[i] - mx); r[i] = e; sum += e; }
+    sum = spg_warp_sum(sum);
+    __syncthreads();
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (tid == 0) { float t = 0.0f; for (int q = 0; q < 8; q++) t += red[q]; bcast = t; }
+    __syncthreads();
+    sum = bcast;
+    if (sum > 0.0f) {
+        const float inv = 1.0f / sum;
+        for (uint32_t i = tid; i < width; i += 256) r[i] *= inv;
+    }
+}
+
 // fp32 -> `parts` 16-bit planes (term p = round(x - sum of earlier terms)).
 template <typename T16>
 __device__ __forceinline__ T16 spg_to16(float v);
@@ -236,6 +268,10 @@ int spgk_softmax_rows(float *y, uint32_t ldy, uint32_t N, uint32_t width, void *
 {
     if (!y || width == 0 || width > 65535u) { spgk_set_error("spgk_softmax_rows", "bad argument"); return SPGK_E_ARG; }
     if (N == 0) return SPGK_OK;
+    if (N <= 64 && width > 64) {
+        spg_softmax_block_kernel<<<N, 256, 0, (cudaStream_t)stream>>>(y, ldy, width);
+        return spgk_check_launch("spg_softmax_block_kernel");
+    }
     spg_softmax_rows_kernel<<<(N + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(y, ldy, N, width);
     return spgk_check_launch("spg_softmax_rows_kernel");
 }

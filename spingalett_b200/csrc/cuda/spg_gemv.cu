@@ -3,53 +3,69 @@
 //   y[n][j] = act(bias[j] + w_scale * sum_k q[j][k] * x[n][k])
 //
 // The layer is bound by reading the packed weights once from HBM, so the kernel
-// is organised around that stream: every lane issues 128-bit loads of two weight
-// rows (rows g and g+8 of a 16-row group), a warp walks 4 such loads (= 4 lanes
-// per row) per step along K, several steps are kept in flight, and the packed
-// integers are expanded to bf16 in registers with mask/magic-number tricks (no
-// per-element conversion instruction).  The multiply-accumulate runs on the
-// warp-level tensor path (mma.sync m16n8k16, bf16 x bf16 -> fp32): the 16 weight
-// rows are the M dimension and the batch is the N dimension.  To keep fp32-class
-// accuracy the activations enter as two or three bf16 terms (x = x1 + x2 [+ x3]),
-// each term occupying its own column of the N dimension, and weights that are not
-// exact in bf16 enter as several exact bf16 terms too (INT8 = 16*high nibble + low
-// nibble, FP16 = 8+3 bits, FP32 = 8+8+8 bits); integer and BF16 weights are exact
-// in one term.  All products are therefore exact and only the fp32 summation
-// order differs from the reference's fp32 dot product (SIMD.c:190-240).
+// is a persistent weight stream: one CTA per SM walks a list of items, an item
+// being 16 weight rows over the whole of K.  A producer thread keeps a ring of
+// TMA boxes (16 rows x up to 256 bytes of the stored, still packed matrix; no
+// multicast) in flight across item boundaries, so HBM never waits for a CTA to
+// start up, and the eight boxes of a chunk are neighbours along K, so every
+// row is read in contiguous kilobyte runs.  Each of the eight consumer warps
+// takes one box of every chunk: a lane reads its two 128-bit row pieces from
+// shared memory, expands the packed integers to bf16 in registers with
+// mask/magic-number tricks (no per-element conversion instruction) and feeds the
+// warp-level tensor path (mma.sync m16n8k16, bf16 x bf16 -> fp32) with the 16
+// weight rows as M and the batch as N.  At the end of an item the eight partial
+// accumulators meet in shared memory and scale, bias and activation are applied:
+// no split-K traffic, no global synchronisation.
 //
-// Because the K order inside one MMA is arbitrary as long as both operands agree,
-// the activation chunk is staged in shared memory in exactly the order in which
-// the mask tricks deliver the weights ("fragment order"), so no shuffles are needed.
+// To keep fp32-class accuracy the activations enter as two or three bf16 terms
+// (x = x1 + x2 [+ x3]), each term in its own column of the N dimension, and
+// weights that are not exact in bf16 enter as several exact bf16 terms too
+// (INT8 = 16*high nibble + low nibble, FP16 = 8+3 bits, FP32 = 8+8+8 bits);
+// integer and BF16 weights are exact in one term.  All products are exact; only
+// the fp32 summation order differs from the reference's dot product
+// (SIMD.c:190-240).
 //
-// Grid: (row blocks of 128 rows) x (K splits).  Each CTA writes fp32 partial sums;
-// the last CTA to finish a row block (atomic ticket) reduces the splits and the
-// activation terms, applies scale, bias and activation and writes y.  The ticket
-// counters live at the start of the scratch buffer, must be zero before the first
-// use and are left at zero.
+// The K order inside one MMA is arbitrary as long as both operands agree, so the
+// activation terms are kept in global memory already in the order in which the
+// mask tricks deliver the weights ("staged" input): a small kernel stages the
+// first layer's input, and every later layer's input is staged by the epilogue
+// of the layer before it.  A chunk's slice of the staged input reaches shared
+// memory with one bulk copy and serves all eight warps.
+//
+// Scratch starts with a status word: it must be zero before first use.  Every
+// mbarrier wait is bounded; on expiry the status word is set, waits turn into
+// no-ops and the CTA runs to its end without computing further.
 #include "spg_common.cuh"
+#include <cuda.h>
 #include <cstdio>
+#include <mutex>
 
 namespace {
 
-constexpr int GEMV_THREADS = 256;          // 8 warps x 16 rows = 128 rows per CTA
-constexpr int ROWS_PER_CTA = 128;
+constexpr int CONSUMER_WARPS = 16;         // two warps per 256-byte slice of a chunk (each takes half of its steps)
+constexpr int CONSUMER_THREADS = 32 * CONSUMER_WARPS;
+constexpr int GEMV_THREADS = CONSUMER_THREADS + 64;     // + one producer warp + one epilogue warp
+constexpr int HANDOFF_THREADS = CONSUMER_THREADS + 32;  // parties of the consumer <-> epilogue named barriers
+constexpr int ITEM_ROWS = 16;              // one MMA row group
 constexpr int MAX_BATCH = 8;
+constexpr uint32_t GEMV_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t HEAD_BYTES = 256;                     // status word at the start of scratch
 
 struct GemvParams {
-    const void *w;
     const float *bias;
     float scale;
     uint32_t in, out;
     int act;
-    const float *x; uint32_t ldx;
     float *y; uint32_t ldy;
     uint32_t N, P, C;                       // rows, bf16 terms per row, C = N*P columns in use
-    uint32_t kchunk, splits, row_blocks;
-    uint32_t *tickets;                      // [row_blocks]
-    float *partial;                         // [splits][row_blocks*128][8*T]
+    uint32_t items;                         // row groups of 16
+    uint32_t nboxes, nchunks;               // boxes along K per item; chunks of 8 boxes
+    uint32_t spb, box_bytes;                // steps (64 bytes per row) per box; bytes of one box = 16 * spb * 64
+    uint32_t ring, xdepth, xchunk_bytes;    // ring depth in chunks (weights + staged input travel together), bytes of staged input per chunk
+    int32_t *status;
     const uint4 *xin;                       // this layer's staged input (see staged_index)
-    __nv_bfloat16 *xout;                    // staged input of the next layer, written by the finishing CTAs (or NULL)
-    int next_prec; uint32_t next_kpad;      // precision of the next layer's weights; its K rounded up to a whole step
+    __nv_bfloat16 *xout;                    // staged input of the next layer, written by the epilogue (or NULL)
+    int next_prec; uint32_t next_kpad;      // precision of the next layer's weights; its K rounded up to a whole chunk
 };
 
 // elements covered by one 128-bit load, per stored precision
@@ -82,37 +98,39 @@ __device__ __forceinline__ void frag_pos(int prec, uint32_t e, uint32_t &block, 
 __host__ __device__ inline uint32_t elems_per_load(int prec) { return 128u / spg_bits_per_elem(prec); }
 
 // Index (in bf16 units) of activation element k, column `col`, inside a staged-input buffer laid out as
-// [step][block][tile][t][8 columns][4]: the order in which the weight loads of a layer stored in
-// precision `prec` consume it.  T = column tiles of 8.
-__device__ __forceinline__ uint64_t staged_index(int prec, uint32_t T, uint32_t k, uint32_t col)
+// [step][block][tile][t][cw columns][4]: the order in which the weight loads of a layer stored in
+// precision `prec` consume it.  cs = columns kept (4, 8 or 16), cw = min(cs, 8) columns per tile.
+__device__ __forceinline__ uint64_t staged_index(int prec, uint32_t cs, uint32_t k, uint32_t col)
 {
     const uint32_t el = elems_per_load(prec), ks = 4 * el, nb = el / 4;
+    const uint32_t cw = cs < 8 ? cs : 8, tiles = cs / cw;
     const uint32_t step = k / ks, rem = k % ks, tt = rem / el, e = rem % el;
     uint32_t block, r;
     frag_pos(prec, e, block, r);
-    const uint64_t slot = ((((uint64_t)step * nb + block) * T + (col >> 3)) * 4 + tt) * 8 + (col & 7u);
+    const uint64_t slot = ((((uint64_t)step * nb + block) * tiles + col / cw) * 4 + tt) * cw + col % cw;
     return slot * 4 + r;
 }
 
 // Splits v into P bf16 terms (term i = round(v - earlier terms)) and stores them for columns n*P .. n*P+P-1.
-__device__ __forceinline__ void stage_value(__nv_bfloat16 *dst, int prec, uint32_t T, uint32_t k, uint32_t n, uint32_t P, float v)
+__device__ __forceinline__ void stage_value(__nv_bfloat16 *dst, int prec, uint32_t cs, uint32_t k, uint32_t n, uint32_t P, float v)
 {
     for (uint32_t q = 0; q < P; q++) {
         const __nv_bfloat16 h = __float2bfloat16_rn(v);
-        dst[staged_index(prec, T, k, n * P + q)] = h;
+        dst[staged_index(prec, cs, k, n * P + q)] = h;
         v -= __bfloat162float(h);
     }
 }
 
 // Stages a whole activation matrix x[N][in] (fp32) for a layer of precision `prec`: one thread per k.
-// Elements k in [in, kpad) are written as zero so that the last partial step multiplies by zero.
+// Elements k in [in, kpad) and the unused columns are written as zero.
 __global__ void __launch_bounds__(256)
 spg_gemv_stage_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t P, uint32_t in, uint32_t kpad,
-                      int prec, uint32_t T, __nv_bfloat16 *__restrict__ dst)
+                      int prec, uint32_t cs, __nv_bfloat16 *__restrict__ dst)
 {
     const uint32_t k = blockIdx.x * 256 + threadIdx.x;
     if (k >= kpad) return;
-    for (uint32_t n = 0; n < N; n++) stage_value(dst, prec, T, k, n, P, k < in ? x[(uint64_t)n * ldx + k] : 0.0f);
+    for (uint32_t n = 0; n < N; n++) stage_value(dst, prec, cs, k, n, P, k < in ? x[(uint64_t)n * ldx + k] : 0.0f);
+    for (uint32_t col = N * P; col < cs; col++) dst[staged_index(prec, cs, k, col)] = __float2bfloat16_rn(0.0f);
 }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
@@ -134,248 +152,407 @@ __device__ __forceinline__ uint32_t int_pair_to_bf16(uint32_t shifted, uint32_t 
 
 __device__ __forceinline__ uint32_t hi16_pair(uint32_t f0, uint32_t f1) { return __byte_perm(f0, f1, 0x7632); }
 
-template <int PREC, int T>
-__global__ void __launch_bounds__(GEMV_THREADS)
-spg_gemv_kernel(const GemvParams p)
+// ---- mbarrier / TMA wrappers (bounded waits) --------------------------------------
+__device__ __forceinline__ uint32_t gsmem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gbar_init(uint32_t bar, uint32_t count)
 {
-    using F = Fmt<PREC>;
-    constexpr int EL = F::EL, KS = 4 * EL, NB = EL / 4;       // per warp step: 4 lanes x EL elements; NB B-blocks per load
-    constexpr int CPAD = 8 * T;
-    extern __shared__ uint2 xs[];                             // [step][block][tile][t][8 columns] of 4 bf16
-    __shared__ int s_last;
-
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
-    const uint32_t rb = blockIdx.x, split = blockIdx.y;
-    const uint32_t k0 = split * p.kchunk;
-    const uint32_t kend = min(k0 + p.kchunk, p.in);
-    const uint32_t steps = (kend - k0 + KS - 1) / KS;
-
-    // ---- issue the first weight loads before staging x, so the two overlap ----
-    const uint32_t row_a = rb * ROWS_PER_CTA + warp * 16 + g, row_b = row_a + 8;
-    const uint8_t *wbase = reinterpret_cast<const uint8_t *>(p.w);
-    auto load_row = [&](uint32_t row, uint32_t step) -> uint4 {
-        const uint32_t kk = k0 + step * KS + t * EL;
-        if (row < p.out && kk < kend)
-            return __ldcs(reinterpret_cast<const uint4 *>(wbase + (((uint64_t)row * p.in + kk) * F::BITS >> 3)));
-        return make_uint4(0, 0, 0, 0);                         // zero bits decode to zero in every format
-    };
-    constexpr int U = 4;                                       // steps in flight per thread (8 x 128-bit loads)
-    uint4 ra[U], rbw[U];
-#pragma unroll
-    for (int u = 0; u < U; u++) { ra[u] = load_row(row_a, u); rbw[u] = load_row(row_b, u); }
-
-    // ---- copy this chunk of the staged input (already split into bf16 terms, in fragment order) ----
-    {
-        const uint32_t per_step = NB * T * 16;                 // 16-byte units per step
-        const uint4 *src = p.xin + (size_t)(k0 / KS) * per_step;
-        uint4 *dst = reinterpret_cast<uint4 *>(xs);
-        for (uint32_t i = tid; i < steps * per_step; i += GEMV_THREADS) dst[i] = __ldg(src + i);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void gbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Returns false once the abort flag is up (then every later wait returns at once) or when the bound is hit.
+__device__ __forceinline__ bool gbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *status, int code)
+{
+    if (*abort_flag) return false;
+    for (uint32_t i = 0; i < GEMV_WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
     }
-    __syncthreads();
+    *abort_flag = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_box_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// Named barriers between the consumer warps and the epilogue warp: the side that hands something over
+// only arrives (does not wait), the side that needs it waits.
+__device__ __forceinline__ void handoff_arrive(uint32_t id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(HANDOFF_THREADS) : "memory"); }
+__device__ __forceinline__ void handoff_wait(uint32_t id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(HANDOFF_THREADS) : "memory"); }
 
-    float acc[T][4];
-    float acc_hi[T][4];                                        // INT8 only: the high-nibble term
+// One step of one warp: 16 rows x (4 lanes x EL elements).  ra / rbv are the lane's 128-bit pieces of rows
+// g and g+8; xb points at this lane's slot of the step's staged activations (CW columns per tile).
+template <int PREC, int T, int CW>
+__device__ __forceinline__ void gemv_step(const uint4 &ra, const uint4 &rbv, const uint2 *xb, bool col_live,
+                                          float (&acc)[T][4], float (&acc_hi)[T][4])
+{
+    constexpr int NB = Fmt<PREC>::EL / 4;
+    const uint32_t wa[4] = { ra.x, ra.y, ra.z, ra.w };
+    const uint32_t wb[4] = { rbv.x, rbv.y, rbv.z, rbv.w };
 #pragma unroll
-    for (int i = 0; i < T; i++)
+    for (int b = 0; b < NB; b++) {
+        uint2 bf[T];
 #pragma unroll
-        for (int j = 0; j < 4; j++) { acc[i][j] = 0.0f; acc_hi[i][j] = 0.0f; }
-
-    for (uint32_t s0 = 0; s0 < steps; s0 += U) {
-        uint4 ca[U], cb[U];
+        for (int i = 0; i < T; i++) bf[i] = col_live ? xb[(b * T + i) * 4 * CW] : make_uint2(0u, 0u);   // lanes of columns not kept multiply by zero
+        if (PREC == SPG_P_I4) {
+            const int j = b >> 1, h = b & 1;
+            const uint32_t va = wa[j] ^ 0x88888888u, vb = wb[j] ^ 0x88888888u;     // nibble + 8
+            const uint32_t a0 = int_pair_to_bf16(va >> (8 * h), 0x000F000Fu, 0x43084308u);
+            const uint32_t a2 = int_pair_to_bf16(va >> (8 * h + 4), 0x000F000Fu, 0x43084308u);
+            const uint32_t a1 = int_pair_to_bf16(vb >> (8 * h), 0x000F000Fu, 0x43084308u);
+            const uint32_t a3 = int_pair_to_bf16(vb >> (8 * h + 4), 0x000F000Fu, 0x43084308u);
 #pragma unroll
-        for (int u = 0; u < U; u++) { ca[u] = ra[u]; cb[u] = rbw[u]; }
+            for (int i = 0; i < T; i++) mma_bf16(acc[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
+        } else if (PREC == SPG_P_I2) {
+            const int j = b >> 2, h = b & 3;
+            const uint32_t va = wa[j] ^ 0xAAAAAAAAu, vb = wb[j] ^ 0xAAAAAAAAu;     // crumb + 2
+            const uint32_t a0 = int_pair_to_bf16(va >> (4 * h), 0x00030003u, 0x43024302u);
+            const uint32_t a2 = int_pair_to_bf16(va >> (4 * h + 2), 0x00030003u, 0x43024302u);
+            const uint32_t a1 = int_pair_to_bf16(vb >> (4 * h), 0x00030003u, 0x43024302u);
+            const uint32_t a3 = int_pair_to_bf16(vb >> (4 * h + 2), 0x00030003u, 0x43024302u);
 #pragma unroll
-        for (int u = 0; u < U; u++) {                          // next group's loads go out before this group's math
-            ra[u] = load_row(row_a, s0 + U + u);
-            rbw[u] = load_row(row_b, s0 + U + u);
-        }
+            for (int i = 0; i < T; i++) mma_bf16(acc[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
+        } else if (PREC == SPG_P_I8) {
+            // q = 16*(q >> 4) + (q & 15): low nibbles are unsigned, high nibbles signed (+8 after the flip)
+            const uint32_t va = wa[b] ^ 0x80808080u, vb = wb[b] ^ 0x80808080u;
+            uint32_t a0 = int_pair_to_bf16(va, 0x000F000Fu, 0x43004300u);
+            uint32_t a2 = int_pair_to_bf16(va >> 8, 0x000F000Fu, 0x43004300u);
+            uint32_t a1 = int_pair_to_bf16(vb, 0x000F000Fu, 0x43004300u);
+            uint32_t a3 = int_pair_to_bf16(vb >> 8, 0x000F000Fu, 0x43004300u);
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const uint32_t step = s0 + u;
-            if (step >= steps) break;
-            const uint32_t wa[4] = { ca[u].x, ca[u].y, ca[u].z, ca[u].w };
-            const uint32_t wb[4] = { cb[u].x, cb[u].y, cb[u].z, cb[u].w };
-            const uint2 *xb = xs + (size_t)step * NB * T * 32 + t * 8 + g;
+            for (int i = 0; i < T; i++) mma_bf16(acc[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
+            a0 = int_pair_to_bf16(va >> 4, 0x000F000Fu, 0x43084308u);
+            a2 = int_pair_to_bf16(va >> 12, 0x000F000Fu, 0x43084308u);
+            a1 = int_pair_to_bf16(vb >> 4, 0x000F000Fu, 0x43084308u);
+            a3 = int_pair_to_bf16(vb >> 12, 0x000F000Fu, 0x43084308u);
 #pragma unroll
-            for (int b = 0; b < NB; b++) {
-                uint2 bf[T];
+            for (int i = 0; i < T; i++) mma_bf16(acc_hi[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
+        } else if (PREC == SPG_P_BF16) {
 #pragma unroll
-                for (int i = 0; i < T; i++) bf[i] = xb[(b * T + i) * 32];
-                if (PREC == SPG_P_I4) {
-                    const int j = b >> 1, h = b & 1;
-                    const uint32_t va = wa[j] ^ 0x88888888u, vb = wb[j] ^ 0x88888888u;     // nibble + 8
-                    const uint32_t a0 = int_pair_to_bf16(va >> (8 * h), 0x000F000Fu, 0x43084308u);
-                    const uint32_t a2 = int_pair_to_bf16(va >> (8 * h + 4), 0x000F000Fu, 0x43084308u);
-                    const uint32_t a1 = int_pair_to_bf16(vb >> (8 * h), 0x000F000Fu, 0x43084308u);
-                    const uint32_t a3 = int_pair_to_bf16(vb >> (8 * h + 4), 0x000F000Fu, 0x43084308u);
+            for (int i = 0; i < T; i++) mma_bf16(acc[i], wa[2 * b], wb[2 * b], wa[2 * b + 1], wb[2 * b + 1], bf[i].x, bf[i].y);
+        } else if (PREC == SPG_P_F16) {
+            // fp16 (11 significant bits) = bf16 head (8 bits) + bf16 tail (3 bits), both exact
+            uint32_t hi[4], lo[4];
+            const uint32_t src[4] = { wa[2 * b], wb[2 * b], wa[2 * b + 1], wb[2 * b + 1] };
 #pragma unroll
-                    for (int i = 0; i < T; i++) mma_bf16(acc[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
-                } else if (PREC == SPG_P_I2) {
-                    const int j = b >> 2, h = b & 3;
-                    const uint32_t va = wa[j] ^ 0xAAAAAAAAu, vb = wb[j] ^ 0xAAAAAAAAu;     // crumb + 2
-                    const uint32_t a0 = int_pair_to_bf16(va >> (4 * h), 0x00030003u, 0x43024302u);
-                    const uint32_t a2 = int_pair_to_bf16(va >> (4 * h + 2), 0x00030003u, 0x43024302u);
-                    const uint32_t a1 = int_pair_to_bf16(vb >> (4 * h), 0x00030003u, 0x43024302u);
-                    const uint32_t a3 = int_pair_to_bf16(vb >> (4 * h + 2), 0x00030003u, 0x43024302u);
+            for (int q = 0; q < 4; q++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&src[q]));
+                const uint32_t u0 = __float_as_uint(f.x) & 0xFFFF0000u, u1 = __float_as_uint(f.y) & 0xFFFF0000u;
+                hi[q] = hi16_pair(u0, u1);
+                lo[q] = hi16_pair(__float_as_uint(f.x - __uint_as_float(u0)), __float_as_uint(f.y - __uint_as_float(u1)));
+            }
 #pragma unroll
-                    for (int i = 0; i < T; i++) mma_bf16(acc[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
-                } else if (PREC == SPG_P_I8) {
-                    // q = 16*(q >> 4) + (q & 15): low nibbles are unsigned, high nibbles signed (+8 after the flip)
-                    const uint32_t va = wa[b] ^ 0x80808080u, vb = wb[b] ^ 0x80808080u;
-                    uint32_t a0 = int_pair_to_bf16(va, 0x000F000Fu, 0x43004300u);
-                    uint32_t a2 = int_pair_to_bf16(va >> 8, 0x000F000Fu, 0x43004300u);
-                    uint32_t a1 = int_pair_to_bf16(vb, 0x000F000Fu, 0x43004300u);
-                    uint32_t a3 = int_pair_to_bf16(vb >> 8, 0x000F000Fu, 0x43004300u);
+            for (int i = 0; i < T; i++) {
+                mma_bf16(acc[i], hi[0], hi[1], hi[2], hi[3], bf[i].x, bf[i].y);
+                mma_bf16(acc[i], lo[0], lo[1], lo[2], lo[3], bf[i].x, bf[i].y);
+            }
+        } else {
+            // fp32 = three bf16 terms of 8 bits each (head, middle, tail), all exact
+            uint32_t t0[4], t1[4], t2[4];
+            const uint32_t src[8] = { wa[0], wa[1], wb[0], wb[1], wa[2], wa[3], wb[2], wb[3] };
 #pragma unroll
-                    for (int i = 0; i < T; i++) mma_bf16(acc[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
-                    a0 = int_pair_to_bf16(va >> 4, 0x000F000Fu, 0x43084308u);
-                    a2 = int_pair_to_bf16(va >> 12, 0x000F000Fu, 0x43084308u);
-                    a1 = int_pair_to_bf16(vb >> 4, 0x000F000Fu, 0x43084308u);
-                    a3 = int_pair_to_bf16(vb >> 12, 0x000F000Fu, 0x43084308u);
+            for (int q = 0; q < 4; q++) {
+                const float f0 = __uint_as_float(src[2 * q]), f1 = __uint_as_float(src[2 * q + 1]);
+                const uint32_t h0 = src[2 * q] & 0xFFFF0000u, h1 = src[2 * q + 1] & 0xFFFF0000u;
+                const float r0 = f0 - __uint_as_float(h0), r1 = f1 - __uint_as_float(h1);
+                const uint32_t m0 = __float_as_uint(r0) & 0xFFFF0000u, m1 = __float_as_uint(r1) & 0xFFFF0000u;
+                t0[q] = hi16_pair(h0, h1);
+                t1[q] = hi16_pair(m0, m1);
+                t2[q] = hi16_pair(__float_as_uint(r0 - __uint_as_float(m0)), __float_as_uint(r1 - __uint_as_float(m1)));
+            }
 #pragma unroll
-                    for (int i = 0; i < T; i++) mma_bf16(acc_hi[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
-                } else if (PREC == SPG_P_BF16) {
-#pragma unroll
-                    for (int i = 0; i < T; i++) mma_bf16(acc[i], wa[2 * b], wb[2 * b], wa[2 * b + 1], wb[2 * b + 1], bf[i].x, bf[i].y);
-                } else if (PREC == SPG_P_F16) {
-                    // fp16 (11 significant bits) = bf16 head (8 bits) + bf16 tail (3 bits), both exact
-                    uint32_t hi[4], lo[4];
-                    const uint32_t src[4] = { wa[2 * b], wb[2 * b], wa[2 * b + 1], wb[2 * b + 1] };
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&src[q]));
-                        const uint32_t u0 = __float_as_uint(f.x) & 0xFFFF0000u, u1 = __float_as_uint(f.y) & 0xFFFF0000u;
-                        hi[q] = hi16_pair(u0, u1);
-                        lo[q] = hi16_pair(__float_as_uint(f.x - __uint_as_float(u0)), __float_as_uint(f.y - __uint_as_float(u1)));
-                    }
-#pragma unroll
-                    for (int i = 0; i < T; i++) {
-                        mma_bf16(acc[i], hi[0], hi[1], hi[2], hi[3], bf[i].x, bf[i].y);
-                        mma_bf16(acc[i], lo[0], lo[1], lo[2], lo[3], bf[i].x, bf[i].y);
-                    }
-                } else {
-                    // fp32 = three bf16 terms of 8 bits each (head, middle, tail), all exact
-                    uint32_t t0[4], t1[4], t2[4];
-                    const uint32_t src[8] = { wa[0], wa[1], wb[0], wb[1], wa[2], wa[3], wb[2], wb[3] };
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const float f0 = __uint_as_float(src[2 * q]), f1 = __uint_as_float(src[2 * q + 1]);
-                        const uint32_t h0 = src[2 * q] & 0xFFFF0000u, h1 = src[2 * q + 1] & 0xFFFF0000u;
-                        const float r0 = f0 - __uint_as_float(h0), r1 = f1 - __uint_as_float(h1);
-                        const uint32_t m0 = __float_as_uint(r0) & 0xFFFF0000u, m1 = __float_as_uint(r1) & 0xFFFF0000u;
-                        t0[q] = hi16_pair(h0, h1);
-                        t1[q] = hi16_pair(m0, m1);
-                        t2[q] = hi16_pair(__float_as_uint(r0 - __uint_as_float(m0)), __float_as_uint(r1 - __uint_as_float(m1)));
-                    }
-#pragma unroll
-                    for (int i = 0; i < T; i++) {
-                        mma_bf16(acc[i], t0[0], t0[1], t0[2], t0[3], bf[i].x, bf[i].y);
-                        mma_bf16(acc[i], t1[0], t1[1], t1[2], t1[3], bf[i].x, bf[i].y);
-                        mma_bf16(acc[i], t2[0], t2[1], t2[2], t2[3], bf[i].x, bf[i].y);
-                    }
-                }
+            for (int i = 0; i < T; i++) {
+                mma_bf16(acc[i], t0[0], t0[1], t0[2], t0[3], bf[i].x, bf[i].y);
+                mma_bf16(acc[i], t1[0], t1[1], t1[2], t1[3], bf[i].x, bf[i].y);
+                mma_bf16(acc[i], t2[0], t2[1], t2[2], t2[3], bf[i].x, bf[i].y);
             }
         }
     }
-
-    // ---- partial sums of this K split: [split][row][column] ----
-    const uint32_t out_pad = p.row_blocks * ROWS_PER_CTA;
-    float *pp = p.partial + ((uint64_t)split * out_pad) * CPAD;
-#pragma unroll
-    for (int i = 0; i < T; i++) {
-        float d0 = acc[i][0], d1 = acc[i][1], d2 = acc[i][2], d3 = acc[i][3];
-        if (PREC == SPG_P_I8) {
-            d0 = fmaf(16.0f, acc_hi[i][0], d0); d1 = fmaf(16.0f, acc_hi[i][1], d1);
-            d2 = fmaf(16.0f, acc_hi[i][2], d2); d3 = fmaf(16.0f, acc_hi[i][3], d3);
-        }
-        __stcg(reinterpret_cast<float2 *>(pp + (uint64_t)row_a * CPAD + i * 8 + 2 * t), make_float2(d0, d1));
-        __stcg(reinterpret_cast<float2 *>(pp + (uint64_t)row_b * CPAD + i * 8 + 2 * t), make_float2(d2, d3));
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const uint32_t ticket = atomicAdd(&p.tickets[rb], 1u);
-        s_last = ticket == p.splits - 1;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-
-    // ---- the last CTA of this row block finishes it: sum splits and terms, scale, bias, activation ----
-    for (uint32_t idx = tid; idx < ROWS_PER_CTA * p.N; idx += GEMV_THREADS) {
-        const uint32_t n = idx / ROWS_PER_CTA, row = rb * ROWS_PER_CTA + idx % ROWS_PER_CTA;
-        if (row >= p.out) continue;
-        float sum = 0.0f;
-        for (uint32_t s = 0; s < p.splits; s++) {
-            const float *src = p.partial + ((uint64_t)s * out_pad + row) * CPAD + n * p.P;
-            float part = 0.0f;
-            for (uint32_t q = p.P; q-- > 0;) part += __ldcg(src + q);      // smallest term first
-            sum += part;
-        }
-        const float yv = spg_activate(fmaf(sum, p.scale, p.bias[row]), p.act);
-        p.y[(uint64_t)n * p.ldy + row] = yv;
-        if (p.xout) stage_value(p.xout, p.next_prec, T, row, n, p.P, yv);
-    }
-    if (p.xout && rb == p.row_blocks - 1) {
-        // zero the tail of the next layer's last step (k in [out, next_kpad)), all columns
-        for (uint32_t idx = tid; idx < (p.next_kpad - p.out) * CPAD; idx += GEMV_THREADS)
-            p.xout[staged_index(p.next_prec, T, p.out + idx / CPAD, idx % CPAD)] = __float2bfloat16_rn(0.0f);
-    }
-    if (tid == 0) p.tickets[rb] = 0;                           // leave the counter ready for the next call
 }
 
-struct Plan { uint32_t P, C, T, kchunk, splits, row_blocks, kpad; size_t tickets_bytes, partial_bytes, staged_bytes, smem; bool ok; };
+template <int PREC, int T, int CW>
+__global__ void __launch_bounds__(GEMV_THREADS, 1)
+spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
+{
+    using F = Fmt<PREC>;
+    constexpr uint32_t EL = F::EL, NB = EL / 4;                // per warp step: 4 lanes x EL elements; NB B-blocks per load
+    constexpr uint32_t STEP_SLOTS = NB * T * 4 * CW;           // uint2 slots of staged input per step
+    constexpr uint32_t CPAD = 8 * T;
 
-int bits_of(int prec) { return (int)spg_bits_per_elem(prec); }
+    extern __shared__ uint8_t gemv_smem_raw[];
+    const uint32_t raw = gsmem_u32(gemv_smem_raw);
+    const uint32_t base = (raw + 127u) & ~127u;
+    uint8_t *smem = gemv_smem_raw + (base - raw);
+    // layout: ring of chunks, each = [16 rows x 8 warp slices of packed weights | staged input of the same K range];
+    // then the reduction buffer, the barriers and the abort flag
+    const uint32_t wchunk_bytes = 8 * p.box_bytes;
+    const uint32_t slot_bytes = wchunk_bytes + p.xchunk_bytes;
+    const uint32_t red_off = p.ring * slot_bytes;
+    constexpr uint32_t RED_FLOATS = CONSUMER_WARPS * ITEM_ROWS * CPAD;
+    const uint32_t bar_off = red_off + 2 * RED_FLOATS * 4;       // two reduction buffers, used alternately
+    const uint32_t full0 = base + bar_off, empty0 = full0 + 8 * p.ring;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + bar_off + 16 * p.ring);
+    float *red = reinterpret_cast<float *>(smem + red_off);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    if (tid == 0) {
+        for (uint32_t s = 0; s < p.ring; s++) { gbar_init(full0 + 8 * s, 1); gbar_init(empty0 + 8 * s, CONSUMER_WARPS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        // ------------------------------ producer: two copies per chunk -------------------
+        if (lane == 0) {
+            uint32_t gchunk = 0, s = 0, ph = 1;
+            bool alive = true;
+            for (uint32_t item = blockIdx.x; item < p.items && alive; item += gridDim.x) {
+                for (uint32_t c = 0; c < p.nchunks; c++, gchunk++) {
+                    if (!gbar_wait(empty0 + 8 * s, ph, abort_flag, p.status, 1)) { alive = false; break; }
+                    gbar_expect_tx(full0 + 8 * s, slot_bytes);
+                    tma_box_2d(base + s * slot_bytes, &wmap, full0 + 8 * s, (int)(c * (wchunk_bytes / ITEM_ROWS / 8)), (int)(item * ITEM_ROWS));
+                    bulk_copy_1d(base + s * slot_bytes + wchunk_bytes,
+                                 reinterpret_cast<const uint8_t *>(p.xin) + (size_t)c * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * s);
+                    if (++s == p.ring) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+        return;
+    }
+
+    if (warp == CONSUMER_WARPS + 1) {
+        // ------------------------------ epilogue warp ------------------------------
+        // Sums the sixteen K slices and the activation terms of each finished item, applies scale, bias and
+        // activation, writes y and stages the next layer's input, while the consumers stream the next item.
+        const uint32_t cs = CW * T, spare = cs - p.C;
+        uint32_t n_item = 0;
+        for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
+            const uint32_t rbuf = n_item & 1u;
+            handoff_wait(1 + rbuf);
+            const float *redb = red + rbuf * RED_FLOATS;
+            for (uint32_t idx = lane; idx < ITEM_ROWS * p.N; idx += 32) {
+                const uint32_t n = idx / ITEM_ROWS, rl = idx % ITEM_ROWS, row = item * ITEM_ROWS + rl;
+                if (row >= p.out) continue;
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < CONSUMER_WARPS; w++) {
+                    const float *src = redb + (w * ITEM_ROWS + rl) * CPAD + n * p.P;
+                    float part = 0.0f;
+                    for (uint32_t q = p.P; q-- > 0;) part += src[q];           // smallest term first
+                    sum += part;
+                }
+                const float yv = spg_activate(fmaf(sum, p.scale, p.bias[row]), p.act);
+                p.y[(uint64_t)n * p.ldy + row] = yv;
+                if (p.xout) stage_value(p.xout, p.next_prec, cs, row, n, p.P, yv);
+            }
+            __threadfence_block();
+            __syncwarp();
+            if (n_item + 2 < (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x) handoff_arrive(3 + rbuf);   // only if a later item will wait for it
+            if (p.xout) {
+                // columns that carry no sample stay zero in the next layer's staged input; so does its K tail
+                for (uint32_t idx = lane; idx < ITEM_ROWS * spare; idx += 32) {
+                    const uint32_t row = item * ITEM_ROWS + idx / spare;
+                    if (row < p.out) p.xout[staged_index(p.next_prec, cs, row, p.C + idx % spare)] = __float2bfloat16_rn(0.0f);
+                }
+                if (item == p.items - 1)
+                    for (uint32_t idx = lane; idx < (p.next_kpad - p.out) * cs; idx += 32)
+                        p.xout[staged_index(p.next_prec, cs, p.out + idx / cs, idx % cs)] = __float2bfloat16_rn(0.0f);
+            }
+        }
+        return;
+    }
+
+    // ------------------------------ consumers --------------------------------------
+    const bool col_live = g < CW;                              // with 4 kept columns only lanes of columns 0..3 load
+    const uint32_t row_pitch = 8 * p.spb * 64u;                // bytes of one chunk row (8 warp slices)
+    uint32_t s = 0, ph = 0, n_item = 0;
+    for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
+        // two accumulator sets (even / odd steps) keep two independent MMA chains in flight
+        float acc[2][T][4], acc_hi[2][T][4];                   // acc_hi: INT8 only (the high-nibble term)
+#pragma unroll
+        for (int e = 0; e < 2; e++)
+#pragma unroll
+            for (int i = 0; i < T; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) { acc[e][i][j] = 0.0f; acc_hi[e][i][j] = 0.0f; }
+
+        for (uint32_t c = 0; c < p.nchunks; c++) {
+            const bool ok = gbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 2);
+            const uint32_t slice = warp & 7u, sub = warp >> 3;             // which 8th of the chunk's K range, which half of its steps
+            const uint32_t per_sub = p.spb > 1 ? p.spb / 2 : 1;
+            if (ok && c * 8u + slice < p.nboxes && sub * per_sub < p.spb) {
+                const uint8_t *box = smem + s * slot_bytes + g * row_pitch + slice * p.spb * 64u + t * 16;
+                const uint2 *xs = reinterpret_cast<const uint2 *>(smem + s * slot_bytes + wchunk_bytes) +
+                                  (size_t)slice * p.spb * STEP_SLOTS + t * CW + (col_live ? g : 0);
+                for (uint32_t st = sub * per_sub; st < (sub + 1) * per_sub; st++) {
+                    const uint4 ra0 = *reinterpret_cast<const uint4 *>(box + st * 64);
+                    const uint4 rb0 = *reinterpret_cast<const uint4 *>(box + 8 * row_pitch + st * 64);
+                    if (st & 1u) gemv_step<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, acc[1], acc_hi[1]);
+                    else gemv_step<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, acc[0], acc_hi[0]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) gbar_arrive(empty0 + 8 * s);
+            if (++s == p.ring) { s = 0; ph ^= 1u; }
+        }
+
+        // ---- the sixteen partial sums go to shared memory [warp][row][column]; the epilogue warp takes over ----
+        const uint32_t rbuf = n_item & 1u;
+        if (n_item >= 2) handoff_wait(3 + rbuf);               // the epilogue warp has read this buffer's previous contents
+        float *redb = red + rbuf * RED_FLOATS;
+#pragma unroll
+        for (int i = 0; i < T; i++) {
+            float d0 = acc[0][i][0] + acc[1][i][0], d1 = acc[0][i][1] + acc[1][i][1];
+            float d2 = acc[0][i][2] + acc[1][i][2], d3 = acc[0][i][3] + acc[1][i][3];
+            if (PREC == SPG_P_I8) {
+                d0 = fmaf(16.0f, acc_hi[0][i][0] + acc_hi[1][i][0], d0); d1 = fmaf(16.0f, acc_hi[0][i][1] + acc_hi[1][i][1], d1);
+                d2 = fmaf(16.0f, acc_hi[0][i][2] + acc_hi[1][i][2], d2); d3 = fmaf(16.0f, acc_hi[0][i][3] + acc_hi[1][i][3], d3);
+            }
+            float *r0 = redb + ((warp * ITEM_ROWS + g) * CPAD) + i * 8 + 2 * t;
+            r0[0] = d0; r0[1] = d1;
+            r0[8 * CPAD] = d2; r0[8 * CPAD + 1] = d3;
+        }
+        __threadfence_block();
+        handoff_arrive(1 + rbuf);                              // no waiting: on to the next item
+    }
+}
+
+struct Plan {
+    uint32_t P, C, cs, T, CW, spb, box_bytes, nboxes, nchunks, kpad, items, ring, xdepth, xchunk_bytes;
+    size_t staged_bytes, smem;
+    bool ok;
+};
 
 Plan make_plan(const spgk_layer *L, uint32_t N)
 {
     Plan pl{};
     pl.ok = false;
-    if (!L || N == 0 || N > MAX_BATCH || (unsigned)L->precision >= SPG_P_COUNT) return pl;
-    const uint32_t el = 128u / (uint32_t)bits_of(L->precision), ks = 4 * el;
-    // 128-bit loads need 16-byte aligned packed rows
-    if (L->in % el || ((uintptr_t)L->w & 15u)) return pl;
-    pl.P = N <= 2 ? 3 : 2;
+    if (!L || N == 0 || N > MAX_BATCH || (unsigned)L->precision >= SPG_P_COUNT || L->in == 0 || L->out == 0) return pl;
+    const uint32_t bits = spg_bits_per_elem(L->precision), el = 128u / bits, ks = 4 * el;
+    const uint64_t row_bytes = (uint64_t)L->in * bits / 8;
+    // TMA needs 16-byte aligned packed rows; very short rows go to the general kernel
+    if (L->in % el || ((uintptr_t)L->w & 15u) || row_bytes < 64) return pl;
+    pl.P = N == 1 ? 3 : 2;
     pl.C = N * pl.P;
-    pl.T = (pl.C + 7) / 8;
-    pl.row_blocks = (L->out + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-    // enough CTAs for ~4 per SM, K chunks a multiple of the widest step (256), shared memory <= 64 KB
-    uint32_t want = (148u * 4 + pl.row_blocks - 1) / pl.row_blocks;
-    uint32_t kchunk = (L->in + want - 1) / want;
-    kchunk = (kchunk + 255u) & ~255u;
-    if (kchunk < 512) kchunk = 512;
-    const uint32_t cap = 65536u / (16u * pl.T);                 // bytes per k element = 8*T columns * 2
-    if (kchunk > cap) kchunk = cap;
-    kchunk = kchunk / ks * ks;
-    pl.kchunk = kchunk;
-    pl.splits = (L->in + kchunk - 1) / kchunk;
-    pl.tickets_bytes = ((size_t)pl.row_blocks * 4 + 255) & ~(size_t)255;
-    pl.partial_bytes = (size_t)pl.splits * pl.row_blocks * ROWS_PER_CTA * 8 * pl.T * sizeof(float);
-    pl.smem = (size_t)((kchunk + ks - 1) / ks) * ks * 16 * pl.T;
-    pl.kpad = (L->in + ks - 1) / ks * ks;
-    pl.staged_bytes = ((size_t)pl.kpad * 16 * pl.T + 255) & ~(size_t)255;
+    pl.cs = pl.C <= 4 ? 4 : (pl.C <= 8 ? 8 : 16);
+    pl.T = pl.cs == 16 ? 2 : 1;
+    pl.CW = pl.cs < 8 ? 4 : 8;
+    // a chunk = 8 boxes (one per warp) of spb steps; its staged input should fit 32 KB (three in flight), at most 64 KB (two)
+    const uint32_t per_spb = 8 * ks * 2 * pl.cs;
+    pl.spb = 0;
+    for (uint32_t s = 4; s >= 1; s >>= 1) if (per_spb * s <= 32768) { pl.spb = s; break; }
+    if (!pl.spb) for (uint32_t s = 4; s >= 1; s >>= 1) if (per_spb * s <= 65536) { pl.spb = s; break; }
+    if (!pl.spb) return pl;
+    pl.xchunk_bytes = per_spb * pl.spb;
+    pl.xdepth = pl.xchunk_bytes <= 32768 ? 3 : 2;
+    pl.box_bytes = ITEM_ROWS * pl.spb * 64;
+    pl.nboxes = (uint32_t)((row_bytes + pl.spb * 64 - 1) / (pl.spb * 64));
+    pl.nchunks = (pl.nboxes + 7) / 8;
+    pl.kpad = pl.nchunks * 8 * pl.spb * ks;
+    pl.items = (L->out + ITEM_ROWS - 1) / ITEM_ROWS;
+    pl.staged_bytes = ((size_t)pl.kpad * 2 * pl.cs + 255) & ~(size_t)255;
+    const size_t red = 2 * (size_t)CONSUMER_WARPS * ITEM_ROWS * 8 * pl.T * 4;
+    const size_t slot = 8 * (size_t)pl.box_bytes + pl.xchunk_bytes;           // one chunk: weights + its staged input
+    uint32_t ring = (uint32_t)((225u * 1024 - 128 - red - 1024) / slot);
+    if (ring > 8) ring = 8;
+    if (ring < 2) return pl;
+    pl.ring = ring;
+    pl.smem = 128 + (size_t)ring * slot + red + 16 * ring + 64;
     pl.ok = true;
     return pl;
 }
 
-template <int PREC, int T>
-int launch(const GemvParams &p, const Plan &pl, cudaStream_t s)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// View of the packed matrix as [out rows][row_bytes / 8] 64-bit words, boxes of 16 rows x box_row_bytes.  Cached per matrix.
+int weight_map(const spgk_layer *L, uint32_t box_row_bytes, CUtensorMap *out_map)
+{
+    struct Entry { const void *w; uint32_t in, out, box; int prec; CUtensorMap map; };
+    static Entry cache[32];
+    static int used = 0, next_slot = 0;
+    static std::mutex mu;
+    static EncodeTiledFn fn = nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; i++)
+        if (cache[i].w == L->w && cache[i].in == L->in && cache[i].out == L->out && cache[i].prec == L->precision && cache[i].box == box_row_bytes) { *out_map = cache[i].map; return SPGK_OK; }
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+            spgk_set_error("cuTensorMapEncodeTiled", "driver entry point not available");
+            return SPGK_E_CUDA;
+        }
+        fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    const cuuint64_t row_bytes = (cuuint64_t)L->in * spg_bits_per_elem(L->precision) / 8;
+    cuuint64_t dims[2] = { row_bytes / 8, L->out };          // 8-byte elements: a box row may then span 2 KB
+    cuuint64_t strides[1] = { row_bytes };
+    cuuint32_t box[2] = { box_row_bytes / 8, ITEM_ROWS };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void *>(L->w), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[64];
+        snprintf(msg, sizeof msg, "CUresult %d", (int)r);
+        spgk_set_error("cuTensorMapEncodeTiled (gemv weights)", msg);
+        return SPGK_E_CUDA;
+    }
+    Entry &e = cache[used < 32 ? used++ : (next_slot++ % 32)];
+    e.w = L->w; e.in = L->in; e.out = L->out; e.box = box_row_bytes; e.prec = L->precision; e.map = m;
+    *out_map = m;
+    return SPGK_OK;
+}
+
+template <int PREC, int T, int CW>
+int launch(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
 {
     static bool attr_done = false;
+    static int sms = 0;
     if (!attr_done) {
-        SPGK_CUDA(cudaFuncSetAttribute(spg_gemv_kernel<PREC, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
+        int dev = 0;
+        SPGK_CUDA(cudaGetDevice(&dev));
+        SPGK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        SPGK_CUDA(cudaFuncSetAttribute(spg_gemv_kernel<PREC, T, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_done = true;
     }
-    dim3 grid(pl.row_blocks, pl.splits);
-    spg_gemv_kernel<PREC, T><<<grid, GEMV_THREADS, pl.smem, s>>>(p);
+    const uint32_t grid = pl.items < (uint32_t)sms ? pl.items : (uint32_t)sms;
+    spg_gemv_kernel<PREC, T, CW><<<grid, GEMV_THREADS, pl.smem, s>>>(map, p);
     return spgk_check_launch("spg_gemv_kernel");
 }
 
 template <int PREC>
-int launch_t(const GemvParams &p, const Plan &pl, cudaStream_t s)
+int launch_t(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
 {
-    return pl.T == 1 ? launch<PREC, 1>(p, pl, s) : launch<PREC, 2>(p, pl, s);
+    if (pl.cs == 4) return launch<PREC, 1, 4>(map, p, pl, s);
+    if (pl.cs == 8) return launch<PREC, 1, 8>(map, p, pl, s);
+    return launch<PREC, 2, 8>(map, p, pl, s);
 }
 
 }  // namespace
@@ -385,14 +562,14 @@ extern "C" {
 size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N)
 {
     Plan pl = make_plan(L, N);
-    return pl.ok ? pl.tickets_bytes + pl.partial_bytes + pl.staged_bytes : 0;
+    return pl.ok ? HEAD_BYTES + pl.staged_bytes : 0;
 }
 
 size_t spgk_gemv_staged_bytes(uint32_t width, uint32_t N)
 {
     if (N == 0 || N > MAX_BATCH) return 0;
-    const uint32_t T = (N * (N <= 2 ? 3u : 2u) + 7) / 8;
-    return ((size_t)((width + 255u) & ~255u) * 16 * T + 255) & ~(size_t)255;
+    const uint32_t C = N * (N == 1 ? 3u : 2u), cs = C <= 4 ? 4 : (C <= 8 ? 8 : 16);
+    return ((size_t)((width + 4095u) & ~4095u) * 2 * cs + 255) & ~(size_t)255;     // K padded to the widest chunk
 }
 
 int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const void *staged_in, void *staged_out,
@@ -403,26 +580,29 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
     if (!pl.ok) return SPGK_E_UNSUPPORTED;
     if (!scratch) { spgk_set_error("spgk_layer_gemv", "scratch is NULL"); return SPGK_E_ARG; }
     cudaStream_t s = (cudaStream_t)stream;
+    CUtensorMap map;
+    int rc = weight_map(L, 8 * pl.spb * 64, &map);
+    if (rc) return rc;
     GemvParams p{};
-    p.w = L->w; p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out;
+    p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out;
     p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
-    p.x = x; p.ldx = ldx; p.y = y; p.ldy = ldy;
+    p.y = y; p.ldy = ldy;
     p.N = N; p.P = pl.P; p.C = pl.C;
-    p.kchunk = pl.kchunk; p.splits = pl.splits; p.row_blocks = pl.row_blocks;
+    p.items = pl.items; p.nboxes = pl.nboxes; p.nchunks = pl.nchunks; p.spb = pl.spb; p.box_bytes = pl.box_bytes;
+    p.ring = pl.ring; p.xdepth = pl.xdepth; p.xchunk_bytes = pl.xchunk_bytes;
     uint8_t *base = reinterpret_cast<uint8_t *>(scratch);
-    p.tickets = reinterpret_cast<uint32_t *>(base);
-    p.partial = reinterpret_cast<float *>(base + pl.tickets_bytes);
+    p.status = reinterpret_cast<int32_t *>(base);
     if (staged_in) {
         p.xin = reinterpret_cast<const uint4 *>(staged_in);
     } else {
         // split x into bf16 terms in the order this layer's weight loads consume them
-        __nv_bfloat16 *own = reinterpret_cast<__nv_bfloat16 *>(base + pl.tickets_bytes + pl.partial_bytes);
-        spg_gemv_stage_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.kpad, L->precision, pl.T, own);
-        int rc = spgk_check_launch("spg_gemv_stage_kernel");
+        __nv_bfloat16 *own = reinterpret_cast<__nv_bfloat16 *>(base + HEAD_BYTES);
+        spg_gemv_stage_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.kpad, L->precision, pl.cs, own);
+        rc = spgk_check_launch("spg_gemv_stage_kernel");
         if (rc) return rc;
         p.xin = reinterpret_cast<const uint4 *>(own);
     }
-    // The finishing CTAs can stage the next layer's input directly, when that layer will also run here
+    // The epilogue can stage the next layer's input directly, when that layer will also run here
     // and this layer's output needs no further pass (softmax) first.
     p.xout = nullptr; p.next_prec = 0; p.next_kpad = 0;
     if (next && staged_out && L->act != SPG_ACT_SOFTMAX && next->in == L->out) {
@@ -430,12 +610,12 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
         if (np.ok) { p.xout = reinterpret_cast<__nv_bfloat16 *>(staged_out); p.next_prec = next->precision; p.next_kpad = np.kpad; }
     }
     switch (L->precision) {
-        case SPG_P_I4:   return launch_t<SPG_P_I4>(p, pl, s);
-        case SPG_P_I2:   return launch_t<SPG_P_I2>(p, pl, s);
-        case SPG_P_I8:   return launch_t<SPG_P_I8>(p, pl, s);
-        case SPG_P_BF16: return launch_t<SPG_P_BF16>(p, pl, s);
-        case SPG_P_F16:  return launch_t<SPG_P_F16>(p, pl, s);
-        default:         return launch_t<SPG_P_F32>(p, pl, s);
+        case SPG_P_I4:   return launch_t<SPG_P_I4>(map, p, pl, s);
+        case SPG_P_I2:   return launch_t<SPG_P_I2>(map, p, pl, s);
+        case SPG_P_I8:   return launch_t<SPG_P_I8>(map, p, pl, s);
+        case SPG_P_BF16: return launch_t<SPG_P_BF16>(map, p, pl, s);
+        case SPG_P_F16:  return launch_t<SPG_P_F16>(map, p, pl, s);
+        default:         return launch_t<SPG_P_F32>(map, p, pl, s);
     }
 }
 
@@ -451,6 +631,22 @@ int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx, float *y,
 {
     if (!x) { spgk_set_error("spgk_layer_gemv", "bad argument"); return SPGK_E_ARG; }
     return spgk_layer_gemv_chain(L, nullptr, nullptr, nullptr, x, ldx, y, ldy, N, scratch, stream);
+}
+
+// Reads back the status word at the start of a GEMV scratch buffer (synchronises the stream).
+int spgk_gemv_status(void *scratch, void *stream)
+{
+    int32_t h = 0;
+    SPGK_CUDA(cudaMemcpyAsync(&h, scratch, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SPGK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (h != 0) {
+        char msg[96];
+        snprintf(msg, sizeof msg, "bounded wait %d gave up inside the GEMV kernel", (int)h);
+        spgk_set_error("spg_gemv_kernel", msg);
+        SPGK_CUDA(cudaMemsetAsync(scratch, 0, sizeof h, (cudaStream_t)stream));
+        return SPGK_E_TIMEOUT;
+    }
+    return SPGK_OK;
 }
 
 }  // extern "C"

@@ -153,6 +153,10 @@ static void prof_mark(spg_net *n);
 static int finish(spg_net *n)
 {
     int rc;
+    if (n->gemv_pending) {
+        n->gemv_pending = false;
+        if ((rc = spg_map_kernel_error(spgk_gemv_status(n->d_gemv_scratch, n->stream), "GEMV"))) return rc;
+    }
     if (n->status_pending) {
         n->status_pending = false;
         if ((rc = spg_map_kernel_error(spgk_gemm_tc_status(n->d_status, n->stream), "tcgen05 GEMM"))) return rc;
@@ -268,7 +272,7 @@ static int small_reserve(spg_net *n, uint32_t N)
 /* Runs N <= SPGK_GEMV_MAX_BATCH rows.  d_x == NULL means the caller already
  * placed the input rows in slot 0 of the workspace (after this function
  * reserved it through a first call with N rows -- see forward()). */
-int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N, float **d_last)
+int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N, float **d_last, float *d_final)
 {
     NeuralNetwork *p = &n->pub;
     int rc = small_reserve(n, N);
@@ -281,12 +285,13 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
         const spgk_layer *next = l + 1 < n->dev_layers ? &n->klayers[l + 1] : NULL;
-        float *y = n->d_small + (size_t)N * p->neuron_offsets[l + 1];
+        float *y = (d_final && l + 1 == n->dev_layers) ? d_final : n->d_small + (size_t)N * p->neuron_offsets[l + 1];
         void *staged_out = n->d_staged[(l + 1) & 1];
         prof_mark(n);
         int k = spgk_layer_gemv_chain(L, next, staged, staged_out, x, xld, y, L->out, N, n->d_gemv_scratch, n->stream);
         prof_mark(n);
         staged = (k == SPGK_OK && next && spgk_gemv_chain_stages_next(L, next, N)) ? staged_out : NULL;
+        if (k == SPGK_OK) n->gemv_pending = true;
         if (k == SPGK_E_UNSUPPORTED) {
             if (n->prof_used >= 2) n->prof_used -= 2;      /* nothing was launched between the two marks */
             path = "simt";
@@ -297,7 +302,7 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
         x = y; xld = L->out;
     }
     spg_note_path(path);
-    *d_last = n->d_small + (size_t)N * p->neuron_offsets[p->layers - 1];
+    *d_last = d_final ? d_final : n->d_small + (size_t)N * p->neuron_offsets[p->layers - 1];
     return SPINGALETT_OK;
 }
 
@@ -452,10 +457,8 @@ float *forward_batch_struct_arguments(ForwardBatchArgs a)
 
     if (N <= SPGK_GEMV_MAX_BATCH) {
         float *d_last = NULL;
-        if (spg_dev_forward_small(n, d_x, in0, N, &d_last)) return NULL;
-        int k = out_dev ? spgk_memcpy_d2d(result, d_last, out_bytes, n->stream)
-                        : spgk_memcpy_d2h(result, d_last, out_bytes, n->stream);
-        if (spg_map_kernel_error(k, "forward_batch: output copy")) return NULL;
+        if (spg_dev_forward_small(n, d_x, in0, N, &d_last, out_dev ? result : NULL)) return NULL;
+        if (!out_dev && spg_map_kernel_error(spgk_memcpy_d2h(result, d_last, out_bytes, n->stream), "forward_batch: output copy")) return NULL;
     } else {
         float *d_out = result;
         if (!out_dev) {

@@ -45,7 +45,7 @@ typedef struct {
     /* small-batch workspace: fp32 activations of every layer for up to
      * small_cap rows, laid out layer after layer ([rows][width] each) */
     float *d_small; uint32_t small_cap;
-    void *d_gemv_scratch; size_t gemv_scratch_bytes;
+    void *d_gemv_scratch; size_t gemv_scratch_bytes; bool gemv_pending;
     void *d_staged[2]; size_t staged_bytes[2];   /* ping-pong staged inputs of the GEMV chain */
 
     /* large-batch workspace */
@@ -95,7 +95,7 @@ SPG_HIDDEN void spg_net_drop_payload(spg_net *n);
 SPG_HIDDEN int spg_dev_ensure(spg_net *n);           /* upload if needed */
 SPG_HIDDEN void spg_dev_release(spg_net *n);
 SPG_HIDDEN void spg_dev_invalidate(spg_net *n);
-SPG_HIDDEN int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N, float **d_last);
+SPG_HIDDEN int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N, float **d_last, float *d_final);
 SPG_HIDDEN int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out);
 SPG_HIDDEN int spg_map_kernel_error(int rc, const char *where);
 /* train.c */

@@ -232,11 +232,11 @@ float *forward_struct_arguments(ForwardArgs args)
     }
     memcpy(pn->h_stage, args.input, (size_t)n->topology[0] * sizeof(float));
     /* the workspace holds every layer's activations; slot 0 is the input */
-    if (spg_dev_forward_small(pn, NULL, 0, 1, NULL) != SPINGALETT_OK) return NULL;      /* reserve */
+    if (spg_dev_forward_small(pn, NULL, 0, 1, NULL, NULL) != SPINGALETT_OK) return NULL;      /* reserve */
     if (spg_map_kernel_error(spgk_memcpy_h2d(pn->d_small, pn->h_stage, (size_t)n->topology[0] * sizeof(float), pn->stream),
                              "forward: input copy")) return NULL;
     float *d_last = NULL;
-    if (spg_dev_forward_small(pn, NULL, 0, 1, &d_last) != SPINGALETT_OK) return NULL;
+    if (spg_dev_forward_small(pn, NULL, 0, 1, &d_last, NULL) != SPINGALETT_OK) return NULL;
     if (spg_map_kernel_error(spgk_memcpy_d2h(pn->h_stage, pn->d_small, need, pn->stream), "forward: copy back")) return NULL;
     if (spg_map_kernel_error(spgk_stream_sync(pn->stream), "forward: sync")) return NULL;
     memcpy(n->neurons, pn->h_stage, need);

@@ -162,6 +162,9 @@ def test_gemv_against_float64(spg, k, oracle, prec, out, inn, n):
     xd = torch.from_numpy(x).cuda()
     y = torch.full((n + 1, out), -9.0, device="cuda")
     nbytes = k.spgk_gemv_scratch_bytes(C.byref(L), n)
+    if inn * {0: 32, 1: 16, 2: 16, 3: 8, 4: 4, 5: 2}[prec] // 8 < 64:
+        assert nbytes == 0                    # packed rows shorter than one 64-byte step: not this kernel's case
+        return
     assert nbytes > 0
     scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
     for rep in range(2):                      # the second call checks the ticket counters were left at zero
@@ -171,7 +174,9 @@ def test_gemv_against_float64(spg, k, oracle, prec, out, inn, n):
         want = ACT[act](x.astype(np.float64) @ dec.T + bias)
         got = y.cpu().numpy()
         assert np.all(got[n] == -9.0)
-        assert np.abs(got[:n] - want).max() <= 3e-6 * max(1.0, np.abs(want).max()) * np.sqrt(inn / 256), (rep, np.abs(got[:n] - want).max())
+        # one row: three bf16 terms (24 bits); more rows: two terms (16 bits) per activation
+        tol = (3e-6 if n == 1 else 3e-5) * max(1.0, np.abs(want).max()) * np.sqrt(inn / 256)
+        assert np.abs(got[:n] - want).max() <= tol, (rep, np.abs(got[:n] - want).max())
 
 
 def test_gemv_declines_unaligned_rows(spg, k):
