@@ -136,6 +136,32 @@ SPGK_API int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, 
                                    const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,
                                    void *scratch, void *stream);
 
+/* ---- K3: weight-streaming tensor-core layer, 1..128 rows --------------------
+ * The memory-bound regime on tcgen05: the 128 rows of the MMA tile are weight
+ * rows, its columns are the batch (each row as two or three bf16 terms, so all
+ * products are exact), the packed INT4 / INT2 / INT8 weights arrive by TMA and
+ * are dequantised in shared memory by converter warps into the K-major operand
+ * tile (BF16 weights are used in place), the accumulator lives in tensor memory.
+ * Needs 16-byte aligned packed rows and N*terms <= 256 columns; FP16/FP32 files
+ * and other shapes return SPGK_E_UNSUPPORTED (use spgk_layer_gemv / _simt).
+ * operand_in : this layer's activation operand as written by the previous call
+ *              (bf16 terms, K order permuted to match the unpacking); NULL makes
+ *              the call build it from x (one small extra kernel).
+ * operand_out: if spgk_wstream_stages_next(L, next, N) == 1 the epilogue writes
+ *              next's operand there (spgk_wstream_operand_bytes(next->in, N) bytes).
+ * scratch    : spgk_wstream_scratch_bytes(L, N) bytes, ZERO-FILLED before first use
+ *              (status word + ticket counters; both are left at zero).
+ * y (fp32 [N][ldy]) is always written; ACT_SOFTMAX is left to spgk_softmax_rows.
+ * Does forward()/batch_forward()'s layer step, reference Network.c:218-247,
+ * Training.c:327-343, with the decode of Serialize.c:222-294 fused in. */
+SPGK_API size_t spgk_wstream_scratch_bytes(const spgk_layer *L, uint32_t N);
+SPGK_API size_t spgk_wstream_operand_bytes(uint32_t width, uint32_t N);
+SPGK_API int spgk_wstream_stages_next(const spgk_layer *L, const spgk_layer *next, uint32_t N);
+SPGK_API int spgk_layer_wstream(const spgk_layer *L, const spgk_layer *next, const void *operand_in, void *operand_out,
+                                const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,
+                                void *scratch, void *stream);
+SPGK_API int spgk_wstream_status(void *scratch, void *stream);
+
 /* ---- K2: large-batch tcgen05 GEMM layer ----------------------------------
  * C[N][out] = act(bias + w_scale * A[N][in] * W^T) with the accumulator in
  * tensor memory; both operands reach shared memory by TMA (no multicast).

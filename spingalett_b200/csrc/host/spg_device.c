@@ -74,6 +74,8 @@ void spg_dev_release(spg_net *n)
     spgk_free(n->d_small); n->d_small = NULL; n->small_cap = 0;
     spgk_free(n->d_gemv_scratch); n->d_gemv_scratch = NULL; n->gemv_scratch_bytes = 0;
     for (int i = 0; i < 2; i++) { spgk_free(n->d_staged[i]); n->d_staged[i] = NULL; n->staged_bytes[i] = 0; }
+    for (int i = 0; i < 2; i++) { spgk_free(n->d_operand[i]); n->d_operand[i] = NULL; n->operand_bytes[i] = 0; }
+    spgk_free(n->d_ws_scratch); n->d_ws_scratch = NULL; n->ws_scratch_bytes = 0;
     spgk_free(n->d_in32); n->d_in32 = NULL; n->in32_bytes = 0;
     spgk_free(n->d_out32); n->d_out32 = NULL; n->out32_bytes = 0;
     for (int i = 0; i < 2; i++) {
@@ -153,6 +155,10 @@ static void prof_mark(spg_net *n);
 static int finish(spg_net *n)
 {
     int rc;
+    if (n->ws_pending) {
+        n->ws_pending = false;
+        if ((rc = spg_map_kernel_error(spgk_wstream_status(n->d_ws_scratch, n->stream), "weight-stream kernel"))) return rc;
+    }
     if (n->gemv_pending) {
         n->gemv_pending = false;
         if ((rc = spg_map_kernel_error(spgk_gemv_status(n->d_gemv_scratch, n->stream), "GEMV"))) return rc;
@@ -239,6 +245,15 @@ static int reserve(void **buf, size_t *have, size_t need, const char *what)
 /* small-batch chain                                                         */
 /* ------------------------------------------------------------------------ */
 
+/* device buffer that must start zero-filled (status words, ticket counters) */
+static int reserve_zeroed(spg_net *n, void **buf, size_t *have, size_t need, const char *what)
+{
+    if (!need || (*have >= need && *buf)) return SPINGALETT_OK;
+    int rc = reserve(buf, have, need, what);
+    if (rc) return rc;
+    return spg_map_kernel_error(spgk_memset(*buf, 0, need, n->stream), what);
+}
+
 static int small_reserve(spg_net *n, uint32_t N)
 {
     NeuralNetwork *p = &n->pub;
@@ -249,29 +264,41 @@ static int small_reserve(spg_net *n, uint32_t N)
         if (rc) return rc;
         n->d_small = b; n->small_cap = N;
     }
-    size_t need = 0, staged = 0;
+    size_t gemv = 0, staged = 0, ws = 0, operand = 0;
     for (uint32_t l = 0; l < n->dev_layers; l++) {
-        size_t s = spgk_gemv_scratch_bytes(&n->klayers[l], N);
-        if (s > need) need = s;
-        s = spgk_gemv_staged_bytes(n->klayers[l].in, N);
-        if (s > staged) staged = s;
+        const spgk_layer *L = &n->klayers[l];
+        size_t s = N <= SPGK_GEMV_MAX_BATCH ? spgk_gemv_scratch_bytes(L, N) : 0;
+        if (s) {
+            if (s > gemv) gemv = s;
+            s = spgk_gemv_staged_bytes(L->in, N);
+            if (s > staged) staged = s;
+            continue;
+        }
+        s = spgk_wstream_scratch_bytes(L, N);
+        if (s > ws) ws = s;
+        if (s && (s = spgk_wstream_operand_bytes(L->in, N)) > operand) operand = s;
     }
-    for (int i = 0; i < 2 && staged; i++) {
-        int rc = reserve(&n->d_staged[i], &n->staged_bytes[i], staged, "gemv staged input");
-        if (rc) return rc;
+    int rc;
+    for (int i = 0; i < 2; i++) {
+        if (staged && (rc = reserve(&n->d_staged[i], &n->staged_bytes[i], staged, "gemv staged input"))) return rc;
+        if (operand && (rc = reserve(&n->d_operand[i], &n->operand_bytes[i], operand, "activation operand"))) return rc;
     }
-    if (need && (n->gemv_scratch_bytes < need || !n->d_gemv_scratch)) {
-        int rc = reserve(&n->d_gemv_scratch, &n->gemv_scratch_bytes, need, "gemv scratch");
-        if (rc) return rc;
-        /* the kernel's ticket counters must start at zero; it leaves them at zero */
-        return spg_map_kernel_error(spgk_memset(n->d_gemv_scratch, 0, need, n->stream), "gemv scratch clear");
-    }
-    return SPINGALETT_OK;
+    if ((rc = reserve_zeroed(n, &n->d_gemv_scratch, &n->gemv_scratch_bytes, gemv, "gemv scratch"))) return rc;
+    return reserve_zeroed(n, &n->d_ws_scratch, &n->ws_scratch_bytes, ws, "weight-stream scratch");
 }
 
-/* Runs N <= SPGK_GEMV_MAX_BATCH rows.  d_x == NULL means the caller already
- * placed the input rows in slot 0 of the workspace (after this function
- * reserved it through a first call with N rows -- see forward()). */
+/* 1 if every layer can run on the weight-streaming tensor-core kernel at this batch */
+static bool all_wstream(const spg_net *n, uint32_t N)
+{
+    for (uint32_t l = 0; l < n->dev_layers; l++)
+        if (!spgk_wstream_scratch_bytes(&n->klayers[l], N)) return false;
+    return true;
+}
+
+/* Small / medium batches (fp32 activations between layers; every layer streams its packed weights once).
+ * Per layer, in order of preference: the weight-streaming tcgen05 kernel, the mma.sync GEMV (<= 8 rows),
+ * the general SIMT kernel.  d_x == NULL means the caller already placed the input rows in slot 0 of the
+ * workspace (after a reservation-only call, see forward()). */
 int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N, float **d_last, float *d_final)
 {
     NeuralNetwork *p = &n->pub;
@@ -280,28 +307,40 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
     if (!d_last) return SPINGALETT_OK;          /* reservation only */
     const float *x = d_x ? d_x : n->d_small;
     uint32_t xld = d_x ? ldx : p->topology[0];
-    const char *path = "gemv";
-    const void *staged = NULL;                       /* input of the layer in flight, already in the kernel's order */
+    const char *path = NULL;
+    const void *staged = NULL, *operand = NULL;      /* input of the layer in flight, already in a kernel's own order */
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
         const spgk_layer *next = l + 1 < n->dev_layers ? &n->klayers[l + 1] : NULL;
         float *y = (d_final && l + 1 == n->dev_layers) ? d_final : n->d_small + (size_t)N * p->neuron_offsets[l + 1];
-        void *staged_out = n->d_staged[(l + 1) & 1];
+        /* up to 8 rows: the mma.sync GEMV first (measured faster there), then the tcgen05 streaming kernel;
+         * more rows: the streaming kernel only */
+        const char *used = "gemv";
+        int k = SPGK_E_UNSUPPORTED;
         prof_mark(n);
-        int k = spgk_layer_gemv_chain(L, next, staged, staged_out, x, xld, y, L->out, N, n->d_gemv_scratch, n->stream);
+        if (N <= SPGK_GEMV_MAX_BATCH) {
+            k = spgk_layer_gemv_chain(L, next, staged, n->d_staged[(l + 1) & 1], x, xld, y, L->out, N, n->d_gemv_scratch, n->stream);
+            if (k == SPGK_OK) n->gemv_pending = true;
+        }
+        if (k == SPGK_E_UNSUPPORTED) {
+            used = "wstream";
+            k = spgk_layer_wstream(L, next, operand, n->d_operand[(l + 1) & 1], x, xld, y, L->out, N, n->d_ws_scratch, n->stream);
+            if (k == SPGK_OK) n->ws_pending = true;
+        }
+        operand = (k == SPGK_OK && used[0] == 'w' && next && spgk_wstream_stages_next(L, next, N)) ? n->d_operand[(l + 1) & 1] : NULL;
+        staged = (k == SPGK_OK && used[0] == 'g' && next && spgk_gemv_chain_stages_next(L, next, N)) ? n->d_staged[(l + 1) & 1] : NULL;
         prof_mark(n);
-        staged = (k == SPGK_OK && next && spgk_gemv_chain_stages_next(L, next, N)) ? staged_out : NULL;
-        if (k == SPGK_OK) n->gemv_pending = true;
         if (k == SPGK_E_UNSUPPORTED) {
             if (n->prof_used >= 2) n->prof_used -= 2;      /* nothing was launched between the two marks */
-            path = "simt";
+            used = "simt";
             k = spgk_layer_simt(L, x, xld, y, L->out, N, n->stream);
         }
         if ((rc = spg_map_kernel_error(k, "layer (small batch)"))) return rc;
         if (L->act == ACT_SOFTMAX && (rc = spg_map_kernel_error(spgk_softmax_rows(y, L->out, N, L->out, n->stream), "softmax"))) return rc;
+        if (!path || used[0] == 's' || (used[0] == 'w' && path[0] == 'g')) path = used;    /* report the most general kernel used */
         x = y; xld = L->out;
     }
-    spg_note_path(path);
+    spg_note_path(path ? path : "none");
     *d_last = d_final ? d_final : n->d_small + (size_t)N * p->neuron_offsets[p->layers - 1];
     return SPINGALETT_OK;
 }
@@ -455,10 +494,19 @@ float *forward_batch_struct_arguments(ForwardBatchArgs a)
         d_x = n->d_in32;
     }
 
-    if (N <= SPGK_GEMV_MAX_BATCH) {
-        float *d_last = NULL;
-        if (spg_dev_forward_small(n, d_x, in0, N, &d_last, out_dev ? result : NULL)) return NULL;
-        if (!out_dev && spg_map_kernel_error(spgk_memcpy_d2h(result, d_last, out_bytes, n->stream), "forward_batch: output copy")) return NULL;
+    /* Up to 8 rows always take the weight-streaming chain; up to 512 rows do so (in groups of at most 128
+     * rows, each group streaming the packed weights once) when every layer is eligible for the tensor-core
+     * streaming kernel; everything else is the large-batch GEMM chain. */
+    const uint32_t group = N <= SPGK_GEMV_MAX_BATCH ? N : 128u;
+    if (N <= SPGK_GEMV_MAX_BATCH || (N <= 512 && all_wstream(n, N < group ? N : group))) {
+        for (uint32_t r0 = 0; r0 < N; r0 += group) {
+            const uint32_t rows = N - r0 < group ? N - r0 : group;
+            float *d_last = NULL;
+            float *dst_dev = out_dev ? result + (size_t)r0 * outw : NULL;
+            if (spg_dev_forward_small(n, d_x + (size_t)r0 * in0, in0, rows, &d_last, dst_dev)) return NULL;
+            if (!out_dev && spg_map_kernel_error(spgk_memcpy_d2h(result + (size_t)r0 * outw, d_last, (size_t)rows * outw * sizeof(float), n->stream),
+                                                 "forward_batch: output copy")) return NULL;
+        }
     } else {
         float *d_out = result;
         if (!out_dev) {

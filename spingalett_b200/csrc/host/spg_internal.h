@@ -47,6 +47,8 @@ typedef struct {
     float *d_small; uint32_t small_cap;
     void *d_gemv_scratch; size_t gemv_scratch_bytes; bool gemv_pending;
     void *d_staged[2]; size_t staged_bytes[2];   /* ping-pong staged inputs of the GEMV chain */
+    void *d_operand[2]; size_t operand_bytes[2]; /* ping-pong activation operands of the weight-streaming chain */
+    void *d_ws_scratch; size_t ws_scratch_bytes; bool ws_pending;
 
     /* large-batch workspace */
     float *d_in32;  size_t in32_bytes;      /* staging for host inputs */

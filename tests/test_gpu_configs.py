@@ -59,7 +59,7 @@ def test_large_int4_mlp_batch_sweep(spg, l_net, n):
     x = nets.normal_inputs(n, nets.L_TOPO[0], seed=100 + n)
     spg.set_math_mode(spg.abi.MATH_EXACT)
     got = net.forward_batch(x)
-    assert spg.last_path() == ("gemv" if n <= 8 else "tcgen05")
+    assert spg.last_path() == ("gemv" if n <= 8 else "wstream")
     rows = np.arange(n) if n <= 64 else np.random.default_rng(2).choice(n, 64, replace=False)
     want = onet.forward_batch(x[rows])
     agree, err = nets.parity(got[rows], want)

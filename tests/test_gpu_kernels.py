@@ -188,3 +188,45 @@ def test_gemv_declines_unaligned_rows(spg, k):
     x = torch.zeros(784, device="cuda")
     y = torch.zeros(16, device="cuda")
     assert k.spgk_layer_gemv(C.byref(L), x.data_ptr(), 784, y.data_ptr(), 16, 1, payload.data_ptr(), None) == -5
+
+
+@pytest.mark.parametrize("prec", [2, 3, 4, 5])
+@pytest.mark.parametrize("out,inn,n", [(128, 256, 1), (100, 1024, 2), (1000, 8192, 3), (130, 512, 8), (257, 4096, 16),
+                                       (640, 2048, 64), (16, 16384, 5), (300, 1280, 128)])
+def test_wstream_against_float64(spg, k, oracle, prec, out, inn, n):
+    """Weight-streaming tcgen05 layer (in-smem dequantisation, K splits, ragged row tiles) vs a float64 product of
+    the decoded weights; products are exact, so only fp32 accumulation and the 16/24-bit activation split remain."""
+    import torch
+    lib = k
+    vp = C.c_void_p
+    lib.spgk_wstream_scratch_bytes.argtypes = [C.POINTER(spg.abi.KLayer), C.c_uint32]
+    lib.spgk_wstream_scratch_bytes.restype = C.c_size_t
+    lib.spgk_layer_wstream.argtypes = [C.POINTER(spg.abi.KLayer), vp, vp, vp, vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, vp, vp]
+    lib.spgk_wstream_status.argtypes = [vp, vp]
+    rng = np.random.default_rng(out * 17 + inn + n)
+    vals = (rng.standard_normal(out * inn) / np.sqrt(inn)).astype(np.float32)
+    raw = oracle.Oracle.encode(vals, prec)
+    dec = oracle.Oracle.decode(raw, out * inn, prec).astype(np.float64).reshape(out, inn)
+    skip = 4 if prec >= 3 else 0
+    amax = float(np.frombuffer(raw[:4].tobytes(), np.float32)[0]) if skip else 1.0
+    scale = amax / {3: 127.0, 4: 7.0, 5: 1.0}[prec] if skip else 1.0
+    payload = torch.from_numpy(np.concatenate([raw[skip:], np.zeros(256, np.uint8)])).cuda()
+    bias = rng.standard_normal(out).astype(np.float32) * 0.1
+    bd = torch.from_numpy(bias).cuda()
+    act = [1, 6, 3, 2, 0, 4][(out + n) % 6]
+    L = spg.abi.KLayer(payload.data_ptr(), bd.data_ptr(), scale, inn, out, prec, act)
+    x = rng.standard_normal((n, inn)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.full((n + 1, out), -9.0, device="cuda")
+    nbytes = lib.spgk_wstream_scratch_bytes(C.byref(L), n)
+    assert nbytes > 0
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    for rep in range(2):                      # the second call checks the ticket counters were left at zero
+        rc = lib.spgk_layer_wstream(C.byref(L), None, None, None, xd.data_ptr(), inn, y.data_ptr(), out, n, scratch.data_ptr(), None)
+        assert rc == 0, lib.spgk_error_string()
+        assert lib.spgk_wstream_status(scratch.data_ptr(), None) == 0, lib.spgk_error_string()
+        want = ACT[act](x.astype(np.float64) @ dec.T + bias)
+        got = y.cpu().numpy()
+        assert np.all(got[n] == -9.0)
+        tol = (3e-6 if n == 1 else 3e-5) * max(1.0, np.abs(want).max()) * np.sqrt(inn / 256)
+        assert np.abs(got[:n] - want).max() <= tol, (rep, np.abs(got[:n] - want).max())
