@@ -74,7 +74,7 @@ def parse():
     ap.add_argument("--workload", default="mlp", choices=list(WORKLOADS), help="mlp = the benchmark line; wide/large = the other configurations")
     ap.add_argument("--dtype", default=None, choices=PRECS)
     ap.add_argument("--batch", type=int, default=None)
-    ap.add_argument("--math", default="exact", choices=["exact", "fast"])
+    ap.add_argument("--math", default="auto", choices=["auto", "exact", "fast"])
     ap.add_argument("--all-dtypes", action="store_true", help="also report every stored precision (fewer steps each)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -307,7 +307,7 @@ def main():
     lib = spg.lib()
     lib.spingalett_set_verbose(False)
     assert lib.spingalett_set_device(local_rank) == 0
-    spg.set_math_mode(spg.abi.MATH_EXACT if args.math == "exact" else spg.abi.MATH_FAST)
+    spg.set_math_mode({"exact": spg.abi.MATH_EXACT, "fast": spg.abi.MATH_FAST, "auto": spg.abi.MATH_AUTO}[args.math])
     pk = peaks()
     tmpdir = tempfile.mkdtemp(prefix=f"spg_bench_r{rank}_")
     batch = args.batch
@@ -332,10 +332,13 @@ def main():
     value = batch * world / (dev_ms * 1e-3)
     e2e_value = batch * world / (e2e_ms * 1e-3)
     passes = 2 if args.math == "exact" else 1
+    compute = {"exact": "bf16(hi+lo)xbf16->f32", "fast": "f16xf16->f32", "auto": "f16xf16->f32 + exact recompute of low-margin rows"}[args.math]
+    if path_taken in ("gemv", "wstream"):
+        compute = "bf16 terms x bf16 -> f32 (exact products)"
     line = {
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16xf16->f32" if args.math == "fast" else "bf16(hi+lo)xbf16->f32", "data": "synthetic",
+        "dtype": compute, "data": "synthetic",
         "config": {"workload": f"MLP {'-'.join(map(str, topo))} forward, weights stored {args.dtype} (.nn), batch {batch} per GPU, "
                                f"{'U[0,1)' if WORKLOADS[args.workload][5] == 'uniform' else 'N(0,1)'} fp32 inputs",
                    "batch_per_gpu": batch, "math_mode": args.math, "path": path_taken,

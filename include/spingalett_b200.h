@@ -297,20 +297,35 @@ SPINGALETT_API float *forward_batch_struct_arguments(ForwardBatchArgs args);
 SPINGALETT_API int spingalett_synchronize(NeuralNetwork *net);
 
 /* How activations are fed to the tensor cores on the large-batch path.
- * EXACT (default): two 16-bit terms hi+lo (>= 16 significant bits) at twice
- *         the tensor work; products with 16-bit or integer weights are exact
- *         and only the fp32 accumulation order differs from the reference.
- *         This is the mode that meets the parity bar (>= 99.9 % argmax
- *         agreement with the reference's fp32 forward).
+ * EXACT : two 16-bit terms hi+lo (>= 16 significant bits) at twice the tensor
+ *         work; products with 16-bit or integer weights are exact and only the
+ *         fp32 accumulation order differs from the reference.
  * FAST  : one 16-bit term (fp16, 11 significant bits; bf16 for BF16 files, 8
- *         bits).  Measured on the 784-512-1000-10 MLP: ~99.95 % argmax
- *         agreement with fp16, ~99.7 % with bf16 -- a speed/accuracy trade
- *         for callers that accept it.
- * The small-batch path always computes in fp32-equivalent precision (it is
- * memory-bound). */
-typedef enum { SPINGALETT_MATH_FAST = 0, SPINGALETT_MATH_EXACT = 1 } SpingalettMathMode;
+ *         bits).  Measured on the 784-512-1000-10 MLP: ~99.95 % argmax agreement
+ *         with the reference with fp16, ~99.7 % with bf16, i.e. at or below the
+ *         99.9 % parity bar.
+ * AUTO (default): the FAST pass, then every row whose two largest softmax
+ *         outputs are within a margin (log p1 - log p2 < margin) is recomputed
+ *         in EXACT mode and written over the fast result, so every argmax is the
+ *         EXACT one at close to FAST cost; the probabilities of the other rows
+ *         keep the FAST error (<= 3e-4 measured with fp16, against a 2e-3 bar).
+ *         The margin is measured, not guessed: on the first AUTO call after a
+ *         net's weights reach the GPU both modes run on up to 2048 rows of the
+ *         batch and the margin becomes four times the largest change of the
+ *         top-two log gap that the FAST pass caused there (measured range: the
+ *         change is below 0.002 with fp16 operands, 0.013 with bf16).
+ *         spingalett_set_auto_margin(m > 0) fixes the margin instead; 0 returns
+ *         to calibration.  Networks that do not end in softmax run EXACT.
+ * The small-batch paths always use exact products (they are memory-bound). */
+typedef enum { SPINGALETT_MATH_FAST = 0, SPINGALETT_MATH_EXACT = 1, SPINGALETT_MATH_AUTO = 2 } SpingalettMathMode;
 SPINGALETT_API void spingalett_set_math_mode(SpingalettMathMode mode);
 SPINGALETT_API SpingalettMathMode spingalett_get_math_mode(void);
+SPINGALETT_API void spingalett_set_auto_margin(float log_gap);
+SPINGALETT_API float spingalett_get_auto_margin(void);
+/* rows the last AUTO-mode call on this net recomputed exactly */
+SPINGALETT_API uint32_t spingalett_last_repaired(NeuralNetwork *net);
+/* the calibrated margin of this net (0 before its first AUTO call) */
+SPINGALETT_API float spingalett_net_margin(NeuralNetwork *net);
 
 /* CUDA device used by the calling process for nets created afterwards
  * (default: the current device).  Returns 0 or an error code. */

@@ -93,6 +93,21 @@ SPGK_API int spgk_layer_simt(const spgk_layer *L, const float *x, uint32_t ldx,
  * by 1/sum only if sum > 0.  width <= 65535. */
 SPGK_API int spgk_softmax_rows(float *y, uint32_t ldy, uint32_t N, uint32_t width, void *stream);
 
+/* ---- margin check of the one-term mode ---------------------------------------
+ * spgk_margin_select appends to idx (and counts in *count, which the caller zeroes)
+ * every row of probs [N][width] whose two largest entries are within `theta` in log
+ * space; spgk_scatter_rows writes recomputed rows back: dst[idx[i]] = src[i].
+ * (No reference counterpart: they let the fast one-term tensor-core pass be followed
+ * by an exact recomputation of just the rows whose argmax it could have changed.) */
+SPGK_API int spgk_margin_select(const float *probs, uint32_t ldp, uint32_t N, uint32_t width, float theta,
+                                uint32_t *idx, uint32_t *count, void *stream);
+/* max over rows of the change in the top-two log gap between a fast and an exact result (float bits in *max_bits,
+ * which the caller zeroes): the calibration measurement behind the margin. */
+SPGK_API int spgk_gap_error(const float *fast, const float *exact, uint32_t ld, uint32_t N, uint32_t width,
+                            uint32_t *max_bits, void *stream);
+SPGK_API int spgk_scatter_rows(const float *src, const uint32_t *idx, float *dst, uint32_t rows, uint32_t width,
+                               uint32_t ldd, void *stream);
+
 /* ---- split fp32 activations into 16-bit terms ----------------------------
  * dst holds `parts` planes of [N][ld16] 16-bit values (plane stride
  * plane_elems): plane 0 = round(x), plane 1 = round(x - plane0), ...

@@ -15,7 +15,7 @@ STRATEGY_SAMPLE, STRATEGY_FULL_BATCH, STRATEGY_SMALL_BATCH = range(3)
 OPTIMIZER_SGD, OPTIMIZER_MOMENTUM, OPTIMIZER_RMSPROP, OPTIMIZER_ADAM, OPTIMIZER_ADAMW = range(5)
 COMPUTE_SINGLE_THREADED, COMPUTE_OPENMP, COMPUTE_OPENBLAS, COMPUTE_CUDA = range(4)
 LOG_DEBUG, LOG_INFO, LOG_WARNING, LOG_ERROR, LOG_NONE = range(5)
-MATH_FAST, MATH_EXACT = 0, 1
+MATH_FAST, MATH_EXACT, MATH_AUTO = 0, 1, 2
 OK, ERR_ALLOC, ERR_INVALID, ERR_DEVICE = 0, 1, 2, 3
 
 PRECISION_NAMES = {"fp32": 0, "fp16": 1, "bf16": 2, "int8": 3, "int4": 4, "int2": 5}
@@ -139,6 +139,7 @@ EXTENSION_SYMBOLS = [
     "spingalett_set_device", "spingalett_get_device_count", "spingalett_set_stream", "spingalett_sync_weights",
     "spingalett_seed", "spingalett_kernel_launches", "spingalett_last_path",
     "spingalett_profile", "spingalett_profile_read", "spingalett_synchronize",
+    "spingalett_set_auto_margin", "spingalett_get_auto_margin", "spingalett_last_repaired", "spingalett_net_margin",
     "spingalett_dist_unique_id", "spingalett_dist_init", "spingalett_dist_shutdown", "spingalett_dist_world",
 ]
 
@@ -160,6 +161,13 @@ def bind_extensions(lib):
     lib.spingalett_seed.restype = None
     lib.spingalett_kernel_launches.restype = C.c_uint64
     lib.spingalett_last_path.restype = C.c_char_p
+    lib.spingalett_set_auto_margin.argtypes = [C.c_float]
+    lib.spingalett_set_auto_margin.restype = None
+    lib.spingalett_get_auto_margin.restype = C.c_float
+    lib.spingalett_last_repaired.argtypes = [NetP]
+    lib.spingalett_last_repaired.restype = C.c_uint32
+    lib.spingalett_net_margin.argtypes = [NetP]
+    lib.spingalett_net_margin.restype = C.c_float
     lib.spingalett_dist_unique_id.argtypes = [C.c_void_p]
     lib.spingalett_dist_unique_id.restype = C.c_int
     lib.spingalett_dist_init.argtypes = [C.c_int, C.c_int, C.c_void_p]

@@ -193,6 +193,71 @@ spg_softmax_block_kernel(float *__restrict__ y, uint32_t ldy, uint32_t width)
     }
 }
 
+// Rows whose two largest outputs are closer than `theta` in log space (log p1 - log p2 < theta) are appended
+// to `idx` (order unspecified) and counted in *count.  One warp per row.
+__global__ void __launch_bounds__(256)
+spg_margin_select_kernel(const float *__restrict__ probs, uint32_t ldp, uint32_t N, uint32_t width, float theta,
+                         uint32_t *__restrict__ idx, uint32_t *__restrict__ count)
+{
+    const uint32_t row = blockIdx.x * 8u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (row >= N) return;
+    const float *r = probs + (uint64_t)row * ldp;
+    float a = -FLT_MAX, b = -FLT_MAX;                          // largest, second largest seen by this lane
+    for (uint32_t i = lane; i < width; i += 32u) {
+        const float v = r[i];
+        if (v > a) { b = a; a = v; } else if (v > b) b = v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {                         // merge the (largest, second) pairs across lanes
+        const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
+        if (oa > a) { b = fmaxf(a, ob); a = oa; } else b = fmaxf(b, oa);
+    }
+    if (lane == 0 && b > 0.0f && logf(a) - logf(b) < theta) idx[atomicAdd(count, 1u)] = row;
+}
+
+// Largest change of the top-two log gap between two sets of row outputs: for every row, the two largest entries
+// of `exact` define the pair (i1, i2); the result is max over rows of |log(f[i1]/f[i2]) - log(e[i1]/e[i2])|,
+// accumulated with atomicMax on the float's bit pattern (the values are non-negative).  One warp per row.
+__global__ void __launch_bounds__(256)
+spg_gap_error_kernel(const float *__restrict__ fast, const float *__restrict__ exact, uint32_t ld, uint32_t N, uint32_t width,
+                     uint32_t *__restrict__ max_bits)
+{
+    const uint32_t row = blockIdx.x * 8u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (row >= N) return;
+    const float *e = exact + (uint64_t)row * ld, *f = fast + (uint64_t)row * ld;
+    float a = -FLT_MAX, b = -FLT_MAX;
+    uint32_t ia = 0, ib = 0;
+    for (uint32_t i = lane; i < width; i += 32u) {
+        const float v = e[i];
+        if (v > a) { b = a; ib = ia; a = v; ia = i; } else if (v > b) { b = v; ib = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
+        const uint32_t oia = __shfl_xor_sync(0xffffffffu, ia, o), oib = __shfl_xor_sync(0xffffffffu, ib, o);
+        if (oa > a || (oa == a && oia < ia)) {
+            if (a > ob || (a == ob && ia < oib)) { b = a; ib = ia; } else { b = ob; ib = oib; }
+            a = oa; ia = oia;
+        } else if (oa > b || (oa == b && oia < ib)) { b = oa; ib = oia; }
+    }
+    if (lane == 0 && b > 0.0f && f[ia] > 0.0f && f[ib] > 0.0f) {
+        const float err = fabsf((logf(f[ia]) - logf(f[ib])) - (logf(a) - logf(b)));
+        if (isfinite(err)) atomicMax(max_bits, __float_as_uint(err));
+    }
+}
+
+// dst[idx[i]][:] = src[i][:]
+__global__ void __launch_bounds__(256)
+spg_scatter_rows_kernel(const float *__restrict__ src, const uint32_t *__restrict__ idx, float *__restrict__ dst,
+                        uint32_t rows, uint32_t width, uint32_t ldd)
+{
+    const uint64_t total = (uint64_t)rows * width;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t rr = (uint32_t)(i / width), c = (uint32_t)(i % width);
+        dst[(uint64_t)idx[rr] * ldd + c] = src[i];
+    }
+}
+
 // fp32 -> `parts` 16-bit planes (term p = round(x - sum of earlier terms)).
 template <typename T16>
 __device__ __forceinline__ T16 spg_to16(float v);
@@ -274,6 +339,33 @@ int spgk_softmax_rows(float *y, uint32_t ldy, uint32_t N, uint32_t width, void *
     }
     spg_softmax_rows_kernel<<<(N + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(y, ldy, N, width);
     return spgk_check_launch("spg_softmax_rows_kernel");
+}
+
+int spgk_margin_select(const float *probs, uint32_t ldp, uint32_t N, uint32_t width, float theta,
+                       uint32_t *idx, uint32_t *count, void *stream)
+{
+    if (!probs || !idx || !count || width < 2) { spgk_set_error("spgk_margin_select", "bad argument"); return SPGK_E_ARG; }
+    if (N == 0) return SPGK_OK;
+    spg_margin_select_kernel<<<(N + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(probs, ldp, N, width, theta, idx, count);
+    return spgk_check_launch("spg_margin_select_kernel");
+}
+
+int spgk_gap_error(const float *fast, const float *exact, uint32_t ld, uint32_t N, uint32_t width, uint32_t *max_bits, void *stream)
+{
+    if (!fast || !exact || !max_bits || width < 2) { spgk_set_error("spgk_gap_error", "bad argument"); return SPGK_E_ARG; }
+    if (N == 0) return SPGK_OK;
+    spg_gap_error_kernel<<<(N + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(fast, exact, ld, N, width, max_bits);
+    return spgk_check_launch("spg_gap_error_kernel");
+}
+
+int spgk_scatter_rows(const float *src, const uint32_t *idx, float *dst, uint32_t rows, uint32_t width, uint32_t ldd, void *stream)
+{
+    if (!src || !idx || !dst) { spgk_set_error("spgk_scatter_rows", "bad argument"); return SPGK_E_ARG; }
+    if (rows == 0 || width == 0) return SPGK_OK;
+    uint64_t total = (uint64_t)rows * width;
+    uint32_t blocks = (uint32_t)((total + 255) / 256 < 148ull * 8 ? (total + 255) / 256 : 148ull * 8);
+    spg_scatter_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(src, idx, dst, rows, width, ldd);
+    return spgk_check_launch("spg_scatter_rows_kernel");
 }
 
 int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in, void *dst, uint32_t ld16,

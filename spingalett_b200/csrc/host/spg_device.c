@@ -76,6 +76,10 @@ void spg_dev_release(spg_net *n)
     for (int i = 0; i < 2; i++) { spgk_free(n->d_staged[i]); n->d_staged[i] = NULL; n->staged_bytes[i] = 0; }
     for (int i = 0; i < 2; i++) { spgk_free(n->d_operand[i]); n->d_operand[i] = NULL; n->operand_bytes[i] = 0; }
     spgk_free(n->d_ws_scratch); n->d_ws_scratch = NULL; n->ws_scratch_bytes = 0;
+    spgk_free(n->d_rep_idx); n->d_rep_idx = NULL; n->rep_idx_bytes = 0;
+    n->auto_calibrated = false;
+    spgk_free(n->d_rep_in); n->d_rep_in = NULL; n->rep_in_bytes = 0;
+    spgk_free(n->d_rep_out); n->d_rep_out = NULL; n->rep_out_bytes = 0;
     spgk_free(n->d_in32); n->d_in32 = NULL; n->in32_bytes = 0;
     spgk_free(n->d_out32); n->d_out32 = NULL; n->out32_bytes = 0;
     for (int i = 0; i < 2; i++) {
@@ -188,6 +192,9 @@ int spingalett_sync_weights(NeuralNetwork *net)
     spg_net_drop_payload(n);            /* the host fp32 arrays are now the truth */
     return SPINGALETT_OK;
 }
+
+uint32_t spingalett_last_repaired(NeuralNetwork *net) { return net ? spg_priv(net)->last_repaired : 0; }
+float spingalett_net_margin(NeuralNetwork *net) { return net ? spg_priv(net)->auto_theta : 0.0f; }
 
 /* ---- optional timing of the layer kernels -------------------------------- */
 void spingalett_profile(NeuralNetwork *net, bool enable)
@@ -383,7 +390,7 @@ static int large_simt(spg_net *n, const float *d_x, uint32_t N, float *d_out)
     return SPINGALETT_OK;
 }
 
-int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out)
+static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool exact)
 {
     NeuralNetwork *p = &n->pub;
     bool tc = true;
@@ -391,7 +398,6 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     for (uint32_t l = 0; l + 1 < n->dev_layers; l++) tc = tc && n->klayers[l].act != ACT_SOFTMAX;   /* softmax only as the last layer */
     if (!tc) return large_simt(n, d_x, N, d_out);
 
-    const bool exact = spingalett_get_math_mode() == SPINGALETT_MATH_EXACT;
     const int prec = n->klayers[0].precision;
     /* 16-bit flavour: the file's own 16-bit type when it has one (exact
      * weights); otherwise fp16 for the one-term mode (11 significant bits) and
@@ -454,6 +460,62 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
             (rc = spg_map_kernel_error(spgk_softmax_rows(d_out, L->out, N, L->out, n->stream), "softmax"))) return rc;
     }
     n->status_pending = true;
+    spg_note_path("tcgen05");
+    return SPINGALETT_OK;
+}
+
+/* Large-batch forward in the selected math mode.  AUTO = the one-term pass, then an exact recomputation of
+ * the rows whose top-two softmax outputs are within the margin (their argmax is the only thing the one-term
+ * pass could have changed), written over the fast result. */
+int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out)
+{
+    NeuralNetwork *p = &n->pub;
+    const SpingalettMathMode mode = spingalett_get_math_mode();
+    const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1];
+    const bool softmax_out = p->act_func[p->layers - 2] == ACT_SOFTMAX && outw >= 2;
+    if (mode != SPINGALETT_MATH_AUTO) return large_chain(n, d_x, N, d_out, mode == SPINGALETT_MATH_EXACT);
+    if (!softmax_out) return large_chain(n, d_x, N, d_out, true);
+
+    int rc = large_chain(n, d_x, N, d_out, false);
+    if (rc) return rc;
+    if (strcmp(spingalett_last_path(), "tcgen05") != 0) return SPINGALETT_OK;      /* the fp32 chain ran: nothing to repair */
+    if ((rc = reserve((void **)&n->d_rep_idx, &n->rep_idx_bytes, (size_t)N * 4 + 256, "repair index"))) return rc;
+    uint32_t *d_count = n->d_rep_idx + N;
+    float theta = spingalett_get_auto_margin();
+    if (theta <= 0.0f) {
+        /* Self-calibration, once per device image of the net: run both modes on up to 2048 rows, measure the
+         * largest change of the top-two log gap the one-term pass causes, and use four times that as margin. */
+        if (!n->auto_calibrated) {
+            const uint32_t rows = N < 2048 ? N : 2048;
+            if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)rows * outw * 4, "calibration outputs"))) return rc;
+            if ((rc = large_chain(n, d_x, rows, n->d_rep_out, true))) return rc;          /* exact rows; d_out already holds the fast ones */
+            if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "calibration clear"))) return rc;
+            if ((rc = spg_map_kernel_error(spgk_gap_error(d_out, n->d_rep_out, outw, rows, outw, d_count, n->stream), "calibration"))) return rc;
+            float emax = 0.0f;
+            if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(&emax, d_count, 4, n->stream), "calibration read"))) return rc;
+            if ((rc = spg_map_kernel_error(spgk_stream_sync(n->stream), "calibration sync"))) return rc;
+            n->auto_theta = emax * 4.0f > 1e-4f ? emax * 4.0f : 1e-4f;
+            n->auto_calibrated = true;
+            spg_log(LOG_DEBUG, "auto math mode: largest top-two log-gap change on %u rows %.3g, margin %.3g", rows, (double)emax, (double)n->auto_theta);
+        }
+        theta = n->auto_theta;
+    }
+    if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
+    if ((rc = spg_map_kernel_error(spgk_margin_select(d_out, outw, N, outw, theta, n->d_rep_idx, d_count, n->stream), "margin check"))) return rc;
+    uint32_t count = 0;
+    if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(&count, d_count, 4, n->stream), "repair count"))) return rc;
+    if ((rc = spg_map_kernel_error(spgk_stream_sync(n->stream), "repair count sync"))) return rc;
+    n->last_repaired = count;
+    if (count == 0) { spg_note_path("tcgen05"); return SPINGALETT_OK; }
+    if ((uint64_t)count * 4 > N) {                                                 /* too many: one exact pass over everything */
+        rc = large_chain(n, d_x, N, d_out, true);
+        return rc;
+    }
+    if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)count * in0 * 4, "repair inputs"))) return rc;
+    if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)count * outw * 4, "repair outputs"))) return rc;
+    if ((rc = spg_map_kernel_error(spgk_gather_rows(d_x, n->d_rep_idx, n->d_rep_in, count, in0, n->stream), "repair gather"))) return rc;
+    if ((rc = large_chain(n, n->d_rep_in, count, n->d_rep_out, true))) return rc;
+    if ((rc = spg_map_kernel_error(spgk_scatter_rows(n->d_rep_out, n->d_rep_idx, d_out, count, outw, outw, n->stream), "repair scatter"))) return rc;
     spg_note_path("tcgen05");
     return SPINGALETT_OK;
 }

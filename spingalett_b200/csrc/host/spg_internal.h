@@ -49,6 +49,9 @@ typedef struct {
     void *d_staged[2]; size_t staged_bytes[2];   /* ping-pong staged inputs of the GEMV chain */
     void *d_operand[2]; size_t operand_bytes[2]; /* ping-pong activation operands of the weight-streaming chain */
     void *d_ws_scratch; size_t ws_scratch_bytes; bool ws_pending;
+    /* AUTO math mode: rows recomputed exactly after the one-term pass */
+    uint32_t *d_rep_idx; size_t rep_idx_bytes; float *d_rep_in; size_t rep_in_bytes; float *d_rep_out; size_t rep_out_bytes;
+    uint32_t last_repaired; bool auto_calibrated; float auto_theta;
 
     /* large-batch workspace */
     float *d_in32;  size_t in32_bytes;      /* staging for host inputs */

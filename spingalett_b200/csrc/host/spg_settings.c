@@ -13,7 +13,8 @@ static _Atomic unsigned s_threads = 0;
 static _Atomic int      s_level = LOG_INFO;
 static _Atomic(LogCallback) s_cb = NULL;
 static _Atomic bool     s_verbose = true;
-static _Atomic int      s_math = SPINGALETT_MATH_EXACT;
+static _Atomic int      s_math = SPINGALETT_MATH_AUTO;
+static _Atomic float    s_margin = 0.0f;                /* 0 = calibrate per net */
 static _Atomic bool     s_mode_note_done = false;
 static _Thread_local const char *t_path = "none";
 
@@ -36,9 +37,11 @@ bool spingalett_get_verbose(void) { return atomic_load(&s_verbose); }
 
 void spingalett_set_math_mode(SpingalettMathMode mode)
 {
-    if (mode == SPINGALETT_MATH_FAST || mode == SPINGALETT_MATH_EXACT) atomic_store(&s_math, (int)mode);
+    if (mode == SPINGALETT_MATH_FAST || mode == SPINGALETT_MATH_EXACT || mode == SPINGALETT_MATH_AUTO) atomic_store(&s_math, (int)mode);
 }
 SpingalettMathMode spingalett_get_math_mode(void) { return (SpingalettMathMode)atomic_load(&s_math); }
+void spingalett_set_auto_margin(float log_gap) { atomic_store(&s_margin, log_gap > 0.0f ? log_gap : 0.0f); }
+float spingalett_get_auto_margin(void) { return atomic_load(&s_margin); }
 
 void spg_note_path(const char *name) { t_path = name; }
 const char *spingalett_last_path(void) { return t_path; }

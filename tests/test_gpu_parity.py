@@ -106,11 +106,11 @@ def test_weights_edited_on_host_are_picked_up_after_sync(spg, oracle):
     net.free()
 
 
-@pytest.fixture(params=["fast", "exact"])
+@pytest.fixture(params=["fast", "exact", "auto"])
 def math_mode(request, spg):
-    spg.set_math_mode(spg.abi.MATH_EXACT if request.param == "exact" else spg.abi.MATH_FAST)
+    spg.set_math_mode({"exact": spg.abi.MATH_EXACT, "fast": spg.abi.MATH_FAST, "auto": spg.abi.MATH_AUTO}[request.param])
     yield request.param
-    spg.set_math_mode(spg.abi.MATH_EXACT)
+    spg.set_math_mode(spg.abi.MATH_AUTO)
 
 
 @pytest.mark.parametrize("prec", PRECS)
@@ -133,7 +133,14 @@ def test_config_mlp_784_512_1000_10(spg, oracle, tmp_path_factory, prec, n, math
     agree, err = nets.parity(got[rows], want)
     flips = int(round((1.0 - agree) * len(rows)))
     assert err <= nets.tolerance(p), (spg.last_path(), math_mode, agree, err)
-    if math_mode == "exact" or n <= 8:
+    if math_mode == "auto" and n > 8:
+        # the default mode: one-term pass + exact recomputation of the low-margin rows.  Argmax must be the
+        # exact mode's (bar: 99.9 %), probabilities keep at most the one-term error (bar: 2e-3 / 5e-3)
+        assert flips <= len(rows) // 5000, (spg.last_path(), math_mode, agree, err)
+        assert err <= (3e-3 if prec == "bf16" else 6e-4)
+        repaired = spg.lib().spingalett_last_repaired(net._h)
+        assert 0 < repaired <= n // 4 or n < 1000, repaired
+    elif math_mode == "exact" or n <= 8:
         # the parity bar: >= 99.9 % argmax agreement (no flip at all on the small batches)
         assert flips <= len(rows) // 1000, (spg.last_path(), math_mode, agree, err)
         assert err <= 5e-5

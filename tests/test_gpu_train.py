@@ -87,8 +87,10 @@ def test_minibatch_training_reduces_loss_on_the_benchmark_mlp(spg, oracle):
     assert np.all(np.isfinite(net.weights))
     # inference afterwards runs on the trained weights (device image refreshed) and matches the oracle on them
     onet = oracle.OracleNet.from_arrays(net.topology, net.acts, net.weights, net.biases)
+    spg.set_math_mode(spg.abi.MATH_EXACT)
     got = net.forward_batch(x[:64])
     assert np.abs(got - onet.forward_batch(x[:64])).max() <= 2e-5
+    spg.set_math_mode(spg.abi.MATH_AUTO)
     acc = np.mean(np.argmax(net.forward_batch(x), 1) == np.argmax(t, 1))
     assert acc > 0.5
     net.free()
