@@ -147,6 +147,11 @@ SPGK_API size_t spgk_gemv_staged_bytes(uint32_t width, uint32_t N);
 /* status word at the start of scratch: SPGK_E_TIMEOUT if a bounded wait inside the kernel gave up (synchronises) */
 SPGK_API int spgk_gemv_status(void *scratch, void *stream);
 SPGK_API int spgk_gemv_chain_stages_next(const spgk_layer *L, const spgk_layer *next, uint32_t N);
+/* INT8 / INT4 / INT2 layers normally run through the integer tensor path (activations as four base-128
+ * digits of a 28-bit fixed-point number, exact integer accumulation); 0 switches them to the bf16
+ * hi/lo-term path that the floating-point formats use.  Process-wide; meant for tests and comparisons. */
+SPGK_API void spgk_gemv_set_int_path(int on);
+SPGK_API int spgk_gemv_get_int_path(void);
 SPGK_API int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const void *staged_in, void *staged_out,
                                    const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,
                                    void *scratch, void *stream);

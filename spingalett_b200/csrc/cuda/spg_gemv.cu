@@ -32,6 +32,20 @@
 // of the layer before it.  A chunk's slice of the staged input reaches shared
 // memory with one bulk copy and serves all eight warps.
 //
+// Integer path.  Files stored as INT8 / INT4 / INT2 take a cheaper route through the integer tensor
+// path (mma.sync m16n8k32, u8/s8 -> s32): the packed weights become s8 operands with one or two
+// logic operations per word (an INT4 nibble moved to the top of its byte IS 16*q in two's
+// complement; INT8 bytes go in untouched), and each activation enters as four base-128 digits of a
+// 28-bit fixed-point number V = round(x / S * (2^27 - 1)), one digit per column of N.  Integer
+// accumulation is exact, so the only error is the fixed-point rounding of x (relative to the
+// row's scale S).  S must be known before a layer's outputs exist, because the epilogue of layer l
+// writes layer l+1's digits as the items finish: the first layer's S is the exact row maximum
+// (the staging kernel computes it), later layers use the bound
+//     |y_j| <= max|bias| + |w_scale| * max|q| * sum_k |x_k|
+// whose last factor is exact integer arithmetic on the digits of the layer's input (each item
+// leaves the partial sum of its |V| next to the staged data; no atomics, nothing to clear).
+// The bound costs about seven of the 28 bits; what is left still exceeds bf16 hi+lo pairs.
+//
 // Scratch starts with a status word: it must be zero before first use.  Every
 // mbarrier wait is bounded; on expiry the status word is set, waits turn into
 // no-ops and the CTA runs to its end without computing further.
@@ -50,6 +64,18 @@ constexpr int ITEM_ROWS = 16;              // one MMA row group
 constexpr int MAX_BATCH = 8;
 constexpr uint32_t GEMV_WAIT_LIMIT = 1u << 22;
 constexpr uint32_t HEAD_BYTES = 256;                     // status word at the start of scratch
+constexpr int DIGITS = 4;                                // base-128 digits per activation on the integer path
+constexpr double DIGIT_FULL = 134217727.0;               // 2^27 - 1: |V| <= this, so the top digit fits [-64, 63]
+constexpr uint32_t INT_PATH_MAX_K = 131072;              // 127 * 128 * K must stay below 2^31
+
+// Every staged-input buffer starts with a head: the scale of each batch row's digits, then (at byte 256)
+// partial sums of |V| per producer item, int64 [nparts][8].  The bf16 path leaves the head unused.
+struct StagedHead { float S[8]; uint32_t nparts; uint32_t pad[7]; };
+__host__ __device__ inline size_t staged_head_bytes(uint32_t width)
+{
+    const size_t parts = (size_t)(width + 15) / 16 + 33;
+    return 256 + ((parts * 64 + 255) & ~(size_t)255);
+}
 
 struct GemvParams {
     const float *bias;
@@ -66,16 +92,18 @@ struct GemvParams {
     const uint4 *xin;                       // this layer's staged input (see staged_index)
     __nv_bfloat16 *xout;                    // staged input of the next layer, written by the epilogue (or NULL)
     int next_prec; uint32_t next_kpad;      // precision of the next layer's weights; its K rounded up to a whole chunk
+    const uint8_t *in_head;                 // integer path: head of this layer's staged input
+    uint8_t *out_head;                      // integer path: head of the next layer's staged input (or NULL)
 };
 
 // elements covered by one 128-bit load, per stored precision
 template <int PREC> struct Fmt;
-template <> struct Fmt<SPG_P_I4>   { static constexpr int EL = 32, BITS = 4; };
-template <> struct Fmt<SPG_P_I2>   { static constexpr int EL = 64, BITS = 2; };
-template <> struct Fmt<SPG_P_I8>   { static constexpr int EL = 16, BITS = 8; };
-template <> struct Fmt<SPG_P_BF16> { static constexpr int EL = 8,  BITS = 16; };
-template <> struct Fmt<SPG_P_F16>  { static constexpr int EL = 8,  BITS = 16; };
-template <> struct Fmt<SPG_P_F32>  { static constexpr int EL = 4,  BITS = 32; };
+template <> struct Fmt<SPG_P_I4>   { static constexpr int EL = 32; };
+template <> struct Fmt<SPG_P_I2>   { static constexpr int EL = 64; };
+template <> struct Fmt<SPG_P_I8>   { static constexpr int EL = 16; };
+template <> struct Fmt<SPG_P_BF16> { static constexpr int EL = 8; };
+template <> struct Fmt<SPG_P_F16>  { static constexpr int EL = 8; };
+template <> struct Fmt<SPG_P_F32>  { static constexpr int EL = 4; };
 
 // Position of element e (0..EL-1 of a lane's 128-bit load) in fragment order: which 4-element
 // B block it belongs to and where inside the block [b0.lo, b0.hi, b1.lo, b1.hi].
@@ -100,14 +128,20 @@ __host__ __device__ inline uint32_t elems_per_load(int prec) { return 128u / spg
 // Index (in bf16 units) of activation element k, column `col`, inside a staged-input buffer laid out as
 // [step][block][tile][t][cw columns][4]: the order in which the weight loads of a layer stored in
 // precision `prec` consume it.  cs = columns kept (4, 8 or 16), cw = min(cs, 8) columns per tile.
+// All the quantities below are powers of two (elements per load, columns per tile), so the index is shifts
+// and masks: the epilogue warp computes it for every value it stages.
+__device__ __forceinline__ uint32_t el_log2_of(int prec)
+{
+    return prec == SPG_P_I4 ? 5u : prec == SPG_P_I2 ? 6u : prec == SPG_P_I8 ? 4u : prec == SPG_P_F32 ? 2u : 3u;
+}
 __device__ __forceinline__ uint64_t staged_index(int prec, uint32_t cs, uint32_t k, uint32_t col)
 {
-    const uint32_t el = elems_per_load(prec), ks = 4 * el, nb = el / 4;
-    const uint32_t cw = cs < 8 ? cs : 8, tiles = cs / cw;
-    const uint32_t step = k / ks, rem = k % ks, tt = rem / el, e = rem % el;
+    const uint32_t el2 = el_log2_of(prec), nb = 1u << (el2 - 2);
+    const uint32_t cw2 = cs < 8 ? 2u : 3u, tiles = cs >> cw2;
+    const uint32_t step = k >> (el2 + 2), rem = k & ((4u << el2) - 1u), tt = rem >> el2, e = rem & ((1u << el2) - 1u);
     uint32_t block, r;
     frag_pos(prec, e, block, r);
-    const uint64_t slot = ((((uint64_t)step * nb + block) * tiles + col / cw) * 4 + tt) * cw + col % cw;
+    const uint64_t slot = (((((uint64_t)step * nb + block) * tiles + (col >> cw2)) * 4 + tt) << cw2) + (col & ((1u << cw2) - 1u));
     return slot * 4 + r;
 }
 
@@ -131,6 +165,123 @@ spg_gemv_stage_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uin
     if (k >= kpad) return;
     for (uint32_t n = 0; n < N; n++) stage_value(dst, prec, cs, k, n, P, k < in ? x[(uint64_t)n * ldx + k] : 0.0f);
     for (uint32_t col = N * P; col < cs; col++) dst[staged_index(prec, cs, k, col)] = __float2bfloat16_rn(0.0f);
+}
+
+// ---- integer path: staged layout and staging -------------------------------------------------
+// Position of element e of a lane's 128-bit load: which k32 MMA of the step consumes it (m) and which
+// byte of the lane's B pair {b0, b1} must hold the matching activation digit (r = 0..7).
+__device__ __forceinline__ void frag_pos_int(int prec, uint32_t e, uint32_t &m, uint32_t &r)
+{
+    if (prec == SPG_P_I4) {            // word m = 8 nibbles: even nibbles feed a0 (b0), odd nibbles a2 (b1)
+        const uint32_t i = e & 7u;
+        m = e >> 3; r = (i & 1u) * 4 + (i >> 1);
+    } else if (prec == SPG_P_I2) {     // word j = 16 crumbs, two MMAs: crumbs 0/1 of every byte, then crumbs 2/3
+        const uint32_t j = e >> 4, i = e & 15u, c = i & 3u;
+        m = 2 * j + (c >> 1); r = (c & 1u) * 4 + (i >> 2);
+    } else {                           // INT8: words 2m and 2m+1 are a0 and a2
+        m = e >> 3; r = e & 7u;
+    }
+}
+
+// Byte index of activation element k, column `col` (col = row * DIGITS + digit) in an integer staged buffer:
+// [step][mma][tile][t][cw columns][8 bytes].
+__device__ __forceinline__ uint64_t staged_index_int(int prec, uint32_t cs, uint32_t k, uint32_t col)
+{
+    const uint32_t el2 = el_log2_of(prec), nbi = 1u << (el2 - 3);
+    const uint32_t cw2 = cs < 8 ? 2u : 3u, tiles = cs >> cw2;
+    const uint32_t step = k >> (el2 + 2), rem = k & ((4u << el2) - 1u), tt = rem >> el2, e = rem & ((1u << el2) - 1u);
+    uint32_t m, r;
+    frag_pos_int(prec, e, m, r);
+    const uint64_t slot = (((((uint64_t)step * nbi + m) * tiles + (col >> cw2)) * 4 + tt) << cw2) + (col & ((1u << cw2) - 1u));
+    return slot * 8 + r;
+}
+
+// Fixed-point value of v at scale inv = DIGIT_FULL / S (0 when S is 0 or v is not finite).
+__device__ __forceinline__ long long fixed_of(float v, double inv)
+{
+    if (!(fabsf(v) <= 3.0e38f)) return 0;
+    double f = (double)v * inv;
+    f = f > DIGIT_FULL ? DIGIT_FULL : (f < -DIGIT_FULL ? -DIGIT_FULL : f);
+    return __double2ll_rn(f);
+}
+
+// The same in fp32, for the epilogue: y has 24 significant bits, so nothing is lost (the clamp is the largest
+// float below 2^27).
+__device__ __forceinline__ long long fixed_of_f(float v, float inv)
+{
+    if (!(fabsf(v) <= 3.0e38f)) return 0;
+    const float f = fminf(fmaxf(v * inv, -134217720.0f), 134217720.0f);
+    return (long long)__float2int_rn(f);
+}
+
+// Stores the four digits of V (three unsigned 7-bit digits and a signed top digit) for row n.
+__device__ __forceinline__ void stage_digits(uint8_t *dst, int prec, uint32_t cs, uint32_t k, uint32_t n, long long V)
+{
+#pragma unroll
+    for (int d = 0; d < DIGITS; d++) {
+        const long long sh = V >> (7 * d);
+        dst[staged_index_int(prec, cs, k, n * DIGITS + d)] = (uint8_t)(d + 1 < DIGITS ? (sh & 127) : (sh & 255));
+    }
+}
+
+// Stages x[N][in] for the integer path: every block finds each row's exact maximum itself (the rows are a
+// few KB and sit in L2), then writes the digits of its 256 k and the sum of |V| over them.
+__global__ void __launch_bounds__(256)
+spg_gemv_stage_int_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t in, uint32_t kpad,
+                          int prec, uint32_t cs, uint8_t *__restrict__ head_raw, uint8_t *__restrict__ dst)
+{
+    __shared__ float wmax[8];
+    __shared__ long long wsum[8];
+    __shared__ int wbad[8];
+    StagedHead *head = reinterpret_cast<StagedHead *>(head_raw);
+    long long *parts = reinterpret_cast<long long *>(head_raw + 256);
+    const uint32_t k = blockIdx.x * 256 + threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    for (uint32_t n = 0; n < N; n++) {
+        const float *row = x + (uint64_t)n * ldx;
+        float m = 0.0f;
+        int bad = 0;
+        for (uint32_t i = threadIdx.x; i < in; i += 256) {
+            const float a = fabsf(row[i]);
+            bad |= !(a <= 3.0e38f);
+            m = fmaxf(m, a);
+        }
+        m = spg_warp_max(m);
+        bad = __any_sync(0xFFFFFFFFu, bad);
+        if (lane == 0) { wmax[warp] = m; wbad[warp] = bad; }
+        __syncthreads();
+        m = 0.0f; bad = 0;
+        for (int w = 0; w < 8; w++) { m = fmaxf(m, wmax[w]); bad |= wbad[w]; }
+        // a row holding an infinity or a NaN cannot be put on a fixed-point grid: its scale becomes NaN,
+        // which turns every output of the row into NaN
+        const float S = bad ? __int_as_float(0x7FC00000) : m;
+        const double inv = (!bad && m > 0.0f) ? DIGIT_FULL / (double)m : 0.0;
+        long long V = 0;
+        if (k < kpad) {
+            V = k < in ? fixed_of(row[k], inv) : 0;
+            stage_digits(dst, prec, cs, k, n, V);
+        }
+        long long a = V < 0 ? -V : V;
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
+        if (lane == 0) wsum[warp] = a;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            long long t = 0;
+            for (int w = 0; w < 8; w++) t += wsum[w];
+            parts[(uint64_t)blockIdx.x * 8 + n] = t;
+            if (blockIdx.x == 0) head->S[n] = S;
+        }
+        __syncthreads();
+    }
+    if (k < kpad) for (uint32_t col = N * DIGITS; col < cs; col++) dst[staged_index_int(prec, cs, k, col)] = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) head->nparts = gridDim.x;
+}
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
@@ -291,13 +442,48 @@ __device__ __forceinline__ void gemv_step(const uint4 &ra, const uint4 &rbv, con
     }
 }
 
+// Integer-path step: the same 16 rows x (4 lanes x EL elements), as EL / 8 k32 MMAs.  The weights become
+// signed bytes holding q * SHIFT (SHIFT = 16 for INT4, 64 for INT2, 1 for INT8) with a shift and a mask.
+template <int PREC> struct IntFmt;
+template <> struct IntFmt<SPG_P_I4> { static constexpr int SHIFT = 16, QMAX = 8; };
+template <> struct IntFmt<SPG_P_I2> { static constexpr int SHIFT = 64, QMAX = 2; };
+template <> struct IntFmt<SPG_P_I8> { static constexpr int SHIFT = 1, QMAX = 128; };
+
 template <int PREC, int T, int CW>
+__device__ __forceinline__ void gemv_step_int(const uint4 &ra, const uint4 &rbv, const uint2 *xb, bool col_live, int (&acc)[T][4])
+{
+    constexpr int NBI = Fmt<PREC>::EL / 8;
+    const uint32_t wa[4] = { ra.x, ra.y, ra.z, ra.w };
+    const uint32_t wb[4] = { rbv.x, rbv.y, rbv.z, rbv.w };
+#pragma unroll
+    for (int m = 0; m < NBI; m++) {
+        uint2 bf[T];
+#pragma unroll
+        for (int i = 0; i < T; i++) bf[i] = col_live ? xb[(m * T + i) * 4 * CW] : make_uint2(0u, 0u);
+        uint32_t a0, a1, a2, a3;
+        if (PREC == SPG_P_I4) {
+            a0 = (wa[m] << 4) & 0xF0F0F0F0u; a2 = wa[m] & 0xF0F0F0F0u;
+            a1 = (wb[m] << 4) & 0xF0F0F0F0u; a3 = wb[m] & 0xF0F0F0F0u;
+        } else if (PREC == SPG_P_I2) {
+            const int j = m >> 1, h = m & 1;
+            a0 = (wa[j] << (6 - 4 * h)) & 0xC0C0C0C0u; a2 = (wa[j] << (4 - 4 * h)) & 0xC0C0C0C0u;
+            a1 = (wb[j] << (6 - 4 * h)) & 0xC0C0C0C0u; a3 = (wb[j] << (4 - 4 * h)) & 0xC0C0C0C0u;
+        } else {
+            a0 = wa[2 * m]; a2 = wa[2 * m + 1];
+            a1 = wb[2 * m]; a3 = wb[2 * m + 1];
+        }
+#pragma unroll
+        for (int i = 0; i < T; i++) mma_s8(acc[i], a0, a1, a2, a3, bf[i].x, bf[i].y);
+    }
+}
+
+template <int PREC, int T, int CW, bool INTP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
 spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
 {
     using F = Fmt<PREC>;
     constexpr uint32_t EL = F::EL, NB = EL / 4;                // per warp step: 4 lanes x EL elements; NB B-blocks per load
-    constexpr uint32_t STEP_SLOTS = NB * T * 4 * CW;           // uint2 slots of staged input per step
+    constexpr uint32_t STEP_SLOTS = (INTP ? EL / 8 : NB) * T * 4 * CW;   // uint2 slots of staged input per step
     constexpr uint32_t CPAD = 8 * T;
 
     extern __shared__ uint8_t gemv_smem_raw[];
@@ -309,13 +495,14 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
     const uint32_t wchunk_bytes = 8 * p.box_bytes;
     const uint32_t slot_bytes = wchunk_bytes + p.xchunk_bytes;
     const uint32_t red_off = p.ring * slot_bytes;
-    constexpr uint32_t RED_FLOATS = CONSUMER_WARPS * ITEM_ROWS * CPAD;
+    constexpr uint32_t RED_FLOATS = (INTP ? 1 : CONSUMER_WARPS) * ITEM_ROWS * CPAD;   // integer path: one shared buffer of sums
     const uint32_t bar_off = red_off + 2 * RED_FLOATS * 4;       // two reduction buffers, used alternately
     const uint32_t full0 = base + bar_off, empty0 = full0 + 8 * p.ring;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + bar_off + 16 * p.ring);
     float *red = reinterpret_cast<float *>(smem + red_off);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    if (INTP) for (uint32_t i = tid; i < 2 * RED_FLOATS; i += GEMV_THREADS) red[i] = 0.0f;      // integer zero too
     if (tid == 0) {
         for (uint32_t s = 0; s < p.ring; s++) { gbar_init(full0 + 8 * s, 1); gbar_init(empty0 + 8 * s, CONSUMER_WARPS); }
         *abort_flag = 0;
@@ -349,28 +536,135 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
         // activation, writes y and stages the next layer's input, while the consumers stream the next item.
         const uint32_t cs = CW * T, spare = cs - p.C;
         uint32_t n_item = 0;
+        if constexpr (INTP) {
+            // ---- integer path: exact integer dot products; scales and the next layer's range bound first ----
+            __shared__ float e_sc[MAX_BATCH], e_inv[MAX_BATCH];
+            const StagedHead *ih = reinterpret_cast<const StagedHead *>(p.in_head);
+            const long long *iparts = reinterpret_cast<const long long *>(p.in_head + 256);
+            float bmax = 0.0f;
+            if (p.xout) {
+                for (uint32_t i = lane; i < p.out; i += 32) bmax = fmaxf(bmax, fabsf(p.bias[i]));
+                bmax = spg_warp_max(bmax);
+            }
+            for (uint32_t n = 0; n < p.N; n++) {
+                const float S = ih->S[n];
+                float inv_next = 0.0f;
+                if (p.xout) {
+                    long long l1 = 0;
+                    for (uint32_t i = lane; i < ih->nparts; i += 32) l1 += iparts[(uint64_t)i * 8 + n];
+                    for (int o = 16; o > 0; o >>= 1) l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
+                    // |y| <= max|bias| + |scale| * max|q| * sum|x'|, x' = V * S / DIGIT_FULL the values the MMAs really see
+                    double bound = (double)bmax + fabs((double)p.scale) * IntFmt<PREC>::QMAX * ((double)S / DIGIT_FULL) * (double)l1;
+                    bound *= 1.0001;
+                    if (p.act == SPG_ACT_SIGMOID) bound = 1.0;
+                    else if (p.act == SPG_ACT_TANH) bound = bound < 1.0 ? bound : 1.0;
+                    float Sn = __double2float_ru(bound);
+                    if (!(Sn <= 3.0e38f)) Sn = __int_as_float(0x7FC00000);        // overflow or NaN input: the row turns into NaN
+                    inv_next = (Sn > 0.0f) ? (float)(DIGIT_FULL / (double)Sn) : 0.0f;
+                    if (blockIdx.x == 0 && lane == 0) reinterpret_cast<StagedHead *>(p.out_head)->S[n] = Sn;
+                }
+                if (lane == 0) {
+                    e_sc[n] = (float)((double)p.scale * (double)S / (DIGIT_FULL * IntFmt<PREC>::SHIFT));
+                    e_inv[n] = inv_next;
+                }
+            }
+            if (p.xout && blockIdx.x == 0 && lane == 0) reinterpret_cast<StagedHead *>(p.out_head)->nparts = p.items;
+            __syncwarp();
+            int *redi = reinterpret_cast<int *>(red);
+            uint8_t *xo = reinterpret_cast<uint8_t *>(p.xout);
+            long long *oparts = p.out_head ? reinterpret_cast<long long *>(p.out_head + 256) : nullptr;
+            constexpr int PER_LANE = ITEM_ROWS * MAX_BATCH / 32;        // outputs of one item a lane may own
+            for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
+                const uint32_t rbuf = n_item & 1u;
+                // what does not depend on the consumers comes first: the biases of this item's rows
+                float bias_r[PER_LANE];
+#pragma unroll
+                for (int u = 0; u < PER_LANE; u++) {
+                    const uint32_t idx = u * 32 + lane, row = item * ITEM_ROWS + idx % ITEM_ROWS;
+                    bias_r[u] = (idx < ITEM_ROWS * p.N && row < p.out) ? p.bias[row] : 0.0f;
+                }
+                handoff_wait(1 + rbuf);
+                int *redb = redi + rbuf * RED_FLOATS;
+                long long tot[PER_LANE];
+#pragma unroll
+                for (int u = 0; u < PER_LANE; u++) {
+                    const uint32_t idx = u * 32 + lane, n = idx / ITEM_ROWS, rl = idx % ITEM_ROWS;
+                    tot[u] = 0;
+                    if (idx < ITEM_ROWS * p.N) {
+                        int *src = redb + rl * CPAD + n * DIGITS;
+#pragma unroll
+                        for (int d = 0; d < DIGITS; d++) { tot[u] += (long long)src[d] << (7 * d); src[d] = 0; }   // leave the sums cleared for the item after next
+                    }
+                }
+                __syncwarp();
+                if (n_item + 2 < (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x) handoff_arrive(3 + rbuf);   // the buffer is free again
+#pragma unroll
+                for (int u = 0; u < PER_LANE; u++) {
+                    const uint32_t idx = u * 32 + lane, n = idx / ITEM_ROWS, rl = idx % ITEM_ROWS, row = item * ITEM_ROWS + rl;
+                    if (u * 32 >= ITEM_ROWS * p.N) break;                  // warp-uniform
+                    long long absV = 0;
+                    if (n < p.N && row < p.out) {
+                        const float yv = spg_activate(fmaf(__ll2float_rn(tot[u]), e_sc[n], bias_r[u]), p.act);
+                        p.y[(uint64_t)n * p.ldy + row] = yv;
+                        if (xo) {
+                            const long long V = fixed_of_f(yv, e_inv[n]);
+                            stage_digits(xo, p.next_prec, cs, row, n, V);
+                            absV = V < 0 ? -V : V;
+                        }
+                    }
+                    if (xo) {
+                        // lanes 0..15 hold one batch row, lanes 16..31 the next: their |V| sums go beside the staged data
+                        for (int o = 8; o > 0; o >>= 1) absV += __shfl_xor_sync(0xFFFFFFFFu, absV, o);
+                        if ((lane & 15u) == 0 && n < p.N) oparts[(uint64_t)item * 8 + n] = absV;
+                    }
+                }
+                if (xo) {
+                    for (uint32_t idx = lane; idx < ITEM_ROWS * spare; idx += 32) {
+                        const uint32_t row = item * ITEM_ROWS + idx / spare;
+                        if (row < p.out) xo[staged_index_int(p.next_prec, cs, row, p.C + idx % spare)] = 0;
+                    }
+                    if (item == p.items - 1)
+                        for (uint32_t idx = lane; idx < (p.next_kpad - p.out) * cs; idx += 32)
+                            xo[staged_index_int(p.next_prec, cs, p.out + idx / cs, idx % cs)] = 0;
+                }
+            }
+        } else {
+        constexpr int PER_LANE = ITEM_ROWS * MAX_BATCH / 32;
         for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
             const uint32_t rbuf = n_item & 1u;
+            float bias_r[PER_LANE], sum_r[PER_LANE];
+#pragma unroll
+            for (int u = 0; u < PER_LANE; u++) {
+                const uint32_t idx = u * 32 + lane, row = item * ITEM_ROWS + idx % ITEM_ROWS;
+                bias_r[u] = (idx < ITEM_ROWS * p.N && row < p.out) ? p.bias[row] : 0.0f;
+            }
             handoff_wait(1 + rbuf);
             const float *redb = red + rbuf * RED_FLOATS;
-            for (uint32_t idx = lane; idx < ITEM_ROWS * p.N; idx += 32) {
-                const uint32_t n = idx / ITEM_ROWS, rl = idx % ITEM_ROWS, row = item * ITEM_ROWS + rl;
-                if (row >= p.out) continue;
-                float sum = 0.0f;
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; w++) {
-                    const float *src = redb + (w * ITEM_ROWS + rl) * CPAD + n * p.P;
-                    float part = 0.0f;
-                    for (uint32_t q = p.P; q-- > 0;) part += src[q];           // smallest term first
-                    sum += part;
+            for (int u = 0; u < PER_LANE; u++) {
+                const uint32_t idx = u * 32 + lane, n = idx / ITEM_ROWS, rl = idx % ITEM_ROWS;
+                float sum = 0.0f;
+                if (idx < ITEM_ROWS * p.N) {
+#pragma unroll
+                    for (int w = 0; w < CONSUMER_WARPS; w++) {
+                        const float *src = redb + (w * ITEM_ROWS + rl) * CPAD + n * p.P;
+                        float part = 0.0f;
+                        for (uint32_t q = p.P; q-- > 0;) part += src[q];           // smallest term first
+                        sum += part;
+                    }
                 }
-                const float yv = spg_activate(fmaf(sum, p.scale, p.bias[row]), p.act);
+                sum_r[u] = sum;
+            }
+            __syncwarp();
+            if (n_item + 2 < (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x) handoff_arrive(3 + rbuf);   // only if a later item will wait for it
+#pragma unroll
+            for (int u = 0; u < PER_LANE; u++) {
+                const uint32_t idx = u * 32 + lane, n = idx / ITEM_ROWS, row = item * ITEM_ROWS + idx % ITEM_ROWS;
+                if (idx >= ITEM_ROWS * p.N || row >= p.out) continue;
+                const float yv = spg_activate(fmaf(sum_r[u], p.scale, bias_r[u]), p.act);
                 p.y[(uint64_t)n * p.ldy + row] = yv;
                 if (p.xout) stage_value(p.xout, p.next_prec, cs, row, n, p.P, yv);
             }
-            __threadfence_block();
-            __syncwarp();
-            if (n_item + 2 < (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x) handoff_arrive(3 + rbuf);   // only if a later item will wait for it
             if (p.xout) {
                 // columns that carry no sample stay zero in the next layer's staged input; so does its K tail
                 for (uint32_t idx = lane; idx < ITEM_ROWS * spare; idx += 32) {
@@ -382,6 +676,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                         p.xout[staged_index(p.next_prec, cs, p.out + idx / cs, idx % cs)] = __float2bfloat16_rn(0.0f);
             }
         }
+        }
         return;
     }
 
@@ -392,12 +687,13 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
         // two accumulator sets (even / odd steps) keep two independent MMA chains in flight
         float acc[2][T][4], acc_hi[2][T][4];                   // acc_hi: INT8 only (the high-nibble term)
+        int iacc[2][T][4];                                     // integer path (the unused set is optimised away)
 #pragma unroll
         for (int e = 0; e < 2; e++)
 #pragma unroll
             for (int i = 0; i < T; i++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) { acc[e][i][j] = 0.0f; acc_hi[e][i][j] = 0.0f; }
+                for (int j = 0; j < 4; j++) { acc[e][i][j] = 0.0f; acc_hi[e][i][j] = 0.0f; iacc[e][i][j] = 0; }
 
         for (uint32_t c = 0; c < p.nchunks; c++) {
             const bool ok = gbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 2);
@@ -410,8 +706,13 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                 for (uint32_t st = sub * per_sub; st < (sub + 1) * per_sub; st++) {
                     const uint4 ra0 = *reinterpret_cast<const uint4 *>(box + st * 64);
                     const uint4 rb0 = *reinterpret_cast<const uint4 *>(box + 8 * row_pitch + st * 64);
-                    if (st & 1u) gemv_step<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, acc[1], acc_hi[1]);
-                    else gemv_step<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, acc[0], acc_hi[0]);
+                    if constexpr (INTP) {
+                        if (st & 1u) gemv_step_int<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, iacc[1]);
+                        else gemv_step_int<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, iacc[0]);
+                    } else {
+                        if (st & 1u) gemv_step<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, acc[1], acc_hi[1]);
+                        else gemv_step<PREC, T, CW>(ra0, rb0, xs + (size_t)st * STEP_SLOTS, col_live, acc[0], acc_hi[0]);
+                    }
                 }
             }
             __syncwarp();
@@ -423,6 +724,16 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
         const uint32_t rbuf = n_item & 1u;
         if (n_item >= 2) handoff_wait(3 + rbuf);               // the epilogue warp has read this buffer's previous contents
         float *redb = red + rbuf * RED_FLOATS;
+        if constexpr (INTP) {
+            // integer sums commute: every warp adds its partials into one [row][column] buffer
+            int *redi = reinterpret_cast<int *>(red) + rbuf * RED_FLOATS;
+#pragma unroll
+            for (int i = 0; i < T; i++) {
+                int *r0 = redi + g * CPAD + i * 8 + 2 * t;
+                atomicAdd(r0, iacc[0][i][0] + iacc[1][i][0]); atomicAdd(r0 + 1, iacc[0][i][1] + iacc[1][i][1]);
+                atomicAdd(r0 + 8 * CPAD, iacc[0][i][2] + iacc[1][i][2]); atomicAdd(r0 + 8 * CPAD + 1, iacc[0][i][3] + iacc[1][i][3]);
+            }
+        } else {
 #pragma unroll
         for (int i = 0; i < T; i++) {
             float d0 = acc[0][i][0] + acc[1][i][0], d1 = acc[0][i][1] + acc[1][i][1];
@@ -435,6 +746,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
             r0[0] = d0; r0[1] = d1;
             r0[8 * CPAD] = d2; r0[8 * CPAD + 1] = d3;
         }
+        }
         __threadfence_block();
         handoff_arrive(1 + rbuf);                              // no waiting: on to the next item
     }
@@ -443,8 +755,15 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
 struct Plan {
     uint32_t P, C, cs, T, CW, spb, box_bytes, nboxes, nchunks, kpad, items, ring, xdepth, xchunk_bytes;
     size_t staged_bytes, smem;
-    bool ok;
+    bool ok, intp;
 };
+
+bool g_int_path = true;         // integer tensor path for INT8 / INT4 / INT2 files (spgk_gemv_set_int_path)
+
+inline bool int_path_for(const spgk_layer *L)
+{
+    return g_int_path && (L->precision == SPG_P_I8 || L->precision == SPG_P_I4 || L->precision == SPG_P_I2) && L->in <= INT_PATH_MAX_K;
+}
 
 Plan make_plan(const spgk_layer *L, uint32_t N)
 {
@@ -455,13 +774,25 @@ Plan make_plan(const spgk_layer *L, uint32_t N)
     const uint64_t row_bytes = (uint64_t)L->in * bits / 8;
     // TMA needs 16-byte aligned packed rows; very short rows go to the general kernel
     if (L->in % el || ((uintptr_t)L->w & 15u) || row_bytes < 64) return pl;
-    pl.P = N == 1 ? 3 : 2;
-    pl.C = N * pl.P;
-    pl.cs = pl.C <= 4 ? 4 : (pl.C <= 8 ? 8 : 16);
-    pl.T = pl.cs == 16 ? 2 : 1;
-    pl.CW = pl.cs < 8 ? 4 : 8;
+    pl.intp = int_path_for(L);
+    uint32_t per_spb;
+    if (pl.intp) {
+        // four digit columns per batch row; one staged byte per column and k
+        pl.P = DIGITS;
+        pl.C = N * DIGITS;
+        pl.cs = N == 1 ? 4 : 8 * ((N + 1) / 2);
+        pl.T = pl.cs <= 8 ? 1 : pl.cs / 8;
+        pl.CW = pl.cs < 8 ? 4 : 8;
+        per_spb = 8 * ks * pl.cs;
+    } else {
+        pl.P = N == 1 ? 3 : 2;
+        pl.C = N * pl.P;
+        pl.cs = pl.C <= 4 ? 4 : (pl.C <= 8 ? 8 : 16);
+        pl.T = pl.cs == 16 ? 2 : 1;
+        pl.CW = pl.cs < 8 ? 4 : 8;
+        per_spb = 8 * ks * 2 * pl.cs;
+    }
     // a chunk = 8 boxes (one per warp) of spb steps; its staged input should fit 32 KB (three in flight), at most 64 KB (two)
-    const uint32_t per_spb = 8 * ks * 2 * pl.cs;
     pl.spb = 0;
     for (uint32_t s = 4; s >= 1; s >>= 1) if (per_spb * s <= 32768) { pl.spb = s; break; }
     if (!pl.spb) for (uint32_t s = 4; s >= 1; s >>= 1) if (per_spb * s <= 65536) { pl.spb = s; break; }
@@ -473,8 +804,8 @@ Plan make_plan(const spgk_layer *L, uint32_t N)
     pl.nchunks = (pl.nboxes + 7) / 8;
     pl.kpad = pl.nchunks * 8 * pl.spb * ks;
     pl.items = (L->out + ITEM_ROWS - 1) / ITEM_ROWS;
-    pl.staged_bytes = ((size_t)pl.kpad * 2 * pl.cs + 255) & ~(size_t)255;
-    const size_t red = 2 * (size_t)CONSUMER_WARPS * ITEM_ROWS * 8 * pl.T * 4;
+    pl.staged_bytes = ((size_t)pl.kpad * (pl.intp ? 1 : 2) * pl.cs + 255) & ~(size_t)255;
+    const size_t red = 2 * (size_t)(pl.intp ? 1 : CONSUMER_WARPS) * ITEM_ROWS * 8 * pl.T * 4;
     const size_t slot = 8 * (size_t)pl.box_bytes + pl.xchunk_bytes;           // one chunk: weights + its staged input
     uint32_t ring = (uint32_t)((225u * 1024 - 128 - red - 1024) / slot);
     if (ring > 8) ring = 8;
@@ -530,7 +861,7 @@ int weight_map(const spgk_layer *L, uint32_t box_row_bytes, CUtensorMap *out_map
     return SPGK_OK;
 }
 
-template <int PREC, int T, int CW>
+template <int PREC, int T, int CW, bool INTP>
 int launch(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
 {
     static bool attr_done = false;
@@ -539,20 +870,32 @@ int launch(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStre
         int dev = 0;
         SPGK_CUDA(cudaGetDevice(&dev));
         SPGK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        SPGK_CUDA(cudaFuncSetAttribute(spg_gemv_kernel<PREC, T, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        SPGK_CUDA(cudaFuncSetAttribute(spg_gemv_kernel<PREC, T, CW, INTP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         attr_done = true;
     }
     const uint32_t grid = pl.items < (uint32_t)sms ? pl.items : (uint32_t)sms;
-    spg_gemv_kernel<PREC, T, CW><<<grid, GEMV_THREADS, pl.smem, s>>>(map, p);
+    spg_gemv_kernel<PREC, T, CW, INTP><<<grid, GEMV_THREADS, pl.smem, s>>>(map, p);
     return spgk_check_launch("spg_gemv_kernel");
 }
 
 template <int PREC>
 int launch_t(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
 {
-    if (pl.cs == 4) return launch<PREC, 1, 4>(map, p, pl, s);
-    if (pl.cs == 8) return launch<PREC, 1, 8>(map, p, pl, s);
-    return launch<PREC, 2, 8>(map, p, pl, s);
+    if (pl.cs == 4) return launch<PREC, 1, 4, false>(map, p, pl, s);
+    if (pl.cs == 8) return launch<PREC, 1, 8, false>(map, p, pl, s);
+    return launch<PREC, 2, 8, false>(map, p, pl, s);
+}
+
+template <int PREC>
+int launch_int(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
+{
+    switch (pl.cs) {
+        case 4:  return launch<PREC, 1, 4, true>(map, p, pl, s);
+        case 8:  return launch<PREC, 1, 8, true>(map, p, pl, s);
+        case 16: return launch<PREC, 2, 8, true>(map, p, pl, s);
+        case 24: return launch<PREC, 3, 8, true>(map, p, pl, s);
+        default: return launch<PREC, 4, 8, true>(map, p, pl, s);
+    }
 }
 
 }  // namespace
@@ -562,15 +905,22 @@ extern "C" {
 size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N)
 {
     Plan pl = make_plan(L, N);
-    return pl.ok ? HEAD_BYTES + pl.staged_bytes : 0;
+    return pl.ok ? HEAD_BYTES + staged_head_bytes(L->in) + pl.staged_bytes : 0;
 }
 
+// Bytes of a staged-input buffer for a layer of `width` inputs at N rows: head + data in either path's layout.
 size_t spgk_gemv_staged_bytes(uint32_t width, uint32_t N)
 {
     if (N == 0 || N > MAX_BATCH) return 0;
     const uint32_t C = N * (N == 1 ? 3u : 2u), cs = C <= 4 ? 4 : (C <= 8 ? 8 : 16);
-    return ((size_t)((width + 4095u) & ~4095u) * 2 * cs + 255) & ~(size_t)255;     // K padded to the widest chunk
+    const size_t bf = (size_t)((width + 4095u) & ~4095u) * 2 * cs;                   // K padded to the widest chunk
+    const uint32_t csi = N == 1 ? 4 : 8 * ((N + 1) / 2);
+    const size_t in = (size_t)((width + 8191u) & ~8191u) * csi;
+    return staged_head_bytes(width) + (((bf > in ? bf : in) + 255) & ~(size_t)255);
 }
+
+void spgk_gemv_set_int_path(int on) { g_int_path = on != 0; }
+int spgk_gemv_get_int_path(void) { return g_int_path ? 1 : 0; }
 
 int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const void *staged_in, void *staged_out,
                           const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N, void *scratch, void *stream)
@@ -592,22 +942,40 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
     p.ring = pl.ring; p.xdepth = pl.xdepth; p.xchunk_bytes = pl.xchunk_bytes;
     uint8_t *base = reinterpret_cast<uint8_t *>(scratch);
     p.status = reinterpret_cast<int32_t *>(base);
+    const size_t in_head_bytes = staged_head_bytes(L->in);
     if (staged_in) {
-        p.xin = reinterpret_cast<const uint4 *>(staged_in);
+        p.in_head = reinterpret_cast<const uint8_t *>(staged_in);
+        p.xin = reinterpret_cast<const uint4 *>(p.in_head + in_head_bytes);
     } else {
-        // split x into bf16 terms in the order this layer's weight loads consume them
-        __nv_bfloat16 *own = reinterpret_cast<__nv_bfloat16 *>(base + HEAD_BYTES);
-        spg_gemv_stage_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.kpad, L->precision, pl.cs, own);
+        // put x into the form and order this layer's weight loads consume
+        uint8_t *own_head = base + HEAD_BYTES, *own = own_head + in_head_bytes;
+        if (pl.intp)
+            spg_gemv_stage_int_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, L->in, pl.kpad, L->precision, pl.cs, own_head, own);
+        else
+            spg_gemv_stage_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.kpad, L->precision, pl.cs,
+                                                                      reinterpret_cast<__nv_bfloat16 *>(own));
         rc = spgk_check_launch("spg_gemv_stage_kernel");
         if (rc) return rc;
+        p.in_head = own_head;
         p.xin = reinterpret_cast<const uint4 *>(own);
     }
-    // The epilogue can stage the next layer's input directly, when that layer will also run here
-    // and this layer's output needs no further pass (softmax) first.
-    p.xout = nullptr; p.next_prec = 0; p.next_kpad = 0;
+    // The epilogue can stage the next layer's input directly, when that layer will also run here on the same
+    // path and this layer's output needs no further pass (softmax) first.
+    p.xout = nullptr; p.out_head = nullptr; p.next_prec = 0; p.next_kpad = 0;
     if (next && staged_out && L->act != SPG_ACT_SOFTMAX && next->in == L->out) {
         Plan np = make_plan(next, N);
-        if (np.ok) { p.xout = reinterpret_cast<__nv_bfloat16 *>(staged_out); p.next_prec = next->precision; p.next_kpad = np.kpad; }
+        if (np.ok && np.intp == pl.intp) {
+            p.out_head = reinterpret_cast<uint8_t *>(staged_out);
+            p.xout = reinterpret_cast<__nv_bfloat16 *>(p.out_head + staged_head_bytes(next->in));
+            p.next_prec = next->precision; p.next_kpad = np.kpad;
+        }
+    }
+    if (pl.intp) {
+        switch (L->precision) {
+            case SPG_P_I4: return launch_int<SPG_P_I4>(map, p, pl, s);
+            case SPG_P_I2: return launch_int<SPG_P_I2>(map, p, pl, s);
+            default:       return launch_int<SPG_P_I8>(map, p, pl, s);
+        }
     }
     switch (L->precision) {
         case SPG_P_I4:   return launch_t<SPG_P_I4>(map, p, pl, s);
@@ -623,7 +991,8 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
 int spgk_gemv_chain_stages_next(const spgk_layer *L, const spgk_layer *next, uint32_t N)
 {
     if (!L || !next || L->act == SPG_ACT_SOFTMAX || next->in != L->out) return 0;
-    return make_plan(L, N).ok && make_plan(next, N).ok ? 1 : 0;
+    const Plan a = make_plan(L, N), b = make_plan(next, N);
+    return a.ok && b.ok && a.intp == b.intp ? 1 : 0;
 }
 
 int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,

@@ -68,3 +68,13 @@ def test_large_int4_mlp_batch_sweep(spg, l_net, n):
     if n == 1:
         one = net.forward(x[0])                                  # the reference's single-sample entry point
         assert np.abs(one - want[0]).max() <= 2e-5
+    if n <= 8:
+        # the integer-digit GEMV (default for integer files) against the bf16-term GEMV on the whole chain
+        lib = spg.lib()
+        lib.spgk_gemv_set_int_path(0)
+        try:
+            other = net.forward_batch(x)
+        finally:
+            lib.spgk_gemv_set_int_path(1)
+        assert spg.last_path() == "gemv"
+        assert np.abs(other - got).max() <= 2e-6, np.abs(other - got).max()

@@ -26,6 +26,7 @@ def k(spg, has_gpu):
     lib.spgk_layer_gemv.argtypes = [C.POINTER(spg.abi.KLayer), vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, vp, vp]
     lib.spgk_gemv_scratch_bytes.argtypes = [C.POINTER(spg.abi.KLayer), C.c_uint32]
     lib.spgk_gemv_scratch_bytes.restype = C.c_size_t
+    lib.spgk_gemv_set_int_path.argtypes = [C.c_int]
     return lib
 
 
@@ -139,13 +140,15 @@ def test_dequant16_every_precision(spg, k, oracle, prec, bits, out_in):
         assert np.abs(rec - dec.astype(np.float64)).max() <= (tol + 3e-7) * np.abs(dec).max()
 
 
-@pytest.mark.parametrize("prec", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("prec,int_path", [(0, 0), (1, 0), (2, 0), (3, 0), (4, 0), (5, 0), (3, 1), (4, 1), (5, 1)])
 @pytest.mark.parametrize("out,inn,n", [(16, 256, 1), (100, 1024, 2), (1000, 8192, 3), (130, 512, 4), (257, 4096, 8),
-                                       (10, 1024, 1), (128, 16384, 5)])
-def test_gemv_against_float64(spg, k, oracle, prec, out, inn, n):
-    """Fused dequant-GEMV (all six stored precisions, K splits, ragged row blocks) vs a float64 product
-    of the decoded weights; the kernel's products are exact, so only fp32 summation error remains."""
+                                       (10, 1024, 1), (128, 16384, 5), (48, 2048, 6), (33, 512, 7)])
+def test_gemv_against_float64(spg, k, oracle, prec, int_path, out, inn, n):
+    """Fused dequant-GEMV (all six stored precisions, both the bf16-term path and the integer-digit path of the
+    integer formats, ragged row blocks) vs a float64 product of the decoded weights.  bf16 path: exact products,
+    fp32 summation.  Integer path: exact sums of 28-bit fixed-point activations (scale = the row's maximum)."""
     import torch
+    k.spgk_gemv_set_int_path(int_path)
     rng = np.random.default_rng(out * 31 + inn + n)
     vals = (rng.standard_normal(out * inn) / np.sqrt(inn)).astype(np.float32)
     raw = oracle.Oracle.encode(vals, prec)
@@ -174,9 +177,10 @@ def test_gemv_against_float64(spg, k, oracle, prec, out, inn, n):
         want = ACT[act](x.astype(np.float64) @ dec.T + bias)
         got = y.cpu().numpy()
         assert np.all(got[n] == -9.0)
-        # one row: three bf16 terms (24 bits); more rows: two terms (16 bits) per activation
-        tol = (3e-6 if n == 1 else 3e-5) * max(1.0, np.abs(want).max()) * np.sqrt(inn / 256)
+        # bf16 path, one row: three bf16 terms (24 bits); more rows: two terms (16 bits) per activation
+        tol = (3e-6 if n == 1 or int_path else 3e-5) * max(1.0, np.abs(want).max()) * np.sqrt(inn / 256)
         assert np.abs(got[:n] - want).max() <= tol, (rep, np.abs(got[:n] - want).max())
+    k.spgk_gemv_set_int_path(1)
 
 
 def test_gemv_declines_unaligned_rows(spg, k):
