@@ -45,6 +45,9 @@ typedef struct {
     uint32_t     out;
     int32_t      precision;  /* PrecisionMode: 0 f32, 1 f16, 2 bf16, 3 i8, 4 i4, 5 i2 */
     int32_t      act;        /* ActivationFunction                            */
+    float        bias_absmax;/* an upper bound of |bias[j]|.  Only the chained integer GEMV reads it
+                              * (for the range of the values it hands to the next layer); a bound
+                              * below a real bias makes that call fail with SPGK_E_ARG.            */
 } spgk_layer;
 
 /* 16-bit operand flavour used on the tensor-core paths. */

@@ -79,7 +79,7 @@ class SaveArgs(C.Structure):
 class KLayer(C.Structure):
     """spgk_layer of include/spingalett_b200_kernels.h"""
     _fields_ = [("w", C.c_void_p), ("bias", C.c_void_p), ("w_scale", C.c_float), ("in_", C.c_uint32),
-                ("out", C.c_uint32), ("precision", C.c_int32), ("act", C.c_int32)]
+                ("out", C.c_uint32), ("precision", C.c_int32), ("act", C.c_int32), ("bias_absmax", C.c_float)]
 
 
 # the 21 exported functions of the reference ABI (Spingalett.h:202-238)

@@ -94,6 +94,7 @@ struct GemvParams {
     int next_prec; uint32_t next_kpad;      // precision of the next layer's weights; its K rounded up to a whole chunk
     const uint8_t *in_head;                 // integer path: head of this layer's staged input
     uint8_t *out_head;                      // integer path: head of the next layer's staged input (or NULL)
+    float bias_absmax;                      // integer path: caller's bound of |bias|, checked against every bias used
 };
 
 // elements covered by one 128-bit load, per stored precision
@@ -541,11 +542,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
             __shared__ float e_sc[MAX_BATCH], e_inv[MAX_BATCH];
             const StagedHead *ih = reinterpret_cast<const StagedHead *>(p.in_head);
             const long long *iparts = reinterpret_cast<const long long *>(p.in_head + 256);
-            float bmax = 0.0f;
-            if (p.xout) {
-                for (uint32_t i = lane; i < p.out; i += 32) bmax = fmaxf(bmax, fabsf(p.bias[i]));
-                bmax = spg_warp_max(bmax);
-            }
+            const float bmax = p.bias_absmax;
             for (uint32_t n = 0; n < p.N; n++) {
                 const float S = ih->S[n];
                 float inv_next = 0.0f;
@@ -568,12 +565,15 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                     e_inv[n] = inv_next;
                 }
             }
-            if (p.xout && blockIdx.x == 0 && lane == 0) reinterpret_cast<StagedHead *>(p.out_head)->nparts = p.items;
+            if (p.xout && blockIdx.x == 0 && lane == 0) reinterpret_cast<StagedHead *>(p.out_head)->nparts = gridDim.x;
             __syncwarp();
             int *redi = reinterpret_cast<int *>(red);
             uint8_t *xo = reinterpret_cast<uint8_t *>(p.xout);
             long long *oparts = p.out_head ? reinterpret_cast<long long *>(p.out_head + 256) : nullptr;
             constexpr int PER_LANE = ITEM_ROWS * MAX_BATCH / 32;        // outputs of one item a lane may own
+            long long abs_run[PER_LANE];                                // this CTA's sum of |V| per batch row (lanes 0 and 16 hold it)
+#pragma unroll
+            for (int u = 0; u < PER_LANE; u++) abs_run[u] = 0;
             for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
                 const uint32_t rbuf = n_item & 1u;
                 // what does not depend on the consumers comes first: the biases of this item's rows
@@ -582,6 +582,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                 for (int u = 0; u < PER_LANE; u++) {
                     const uint32_t idx = u * 32 + lane, row = item * ITEM_ROWS + idx % ITEM_ROWS;
                     bias_r[u] = (idx < ITEM_ROWS * p.N && row < p.out) ? p.bias[row] : 0.0f;
+                    if (xo && !(fabsf(bias_r[u]) <= bmax)) atomicCAS(p.status, 0, 9);       // the caller's bound is wrong
                 }
                 handoff_wait(1 + rbuf);
                 int *redb = redi + rbuf * RED_FLOATS;
@@ -615,7 +616,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                     if (xo) {
                         // lanes 0..15 hold one batch row, lanes 16..31 the next: their |V| sums go beside the staged data
                         for (int o = 8; o > 0; o >>= 1) absV += __shfl_xor_sync(0xFFFFFFFFu, absV, o);
-                        if ((lane & 15u) == 0 && n < p.N) oparts[(uint64_t)item * 8 + n] = absV;
+                        abs_run[u] += absV;
                     }
                 }
                 if (xo) {
@@ -626,6 +627,13 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                     if (item == p.items - 1)
                         for (uint32_t idx = lane; idx < (p.next_kpad - p.out) * cs; idx += 32)
                             xo[staged_index_int(p.next_prec, cs, p.out + idx / cs, idx % cs)] = 0;
+                }
+            }
+            if (xo && (lane & 15u) == 0) {
+#pragma unroll
+                for (int u = 0; u < PER_LANE; u++) {
+                    const uint32_t n = (u * 32 + lane) / ITEM_ROWS;
+                    if (n < p.N) oparts[(uint64_t)blockIdx.x * 8 + n] = abs_run[u];
                 }
             }
         } else {
@@ -934,7 +942,7 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
     int rc = weight_map(L, 8 * pl.spb * 64, &map);
     if (rc) return rc;
     GemvParams p{};
-    p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out;
+    p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out; p.bias_absmax = L->bias_absmax;
     p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
     p.y = y; p.ldy = ldy;
     p.N = N; p.P = pl.P; p.C = pl.C;
@@ -1008,6 +1016,11 @@ int spgk_gemv_status(void *scratch, void *stream)
     int32_t h = 0;
     SPGK_CUDA(cudaMemcpyAsync(&h, scratch, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     SPGK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (h == 9) {
+        spgk_set_error("spg_gemv_kernel", "spgk_layer.bias_absmax is smaller than a bias of the layer");
+        SPGK_CUDA(cudaMemsetAsync(scratch, 0, sizeof h, (cudaStream_t)stream));
+        return SPGK_E_ARG;
+    }
     if (h != 0) {
         char msg[96];
         snprintf(msg, sizeof msg, "bounded wait %d gave up inside the GEMV kernel", (int)h);

@@ -9,6 +9,7 @@
  * the CPU. */
 #include "spg_internal.h"
 #include <stdlib.h>
+#include <math.h>
 #include <string.h>
 
 int spg_map_kernel_error(int rc, const char *where)
@@ -136,8 +137,13 @@ int spg_dev_ensure(spg_net *n)
         if ((rc = spg_map_kernel_error(spgk_malloc(&db, (size_t)out * sizeof(float)), "bias allocation"))) goto fail;
         n->d_bias[l] = db;
         if ((rc = spg_map_kernel_error(spgk_memcpy_h2d(db, p->biases + p->bias_offsets[l], (size_t)out * sizeof(float), n->stream), "bias upload"))) goto fail;
+        float babs = 0.0f;
+        for (uint32_t j = 0; j < out; j++) {
+            const float a = fabsf(p->biases[p->bias_offsets[l] + j]);
+            if (a > babs) babs = a;
+        }
         n->klayers[l] = (spgk_layer){ .w = n->d_w[l], .bias = n->d_bias[l], .w_scale = scale, .in = in, .out = out,
-                                      .precision = (int32_t)prec, .act = (int32_t)p->act_func[l] };
+                                      .precision = (int32_t)prec, .act = (int32_t)p->act_func[l], .bias_absmax = babs };
     }
     void *st = NULL;
     if ((rc = spg_map_kernel_error(spgk_malloc(&st, 64), "status allocation"))) goto fail;
