@@ -163,6 +163,7 @@ spg_gemv_stage_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uin
                       int prec, uint32_t cs, __nv_bfloat16 *__restrict__ dst)
 {
     const uint32_t k = blockIdx.x * 256 + threadIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the layer kernel behind this one may start fetching weights
     if (k >= kpad) return;
     for (uint32_t n = 0; n < N; n++) stage_value(dst, prec, cs, k, n, P, k < in ? x[(uint64_t)n * ldx + k] : 0.0f);
     for (uint32_t col = N * P; col < cs; col++) dst[staged_index(prec, cs, k, col)] = __float2bfloat16_rn(0.0f);
@@ -237,6 +238,7 @@ spg_gemv_stage_int_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N,
     StagedHead *head = reinterpret_cast<StagedHead *>(head_raw);
     long long *parts = reinterpret_cast<long long *>(head_raw + 256);
     const uint32_t k = blockIdx.x * 256 + threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the layer kernel behind this one may start fetching weights
     for (uint32_t n = 0; n < N; n++) {
         const float *row = x + (uint64_t)n * ldx;
         float m = 0.0f;
@@ -509,23 +511,39 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel may start on SMs this grid leaves
     }
     __syncthreads();
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------ producer: two copies per chunk -------------------
+        // The weights do not depend on the layer before this one, the staged input does: the first ring of
+        // weight boxes is requested at once, and only then does the thread wait for the preceding kernel in
+        // the stream (programmatic dependent launch), so the start of this layer overlaps the end of the last.
         if (lane == 0) {
-            uint32_t gchunk = 0, s = 0, ph = 1;
-            bool alive = true;
-            for (uint32_t item = blockIdx.x; item < p.items && alive; item += gridDim.x) {
-                for (uint32_t c = 0; c < p.nchunks; c++, gchunk++) {
-                    if (!gbar_wait(empty0 + 8 * s, ph, abort_flag, p.status, 1)) { alive = false; break; }
-                    gbar_expect_tx(full0 + 8 * s, slot_bytes);
-                    tma_box_2d(base + s * slot_bytes, &wmap, full0 + 8 * s, (int)(c * (wchunk_bytes / ITEM_ROWS / 8)), (int)(item * ITEM_ROWS));
-                    bulk_copy_1d(base + s * slot_bytes + wchunk_bytes,
-                                 reinterpret_cast<const uint8_t *>(p.xin) + (size_t)c * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * s);
-                    if (++s == p.ring) { s = 0; ph ^= 1u; }
-                }
+            const uint32_t my_items = p.items > blockIdx.x ? (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const uint32_t total = my_items * p.nchunks;
+            const uint32_t head = total < p.ring ? total : p.ring;
+            for (uint32_t q = 0; q < head; q++) {                       // slots are free at the start: no wait needed
+                const uint32_t item = blockIdx.x + (q / p.nchunks) * gridDim.x, c = q % p.nchunks;
+                gbar_expect_tx(full0 + 8 * q, slot_bytes);
+                tma_box_2d(base + q * slot_bytes, &wmap, full0 + 8 * q, (int)(c * (wchunk_bytes / ITEM_ROWS / 8)), (int)(item * ITEM_ROWS));
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (uint32_t q = 0; q < head; q++) {
+                const uint32_t c = q % p.nchunks;
+                bulk_copy_1d(base + q * slot_bytes + wchunk_bytes,
+                             reinterpret_cast<const uint8_t *>(p.xin) + (size_t)c * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * q);
+            }
+            uint32_t s = head == p.ring ? 0 : head, ph = head == p.ring ? 0 : 1;
+            for (uint32_t q = head; q < total; q++) {
+                const uint32_t item = blockIdx.x + (q / p.nchunks) * gridDim.x, c = q % p.nchunks;
+                if (!gbar_wait(empty0 + 8 * s, ph, abort_flag, p.status, 1)) break;
+                gbar_expect_tx(full0 + 8 * s, slot_bytes);
+                tma_box_2d(base + s * slot_bytes, &wmap, full0 + 8 * s, (int)(c * (wchunk_bytes / ITEM_ROWS / 8)), (int)(item * ITEM_ROWS));
+                bulk_copy_1d(base + s * slot_bytes + wchunk_bytes,
+                             reinterpret_cast<const uint8_t *>(p.xin) + (size_t)c * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * s);
+                if (++s == p.ring) { s = 0; ph ^= 1u; }
             }
         }
         return;
@@ -537,6 +555,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
         // activation, writes y and stages the next layer's input, while the consumers stream the next item.
         const uint32_t cs = CW * T, spare = cs - p.C;
         uint32_t n_item = 0;
+        asm volatile("griddepcontrol.wait;" ::: "memory");       // everything this warp reads or writes is ordered after the kernel before
         if constexpr (INTP) {
             // ---- integer path: exact integer dot products; scales and the next layer's range bound first ----
             __shared__ float e_sc[MAX_BATCH], e_inv[MAX_BATCH];
@@ -882,7 +901,13 @@ int launch(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStre
         attr_done = true;
     }
     const uint32_t grid = pl.items < (uint32_t)sms ? pl.items : (uint32_t)sms;
-    spg_gemv_kernel<PREC, T, CW, INTP><<<grid, GEMV_THREADS, pl.smem, s>>>(map, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMV_THREADS); cfg.dynamicSmemBytes = pl.smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    SPGK_CUDA(cudaLaunchKernelEx(&cfg, spg_gemv_kernel<PREC, T, CW, INTP>, map, p));
     return spgk_check_launch("spg_gemv_kernel");
 }
 
