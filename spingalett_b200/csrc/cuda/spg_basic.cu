@@ -144,10 +144,11 @@ spg_layer_simt_kernel(const void *__restrict__ w, const float *__restrict__ bias
 
 // Row softmax, one warp per row (Activation.c:5-21).
 __global__ void __launch_bounds__(256)
-spg_softmax_rows_kernel(float *__restrict__ y, uint32_t ldy, uint32_t N, uint32_t width)
+spg_softmax_rows_kernel(float *__restrict__ y, uint32_t ldy, uint32_t N, uint32_t width, const uint32_t *__restrict__ limit)
 {
-    const uint32_t row = blockIdx.x * 8u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
-    if (row >= N) return;
+    N = spg_limit_rows(N, limit);
+    const uint32_t lane = threadIdx.x & 31u;
+    for (uint32_t row = blockIdx.x * 8u + (threadIdx.x >> 5); row < N; row += gridDim.x * 8u) {
     float *r = y + (uint64_t)row * ldy;
     float mx = -FLT_MAX;
     for (uint32_t i = lane; i < width; i += 32u) { float v = r[i]; if (v > mx) mx = v; }
@@ -158,6 +159,7 @@ spg_softmax_rows_kernel(float *__restrict__ y, uint32_t ldy, uint32_t N, uint32_
     if (sum > 0.0f) {
         float inv = 1.0f / sum;
         for (uint32_t i = lane; i < width; i += 32u) r[i] *= inv;
+    }
     }
 }
 
@@ -249,8 +251,9 @@ spg_gap_error_kernel(const float *__restrict__ fast, const float *__restrict__ e
 // dst[idx[i]][:] = src[i][:]
 __global__ void __launch_bounds__(256)
 spg_scatter_rows_kernel(const float *__restrict__ src, const uint32_t *__restrict__ idx, float *__restrict__ dst,
-                        uint32_t rows, uint32_t width, uint32_t ldd)
+                        uint32_t rows, uint32_t width, uint32_t ldd, const uint32_t *__restrict__ limit)
 {
+    rows = spg_limit_rows(rows, limit);
     const uint64_t total = (uint64_t)rows * width;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t rr = (uint32_t)(i / width), c = (uint32_t)(i % width);
@@ -273,8 +276,9 @@ template <> __device__ __forceinline__ float spg_from16<__nv_bfloat16>(__nv_bflo
 template <typename T16, bool VEC>
 __global__ void __launch_bounds__(256)
 spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t in,
-                   T16 *__restrict__ dst, uint32_t ld16, uint64_t plane_elems, int parts)
+                   T16 *__restrict__ dst, uint32_t ld16, uint64_t plane_elems, int parts, const uint32_t *__restrict__ limit)
 {
+    N = spg_limit_rows(N, limit);
     const uint32_t chunks = ld16 >> 3;
     const uint64_t total = (uint64_t)N * chunks;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -299,7 +303,11 @@ spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32
     }
 }
 
+thread_local const uint32_t *spg_tls_rows_limit = nullptr;
+
 extern "C" {
+
+void spgk_set_dynamic_rows(const uint32_t *rows_dev) { spg_tls_rows_limit = rows_dev; }
 
 int spgk_layer_simt(const spgk_layer *L, const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N, void *stream)
 {
@@ -333,11 +341,13 @@ int spgk_softmax_rows(float *y, uint32_t ldy, uint32_t N, uint32_t width, void *
 {
     if (!y || width == 0 || width > 65535u) { spgk_set_error("spgk_softmax_rows", "bad argument"); return SPGK_E_ARG; }
     if (N == 0) return SPGK_OK;
-    if (N <= 64 && width > 64) {
+    if (N <= 64 && width > 64 && !spg_tls_rows_limit) {
         spg_softmax_block_kernel<<<N, 256, 0, (cudaStream_t)stream>>>(y, ldy, width);
         return spgk_check_launch("spg_softmax_block_kernel");
     }
-    spg_softmax_rows_kernel<<<(N + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(y, ldy, N, width);
+    uint32_t blocks = (N + 7u) / 8u;
+    if (blocks > 148u * 64u) blocks = 148u * 64u;
+    spg_softmax_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(y, ldy, N, width, spg_tls_rows_limit);
     return spgk_check_launch("spg_softmax_rows_kernel");
 }
 
@@ -364,7 +374,7 @@ int spgk_scatter_rows(const float *src, const uint32_t *idx, float *dst, uint32_
     if (rows == 0 || width == 0) return SPGK_OK;
     uint64_t total = (uint64_t)rows * width;
     uint32_t blocks = (uint32_t)((total + 255) / 256 < 148ull * 8 ? (total + 255) / 256 : 148ull * 8);
-    spg_scatter_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(src, idx, dst, rows, width, ldd);
+    spg_scatter_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(src, idx, dst, rows, width, ldd, spg_tls_rows_limit);
     return spgk_check_launch("spg_scatter_rows_kernel");
 }
 
@@ -379,11 +389,11 @@ int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in, void *ds
     const bool vec = ((uintptr_t)x & 15u) == 0 && (ldx & 3u) == 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (type == SPGK_T_F16) {
-        if (vec) spg_split16_kernel<__half, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts);
-        else spg_split16_kernel<__half, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts);
+        if (vec) spg_split16_kernel<__half, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
+        else spg_split16_kernel<__half, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
     } else {
-        if (vec) spg_split16_kernel<__nv_bfloat16, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts);
-        else spg_split16_kernel<__nv_bfloat16, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts);
+        if (vec) spg_split16_kernel<__nv_bfloat16, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
+        else spg_split16_kernel<__nv_bfloat16, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
     }
     return spgk_check_launch("spg_split16_kernel");
 }

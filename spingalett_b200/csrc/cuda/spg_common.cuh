@@ -104,3 +104,14 @@ __device__ __forceinline__ float spg_warp_max(float v)
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+
+// Device-resident row count set by spgk_set_dynamic_rows for the calling thread (NULL = off): the row-wise
+// kernels launched afterwards process min(rows argument, *limit) rows, the limit being read on the device.
+extern thread_local const uint32_t *spg_tls_rows_limit;
+__device__ __forceinline__ uint32_t spg_limit_rows(uint32_t rows, const uint32_t *limit)
+{
+    if (!limit) return rows;
+    const uint32_t v = *limit;
+    return v < rows ? v : rows;
+}
+

@@ -49,6 +49,7 @@ struct GemmParams {
     void *out16; uint32_t ldo16; uint64_t o_plane; int out_parts; int type16;
     float *out32; uint32_t ldo32;
     int32_t *status;
+    const uint32_t *m_limit;      // optional device-resident row count: the kernel works on min(M, *m_limit) rows
 };
 
 // ---- raw PTX wrappers -------------------------------------------------------
@@ -327,8 +328,14 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p)
+spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p_in)
 {
+    // rows may be limited by a count that only exists on the device (every role derives the same tile list from it)
+    GemmParams p = p_in;
+    if (p_in.m_limit) {
+        const uint32_t m = *p_in.m_limit;
+        if (m < p.M) { p.M = m; p.m_tiles = (m + BM - 1) / BM; if (p.m_tiles && p.group_m > p.m_tiles) p.group_m = p.m_tiles; }
+    }
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment of the operand tiles (required by the 128-byte swizzle atoms)
     const uint32_t raw = smem_u32(smem_raw);
@@ -604,6 +611,7 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     p.out16 = out16; p.ldo16 = ldo16; p.o_plane = o_plane; p.out_parts = out_parts; p.type16 = type16;
     p.out32 = out32; p.ldo32 = ldo32;
     p.status = status;
+    p.m_limit = spg_tls_rows_limit;
 
     CUtensorMap map_a, map_w;
     int rc = make_map(&map_a, a16, type16, L->in, N, lda, a_plane, a_parts, BM);

@@ -90,6 +90,12 @@ void spg_dev_release(spg_net *n)
     n->act16_bytes = 0; n->act32_bytes = 0;
     spgk_free(n->d_status); n->d_status = NULL;
     spgk_free(n->d_w16); n->d_w16 = NULL; n->w16_bytes = 0;
+    spgk_host_free(n->h_count); n->h_count = NULL; n->count_pending = false;
+    for (int t = 0; t < 2; t++) {
+        if (n->d_w16c[t]) for (uint32_t l = 0; l < n->dev_layers; l++) spgk_free(n->d_w16c[t][l]);
+        free(n->d_w16c[t]); n->d_w16c[t] = NULL;
+        free(n->w16c_parts[t]); n->w16c_parts[t] = NULL;
+    }
     for (uint32_t i = 0; i < n->prof_cap; i++) spgk_event_destroy(n->prof_ev[i]);
     free(n->prof_ev); n->prof_ev = NULL; n->prof_cap = 0; n->prof_used = 0;
     n->dev_ready = false;
@@ -199,7 +205,16 @@ int spingalett_sync_weights(NeuralNetwork *net)
     return SPINGALETT_OK;
 }
 
-uint32_t spingalett_last_repaired(NeuralNetwork *net) { return net ? spg_priv(net)->last_repaired : 0; }
+uint32_t spingalett_last_repaired(NeuralNetwork *net)
+{
+    if (!net) return 0;
+    spg_net *n = spg_priv(net);
+    if (n->count_pending) {                       /* the count was copied asynchronously: wait for it */
+        n->count_pending = false;
+        if (spgk_stream_sync(n->stream) == 0 && n->h_count) n->last_repaired = *n->h_count;
+    }
+    return n->last_repaired;
+}
 float spingalett_net_margin(NeuralNetwork *net) { return net ? spg_priv(net)->auto_theta : 0.0f; }
 
 /* ---- optional timing of the layer kernels -------------------------------- */
@@ -364,6 +379,8 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
 
 static uint32_t round8(uint32_t v) { return (v + 7u) & ~7u; }
 
+#define SPG_W16_KEEP_MAX ((size_t)256 << 20)    /* keep expanded 16-bit weight operands between calls up to this many bytes per net and type */
+
 static int large_simt(spg_net *n, const float *d_x, uint32_t N, float *d_out)
 {
     NeuralNetwork *p = &n->pub;
@@ -424,17 +441,25 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
         }
         n->act16_bytes = need;
     }
-    /* scratch for the 16-bit weight operand of layers that are not stored as one */
-    size_t wneed = 0;
+    /* 16-bit weight operand of layers that are not stored as one: expanded once and kept while the whole net's
+     * operands fit the budget below (the benchmark MLP: 1.8 MB), otherwise expanded into a scratch per call */
+    size_t wneed = 0, wtotal = 0;
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
         if (!spgk_weights16_direct(L, type)) {
             size_t b = spgk_weights16_bytes(L, (exact && L->precision == PRECISION_FLOAT32) ? 2 : 1);
             if (b > wneed) wneed = b;
+            wtotal += b;
         }
     }
+    const bool keep = wtotal && wtotal <= SPG_W16_KEEP_MAX;
     int rc;
-    if (wneed && (rc = reserve(&n->d_w16, &n->w16_bytes, wneed, "16-bit weight operand scratch"))) return rc;
+    if (keep && !n->d_w16c[type]) {
+        n->d_w16c[type] = calloc(n->dev_layers, sizeof(void *));
+        n->w16c_parts[type] = calloc(n->dev_layers, 1);
+        if (!n->d_w16c[type] || !n->w16c_parts[type]) { spg_set_error(SPINGALETT_ERR_ALLOC, "weight operand table"); return SPINGALETT_ERR_ALLOC; }
+    }
+    if (!keep && wneed && (rc = reserve(&n->d_w16, &n->w16_bytes, wneed, "16-bit weight operand scratch"))) return rc;
     rc = spg_map_kernel_error(spgk_split16(d_x, p->topology[0], N, p->topology[0], n->d_act16[0],
                                            round8(p->topology[0]), plane, parts, type, n->stream), "input split");
     if (rc) return rc;
@@ -452,8 +477,18 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
             w_parts = (exact && L->precision == PRECISION_FLOAT32) ? 2 : 1;
             ldw = round8(L->in);
             w_plane = (uint64_t)L->out * ldw;
-            w16 = n->d_w16;
-            if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16, ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
+            if (keep) {
+                if (n->d_w16c[type][l] && n->w16c_parts[type][l] != w_parts) { spgk_free(n->d_w16c[type][l]); n->d_w16c[type][l] = NULL; }
+                if (!n->d_w16c[type][l]) {
+                    if ((rc = spg_map_kernel_error(spgk_malloc(&n->d_w16c[type][l], spgk_weights16_bytes(L, w_parts)), "kept weight operand"))) return rc;
+                    n->w16c_parts[type][l] = (uint8_t)w_parts;
+                    if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16c[type][l], ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
+                }
+                w16 = n->d_w16c[type][l];
+            } else {
+                w16 = n->d_w16;
+                if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16, ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
+            }
         }
         prof_mark(n);
         rc = spg_map_kernel_error(spgk_layer_gemm_tc(L, w16, ldw, w_plane, w_parts, type,
@@ -508,20 +543,24 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     }
     if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
     if ((rc = spg_map_kernel_error(spgk_margin_select(d_out, outw, N, outw, theta, n->d_rep_idx, d_count, n->stream), "margin check"))) return rc;
-    uint32_t count = 0;
-    if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(&count, d_count, 4, n->stream), "repair count"))) return rc;
-    if ((rc = spg_map_kernel_error(spgk_stream_sync(n->stream), "repair count sync"))) return rc;
-    n->last_repaired = count;
-    if (count == 0) { spg_note_path("tcgen05"); return SPINGALETT_OK; }
-    if ((uint64_t)count * 4 > N) {                                                 /* too many: one exact pass over everything */
-        rc = large_chain(n, d_x, N, d_out, true);
-        return rc;
+    /* The row count stays on the device: the gather, the exact chain and the scatter below are launched for
+     * N rows of capacity and read the count when they run, so the call needs no host round trip.  A copy
+     * travels to pinned host memory for spingalett_last_repaired(). */
+    if (!n->h_count) {
+        void *h = NULL;
+        if ((rc = spg_map_kernel_error(spgk_host_alloc(&h, 64), "repair count (host)"))) return rc;
+        n->h_count = h;
     }
-    if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)count * in0 * 4, "repair inputs"))) return rc;
-    if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)count * outw * 4, "repair outputs"))) return rc;
-    if ((rc = spg_map_kernel_error(spgk_gather_rows(d_x, n->d_rep_idx, n->d_rep_in, count, in0, n->stream), "repair gather"))) return rc;
-    if ((rc = large_chain(n, n->d_rep_in, count, n->d_rep_out, true))) return rc;
-    if ((rc = spg_map_kernel_error(spgk_scatter_rows(n->d_rep_out, n->d_rep_idx, d_out, count, outw, outw, n->stream), "repair scatter"))) return rc;
+    if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(n->h_count, d_count, 4, n->stream), "repair count"))) return rc;
+    n->count_pending = true;
+    if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
+    if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)N * outw * 4, "repair outputs"))) return rc;
+    spgk_set_dynamic_rows(d_count);
+    rc = spg_map_kernel_error(spgk_gather_rows(d_x, n->d_rep_idx, n->d_rep_in, N, in0, n->stream), "repair gather");
+    if (!rc) rc = large_chain(n, n->d_rep_in, N, n->d_rep_out, true);
+    if (!rc) rc = spg_map_kernel_error(spgk_scatter_rows(n->d_rep_out, n->d_rep_idx, d_out, N, outw, outw, n->stream), "repair scatter");
+    spgk_set_dynamic_rows(NULL);
+    if (rc) return rc;
     spg_note_path("tcgen05");
     return SPINGALETT_OK;
 }

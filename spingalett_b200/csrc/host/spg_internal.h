@@ -52,6 +52,7 @@ typedef struct {
     /* AUTO math mode: rows recomputed exactly after the one-term pass */
     uint32_t *d_rep_idx; size_t rep_idx_bytes; float *d_rep_in; size_t rep_in_bytes; float *d_rep_out; size_t rep_out_bytes;
     uint32_t last_repaired; bool auto_calibrated; float auto_theta;
+    uint32_t *h_count; bool count_pending;      /* pinned copy of the repaired-row count of the last AUTO call */
 
     /* large-batch workspace */
     float *d_in32;  size_t in32_bytes;      /* staging for host inputs */
@@ -60,6 +61,8 @@ typedef struct {
     float *d_act32[2]; size_t act32_bytes;  /* ping-pong fp32 activations (SIMT chain) */
     int32_t *d_status; bool status_pending;
     void *d_w16; size_t w16_bytes;         /* 16-bit weight operand of the layer in flight */
+    /* 16-bit weight operands kept between calls (nets whose expanded weights are small): [fp16 | bf16][layer] */
+    void **d_w16c[2]; uint8_t *w16c_parts[2];
 
     float *h_out; size_t h_out_bytes;       /* library-owned pinned output buffer */
     float *h_stage; size_t h_stage_bytes;   /* pinned staging for forward() */
