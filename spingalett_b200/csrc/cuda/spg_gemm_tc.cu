@@ -34,6 +34,9 @@ constexpr uint32_t NUM_THREADS = 64 + 32 * EPI_WARPS;   // warp 0 TMA, warp 1 MM
 constexpr uint32_t WAIT_LIMIT = 1u << 23;
 constexpr uint32_t MAX_PASSES = 4;
 constexpr uint32_t SOFTMAX_FUSE_MAX = 256;
+constexpr uint32_t STG_PITCH = 80;                        // bytes per staged row: 32 columns x 2 bytes + 16 (bank spread for 16-byte accesses)
+constexpr uint32_t PATCH_BYTES = 32 * 128;                 // TMA-store patch: 32 rows x 64 columns, 128-byte swizzled rows
+constexpr uint32_t STG_BYTES = EPI_WARPS * PATCH_BYTES;    // per epilogue warp: one patch (the register-store path uses 32 x STG_PITCH of it)
 
 struct GemmParams {
     uint32_t M, N, K;
@@ -49,6 +52,7 @@ struct GemmParams {
     void *out16; uint32_t ldo16; uint64_t o_plane; int out_parts; int type16;
     float *out32; uint32_t ldo32;
     int32_t *status;
+    int tma_store;                // 16-bit output leaves through TMA stores (one plane, tiles at least 128 wide)
     const uint32_t *m_limit;      // optional device-resident row count: the kernel works on min(M, *m_limit) rows
 };
 
@@ -162,30 +166,6 @@ template <typename T16> __device__ __forceinline__ float round16(float a);
 template <> __device__ __forceinline__ float round16<__half>(float a) { return __half2float(__float2half_rn(a)); }
 template <> __device__ __forceinline__ float round16<__nv_bfloat16>(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
 
-// store 16 consecutive activations of one row as 16-bit planes (hi [, lo])
-template <typename T16>
-__device__ __forceinline__ void store16(const GemmParams &p, uint32_t row, uint32_t col0, const float (&v)[16])
-{
-    T16 *base = reinterpret_cast<T16 *>(p.out16) + (uint64_t)row * p.ldo16 + col0;
-#pragma unroll
-    for (int g = 0; g < 2; g++) {
-        if (col0 + 8u * g >= p.ldo16) break;                    // ldo16 is a multiple of 8
-        uint4 hi;
-        hi.x = pack2<T16>(v[8 * g + 0], v[8 * g + 1]); hi.y = pack2<T16>(v[8 * g + 2], v[8 * g + 3]);
-        hi.z = pack2<T16>(v[8 * g + 4], v[8 * g + 5]); hi.w = pack2<T16>(v[8 * g + 6], v[8 * g + 7]);
-        *reinterpret_cast<uint4 *>(base + 8 * g) = hi;
-        if (p.out_parts > 1) {
-            float r[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) r[i] = v[8 * g + i] - round16<T16>(v[8 * g + i]);
-            uint4 lo;
-            lo.x = pack2<T16>(r[0], r[1]); lo.y = pack2<T16>(r[2], r[3]);
-            lo.z = pack2<T16>(r[4], r[5]); lo.w = pack2<T16>(r[6], r[7]);
-            *reinterpret_cast<uint4 *>(base + p.o_plane + 8 * g) = lo;
-        }
-    }
-}
-
 // 16 accumulator columns of one row -> scale, bias, activation.  `full` says all 16 columns exist.
 template <int ACT>
 __device__ __forceinline__ void finish16(const GemmParams &p, const uint32_t (&r)[16], uint32_t col0, bool full, float (&v)[16])
@@ -208,22 +188,62 @@ __device__ __forceinline__ void finish16(const GemmParams &p, const uint32_t (&r
     }
 }
 
-__device__ __forceinline__ void write16(const GemmParams &p, uint32_t row, uint32_t col0, const float (&v)[16])
+__device__ __forceinline__ void write32(const GemmParams &p, uint32_t row, uint32_t col0, const float (&v)[16])
 {
-    if (p.out16) {
-        if (p.type16 == SPGK_T_F16) store16<__half>(p, row, col0, v);
-        else store16<__nv_bfloat16>(p, row, col0, v);
+    float *o = p.out32 + (uint64_t)row * p.ldo32 + col0;
+    if ((p.ldo32 & 3u) == 0 && col0 + 16 <= p.N) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<float4 *>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) if (col0 + i < p.N) o[i] = v[i];
     }
-    if (p.out32) {
-        float *o = p.out32 + (uint64_t)row * p.ldo32 + col0;
-        if ((p.ldo32 & 3u) == 0 && col0 + 16 <= p.N) {
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// generic-proxy writes to shared memory -> visible to the bulk-copy (async) proxy
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// 16-bit output of a 32-row x 32-column patch.  Each thread owns one row of the accumulator, so writing
+// straight from registers would send every 16-byte store of a warp to a different row of C (32 cache lines
+// per instruction -- measured: a third of the kernel's time).  The patch goes through shared memory instead:
+// written row-wise by its owners, read back so that a store instruction covers 8 rows x 64 contiguous bytes.
+template <typename T16>
+__device__ __forceinline__ void store_patch(const GemmParams &p, uint8_t *stg, uint32_t lane, uint32_t row0, uint32_t col0,
+                                            const float (&v0)[16], const float (&v1)[16], bool second)
+{
+    const uint32_t pieces = second ? 4u : 2u;
+    for (int part = 0; part < p.out_parts; part++) {
+        uint4 q[4];
 #pragma unroll
-            for (int i = 0; i < 16; i += 4)
-                *reinterpret_cast<float4 *>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-        } else {
+        for (int g = 0; g < 4; g++) {
+            const float *v = g < 2 ? v0 + 8 * g : v1 + 8 * (g - 2);
+            float w[8];
 #pragma unroll
-            for (int i = 0; i < 16; i++) if (col0 + i < p.N) o[i] = v[i];
+            for (int i = 0; i < 8; i++) w[i] = part == 0 ? v[i] : v[i] - round16<T16>(v[i]);
+            q[g].x = pack2<T16>(w[0], w[1]); q[g].y = pack2<T16>(w[2], w[3]);
+            q[g].z = pack2<T16>(w[4], w[5]); q[g].w = pack2<T16>(w[6], w[7]);
         }
+#pragma unroll
+        for (int g = 0; g < 4; g++) if ((uint32_t)g < pieces) *reinterpret_cast<uint4 *>(stg + lane * STG_PITCH + g * 16) = q[g];
+        __syncwarp();
+        T16 *plane = reinterpret_cast<T16 *>(p.out16) + (uint64_t)part * p.o_plane;
+#pragma unroll
+        for (int pass = 0; pass < 4; pass++) {
+            const uint32_t rr = pass * 8 + (lane >> 2), piece = lane & 3u;
+            const uint32_t row = row0 + rr, col = col0 + piece * 8;
+            if (piece < pieces && row < p.M && col < p.ldo16)
+                *reinterpret_cast<uint4 *>(plane + (uint64_t)row * p.ldo16 + col) = *reinterpret_cast<const uint4 *>(stg + rr * STG_PITCH + piece * 16);
+        }
+        __syncwarp();
     }
 }
 
@@ -232,8 +252,11 @@ __device__ __forceinline__ void write16(const GemmParams &p, uint32_t row, uint3
 // chunks of 32 (two tcgen05.ld in flight per wait).
 template <int ACT>
 __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
-                                              volatile int *abort_flag, uint32_t warp, uint32_t lane)
+                                              volatile int *abort_flag, uint32_t warp, uint32_t lane, uint8_t *stage,
+                                              const CUtensorMap *map_o)
 {
+    uint8_t *stg = stage + (warp - 2u) * PATCH_BYTES;          // 1024-byte aligned: a swizzle atom is 8 rows x 128 bytes
+    const uint32_t stg_addr = smem_u32(stg);
     const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
     const uint32_t total_tiles = p.m_tiles * p.n_tiles;
     const uint32_t span = p.BN >= 32 ? p.BN / 2 : p.BN;            // columns per warp
@@ -259,18 +282,52 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
                 tmem_ld16(taddr + c0, r0);
                 if (second) tmem_ld16(taddr + c0 + 16, r1);
                 tmem_ld_wait();
-                float v[16];
+                float v[16], v2[16];
                 finish16<ACT>(p, r0, n0 + c0, vec_bias && n0 + c0 + 16 <= p.N, v);
-                if (row_ok) write16(p, row, n0 + c0, v);
-                if (second) {
-                    finish16<ACT>(p, r1, n0 + c0 + 16, vec_bias && n0 + c0 + 32 <= p.N, v);
-                    if (row_ok) write16(p, row, n0 + c0 + 16, v);
+                if (second) finish16<ACT>(p, r1, n0 + c0 + 16, vec_bias && n0 + c0 + 32 <= p.N, v2);
+                if (p.tma_store) {
+                    // Two 32-column chunks fill one 64-column patch: 128-byte rows in the swizzled order the tensor
+                    // map expects, then one bulk store moves the patch (rows and columns outside C are clipped).
+                    const uint32_t h32 = ((c0 - c_begin) >> 5) & 1u;
+                    if (h32 == 0) { if (lane == 0) tma_store_wait_read(); __syncwarp(); }     // the store before has read the patch
+                    if (!second) {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v2[i] = 0.0f;
+                    }
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        const float *w = g < 2 ? v + 8 * g : v2 + 8 * (g - 2);
+                        uint4 qv;
+                        if (p.type16 == SPGK_T_F16) {
+                            qv.x = pack2<__half>(w[0], w[1]); qv.y = pack2<__half>(w[2], w[3]);
+                            qv.z = pack2<__half>(w[4], w[5]); qv.w = pack2<__half>(w[6], w[7]);
+                        } else {
+                            qv.x = pack2<__nv_bfloat16>(w[0], w[1]); qv.y = pack2<__nv_bfloat16>(w[2], w[3]);
+                            qv.z = pack2<__nv_bfloat16>(w[4], w[5]); qv.w = pack2<__nv_bfloat16>(w[6], w[7]);
+                        }
+                        const uint32_t chunk = (h32 * 4u + g) ^ (lane & 7u);
+                        *reinterpret_cast<uint4 *>(stg + lane * 128u + chunk * 16u) = qv;
+                    }
+                    const bool patch_done = h32 == 1 || c0 + 32 >= c_begin + span || n0 + c0 + 32 >= p.N;
+                    if (patch_done) {
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) tma_store_3d(map_o, stg_addr, (int)(n0 + c0 - 32u * h32), (int)(mt * BM + q * 32u), 0);
+                    }
+                } else if (p.out16) {
+                    if (p.type16 == SPGK_T_F16) store_patch<__half>(p, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
+                    else store_patch<__nv_bfloat16>(p, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
+                }
+                if (p.out32 && row_ok) {
+                    write32(p, row, n0 + c0, v);
+                    if (second) write32(p, row, n0 + c0 + 16, v2);
                 }
             }
         }
         tc_fence_before();
         mbar_arrive(tempty0 + 8 * acc);                            // every epilogue thread hands the accumulator back
     }
+    if (p.tma_store && lane == 0) tma_store_wait_all();            // shared memory must outlive the last bulk store
 }
 
 // Fused row softmax (reference Activation.c:5-21): the whole row (N <= BN) sits in one TMEM lane, so
@@ -328,7 +385,8 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p_in)
+spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                   const __grid_constant__ CUtensorMap map_o, const GemmParams p_in)
 {
     // rows may be limited by a count that only exists on the device (every role derives the same tile list from it)
     GemmParams p = p_in;
@@ -344,13 +402,15 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     const uint32_t b_tile_bytes = p.BN * BK * 2;
     const uint32_t a_off = 0, b_off = p.stages * A_TILE_BYTES;
-    const uint32_t bar_off = b_off + p.stages * b_tile_bytes;
+    const uint32_t stg_off = b_off + p.stages * b_tile_bytes;        // epilogue patches, 1024-byte aligned like the tiles
+    const uint32_t bar_off = stg_off + STG_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + bar_off);
     // barrier table: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
     const uint32_t full0 = base + bar_off, empty0 = full0 + 8 * p.stages;
     const uint32_t tfull0 = empty0 + 8 * p.stages, tempty0 = tfull0 + 16;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    uint8_t *stage = smem + stg_off;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t tmem_cols = 2 * p.BN < 32 ? 32 : 2 * p.BN;       // power of two: BN in {16,32,64,128,256}
@@ -427,12 +487,12 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // The activation is resolved once, outside every loop, so the per-element code is branch-free.
         switch (p.softmax ? -1 : p.act) {
             case -1:               epilogue_softmax(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
-            case SPG_ACT_RELU:     epilogue_loop<SPG_ACT_RELU>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
-            case SPG_ACT_LEAKY:    epilogue_loop<SPG_ACT_LEAKY>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
-            case SPG_ACT_FOO52:    epilogue_loop<SPG_ACT_FOO52>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
-            case SPG_ACT_TANH:     epilogue_loop<SPG_ACT_TANH>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
-            case SPG_ACT_SIGMOID:  epilogue_loop<SPG_ACT_SIGMOID>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
-            default:               epilogue_loop<SPG_ACT_NONE>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case SPG_ACT_RELU:     epilogue_loop<SPG_ACT_RELU>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
+            case SPG_ACT_LEAKY:    epilogue_loop<SPG_ACT_LEAKY>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
+            case SPG_ACT_FOO52:    epilogue_loop<SPG_ACT_FOO52>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
+            case SPG_ACT_TANH:     epilogue_loop<SPG_ACT_TANH>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
+            case SPG_ACT_SIGMOID:  epilogue_loop<SPG_ACT_SIGMOID>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
+            default:               epilogue_loop<SPG_ACT_NONE>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
         }
     }
 
@@ -595,7 +655,7 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     if (a_parts > 1) { p.pass_a[p.npass] = 1; p.pass_w[p.npass] = 0; p.npass++; }
     if (w_parts > 1) { p.pass_a[p.npass] = 0; p.pass_w[p.npass] = 1; p.npass++; }
     const uint32_t stage_bytes = A_TILE_BYTES + p.BN * BK * 2;
-    const size_t fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 4) + 64;
+    const size_t fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 4) + 64 + STG_BYTES;
     uint32_t stages = (uint32_t)((smem_max - fixed) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) { spgk_set_error("spgk_layer_gemm_tc", "not enough shared memory"); return SPGK_E_UNSUPPORTED; }
@@ -619,10 +679,17 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     rc = make_map(&map_w, w16, w_type16, L->in, L->out, ldw, w_plane, w_parts, p.BN);
     if (rc) return rc;
 
+    // 16-bit output through TMA stores when it is one plane and the tiles are wide enough for 64-column patches
+    CUtensorMap map_o = map_a;
+    p.tma_store = (out16 && out_parts == 1 && p.BN >= 128 && !softmax_fused) ? 1 : 0;
+    if (p.tma_store) {
+        rc = make_map(&map_o, out16, type16, ldo16, N, ldo16, o_plane, 1, 32);
+        if (rc) return rc;
+    }
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
-    const size_t smem = 1024 + (size_t)stages * stage_bytes + 8 * (2 * stages + 4) + 64;
-    spg_gemm_tc_kernel<<<grid, NUM_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_w, p);
+    const size_t smem = 1024 + (size_t)stages * stage_bytes + STG_BYTES + 8 * (2 * stages + 4) + 64;
+    spg_gemm_tc_kernel<<<grid, NUM_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_w, map_o, p);
     return spgk_check_launch("spg_gemm_tc_kernel");
 }
 
