@@ -102,12 +102,18 @@ SPGK_API int spgk_softmax_rows(float *y, uint32_t ldy, uint32_t N, uint32_t widt
  * space; spgk_scatter_rows writes recomputed rows back: dst[idx[i]] = src[i].
  * (No reference counterpart: they let the fast one-term tensor-core pass be followed
  * by an exact recomputation of just the rows whose argmax it could have changed.) */
-/* Row counts that exist only on the device.  After spgk_set_dynamic_rows(ptr) the row-wise calls made by
+/* Row counts that exist only on the device.  After spgk_set_dynamic_rows(ptr, expected) the row-wise calls made by
  * this thread -- spgk_split16, spgk_gather_rows, spgk_scatter_rows, spgk_softmax_rows, spgk_layer_gemm_tc --
  * treat their row argument as a capacity and work on min(rows, *ptr) rows, *ptr being read by the kernels
  * when they run, so a selection made on the device (spgk_margin_select) can be followed up without a host
- * round trip.  NULL switches it off.  (No reference counterpart.) */
-SPGK_API void spgk_set_dynamic_rows(const uint32_t *rows_dev);
+ * round trip.  `expected` is the caller's guess of the count (0 = none); it only steers tile shapes.  NULL
+ * switches it off.  (No reference counterpart.) */
+SPGK_API void spgk_set_dynamic_rows(const uint32_t *rows_dev, uint32_t expected);
+/* After spgk_set_margin_sink(theta, idx, count) the next spgk_layer_gemm_tc calls of this thread that finish a
+ * softmax row in their epilogue (softmax_fused = 1) do the work of spgk_margin_select on the way: rows whose two
+ * largest logits are within theta are appended to idx and counted in *count (which the caller zeroes).
+ * idx == NULL switches it off. */
+SPGK_API void spgk_set_margin_sink(float theta, uint32_t *idx, uint32_t *count);
 SPGK_API int spgk_margin_select(const float *probs, uint32_t ldp, uint32_t N, uint32_t width, float theta,
                                 uint32_t *idx, uint32_t *count, void *stream);
 /* max over rows of the change in the top-two log gap between a fast and an exact result (float bits in *max_bits,

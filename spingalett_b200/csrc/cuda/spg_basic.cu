@@ -304,10 +304,18 @@ spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32
 }
 
 thread_local const uint32_t *spg_tls_rows_limit = nullptr;
+thread_local uint32_t spg_tls_rows_expected = 0;
+thread_local float spg_tls_margin_theta = 0.0f;
+thread_local uint32_t *spg_tls_margin_idx = nullptr, *spg_tls_margin_count = nullptr;
 
 extern "C" {
 
-void spgk_set_dynamic_rows(const uint32_t *rows_dev) { spg_tls_rows_limit = rows_dev; }
+void spgk_set_dynamic_rows(const uint32_t *rows_dev, uint32_t expected) { spg_tls_rows_limit = rows_dev; spg_tls_rows_expected = rows_dev ? expected : 0; }
+void spgk_set_margin_sink(float theta, uint32_t *idx, uint32_t *count)
+{
+    spg_tls_margin_theta = theta; spg_tls_margin_idx = idx; spg_tls_margin_count = idx ? count : nullptr;
+    if (!count) spg_tls_margin_idx = nullptr;
+}
 
 int spgk_layer_simt(const spgk_layer *L, const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N, void *stream)
 {

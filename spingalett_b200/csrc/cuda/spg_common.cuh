@@ -108,6 +108,10 @@ __device__ __forceinline__ float spg_warp_max(float v)
 // Device-resident row count set by spgk_set_dynamic_rows for the calling thread (NULL = off): the row-wise
 // kernels launched afterwards process min(rows argument, *limit) rows, the limit being read on the device.
 extern thread_local const uint32_t *spg_tls_rows_limit;
+extern thread_local uint32_t spg_tls_rows_expected;      // the caller's estimate of *limit (0 = none)
+// margin sink set by spgk_set_margin_sink for the calling thread (idx == NULL: off)
+extern thread_local float spg_tls_margin_theta;
+extern thread_local uint32_t *spg_tls_margin_idx, *spg_tls_margin_count;
 __device__ __forceinline__ uint32_t spg_limit_rows(uint32_t rows, const uint32_t *limit)
 {
     if (!limit) return rows;

@@ -52,6 +52,7 @@ struct GemmParams {
     void *out16; uint32_t ldo16; uint64_t o_plane; int out_parts; int type16;
     float *out32; uint32_t ldo32;
     int32_t *status;
+    float margin_theta; uint32_t *margin_idx, *margin_count;   // fused-softmax rows with top-two logit gap < theta are appended here (optional)
     int tma_store;                // 16-bit output leaves through TMA stores (one plane, tiles at least 128 wide)
     const uint32_t *m_limit;      // optional device-resident row count: the kernel works on min(M, *m_limit) rows
 };
@@ -348,15 +349,20 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
         if (half == 0) {
             const uint32_t row = mt * BM + q * 32u + lane;
             const uint32_t taddr = tmem_base + acc * p.BN + ((q * 32u) << 16);
-            float mx = -FLT_MAX, sum = 0.0f;
+            float mx = -FLT_MAX, second = -FLT_MAX, sum = 0.0f;
             for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; i++)
-                    if (c0 + i < p.N) { const float v = fmaf(__uint_as_float(r[i]), p.scale, p.bias[c0 + i]); if (v > mx) mx = v; }
+                    if (c0 + i < p.N) {
+                        const float v = fmaf(__uint_as_float(r[i]), p.scale, p.bias[c0 + i]);
+                        if (v > mx) { second = mx; mx = v; } else if (v > second) second = v;
+                    }
             }
+            // log p1 - log p2 of the softmax equals the gap of the two largest logits
+            if (p.margin_idx && row < p.M && p.N >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
             for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
@@ -647,7 +653,13 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     }
     GemmParams p{};
     p.M = N; p.N = L->out; p.K = L->in;
-    p.BN = softmax_fused ? pick_bn(L->out) : pick_bn(L->out);
+    p.BN = pick_bn(L->out);
+    // a device-resident row count usually means a small selection of a large batch: when the caller's estimate of
+    // it gives fewer tiles than SMs, narrower tiles spread the work (at the price of re-reading the rows more often)
+    if (spg_tls_rows_limit && spg_tls_rows_expected && !softmax_fused) {
+        const uint32_t mt = (spg_tls_rows_expected + BM - 1) / BM;
+        while (p.BN > 64 && mt * ((L->out + p.BN - 1) / p.BN) < (uint32_t)sm_count) p.BN >>= 1;
+    }
     p.kblocks = (L->in + BK - 1) / BK;
     // passes: hi*hi first, then the correction terms (lo*hi, hi*lo); lo*lo is below fp32 resolution
     p.npass = 0;
@@ -672,6 +684,7 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     p.out32 = out32; p.ldo32 = ldo32;
     p.status = status;
     p.m_limit = spg_tls_rows_limit;
+    if (softmax_fused && spg_tls_margin_idx) { p.margin_theta = spg_tls_margin_theta; p.margin_idx = spg_tls_margin_idx; p.margin_count = spg_tls_margin_count; }
 
     CUtensorMap map_a, map_w;
     int rc = make_map(&map_a, a16, type16, L->in, N, lda, a_plane, a_parts, BM);

@@ -90,7 +90,7 @@ void spg_dev_release(spg_net *n)
     n->act16_bytes = 0; n->act32_bytes = 0;
     spgk_free(n->d_status); n->d_status = NULL;
     spgk_free(n->d_w16); n->d_w16 = NULL; n->w16_bytes = 0;
-    spgk_host_free(n->h_count); n->h_count = NULL; n->count_pending = false;
+    spgk_host_free(n->h_count); n->h_count = NULL; n->count_pending = false; n->count_seen = false;
     for (int t = 0; t < 2; t++) {
         if (n->d_w16c[t]) for (uint32_t l = 0; l < n->dev_layers; l++) spgk_free(n->d_w16c[t][l]);
         free(n->d_w16c[t]); n->d_w16c[t] = NULL;
@@ -517,12 +517,23 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     if (mode != SPINGALETT_MATH_AUTO) return large_chain(n, d_x, N, d_out, mode == SPINGALETT_MATH_EXACT);
     if (!softmax_out) return large_chain(n, d_x, N, d_out, true);
 
-    int rc = large_chain(n, d_x, N, d_out, false);
-    if (rc) return rc;
-    if (strcmp(spingalett_last_path(), "tcgen05") != 0) return SPINGALETT_OK;      /* the fp32 chain ran: nothing to repair */
+    int rc;
     if ((rc = reserve((void **)&n->d_rep_idx, &n->rep_idx_bytes, (size_t)N * 4 + 256, "repair index"))) return rc;
     uint32_t *d_count = n->d_rep_idx + N;
     float theta = spingalett_get_auto_margin();
+    if (theta <= 0.0f && n->auto_calibrated) theta = n->auto_theta;
+    /* with the margin known in advance, the softmax epilogue of the last layer picks the rows out itself */
+    const spgk_layer *Llast = &n->klayers[n->dev_layers - 1];
+    const bool sink = theta > 0.0f && Llast->out <= spgk_gemm_tc_softmax_max();
+    if (sink) {
+        if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
+        spgk_set_margin_sink(theta, n->d_rep_idx, d_count);
+    }
+    rc = large_chain(n, d_x, N, d_out, false);
+    spgk_set_margin_sink(0.0f, NULL, NULL);
+    if (rc) return rc;
+    if (strcmp(spingalett_last_path(), "tcgen05") != 0) return SPINGALETT_OK;      /* the fp32 chain ran: nothing to repair */
+    theta = spingalett_get_auto_margin();
     if (theta <= 0.0f) {
         /* Self-calibration, once per device image of the net: run both modes on up to 2048 rows, measure the
          * largest change of the top-two log gap the one-term pass causes, and use four times that as margin. */
@@ -541,8 +552,10 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
         }
         theta = n->auto_theta;
     }
-    if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
-    if ((rc = spg_map_kernel_error(spgk_margin_select(d_out, outw, N, outw, theta, n->d_rep_idx, d_count, n->stream), "margin check"))) return rc;
+    if (!sink) {
+        if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
+        if ((rc = spg_map_kernel_error(spgk_margin_select(d_out, outw, N, outw, theta, n->d_rep_idx, d_count, n->stream), "margin check"))) return rc;
+    }
     /* The row count stays on the device: the gather, the exact chain and the scatter below are launched for
      * N rows of capacity and read the count when they run, so the call needs no host round trip.  A copy
      * travels to pinned host memory for spingalett_last_repaired(). */
@@ -551,15 +564,16 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
         if ((rc = spg_map_kernel_error(spgk_host_alloc(&h, 64), "repair count (host)"))) return rc;
         n->h_count = h;
     }
+    const uint32_t expected = n->count_seen ? *(volatile uint32_t *)n->h_count : 0;    /* the count of the call before: a guide to tile shapes only */
     if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(n->h_count, d_count, 4, n->stream), "repair count"))) return rc;
-    n->count_pending = true;
+    n->count_pending = true; n->count_seen = true;
     if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
     if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)N * outw * 4, "repair outputs"))) return rc;
-    spgk_set_dynamic_rows(d_count);
+    spgk_set_dynamic_rows(d_count, expected);
     rc = spg_map_kernel_error(spgk_gather_rows(d_x, n->d_rep_idx, n->d_rep_in, N, in0, n->stream), "repair gather");
     if (!rc) rc = large_chain(n, n->d_rep_in, N, n->d_rep_out, true);
     if (!rc) rc = spg_map_kernel_error(spgk_scatter_rows(n->d_rep_out, n->d_rep_idx, d_out, N, outw, outw, n->stream), "repair scatter");
-    spgk_set_dynamic_rows(NULL);
+    spgk_set_dynamic_rows(NULL, 0);
     if (rc) return rc;
     spg_note_path("tcgen05");
     return SPINGALETT_OK;

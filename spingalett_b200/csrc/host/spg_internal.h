@@ -52,7 +52,7 @@ typedef struct {
     /* AUTO math mode: rows recomputed exactly after the one-term pass */
     uint32_t *d_rep_idx; size_t rep_idx_bytes; float *d_rep_in; size_t rep_in_bytes; float *d_rep_out; size_t rep_out_bytes;
     uint32_t last_repaired; bool auto_calibrated; float auto_theta;
-    uint32_t *h_count; bool count_pending;      /* pinned copy of the repaired-row count of the last AUTO call */
+    uint32_t *h_count; bool count_pending, count_seen;      /* pinned copy of the repaired-row count of the last AUTO call */
 
     /* large-batch workspace */
     float *d_in32;  size_t in32_bytes;      /* staging for host inputs */
