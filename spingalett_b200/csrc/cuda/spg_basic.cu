@@ -253,6 +253,8 @@ __global__ void __launch_bounds__(256)
 spg_scatter_rows_kernel(const float *__restrict__ src, const uint32_t *__restrict__ idx, float *__restrict__ dst,
                         uint32_t rows, uint32_t width, uint32_t ldd, const uint32_t *__restrict__ limit)
 {
+    spg_grid_trigger();
+    spg_grid_wait();
     rows = spg_limit_rows(rows, limit);
     const uint64_t total = (uint64_t)rows * width;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -278,6 +280,8 @@ __global__ void __launch_bounds__(256)
 spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t in,
                    T16 *__restrict__ dst, uint32_t ld16, uint64_t plane_elems, int parts, const uint32_t *__restrict__ limit)
 {
+    spg_grid_trigger();
+    spg_grid_wait();
     N = spg_limit_rows(N, limit);
     const uint32_t chunks = ld16 >> 3;
     const uint64_t total = (uint64_t)N * chunks;
@@ -382,7 +386,7 @@ int spgk_scatter_rows(const float *src, const uint32_t *idx, float *dst, uint32_
     if (rows == 0 || width == 0) return SPGK_OK;
     uint64_t total = (uint64_t)rows * width;
     uint32_t blocks = (uint32_t)((total + 255) / 256 < 148ull * 8 ? (total + 255) / 256 : 148ull * 8);
-    spg_scatter_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(src, idx, dst, rows, width, ldd, spg_tls_rows_limit);
+    SPGK_CUDA(spg_launch_chained(spg_scatter_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, src, idx, dst, rows, width, ldd, spg_tls_rows_limit));
     return spgk_check_launch("spg_scatter_rows_kernel");
 }
 
@@ -397,11 +401,11 @@ int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in, void *ds
     const bool vec = ((uintptr_t)x & 15u) == 0 && (ldx & 3u) == 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (type == SPGK_T_F16) {
-        if (vec) spg_split16_kernel<__half, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
-        else spg_split16_kernel<__half, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
+        if (vec) SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__half, true>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
+        else SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__half, false>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
     } else {
-        if (vec) spg_split16_kernel<__nv_bfloat16, true><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
-        else spg_split16_kernel<__nv_bfloat16, false><<<blocks, 256, 0, st>>>(x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit);
+        if (vec) SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__nv_bfloat16, true>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
+        else SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
     }
     return spgk_check_launch("spg_split16_kernel");
 }

@@ -119,3 +119,21 @@ __device__ __forceinline__ uint32_t spg_limit_rows(uint32_t rows, const uint32_t
     return v < rows ? v : rows;
 }
 
+// Programmatic dependent launch.  A kernel started through spg_launch_chained may be scheduled while the kernel
+// before it in the stream is still draining; it must call spg_grid_wait() before it reads or writes anything
+// that an earlier kernel of the stream touches, and spg_grid_trigger() lets the kernel behind it do the same.
+__device__ __forceinline__ void spg_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void spg_grid_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t spg_launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+

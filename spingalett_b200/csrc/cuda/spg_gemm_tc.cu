@@ -394,12 +394,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_o, const GemmParams p_in)
 {
-    // rows may be limited by a count that only exists on the device (every role derives the same tile list from it)
     GemmParams p = p_in;
-    if (p_in.m_limit) {
-        const uint32_t m = *p_in.m_limit;
-        if (m < p.M) { p.M = m; p.m_tiles = (m + BM - 1) / BM; if (p.m_tiles && p.group_m > p.m_tiles) p.group_m = p.m_tiles; }
-    }
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment of the operand tiles (required by the 128-byte swizzle atoms)
     const uint32_t raw = smem_u32(smem_raw);
@@ -437,6 +432,15 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this CTA's shared and tensor memory, so it may overlap the tail of the kernel
+    // before this one in the stream; from here on its results are needed.
+    spg_grid_trigger();
+    spg_grid_wait();
+    // rows may be limited by a count that only exists on the device (every role derives the same tile list from it)
+    if (p_in.m_limit) {
+        const uint32_t m = *p_in.m_limit;
+        if (m < p.M) { p.M = m; p.m_tiles = (m + BM - 1) / BM; if (p.m_tiles && p.group_m > p.m_tiles) p.group_m = p.m_tiles; }
+    }
 
     const uint32_t total_tiles = p.m_tiles * p.n_tiles;
     const uint32_t iters_per_tile = p.npass * p.kblocks;
@@ -702,7 +706,7 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
     const size_t smem = 1024 + (size_t)stages * stage_bytes + STG_BYTES + 8 * (2 * stages + 4) + 64;
-    spg_gemm_tc_kernel<<<grid, NUM_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_w, map_o, p);
+    SPGK_CUDA(spg_launch_chained(spg_gemm_tc_kernel, dim3(grid), dim3(NUM_THREADS), smem, (cudaStream_t)stream, map_a, map_w, map_o, p));
     return spgk_check_launch("spg_gemm_tc_kernel");
 }
 

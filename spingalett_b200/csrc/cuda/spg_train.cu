@@ -138,6 +138,8 @@ __global__ void __launch_bounds__(256)
 spg_gather_rows_kernel(const float *__restrict__ src, const uint32_t *__restrict__ idx, float *__restrict__ dst,
                        uint32_t rows, uint32_t width, const uint32_t *__restrict__ limit)
 {
+    spg_grid_trigger();
+    spg_grid_wait();
     rows = spg_limit_rows(rows, limit);
     const uint64_t total = (uint64_t)rows * width;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -254,7 +256,7 @@ int spgk_gather_rows(const float *src, const uint32_t *idx, float *dst, uint32_t
 {
     if (!src || !idx || !dst) { spgk_set_error("spgk_gather_rows", "bad argument"); return SPGK_E_ARG; }
     if (rows == 0 || width == 0) return SPGK_OK;
-    spg_gather_rows_kernel<<<blocks_for((uint64_t)rows * width), 256, 0, (cudaStream_t)stream>>>(src, idx, dst, rows, width, spg_tls_rows_limit);
+    SPGK_CUDA(spg_launch_chained(spg_gather_rows_kernel, dim3(blocks_for((uint64_t)rows * width)), dim3(256), 0, (cudaStream_t)stream, src, idx, dst, rows, width, spg_tls_rows_limit));
     return spgk_check_launch("spg_gather_rows_kernel");
 }
 
