@@ -114,6 +114,8 @@ SPGK_API void spgk_set_dynamic_rows(const uint32_t *rows_dev, uint32_t expected)
  * largest logits are within theta are appended to idx and counted in *count (which the caller zeroes).
  * idx == NULL switches it off. */
 SPGK_API void spgk_set_margin_sink(float theta, uint32_t *idx, uint32_t *count);
+/* a batch walked in row chunks: the sink records row + row0 */
+SPGK_API void spgk_set_margin_row_base(uint32_t row0);
 SPGK_API int spgk_margin_select(const float *probs, uint32_t ldp, uint32_t N, uint32_t width, float theta,
                                 uint32_t *idx, uint32_t *count, void *stream);
 /* max over rows of the change in the top-two log gap between a fast and an exact result (float bits in *max_bits,
@@ -232,6 +234,21 @@ SPGK_API int spgk_layer_gemm_tc(const spgk_layer *L,
                                 void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
                                 float *out32, uint32_t ldo32,
                                 uint32_t N, int softmax_fused, int32_t *status, void *stream);
+/* The same layer with the network's narrow last layer ("head", at most 16 outputs) finished in its epilogue:
+ * each epilogue thread keeps the head's dot products of its row in registers (fp32 FMAs against head weights
+ * staged in shared memory) while it walks the row's column tiles, so the wide activation matrix is never
+ * written and the head needs no kernel of its own.  out32 [N][head->out] receives head_act(bias_h + scale_h *
+ * Wh * act(...)), a softmax head included (and the margin sink, if set, is served).  head_w comes from
+ * spgk_head_weights (spgk_head_weights_bytes bytes; it depends only on the head's weights and can be kept).
+ * Replaces the last two iterations of the layer loop of batch_forward (Training.c:327-343). */
+SPGK_API int spgk_gemm_tc_head_supported(const spgk_layer *L, const spgk_layer *head);
+SPGK_API size_t spgk_head_weights_bytes(const spgk_layer *head);
+SPGK_API int spgk_head_weights(const spgk_layer *head, float *dst, void *stream);
+SPGK_API int spgk_layer_gemm_tc_head(const spgk_layer *L,
+                                     const void *w16, uint32_t ldw, uint64_t w_plane, int w_parts, int w_type16,
+                                     const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
+                                     const spgk_layer *head, const float *head_w, float *out32, uint32_t ldo32,
+                                     uint32_t N, int32_t *status, void *stream);
 SPGK_API int spgk_gemm_tc_status(int32_t *status, void *stream);
 
 /* ---- training step (fp32, as the reference) -------------------------------

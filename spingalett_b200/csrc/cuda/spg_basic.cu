@@ -311,10 +311,12 @@ thread_local const uint32_t *spg_tls_rows_limit = nullptr;
 thread_local uint32_t spg_tls_rows_expected = 0;
 thread_local float spg_tls_margin_theta = 0.0f;
 thread_local uint32_t *spg_tls_margin_idx = nullptr, *spg_tls_margin_count = nullptr;
+thread_local uint32_t spg_tls_margin_row0 = 0;
 
 extern "C" {
 
 void spgk_set_dynamic_rows(const uint32_t *rows_dev, uint32_t expected) { spg_tls_rows_limit = rows_dev; spg_tls_rows_expected = rows_dev ? expected : 0; }
+void spgk_set_margin_row_base(uint32_t row0) { spg_tls_margin_row0 = row0; }
 void spgk_set_margin_sink(float theta, uint32_t *idx, uint32_t *count)
 {
     spg_tls_margin_theta = theta; spg_tls_margin_idx = idx; spg_tls_margin_count = idx ? count : nullptr;

@@ -52,7 +52,11 @@ struct GemmParams {
     void *out16; uint32_t ldo16; uint64_t o_plane; int out_parts; int type16;
     float *out32; uint32_t ldo32;
     int32_t *status;
-    float margin_theta; uint32_t *margin_idx, *margin_count;   // fused-softmax rows with top-two logit gap < theta are appended here (optional)
+    // optional narrow last layer ("head") finished inside this layer's epilogue: out = head_act(head_bias + head_scale * Wh * act(...))
+    const float *head_w;          // [round_up(N, 32)][HP] fp32, unscaled, rows beyond N zero (staged into shared memory)
+    const float *head_bias; float head_scale; uint32_t head_out, head_hp; int head_act, head_softmax;
+    uint32_t stg_bytes;           // bytes of the epilogue's shared-memory region (patches, or head weights + exchange)
+    float margin_theta; uint32_t *margin_idx, *margin_count, margin_row0;   // fused-softmax rows with top-two logit gap < theta are appended here (optional)
     int tma_store;                // 16-bit output leaves through TMA stores (one plane, tiles at least 128 wide)
     const uint32_t *m_limit;      // optional device-resident row count: the kernel works on min(M, *m_limit) rows
 };
@@ -150,6 +154,24 @@ __device__ __forceinline__ void tile_coords(const GemmParams &p, uint32_t t, uin
     const uint32_t rows_here = min(p.group_m, p.m_tiles - g * p.group_m);
     m_tile = g * p.group_m + r % rows_here;
     n_tile = r / rows_here;
+}
+
+
+// The tiles of this CTA, in order.  Normally tile blockIdx.x + i * gridDim.x of the banded walk; with a fused head
+// a CTA owns whole row tiles (all their column tiles in a row), because the head sums over every column of a row.
+__device__ __forceinline__ uint32_t my_tile_count(const GemmParams &p)
+{
+    if (p.head_w) {
+        const uint32_t rt = p.m_tiles > blockIdx.x ? (p.m_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        return rt * p.n_tiles;
+    }
+    const uint32_t total = p.m_tiles * p.n_tiles;
+    return total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+}
+__device__ __forceinline__ void my_tile(const GemmParams &p, uint32_t i, uint32_t &m_tile, uint32_t &n_tile)
+{
+    if (p.head_w) { m_tile = blockIdx.x + (i / p.n_tiles) * gridDim.x; n_tile = i % p.n_tiles; }
+    else tile_coords(p, blockIdx.x + i * gridDim.x, m_tile, n_tile);
 }
 
 template <typename T16> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -251,28 +273,34 @@ __device__ __forceinline__ void store_patch(const GemmParams &p, uint8_t *stg, u
 // Epilogue role.  Warp w reads TMEM lanes 32*(w%4).. (its quadrant) and, of the tile's BN columns,
 // the half selected by (w-2)/4; each thread therefore owns one row of C and walks its columns in
 // chunks of 32 (two tcgen05.ld in flight per wait).
-template <int ACT>
+template <int ACT, int HP>
 __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
                                               volatile int *abort_flag, uint32_t warp, uint32_t lane, uint8_t *stage,
-                                              const CUtensorMap *map_o)
+                                              const CUtensorMap *map_o, uint32_t hx0)
 {
     uint8_t *stg = stage + (warp - 2u) * PATCH_BYTES;          // 1024-byte aligned: a swizzle atom is 8 rows x 128 bytes
     const uint32_t stg_addr = smem_u32(stg);
     const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    const uint32_t ntile = my_tile_count(p);
     const uint32_t span = p.BN >= 32 ? p.BN / 2 : p.BN;            // columns per warp
     const uint32_t c_begin = p.BN >= 32 ? half * span : 0;
     const bool idle = p.BN < 32 && half == 1;                      // a 16-wide tile has work for one warp per quadrant
     const bool vec_bias = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
-    uint32_t tcount = 0;
-    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, tcount++) {
+    float hacc[HP > 0 ? HP : 1];
+    const float *headw = reinterpret_cast<const float *>(stage);               // head mode: the staged head weights
+    float *xch = reinterpret_cast<float *>(stage + p.stg_bytes - 4 * 2 * 32 * 16 * 4) ;   // head mode: [parity][quadrant][lane][16] exchange
+    for (uint32_t tcount = 0; tcount < ntile; tcount++) {
         uint32_t mt, nt;
-        tile_coords(p, t, mt, nt);
+        my_tile(p, tcount, mt, nt);
         const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
         if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, p.status, 4)) break;
         tc_fence_after();
         const uint32_t row = mt * BM + q * 32u + lane;
         const uint32_t n0 = nt * p.BN;
+        if (HP > 0 && nt == 0) {
+#pragma unroll
+            for (int j = 0; j < (HP > 0 ? HP : 1); j++) hacc[j] = 0.0f;
+        }
         const uint32_t taddr = tmem_base + acc * p.BN + ((q * 32u) << 16);
         const bool row_ok = row < p.M;
         if (!idle) {
@@ -286,7 +314,30 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
                 float v[16], v2[16];
                 finish16<ACT>(p, r0, n0 + c0, vec_bias && n0 + c0 + 16 <= p.N, v);
                 if (second) finish16<ACT>(p, r1, n0 + c0 + 16, vec_bias && n0 + c0 + 32 <= p.N, v2);
-                if (p.tma_store) {
+                if (HP > 0) {
+                    // the head's partial dot products over these columns (its weights beyond N are zero in shared memory)
+                    const float *hw = headw + (size_t)(n0 + c0) * HP;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+#pragma unroll
+                        for (int j = 0; j < HP; j += 4) {
+                            const float4 w4 = *reinterpret_cast<const float4 *>(hw + i * HP + j);
+                            hacc[j] = fmaf(v[i], w4.x, hacc[j]); hacc[j + 1] = fmaf(v[i], w4.y, hacc[j + 1]);
+                            hacc[j + 2] = fmaf(v[i], w4.z, hacc[j + 2]); hacc[j + 3] = fmaf(v[i], w4.w, hacc[j + 3]);
+                        }
+                    }
+                    if (second) {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+#pragma unroll
+                            for (int j = 0; j < HP; j += 4) {
+                                const float4 w4 = *reinterpret_cast<const float4 *>(hw + (16 + i) * HP + j);
+                                hacc[j] = fmaf(v2[i], w4.x, hacc[j]); hacc[j + 1] = fmaf(v2[i], w4.y, hacc[j + 1]);
+                                hacc[j + 2] = fmaf(v2[i], w4.z, hacc[j + 2]); hacc[j + 3] = fmaf(v2[i], w4.w, hacc[j + 3]);
+                            }
+                        }
+                    }
+                } else if (p.tma_store) {
                     // Two 32-column chunks fill one 64-column patch: 128-byte rows in the swizzled order the tensor
                     // map expects, then one bulk store moves the patch (rows and columns outside C are clipped).
                     const uint32_t h32 = ((c0 - c_begin) >> 5) & 1u;
@@ -319,7 +370,7 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
                     if (p.type16 == SPGK_T_F16) store_patch<__half>(p, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
                     else store_patch<__nv_bfloat16>(p, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
                 }
-                if (p.out32 && row_ok) {
+                if (HP == 0 && p.out32 && row_ok) {
                     write32(p, row, n0 + c0, v);
                     if (second) write32(p, row, n0 + c0 + 16, v2);
                 }
@@ -327,6 +378,42 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
         }
         tc_fence_before();
         mbar_arrive(tempty0 + 8 * acc);                            // every epilogue thread hands the accumulator back
+        if (HP > 0 && nt == p.n_tiles - 1) {
+            // The row is complete: the warp of the upper column half hands its sums to the warp of the lower half
+            // (same rows), which adds bias, applies the head's activation or softmax and writes the outputs.
+            float *slot = xch + ((((tcount / p.n_tiles) & 1u) * 4 + q) * 32 + lane) * 16;
+            if (half == 1) {
+#pragma unroll
+                for (int j = 0; j < HP; j += 4) *reinterpret_cast<float4 *>(slot + j) = make_float4(hacc[j], hacc[j + 1], hacc[j + 2], hacc[j + 3]);
+            }
+            const uint32_t rt = tcount / p.n_tiles;                  // this CTA's row-tile counter: exchange phase and slot parity
+            if (half == 1) mbar_arrive(hx0 + 8 * q);
+            else if (!mbar_wait(hx0 + 8 * q, rt & 1u, abort_flag, p.status, 5)) break;
+            if (half == 0) {
+                float z[HP > 0 ? HP : 1];
+#pragma unroll
+                for (int j = 0; j < HP; j++)
+                    z[j] = (uint32_t)j < p.head_out ? fmaf(hacc[j] + slot[j], p.head_scale, p.head_bias[j]) : -FLT_MAX;
+                if (p.head_softmax) {
+                    float mx = -FLT_MAX, second = -FLT_MAX, sum = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < HP; j++) if ((uint32_t)j < p.head_out) { if (z[j] > mx) { second = mx; mx = z[j]; } else if (z[j] > second) second = z[j]; }
+#pragma unroll
+                    for (int j = 0; j < HP; j++) if ((uint32_t)j < p.head_out) { z[j] = expf(z[j] - mx); sum += z[j]; }
+                    const float inv = sum > 0.0f ? 1.0f / sum : 1.0f;
+#pragma unroll
+                    for (int j = 0; j < HP; j++) z[j] *= inv;
+                    if (p.margin_idx && row < p.M && p.head_out >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row + p.margin_row0;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < HP; j++) z[j] = spg_activate(z[j], p.head_act);
+                }
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < HP; j++) if ((uint32_t)j < p.head_out) p.out32[(uint64_t)row * p.ldo32 + j] = z[j];
+                }
+            }
+        }
     }
     if (p.tma_store && lane == 0) tma_store_wait_all();            // shared memory must outlive the last bulk store
 }
@@ -338,11 +425,10 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
                                                  volatile int *abort_flag, uint32_t warp, uint32_t lane)
 {
     const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
-    uint32_t tcount = 0;
-    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, tcount++) {
+    const uint32_t ntile = my_tile_count(p);
+    for (uint32_t tcount = 0; tcount < ntile; tcount++) {
         uint32_t mt, nt;
-        tile_coords(p, t, mt, nt);
+        my_tile(p, tcount, mt, nt);
         const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
         if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, p.status, 4)) break;
         tc_fence_after();
@@ -362,7 +448,7 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
                     }
             }
             // log p1 - log p2 of the softmax equals the gap of the two largest logits
-            if (p.margin_idx && row < p.M && p.N >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
+            if (p.margin_idx && row < p.M && p.N >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row + p.margin_row0;
             for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
@@ -404,12 +490,12 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const uint32_t b_tile_bytes = p.BN * BK * 2;
     const uint32_t a_off = 0, b_off = p.stages * A_TILE_BYTES;
     const uint32_t stg_off = b_off + p.stages * b_tile_bytes;        // epilogue patches, 1024-byte aligned like the tiles
-    const uint32_t bar_off = stg_off + STG_BYTES;
+    const uint32_t bar_off = stg_off + p.stg_bytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + bar_off);
-    // barrier table: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
+    // barrier table: full[stages], empty[stages], tmem_full[2], tmem_empty[2], head_exchange[4]
     const uint32_t full0 = base + bar_off, empty0 = full0 + 8 * p.stages;
-    const uint32_t tfull0 = empty0 + 8 * p.stages, tempty0 = tfull0 + 16;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
+    const uint32_t tfull0 = empty0 + 8 * p.stages, tempty0 = tfull0 + 16, hx0 = tempty0 + 16;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 8);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     uint8_t *stage = smem + stg_off;
 
@@ -419,6 +505,7 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (uint32_t a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 32 * EPI_WARPS); }
+        for (uint32_t a = 0; a < 4; a++) mbar_init(hx0 + 8 * a, 32);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -442,17 +529,25 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (m < p.M) { p.M = m; p.m_tiles = (m + BM - 1) / BM; if (p.m_tiles && p.group_m > p.m_tiles) p.group_m = p.m_tiles; }
     }
 
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    const uint32_t ntile = my_tile_count(p);
     const uint32_t iters_per_tile = p.npass * p.kblocks;
+    if (p.head_w) {
+        // the head's weights (a few tens of KB) live in shared memory for the whole kernel
+        const uint32_t n4 = ((p.N + 31u) & ~31u) * p.head_hp / 4;
+        const float4 *src = reinterpret_cast<const float4 *>(p.head_w);
+        float4 *dst = reinterpret_cast<float4 *>(stage);
+        for (uint32_t i = threadIdx.x; i < n4; i += NUM_THREADS) dst[i] = src[i];
+        __syncthreads();
+    }
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             uint32_t it = 0;
             bool alive = true;
-            for (uint32_t t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+            for (uint32_t ti = 0; ti < ntile && alive; ti++) {
                 uint32_t mt, nt;
-                tile_coords(p, t, mt, nt);
+                my_tile(p, ti, mt, nt);
                 for (uint32_t ps = 0; ps < p.npass && alive; ps++) {
                     for (uint32_t kb = 0; kb < p.kblocks; kb++, it++) {
                         const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
@@ -470,9 +565,9 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
+            uint32_t it = 0;
             bool alive = true;
-            for (uint32_t t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, tcount++) {
+            for (uint32_t tcount = 0; tcount < ntile && alive; tcount++) {
                 const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1u, abort_flag, p.status, 2)) break;
                 tc_fence_after();
@@ -495,15 +590,21 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else {
         // ------------------------------ epilogue ----------------------------------
         // The activation is resolved once, outside every loop, so the per-element code is branch-free.
+        // The activation (and the width of a fused head) is resolved once, outside every loop.
+#define SPG_EPI(ACTV) \
+        if (p.head_hp == 0) epilogue_loop<ACTV, 0>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0); \
+        else if (p.head_hp == 12) epilogue_loop<ACTV, 12>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0); \
+        else epilogue_loop<ACTV, 16>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0)
         switch (p.softmax ? -1 : p.act) {
             case -1:               epilogue_softmax(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
-            case SPG_ACT_RELU:     epilogue_loop<SPG_ACT_RELU>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
-            case SPG_ACT_LEAKY:    epilogue_loop<SPG_ACT_LEAKY>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
-            case SPG_ACT_FOO52:    epilogue_loop<SPG_ACT_FOO52>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
-            case SPG_ACT_TANH:     epilogue_loop<SPG_ACT_TANH>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
-            case SPG_ACT_SIGMOID:  epilogue_loop<SPG_ACT_SIGMOID>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
-            default:               epilogue_loop<SPG_ACT_NONE>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o); break;
+            case SPG_ACT_RELU:     SPG_EPI(SPG_ACT_RELU); break;
+            case SPG_ACT_LEAKY:    SPG_EPI(SPG_ACT_LEAKY); break;
+            case SPG_ACT_FOO52:    SPG_EPI(SPG_ACT_FOO52); break;
+            case SPG_ACT_TANH:     SPG_EPI(SPG_ACT_TANH); break;
+            case SPG_ACT_SIGMOID:  SPG_EPI(SPG_ACT_SIGMOID); break;
+            default:               SPG_EPI(SPG_ACT_NONE); break;
         }
+#undef SPG_EPI
     }
 
     // ------------------------------ common tail -----------------------------------
@@ -537,6 +638,18 @@ spg_dequant16_kernel(const void *__restrict__ w, int precision, uint32_t in, uin
             dst[(uint64_t)pt * plane + i] = h;
             v -= back;
         }
+    }
+}
+
+// Head weights for the fused narrow last layer: dst[c][j] = q(H.w[j][c]) (unscaled), c < round_up(in, 32), j < hp;
+// entries beyond the layer's real size are zero.
+__global__ void __launch_bounds__(256)
+spg_head_weights_kernel(const void *__restrict__ w, int precision, uint32_t in, uint32_t out, uint32_t hp, uint32_t rows, float *__restrict__ dst)
+{
+    const uint32_t total = rows * hp;
+    for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < total; i += gridDim.x * 256) {
+        const uint32_t c = i / hp, j = i % hp;
+        dst[i] = (c < in && j < out) ? spg_decode_elem(w, (uint64_t)j * in + c, precision) : 0.0f;
     }
 }
 
@@ -631,12 +744,39 @@ int spgk_dequant16(const spgk_layer *L, void *dst, uint32_t ldw, uint64_t plane,
     return spgk_check_launch("spg_dequant16_kernel");
 }
 
-int spgk_layer_gemm_tc(const spgk_layer *L,
+size_t spgk_head_weights_bytes(const spgk_layer *H);
+static uint32_t head_hp(const spgk_layer *H) { return H->out <= 12 ? 12u : 16u; }
+
+int spgk_gemm_tc_head_supported(const spgk_layer *L, const spgk_layer *H)
+{
+    // a head of at most 16 outputs behind a layer of more than one 256-wide column tile whose weights fit shared memory
+    if (!L || !H || H->in != L->out || H->out == 0 || H->out > 16 || L->out <= 256 || L->act == SPG_ACT_SOFTMAX) return 0;
+    if ((unsigned)H->precision >= SPG_P_COUNT || !H->w || !H->bias) return 0;
+    return spgk_head_weights_bytes(H) <= 96u * 1024 ? 1 : 0;
+}
+
+size_t spgk_head_weights_bytes(const spgk_layer *H)
+{
+    return H ? (size_t)((H->in + 31u) & ~31u) * head_hp(H) * sizeof(float) : 0;
+}
+
+int spgk_head_weights(const spgk_layer *H, float *dst, void *stream)
+{
+    if (!H || !dst || !H->w) { spgk_set_error("spgk_head_weights", "bad argument"); return SPGK_E_ARG; }
+    const uint32_t rows = (H->in + 31u) & ~31u, hp = head_hp(H);
+    uint32_t blocks = (rows * hp + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    spg_head_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(H->w, H->precision, H->in, H->out, hp, rows, dst);
+    return spgk_check_launch("spg_head_weights_kernel");
+}
+
+static int gemm_launch(const spgk_layer *L,
                        const void *w16, uint32_t ldw, uint64_t w_plane, int w_parts, int w_type16,
                        const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
                        void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
                        float *out32, uint32_t ldo32,
-                       uint32_t N, int softmax_fused, int32_t *status, void *stream)
+                       uint32_t N, int softmax_fused, int32_t *status, void *stream,
+                       const spgk_layer *head, const float *head_w)
 {
     if (!L || !w16 || !a16 || !L->bias || (!out16 && !out32) || !status || a_parts < 1 || a_parts > 2 || w_parts < 1 || w_parts > 2 ||
         (out16 && (ldo16 & 7u)) || (softmax_fused && (!out32 || L->out > SOFTMAX_FUSE_MAX))) {
@@ -671,7 +811,15 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     if (a_parts > 1) { p.pass_a[p.npass] = 1; p.pass_w[p.npass] = 0; p.npass++; }
     if (w_parts > 1) { p.pass_a[p.npass] = 0; p.pass_w[p.npass] = 1; p.npass++; }
     const uint32_t stage_bytes = A_TILE_BYTES + p.BN * BK * 2;
-    const size_t fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 4) + 64 + STG_BYTES;
+    if (head) {
+        p.head_w = head_w; p.head_bias = head->bias; p.head_scale = head->w_scale; p.head_out = head->out; p.head_hp = head_hp(head);
+        p.head_softmax = head->act == SPG_ACT_SOFTMAX ? 1 : 0;
+        p.head_act = head->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : head->act;
+        p.stg_bytes = (uint32_t)((spgk_head_weights_bytes(head) + 1023) & ~(size_t)1023) + 4 * 2 * 32 * 16 * 4;
+    } else {
+        p.stg_bytes = STG_BYTES;
+    }
+    const size_t fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 8) + 64 + p.stg_bytes;
     uint32_t stages = (uint32_t)((smem_max - fixed) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) { spgk_set_error("spgk_layer_gemm_tc", "not enough shared memory"); return SPGK_E_UNSUPPORTED; }
@@ -688,7 +836,7 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
     p.out32 = out32; p.ldo32 = ldo32;
     p.status = status;
     p.m_limit = spg_tls_rows_limit;
-    if (softmax_fused && spg_tls_margin_idx) { p.margin_theta = spg_tls_margin_theta; p.margin_idx = spg_tls_margin_idx; p.margin_count = spg_tls_margin_count; }
+    if ((softmax_fused || (head && head->act == SPG_ACT_SOFTMAX)) && spg_tls_margin_idx) { p.margin_theta = spg_tls_margin_theta; p.margin_idx = spg_tls_margin_idx; p.margin_count = spg_tls_margin_count; p.margin_row0 = spg_tls_margin_row0; }
 
     CUtensorMap map_a, map_w;
     int rc = make_map(&map_a, a16, type16, L->in, N, lda, a_plane, a_parts, BM);
@@ -698,16 +846,38 @@ int spgk_layer_gemm_tc(const spgk_layer *L,
 
     // 16-bit output through TMA stores when it is one plane and the tiles are wide enough for 64-column patches
     CUtensorMap map_o = map_a;
-    p.tma_store = (out16 && out_parts == 1 && p.BN >= 128 && !softmax_fused) ? 1 : 0;
+    p.tma_store = (out16 && out_parts == 1 && p.BN >= 128 && !softmax_fused && !head) ? 1 : 0;
     if (p.tma_store) {
         rc = make_map(&map_o, out16, type16, ldo16, N, ldo16, o_plane, 1, 32);
         if (rc) return rc;
     }
-    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    const uint32_t tiles = head ? p.m_tiles : p.m_tiles * p.n_tiles;       // with a head a CTA owns whole row tiles
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
-    const size_t smem = 1024 + (size_t)stages * stage_bytes + STG_BYTES + 8 * (2 * stages + 4) + 64;
+    const size_t smem = 1024 + (size_t)stages * stage_bytes + p.stg_bytes + 8 * (2 * stages + 8) + 64;
     SPGK_CUDA(spg_launch_chained(spg_gemm_tc_kernel, dim3(grid), dim3(NUM_THREADS), smem, (cudaStream_t)stream, map_a, map_w, map_o, p));
     return spgk_check_launch("spg_gemm_tc_kernel");
+}
+
+int spgk_layer_gemm_tc(const spgk_layer *L,
+                       const void *w16, uint32_t ldw, uint64_t w_plane, int w_parts, int w_type16,
+                       const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
+                       void *out16, uint32_t ldo16, uint64_t o_plane, int out_parts,
+                       float *out32, uint32_t ldo32,
+                       uint32_t N, int softmax_fused, int32_t *status, void *stream)
+{
+    return gemm_launch(L, w16, ldw, w_plane, w_parts, w_type16, a16, lda, a_plane, a_parts, type16,
+                       out16, ldo16, o_plane, out_parts, out32, ldo32, N, softmax_fused, status, stream, nullptr, nullptr);
+}
+
+int spgk_layer_gemm_tc_head(const spgk_layer *L,
+                            const void *w16, uint32_t ldw, uint64_t w_plane, int w_parts, int w_type16,
+                            const void *a16, uint32_t lda, uint64_t a_plane, int a_parts, int type16,
+                            const spgk_layer *head, const float *head_w, float *out32, uint32_t ldo32,
+                            uint32_t N, int32_t *status, void *stream)
+{
+    if (!head || !head_w || !out32 || !spgk_gemm_tc_head_supported(L, head)) { spgk_set_error("spgk_layer_gemm_tc_head", "bad argument"); return SPGK_E_ARG; }
+    return gemm_launch(L, w16, ldw, w_plane, w_parts, w_type16, a16, lda, a_plane, a_parts, type16,
+                       nullptr, 0, 0, 1, out32, ldo32, N, 0, status, stream, head, head_w);
 }
 
 // Reads back and clears the status word the GEMM kernels report bounded-wait

@@ -90,6 +90,7 @@ void spg_dev_release(spg_net *n)
     n->act16_bytes = 0; n->act32_bytes = 0;
     spgk_free(n->d_status); n->d_status = NULL;
     spgk_free(n->d_w16); n->d_w16 = NULL; n->w16_bytes = 0;
+    spgk_free(n->d_head_w); n->d_head_w = NULL;
     spgk_host_free(n->h_count); n->h_count = NULL; n->count_pending = false; n->count_seen = false;
     for (int t = 0; t < 2; t++) {
         if (n->d_w16c[t]) for (uint32_t l = 0; l < n->dev_layers; l++) spgk_free(n->d_w16c[t][l]);
@@ -413,7 +414,9 @@ static int large_simt(spg_net *n, const float *d_x, uint32_t N, float *d_out)
     return SPINGALETT_OK;
 }
 
-static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool exact)
+static _Thread_local bool dynamic_rows = false;      /* true around the repair chain of the AUTO mode */
+
+static int large_chain_rows(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool exact)
 {
     NeuralNetwork *p = &n->pub;
     bool tc = true;
@@ -490,6 +493,26 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
                 if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16, ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
             }
         }
+        /* Measured on the benchmark MLP at 65536 rows: it wins in the two-term mode (141.8 us against 155.5 us for two
+         * kernels), ties in the one-term mode where the epilogue's fp32 FMAs become the limit (106.7 / 105.4 us), and
+         * loses for few rows, because a CTA owns whole row tiles there: so only full exact passes over large batches. */
+        if (l + 2 == n->dev_layers && exact && !dynamic_rows && N >= 16384 && spgk_gemm_tc_head_supported(L, &n->klayers[l + 1])) {
+            /* the narrow last layer rides in this layer's epilogue: its input matrix is never written */
+            const spgk_layer *H = &n->klayers[l + 1];
+            if (!n->d_head_w) {
+                void *hw = NULL;
+                if ((rc = spg_map_kernel_error(spgk_malloc(&hw, spgk_head_weights_bytes(H)), "head weights"))) return rc;
+                n->d_head_w = hw;
+                if ((rc = spg_map_kernel_error(spgk_head_weights(H, n->d_head_w, n->stream), "head weights"))) return rc;
+            }
+            prof_mark(n);
+            rc = spg_map_kernel_error(spgk_layer_gemm_tc_head(L, w16, ldw, w_plane, w_parts, type,
+                                                              n->d_act16[l & 1], round8(L->in), plane, parts, type,
+                                                              H, n->d_head_w, d_out, H->out, N, n->d_status, n->stream), "layer + head (tcgen05)");
+            prof_mark(n);
+            if (rc) return rc;
+            break;
+        }
         prof_mark(n);
         rc = spg_map_kernel_error(spgk_layer_gemm_tc(L, w16, ldw, w_plane, w_parts, type,
                                                      n->d_act16[l & 1], round8(L->in), plane, parts, type,
@@ -502,6 +525,36 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
     }
     n->status_pending = true;
     spg_note_path("tcgen05");
+    return SPINGALETT_OK;
+}
+
+/* The tcgen05 chain over a large batch, walked in row chunks small enough for the 16-bit activations of all
+ * layers of a chunk to stay in the 126 MB L2 between the kernels that write and read them, so DRAM sees little
+ * more than the fp32 input.  Chunks are whole multiples of 148 row tiles (one per SM). */
+static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool exact)
+{
+    NeuralNetwork *p = &n->pub;
+    uint64_t row_bytes = 0;
+    for (uint32_t l = 0; l + 1 < p->layers; l++) row_bytes += (uint64_t)round8(p->topology[l]) * 2u * (exact ? 2u : 1u);
+    row_bytes += (uint64_t)p->topology[0] * 4u;
+    uint32_t chunk = 0;
+    const char *e = getenv("SPG_CHUNK");
+    if (e) chunk = (uint32_t)atoi(e);
+    else if (row_bytes) {
+        const uint64_t fit = ((uint64_t)96 << 20) / row_bytes;            /* rows whose working set is about three quarters of L2 */
+        chunk = (uint32_t)(fit / (148u * 128u)) * (148u * 128u);
+    }
+    if (!chunk || dynamic_rows || N < chunk + chunk / 2) return large_chain_rows(n, d_x, N, d_out, exact);
+    const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1];
+    for (uint32_t r0 = 0; r0 < N;) {
+        uint32_t rows = N - r0 < chunk ? N - r0 : chunk;
+        if (N - r0 - rows < chunk / 4) rows = N - r0;                     /* a short tail rides with the last chunk */
+        spgk_set_margin_row_base(r0);
+        int rc = large_chain_rows(n, d_x + (size_t)r0 * in0, rows, d_out + (size_t)r0 * outw, exact);
+        spgk_set_margin_row_base(0);
+        if (rc) return rc;
+        r0 += rows;
+    }
     return SPINGALETT_OK;
 }
 
@@ -570,10 +623,12 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
     if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)N * outw * 4, "repair outputs"))) return rc;
     spgk_set_dynamic_rows(d_count, expected);
+    dynamic_rows = true;
     rc = spg_map_kernel_error(spgk_gather_rows(d_x, n->d_rep_idx, n->d_rep_in, N, in0, n->stream), "repair gather");
     if (!rc) rc = large_chain(n, n->d_rep_in, N, n->d_rep_out, true);
     if (!rc) rc = spg_map_kernel_error(spgk_scatter_rows(n->d_rep_out, n->d_rep_idx, d_out, N, outw, outw, n->stream), "repair scatter");
     spgk_set_dynamic_rows(NULL, 0);
+    dynamic_rows = false;
     if (rc) return rc;
     spg_note_path("tcgen05");
     return SPINGALETT_OK;

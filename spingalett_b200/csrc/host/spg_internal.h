@@ -63,6 +63,7 @@ typedef struct {
     void *d_w16; size_t w16_bytes;         /* 16-bit weight operand of the layer in flight */
     /* 16-bit weight operands kept between calls (nets whose expanded weights are small): [fp16 | bf16][layer] */
     void **d_w16c[2]; uint8_t *w16c_parts[2];
+    float *d_head_w;                       /* fp32 weights of a narrow last layer fused into the layer before it */
 
     float *h_out; size_t h_out_bytes;       /* library-owned pinned output buffer */
     float *h_stage; size_t h_stage_bytes;   /* pinned staging for forward() */

@@ -234,3 +234,69 @@ def test_wstream_against_float64(spg, k, oracle, prec, out, inn, n):
         assert np.all(got[n] == -9.0)
         tol = (3e-6 if n == 1 else 3e-5) * max(1.0, np.abs(want).max()) * np.sqrt(inn / 256)
         assert np.abs(got[:n] - want).max() <= tol, (rep, np.abs(got[:n] - want).max())
+
+
+@pytest.mark.parametrize("M,N,K,H", [(256, 512, 64, 10), (1000, 1000, 512, 10), (4096, 300, 136, 16), (640, 520, 264, 3)])
+@pytest.mark.parametrize("parts", [1, 2])
+@pytest.mark.parametrize("hprec,hact", [(0, 5), (3, 5), (4, 1), (2, 0)])
+def test_gemm_tc_with_fused_head(spg, k, oracle, M, N, K, H, parts, hprec, hact):
+    """A wide layer with the narrow last layer finished in its epilogue (softmax or plain activation, head weights in
+    any stored precision) vs float64 on the same rounded operands."""
+    import torch
+    lib = k
+    vp = C.c_void_p
+    lib.spgk_gemm_tc_head_supported.argtypes = [C.POINTER(spg.abi.KLayer), C.POINTER(spg.abi.KLayer)]
+    lib.spgk_head_weights_bytes.argtypes = [C.POINTER(spg.abi.KLayer)]
+    lib.spgk_head_weights_bytes.restype = C.c_size_t
+    lib.spgk_head_weights.argtypes = [C.POINTER(spg.abi.KLayer), vp, vp]
+    lib.spgk_layer_gemm_tc_head.argtypes = [C.POINTER(spg.abi.KLayer), vp, C.c_uint32, C.c_uint64, C.c_int, C.c_int,
+                                            vp, C.c_uint32, C.c_uint64, C.c_int, C.c_int,
+                                            C.POINTER(spg.abi.KLayer), vp, vp, C.c_uint32, C.c_uint32, vp, vp]
+    rng = np.random.default_rng(M + N * 3 + K * 7 + H)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    act = [1, 3, 2, 4][(M + N) % 4]
+    ld = (K + 7) & ~7
+    dt = torch.bfloat16
+    a16 = torch.zeros((parts, M, ld), dtype=dt, device="cuda")
+    assert lib.spgk_split16(torch.from_numpy(x).cuda().data_ptr(), K, M, K, a16.data_ptr(), ld, M * ld, parts, 1, None) == 0
+    w16 = torch.zeros((1, N, ld), dtype=dt, device="cuda")
+    w16[0, :, :K] = torch.from_numpy(w).cuda().to(dt)
+    bd = torch.from_numpy(bias).cuda()
+    L = spg.abi.KLayer(w16.data_ptr(), bd.data_ptr(), 0.5, K, N, 2, act)
+    # the head, stored in precision hprec
+    hv = (rng.standard_normal(H * N) / np.sqrt(N)).astype(np.float32)
+    raw = oracle.Oracle.encode(hv, hprec)
+    hdec = oracle.Oracle.decode(raw, H * N, hprec).astype(np.float64).reshape(H, N)
+    skip = 4 if hprec >= 3 else 0
+    amax = float(np.frombuffer(raw[:4].tobytes(), np.float32)[0]) if skip else 1.0
+    hscale = amax / {3: 127.0, 4: 7.0, 5: 1.0}[hprec] if skip else 1.0
+    hpay = torch.from_numpy(np.concatenate([raw[skip:], np.zeros(256, np.uint8)])).cuda()
+    hb = (rng.standard_normal(H) * 0.1).astype(np.float32)
+    hbd = torch.from_numpy(hb).cuda()
+    Hl = spg.abi.KLayer(hpay.data_ptr(), hbd.data_ptr(), hscale, N, H, hprec, hact)
+    ok = lib.spgk_gemm_tc_head_supported(C.byref(L), C.byref(Hl))
+    assert ok == (1 if N > 256 else 0)
+    if not ok:
+        return
+    hw = torch.zeros(lib.spgk_head_weights_bytes(C.byref(Hl)) // 4, device="cuda")
+    assert lib.spgk_head_weights(C.byref(Hl), hw.data_ptr(), None) == 0
+    out = torch.full((M + 1, H), -7.0, device="cuda")
+    st = torch.zeros(16, dtype=torch.int32, device="cuda")
+    rc = lib.spgk_layer_gemm_tc_head(C.byref(L), w16.data_ptr(), ld, N * ld, 1, 1, a16.data_ptr(), ld, M * ld, parts, 1,
+                                     C.byref(Hl), hw.data_ptr(), out.data_ptr(), H, M, st.data_ptr(), None)
+    assert rc == 0, lib.spgk_error_string()
+    assert lib.spgk_gemm_tc_status(st.data_ptr(), None) == 0
+    xa = a16.float().cpu().numpy().astype(np.float64).sum(0)[:, :K]
+    wa = w16.float().cpu().numpy().astype(np.float64)[0, :, :K]
+    h = ACT[act](0.5 * (xa @ wa.T) + bias)
+    z = h @ hdec.T + hb
+    if hact == 5:
+        e = np.exp(z - z.max(1, keepdims=True))
+        want = e / e.sum(1, keepdims=True)
+    else:
+        want = ACT[hact](z)
+    got = out.cpu().numpy()
+    assert np.all(got[M] == -7.0)
+    assert np.abs(got[:M] - want).max() <= 2e-5 * max(1.0, np.abs(want).max()), np.abs(got[:M] - want).max()
