@@ -114,8 +114,9 @@ SPGK_API void spgk_set_dynamic_rows(const uint32_t *rows_dev, uint32_t expected)
  * largest logits are within theta are appended to idx and counted in *count (which the caller zeroes).
  * idx == NULL switches it off. */
 SPGK_API void spgk_set_margin_sink(float theta, uint32_t *idx, uint32_t *count);
-/* a batch walked in row chunks: the sink records row + row0 */
-SPGK_API void spgk_set_margin_row_base(uint32_t row0);
+/* After spgk_set_output_rows(idx) the fp32 output of this thread's spgk_layer_gemm_tc calls is scattered: row r of the
+ * result is written to row idx[r] of out32 (the counterpart of spgk_split16_rows).  NULL switches it off. */
+SPGK_API void spgk_set_output_rows(const uint32_t *rows_idx);
 SPGK_API int spgk_margin_select(const float *probs, uint32_t ldp, uint32_t N, uint32_t width, float theta,
                                 uint32_t *idx, uint32_t *count, void *stream);
 /* max over rows of the change in the top-two log gap between a fast and an exact result (float bits in *max_bits,
@@ -130,6 +131,10 @@ SPGK_API int spgk_scatter_rows(const float *src, const uint32_t *idx, float *dst
  * plane_elems): plane 0 = round(x), plane 1 = round(x - plane0), ...
  * Columns in..ld16 are zero-filled.  type = SPGK_T_F16 / SPGK_T_BF16. */
 SPGK_API int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in,
+                          void *dst, uint32_t ld16, uint64_t plane_elems,
+                          int parts, int type, void *stream);
+/* the same with a gather in front: plane row n is built from x row rows_idx[n] (device array) */
+SPGK_API int spgk_split16_rows(const float *x, uint32_t ldx, const uint32_t *rows_idx, uint32_t N, uint32_t in,
                           void *dst, uint32_t ld16, uint64_t plane_elems,
                           int parts, int type, void *stream);
 

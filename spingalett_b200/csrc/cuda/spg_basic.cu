@@ -278,7 +278,8 @@ template <> __device__ __forceinline__ float spg_from16<__nv_bfloat16>(__nv_bflo
 template <typename T16, bool VEC>
 __global__ void __launch_bounds__(256)
 spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32_t in,
-                   T16 *__restrict__ dst, uint32_t ld16, uint64_t plane_elems, int parts, const uint32_t *__restrict__ limit)
+                   T16 *__restrict__ dst, uint32_t ld16, uint64_t plane_elems, int parts, const uint32_t *__restrict__ limit,
+                   const uint32_t *__restrict__ rows_idx)
 {
     spg_grid_trigger();
     spg_grid_wait();
@@ -287,7 +288,7 @@ spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32
     const uint64_t total = (uint64_t)N * chunks;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t n = (uint32_t)(i / chunks), k0 = (uint32_t)(i % chunks) << 3;
-        const float *src = x + (uint64_t)n * ldx + k0;
+        const float *src = x + (uint64_t)(rows_idx ? rows_idx[n] : n) * ldx + k0;      // optional gather: row n comes from row rows_idx[n]
         float v[8];
         if (VEC && k0 + 8 <= in) {
             const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
@@ -311,12 +312,12 @@ thread_local const uint32_t *spg_tls_rows_limit = nullptr;
 thread_local uint32_t spg_tls_rows_expected = 0;
 thread_local float spg_tls_margin_theta = 0.0f;
 thread_local uint32_t *spg_tls_margin_idx = nullptr, *spg_tls_margin_count = nullptr;
-thread_local uint32_t spg_tls_margin_row0 = 0;
+thread_local const uint32_t *spg_tls_out_rows = nullptr;
 
 extern "C" {
 
 void spgk_set_dynamic_rows(const uint32_t *rows_dev, uint32_t expected) { spg_tls_rows_limit = rows_dev; spg_tls_rows_expected = rows_dev ? expected : 0; }
-void spgk_set_margin_row_base(uint32_t row0) { spg_tls_margin_row0 = row0; }
+void spgk_set_output_rows(const uint32_t *rows_idx) { spg_tls_out_rows = rows_idx; }
 void spgk_set_margin_sink(float theta, uint32_t *idx, uint32_t *count)
 {
     spg_tls_margin_theta = theta; spg_tls_margin_idx = idx; spg_tls_margin_count = idx ? count : nullptr;
@@ -395,6 +396,12 @@ int spgk_scatter_rows(const float *src, const uint32_t *idx, float *dst, uint32_
 int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in, void *dst, uint32_t ld16,
                  uint64_t plane_elems, int parts, int type, void *stream)
 {
+    return spgk_split16_rows(x, ldx, nullptr, N, in, dst, ld16, plane_elems, parts, type, stream);
+}
+
+int spgk_split16_rows(const float *x, uint32_t ldx, const uint32_t *rows_idx, uint32_t N, uint32_t in, void *dst, uint32_t ld16,
+                      uint64_t plane_elems, int parts, int type, void *stream)
+{
     if (!x || !dst || parts < 1 || parts > 3 || ld16 < in) { spgk_set_error("spgk_split16", "bad argument"); return SPGK_E_ARG; }
     if (N == 0) return SPGK_OK;
     if ((ld16 & 7u) || (plane_elems & 7u) || ((uintptr_t)dst & 15u)) { spgk_set_error("spgk_split16", "destination planes must be 16-byte aligned"); return SPGK_E_ARG; }
@@ -403,11 +410,11 @@ int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in, void *ds
     const bool vec = ((uintptr_t)x & 15u) == 0 && (ldx & 3u) == 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (type == SPGK_T_F16) {
-        if (vec) SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__half, true>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
-        else SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__half, false>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
+        if (vec) SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__half, true>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit, rows_idx));
+        else SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__half, false>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__half *)dst, ld16, plane_elems, parts, spg_tls_rows_limit, rows_idx));
     } else {
-        if (vec) SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__nv_bfloat16, true>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
-        else SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit));
+        if (vec) SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__nv_bfloat16, true>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit, rows_idx));
+        else SPGK_CUDA(spg_launch_chained(spg_split16_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(256), 0, st, x, ldx, N, in, (__nv_bfloat16 *)dst, ld16, plane_elems, parts, spg_tls_rows_limit, rows_idx));
     }
     return spgk_check_launch("spg_split16_kernel");
 }

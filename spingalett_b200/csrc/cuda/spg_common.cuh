@@ -112,7 +112,7 @@ extern thread_local uint32_t spg_tls_rows_expected;      // the caller's estimat
 // margin sink set by spgk_set_margin_sink for the calling thread (idx == NULL: off)
 extern thread_local float spg_tls_margin_theta;
 extern thread_local uint32_t *spg_tls_margin_idx, *spg_tls_margin_count;
-extern thread_local uint32_t spg_tls_margin_row0;          // added to the row numbers the sink records (batches walked in chunks)
+extern thread_local const uint32_t *spg_tls_out_rows;      // spgk_set_output_rows: fp32 output row r of the tensor-core layer goes to row out_rows[r]
 __device__ __forceinline__ uint32_t spg_limit_rows(uint32_t rows, const uint32_t *limit)
 {
     if (!limit) return rows;

@@ -56,10 +56,13 @@ struct GemmParams {
     const float *head_w;          // [round_up(N, 32)][HP] fp32, unscaled, rows beyond N zero (staged into shared memory)
     const float *head_bias; float head_scale; uint32_t head_out, head_hp; int head_act, head_softmax;
     uint32_t stg_bytes;           // bytes of the epilogue's shared-memory region (patches, or head weights + exchange)
-    float margin_theta; uint32_t *margin_idx, *margin_count, margin_row0;   // fused-softmax rows with top-two logit gap < theta are appended here (optional)
+    float margin_theta; uint32_t *margin_idx, *margin_count;
+    const uint32_t *out_rows;     // optional scatter of the fp32 output rows   // fused-softmax rows with top-two logit gap < theta are appended here (optional)
     int tma_store;                // 16-bit output leaves through TMA stores (one plane, tiles at least 128 wide)
     const uint32_t *m_limit;      // optional device-resident row count: the kernel works on min(M, *m_limit) rows
 };
+
+struct RowLimit { uint32_t m_tiles, group_m; };   // tile counts for the rows actually present (<= the launch's capacity)
 
 // ---- raw PTX wrappers -------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -145,33 +148,33 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
     return d;
 }
 
-__device__ __forceinline__ void tile_coords(const GemmParams &p, uint32_t t, uint32_t &m_tile, uint32_t &n_tile)
+__device__ __forceinline__ void tile_coords(const GemmParams &p, const RowLimit &rl, uint32_t t, uint32_t &m_tile, uint32_t &n_tile)
 {
     // Tiles are walked in bands of group_m row-tiles, row-tile fastest inside a band,
     // so CTAs running at the same time share W tiles and a small set of A tiles in L2.
-    const uint32_t band = p.group_m * p.n_tiles;
+    const uint32_t band = rl.group_m * p.n_tiles;
     const uint32_t g = t / band, r = t % band;
-    const uint32_t rows_here = min(p.group_m, p.m_tiles - g * p.group_m);
-    m_tile = g * p.group_m + r % rows_here;
+    const uint32_t rows_here = min(rl.group_m, rl.m_tiles - g * rl.group_m);
+    m_tile = g * rl.group_m + r % rows_here;
     n_tile = r / rows_here;
 }
 
 
 // The tiles of this CTA, in order.  Normally tile blockIdx.x + i * gridDim.x of the banded walk; with a fused head
 // a CTA owns whole row tiles (all their column tiles in a row), because the head sums over every column of a row.
-__device__ __forceinline__ uint32_t my_tile_count(const GemmParams &p)
+__device__ __forceinline__ uint32_t my_tile_count(const GemmParams &p, const RowLimit &rl)
 {
     if (p.head_w) {
-        const uint32_t rt = p.m_tiles > blockIdx.x ? (p.m_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const uint32_t rt = rl.m_tiles > blockIdx.x ? (rl.m_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         return rt * p.n_tiles;
     }
-    const uint32_t total = p.m_tiles * p.n_tiles;
+    const uint32_t total = rl.m_tiles * p.n_tiles;
     return total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 }
-__device__ __forceinline__ void my_tile(const GemmParams &p, uint32_t i, uint32_t &m_tile, uint32_t &n_tile)
+__device__ __forceinline__ void my_tile(const GemmParams &p, const RowLimit &rl, uint32_t i, uint32_t &m_tile, uint32_t &n_tile)
 {
     if (p.head_w) { m_tile = blockIdx.x + (i / p.n_tiles) * gridDim.x; n_tile = i % p.n_tiles; }
-    else tile_coords(p, blockIdx.x + i * gridDim.x, m_tile, n_tile);
+    else tile_coords(p, rl, blockIdx.x + i * gridDim.x, m_tile, n_tile);
 }
 
 template <typename T16> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -213,7 +216,7 @@ __device__ __forceinline__ void finish16(const GemmParams &p, const uint32_t (&r
 
 __device__ __forceinline__ void write32(const GemmParams &p, uint32_t row, uint32_t col0, const float (&v)[16])
 {
-    float *o = p.out32 + (uint64_t)row * p.ldo32 + col0;
+    float *o = p.out32 + (uint64_t)(p.out_rows ? p.out_rows[row] : row) * p.ldo32 + col0;
     if ((p.ldo32 & 3u) == 0 && col0 + 16 <= p.N) {
 #pragma unroll
         for (int i = 0; i < 16; i += 4)
@@ -240,7 +243,7 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // per instruction -- measured: a third of the kernel's time).  The patch goes through shared memory instead:
 // written row-wise by its owners, read back so that a store instruction covers 8 rows x 64 contiguous bytes.
 template <typename T16>
-__device__ __forceinline__ void store_patch(const GemmParams &p, uint8_t *stg, uint32_t lane, uint32_t row0, uint32_t col0,
+__device__ __forceinline__ void store_patch(const GemmParams &p, uint32_t rows, uint8_t *stg, uint32_t lane, uint32_t row0, uint32_t col0,
                                             const float (&v0)[16], const float (&v1)[16], bool second)
 {
     const uint32_t pieces = second ? 4u : 2u;
@@ -263,7 +266,7 @@ __device__ __forceinline__ void store_patch(const GemmParams &p, uint8_t *stg, u
         for (int pass = 0; pass < 4; pass++) {
             const uint32_t rr = pass * 8 + (lane >> 2), piece = lane & 3u;
             const uint32_t row = row0 + rr, col = col0 + piece * 8;
-            if (piece < pieces && row < p.M && col < p.ldo16)
+            if (piece < pieces && row < rows && col < p.ldo16)
                 *reinterpret_cast<uint4 *>(plane + (uint64_t)row * p.ldo16 + col) = *reinterpret_cast<const uint4 *>(stg + rr * STG_PITCH + piece * 16);
         }
         __syncwarp();
@@ -274,14 +277,14 @@ __device__ __forceinline__ void store_patch(const GemmParams &p, uint8_t *stg, u
 // the half selected by (w-2)/4; each thread therefore owns one row of C and walks its columns in
 // chunks of 32 (two tcgen05.ld in flight per wait).
 template <int ACT, int HP>
-__device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
+__device__ __forceinline__ void epilogue_loop(const GemmParams &p, const RowLimit &rl, uint32_t rows, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
                                               volatile int *abort_flag, uint32_t warp, uint32_t lane, uint8_t *stage,
                                               const CUtensorMap *map_o, uint32_t hx0)
 {
     uint8_t *stg = stage + (warp - 2u) * PATCH_BYTES;          // 1024-byte aligned: a swizzle atom is 8 rows x 128 bytes
     const uint32_t stg_addr = smem_u32(stg);
     const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
-    const uint32_t ntile = my_tile_count(p);
+    const uint32_t ntile = my_tile_count(p, rl);
     const uint32_t span = p.BN >= 32 ? p.BN / 2 : p.BN;            // columns per warp
     const uint32_t c_begin = p.BN >= 32 ? half * span : 0;
     const bool idle = p.BN < 32 && half == 1;                      // a 16-wide tile has work for one warp per quadrant
@@ -291,7 +294,7 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
     float *xch = reinterpret_cast<float *>(stage + p.stg_bytes - 4 * 2 * 32 * 16 * 4) ;   // head mode: [parity][quadrant][lane][16] exchange
     for (uint32_t tcount = 0; tcount < ntile; tcount++) {
         uint32_t mt, nt;
-        my_tile(p, tcount, mt, nt);
+        my_tile(p, rl, tcount, mt, nt);
         const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
         if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, p.status, 4)) break;
         tc_fence_after();
@@ -302,7 +305,7 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
             for (int j = 0; j < (HP > 0 ? HP : 1); j++) hacc[j] = 0.0f;
         }
         const uint32_t taddr = tmem_base + acc * p.BN + ((q * 32u) << 16);
-        const bool row_ok = row < p.M;
+        const bool row_ok = row < rows;
         if (!idle) {
             for (uint32_t c0 = c_begin; c0 < c_begin + span; c0 += 32) {
                 if (n0 + c0 >= p.N) break;                         // only zero-filled W rows beyond N
@@ -367,8 +370,8 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
                         if (lane == 0) tma_store_3d(map_o, stg_addr, (int)(n0 + c0 - 32u * h32), (int)(mt * BM + q * 32u), 0);
                     }
                 } else if (p.out16) {
-                    if (p.type16 == SPGK_T_F16) store_patch<__half>(p, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
-                    else store_patch<__nv_bfloat16>(p, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
+                    if (p.type16 == SPGK_T_F16) store_patch<__half>(p, rows, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
+                    else store_patch<__nv_bfloat16>(p, rows, stg, lane, mt * BM + q * 32u, n0 + c0, v, v2, second);
                 }
                 if (HP == 0 && p.out32 && row_ok) {
                     write32(p, row, n0 + c0, v);
@@ -403,14 +406,15 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
                     const float inv = sum > 0.0f ? 1.0f / sum : 1.0f;
 #pragma unroll
                     for (int j = 0; j < HP; j++) z[j] *= inv;
-                    if (p.margin_idx && row < p.M && p.head_out >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row + p.margin_row0;
+                    if (p.margin_idx && row < rows && p.head_out >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
                 } else {
 #pragma unroll
                     for (int j = 0; j < HP; j++) z[j] = spg_activate(z[j], p.head_act);
                 }
-                if (row < p.M) {
+                if (row < rows) {
+                    const uint64_t orow = p.out_rows ? p.out_rows[row] : row;
 #pragma unroll
-                    for (int j = 0; j < HP; j++) if ((uint32_t)j < p.head_out) p.out32[(uint64_t)row * p.ldo32 + j] = z[j];
+                    for (int j = 0; j < HP; j++) if ((uint32_t)j < p.head_out) p.out32[orow * p.ldo32 + j] = z[j];
                 }
             }
         }
@@ -421,14 +425,14 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, uint32_t tmem
 // Fused row softmax (reference Activation.c:5-21): the whole row (N <= BN) sits in one TMEM lane, so
 // one thread per row sweeps it three times: running max from -FLT_MAX, sum of expf(v - max), then
 // expf(v - max) / sum written out (the division happens only when the sum is positive).
-__device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
+__device__ __forceinline__ void epilogue_softmax(const GemmParams &p, const RowLimit &rl, uint32_t rows, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
                                                  volatile int *abort_flag, uint32_t warp, uint32_t lane)
 {
     const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
-    const uint32_t ntile = my_tile_count(p);
+    const uint32_t ntile = my_tile_count(p, rl);
     for (uint32_t tcount = 0; tcount < ntile; tcount++) {
         uint32_t mt, nt;
-        my_tile(p, tcount, mt, nt);
+        my_tile(p, rl, tcount, mt, nt);
         const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
         if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, p.status, 4)) break;
         tc_fence_after();
@@ -448,7 +452,7 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
                     }
             }
             // log p1 - log p2 of the softmax equals the gap of the two largest logits
-            if (p.margin_idx && row < p.M && p.N >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row + p.margin_row0;
+            if (p.margin_idx && row < rows && p.N >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
             for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
@@ -462,11 +466,12 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
                 tmem_ld_wait();
-                if (row < p.M) {
+                if (row < rows) {
+                    const uint64_t orow = p.out_rows ? p.out_rows[row] : row;
 #pragma unroll
                     for (int i = 0; i < 16; i++)
                         if (c0 + i < p.N)
-                            p.out32[(uint64_t)row * p.ldo32 + c0 + i] =
+                            p.out32[orow * p.ldo32 + c0 + i] =
                                 expf(fmaf(__uint_as_float(r[i]), p.scale, p.bias[c0 + i]) - mx) * inv;
                 }
             }
@@ -478,9 +483,8 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, uint32_t t
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                   const __grid_constant__ CUtensorMap map_o, const GemmParams p_in)
+                   const __grid_constant__ CUtensorMap map_o, const GemmParams p)
 {
-    GemmParams p = p_in;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment of the operand tiles (required by the 128-byte swizzle atoms)
     const uint32_t raw = smem_u32(smem_raw);
@@ -523,13 +527,18 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // before this one in the stream; from here on its results are needed.
     spg_grid_trigger();
     spg_grid_wait();
-    // rows may be limited by a count that only exists on the device (every role derives the same tile list from it)
-    if (p_in.m_limit) {
-        const uint32_t m = *p_in.m_limit;
-        if (m < p.M) { p.M = m; p.m_tiles = (m + BM - 1) / BM; if (p.m_tiles && p.group_m > p.m_tiles) p.group_m = p.m_tiles; }
+    // rows may be limited by a count that only exists on the device (every role derives the same tile list from it);
+    // the effective sizes live in their own small struct: the kernel parameters themselves stay untouched
+    uint32_t rows = p.M;
+    if (p.m_limit) {
+        const uint32_t m = *reinterpret_cast<const volatile uint32_t *>(p.m_limit);
+        rows = m < rows ? m : rows;
     }
+    RowLimit rl;
+    rl.m_tiles = (rows + BM - 1) / BM;
+    rl.group_m = (rl.m_tiles && p.group_m > rl.m_tiles) ? rl.m_tiles : p.group_m;
 
-    const uint32_t ntile = my_tile_count(p);
+    const uint32_t ntile = my_tile_count(p, rl);
     const uint32_t iters_per_tile = p.npass * p.kblocks;
     if (p.head_w) {
         // the head's weights (a few tens of KB) live in shared memory for the whole kernel
@@ -547,7 +556,7 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             bool alive = true;
             for (uint32_t ti = 0; ti < ntile && alive; ti++) {
                 uint32_t mt, nt;
-                my_tile(p, ti, mt, nt);
+                my_tile(p, rl, ti, mt, nt);
                 for (uint32_t ps = 0; ps < p.npass && alive; ps++) {
                     for (uint32_t kb = 0; kb < p.kblocks; kb++, it++) {
                         const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
@@ -592,11 +601,11 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // The activation is resolved once, outside every loop, so the per-element code is branch-free.
         // The activation (and the width of a fused head) is resolved once, outside every loop.
 #define SPG_EPI(ACTV) \
-        if (p.head_hp == 0) epilogue_loop<ACTV, 0>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0); \
-        else if (p.head_hp == 12) epilogue_loop<ACTV, 12>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0); \
-        else epilogue_loop<ACTV, 16>(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0)
+        if (p.head_hp == 0) epilogue_loop<ACTV, 0>(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0); \
+        else if (p.head_hp == 12) epilogue_loop<ACTV, 12>(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0); \
+        else epilogue_loop<ACTV, 16>(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0)
         switch (p.softmax ? -1 : p.act) {
-            case -1:               epilogue_softmax(p, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case -1:               epilogue_softmax(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
             case SPG_ACT_RELU:     SPG_EPI(SPG_ACT_RELU); break;
             case SPG_ACT_LEAKY:    SPG_EPI(SPG_ACT_LEAKY); break;
             case SPG_ACT_FOO52:    SPG_EPI(SPG_ACT_FOO52); break;
@@ -836,7 +845,8 @@ static int gemm_launch(const spgk_layer *L,
     p.out32 = out32; p.ldo32 = ldo32;
     p.status = status;
     p.m_limit = spg_tls_rows_limit;
-    if ((softmax_fused || (head && head->act == SPG_ACT_SOFTMAX)) && spg_tls_margin_idx) { p.margin_theta = spg_tls_margin_theta; p.margin_idx = spg_tls_margin_idx; p.margin_count = spg_tls_margin_count; p.margin_row0 = spg_tls_margin_row0; }
+    if ((softmax_fused || (head && head->act == SPG_ACT_SOFTMAX)) && spg_tls_margin_idx) { p.margin_theta = spg_tls_margin_theta; p.margin_idx = spg_tls_margin_idx; p.margin_count = spg_tls_margin_count; }
+    p.out_rows = spg_tls_out_rows;
 
     CUtensorMap map_a, map_w;
     int rc = make_map(&map_a, a16, type16, L->in, N, lda, a_plane, a_parts, BM);

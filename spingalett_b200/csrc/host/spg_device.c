@@ -415,8 +415,9 @@ static int large_simt(spg_net *n, const float *d_x, uint32_t N, float *d_out)
 }
 
 static _Thread_local bool dynamic_rows = false;      /* true around the repair chain of the AUTO mode */
+static _Thread_local const uint32_t *repair_rows = NULL;   /* repair chain: input row i is row repair_rows[i] of d_x, and its result goes back there */
 
-static int large_chain_rows(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool exact)
+static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool exact)
 {
     NeuralNetwork *p = &n->pub;
     bool tc = true;
@@ -463,8 +464,8 @@ static int large_chain_rows(spg_net *n, const float *d_x, uint32_t N, float *d_o
         if (!n->d_w16c[type] || !n->w16c_parts[type]) { spg_set_error(SPINGALETT_ERR_ALLOC, "weight operand table"); return SPINGALETT_ERR_ALLOC; }
     }
     if (!keep && wneed && (rc = reserve(&n->d_w16, &n->w16_bytes, wneed, "16-bit weight operand scratch"))) return rc;
-    rc = spg_map_kernel_error(spgk_split16(d_x, p->topology[0], N, p->topology[0], n->d_act16[0],
-                                           round8(p->topology[0]), plane, parts, type, n->stream), "input split");
+    rc = spg_map_kernel_error(spgk_split16_rows(d_x, p->topology[0], repair_rows, N, p->topology[0], n->d_act16[0],
+                                                round8(p->topology[0]), plane, parts, type, n->stream), "input split");
     if (rc) return rc;
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
@@ -514,10 +515,12 @@ static int large_chain_rows(spg_net *n, const float *d_x, uint32_t N, float *d_o
             break;
         }
         prof_mark(n);
+        if (last) spgk_set_output_rows(repair_rows);
         rc = spg_map_kernel_error(spgk_layer_gemm_tc(L, w16, ldw, w_plane, w_parts, type,
                                                      n->d_act16[l & 1], round8(L->in), plane, parts, type,
                                                      o16, round8(L->out), plane, parts, o32, L->out,
                                                      N, (last && fuse_sm) ? 1 : 0, n->d_status, n->stream), "layer (tcgen05)");
+        spgk_set_output_rows(NULL);
         prof_mark(n);
         if (rc) return rc;
         if (last && L->act == ACT_SOFTMAX && !fuse_sm &&
@@ -525,36 +528,6 @@ static int large_chain_rows(spg_net *n, const float *d_x, uint32_t N, float *d_o
     }
     n->status_pending = true;
     spg_note_path("tcgen05");
-    return SPINGALETT_OK;
-}
-
-/* The tcgen05 chain over a large batch, walked in row chunks small enough for the 16-bit activations of all
- * layers of a chunk to stay in the 126 MB L2 between the kernels that write and read them, so DRAM sees little
- * more than the fp32 input.  Chunks are whole multiples of 148 row tiles (one per SM). */
-static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool exact)
-{
-    NeuralNetwork *p = &n->pub;
-    uint64_t row_bytes = 0;
-    for (uint32_t l = 0; l + 1 < p->layers; l++) row_bytes += (uint64_t)round8(p->topology[l]) * 2u * (exact ? 2u : 1u);
-    row_bytes += (uint64_t)p->topology[0] * 4u;
-    uint32_t chunk = 0;
-    const char *e = getenv("SPG_CHUNK");
-    if (e) chunk = (uint32_t)atoi(e);
-    else if (row_bytes) {
-        const uint64_t fit = ((uint64_t)96 << 20) / row_bytes;            /* rows whose working set is about three quarters of L2 */
-        chunk = (uint32_t)(fit / (148u * 128u)) * (148u * 128u);
-    }
-    if (!chunk || dynamic_rows || N < chunk + chunk / 2) return large_chain_rows(n, d_x, N, d_out, exact);
-    const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1];
-    for (uint32_t r0 = 0; r0 < N;) {
-        uint32_t rows = N - r0 < chunk ? N - r0 : chunk;
-        if (N - r0 - rows < chunk / 4) rows = N - r0;                     /* a short tail rides with the last chunk */
-        spgk_set_margin_row_base(r0);
-        int rc = large_chain_rows(n, d_x + (size_t)r0 * in0, rows, d_out + (size_t)r0 * outw, exact);
-        spgk_set_margin_row_base(0);
-        if (rc) return rc;
-        r0 += rows;
-    }
     return SPINGALETT_OK;
 }
 
@@ -620,13 +593,22 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     const uint32_t expected = n->count_seen ? *(volatile uint32_t *)n->h_count : 0;    /* the count of the call before: a guide to tile shapes only */
     if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(n->h_count, d_count, 4, n->stream), "repair count"))) return rc;
     n->count_pending = true; n->count_seen = true;
-    if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
-    if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)N * outw * 4, "repair outputs"))) return rc;
+    if (Llast->act == ACT_SOFTMAX && Llast->out > spgk_gemm_tc_softmax_max()) {
+        if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
+        if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)N * outw * 4, "repair outputs"))) return rc;
+    }
     spgk_set_dynamic_rows(d_count, expected);
     dynamic_rows = true;
-    rc = spg_map_kernel_error(spgk_gather_rows(d_x, n->d_rep_idx, n->d_rep_in, N, in0, n->stream), "repair gather");
-    if (!rc) rc = large_chain(n, n->d_rep_in, N, n->d_rep_out, true);
-    if (!rc) rc = spg_map_kernel_error(spgk_scatter_rows(n->d_rep_out, n->d_rep_idx, d_out, N, outw, outw, n->stream), "repair scatter");
+    if (Llast->act != ACT_SOFTMAX || Llast->out <= spgk_gemm_tc_softmax_max()) {
+        /* the split reads the flagged rows in place and the last layer's epilogue writes them back in place */
+        repair_rows = n->d_rep_idx;
+        rc = large_chain(n, d_x, N, d_out, true);
+        repair_rows = NULL;
+    } else {
+        rc = spg_map_kernel_error(spgk_gather_rows(d_x, n->d_rep_idx, n->d_rep_in, N, in0, n->stream), "repair gather");
+        if (!rc) rc = large_chain(n, n->d_rep_in, N, n->d_rep_out, true);
+        if (!rc) rc = spg_map_kernel_error(spgk_scatter_rows(n->d_rep_out, n->d_rep_idx, d_out, N, outw, outw, n->stream), "repair scatter");
+    }
     spgk_set_dynamic_rows(NULL, 0);
     dynamic_rows = false;
     if (rc) return rc;

@@ -300,3 +300,54 @@ def test_gemm_tc_with_fused_head(spg, k, oracle, M, N, K, H, parts, hprec, hact)
     got = out.cpu().numpy()
     assert np.all(got[M] == -7.0)
     assert np.abs(got[:M] - want).max() <= 2e-5 * max(1.0, np.abs(want).max()), np.abs(got[:M] - want).max()
+
+
+@pytest.mark.parametrize("cap,K,rows,parts", [(300, 64, [10, 20, 30, 40, 50], 2), (300, 64, [299, 7, 130], 1),
+                                              (256, 784, [5, 6, 250], 2), (1000, 136, list(range(100, 240)), 2)])
+def test_device_resident_row_count_with_gather_and_scatter(spg, k, cap, K, rows, parts):
+    """A selection of rows known only on the device: split16 gathers them, the softmax layer runs on min(capacity, count)
+    rows and scatters its output back; rows outside the selection must stay untouched (the index array beyond the
+    count holds decoys)."""
+    import torch
+    lib = k
+    vp = C.c_void_p
+    lib.spgk_split16_rows.argtypes = [vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, vp, C.c_uint32, C.c_uint64, C.c_int, C.c_int, vp]
+    lib.spgk_set_dynamic_rows.argtypes = [vp, C.c_uint32]
+    lib.spgk_set_output_rows.argtypes = [vp]
+    N = 10
+    rng = np.random.default_rng(cap + K)
+    x = rng.standard_normal((cap, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    ld = (K + 7) & ~7
+    dt = torch.bfloat16
+    w16 = torch.zeros((1, N, ld), dtype=dt, device="cuda")
+    w16[0, :, :K] = torch.from_numpy(w).cuda().to(dt)
+    b = torch.zeros(N, device="cuda")
+    L = spg.abi.KLayer(w16.data_ptr(), b.data_ptr(), 1.0, K, N, 2, 5)
+    idx = (torch.arange(cap, dtype=torch.int32, device="cuda") % 97) + 150          # decoys beyond the count
+    idx[:len(rows)] = torch.tensor(rows, dtype=torch.int32)
+    cnt = torch.tensor([len(rows)], dtype=torch.int32, device="cuda")
+    a16 = torch.zeros((parts, cap, ld), dtype=dt, device="cuda")
+    out = torch.full((cap, N), -3.0, device="cuda")
+    st = torch.zeros(16, dtype=torch.int32, device="cuda")
+    lib.spgk_set_dynamic_rows(cnt.data_ptr(), 0)
+    try:
+        assert lib.spgk_split16_rows(xd.data_ptr(), K, idx.data_ptr(), cap, K, a16.data_ptr(), ld, cap * ld, parts, 1, None) == 0
+        lib.spgk_set_output_rows(idx.data_ptr())
+        rc = lib.spgk_layer_gemm_tc(C.byref(L), w16.data_ptr(), ld, N * ld, 1, 1, a16.data_ptr(), ld, cap * ld, parts, 1,
+                                    None, 0, 0, 1, out.data_ptr(), N, cap, 1, st.data_ptr(), None)
+    finally:
+        lib.spgk_set_output_rows(None)
+        lib.spgk_set_dynamic_rows(None, 0)
+    assert rc == 0, lib.spgk_error_string()
+    assert lib.spgk_gemm_tc_status(st.data_ptr(), None) == 0
+    got = out.cpu().numpy()
+    a = a16.float().cpu().numpy().astype(np.float64)
+    assert np.all(a[:, len(rows):] == 0)                                            # the split stopped at the count
+    z = a.sum(0)[:len(rows), :K] @ w16.float().cpu().numpy().astype(np.float64)[0, :, :K].T
+    e = np.exp(z - z.max(1, keepdims=True))
+    want = e / e.sum(1, keepdims=True)
+    touched = np.where((got != -3.0).any(1))[0]
+    assert touched.tolist() == sorted(rows)
+    assert np.abs(got[rows] - want).max() <= 2e-6
