@@ -340,7 +340,9 @@ def main():
     e2e_value = batch * world / (e2e_ms * 1e-3)
     passes = 2 if args.math == "exact" else 1
     compute = {"exact": "bf16(hi+lo)xbf16->f32", "fast": "f16xf16->f32", "auto": "f16xf16->f32 + exact recompute of low-margin rows"}[args.math]
-    if path_taken in ("gemv", "wstream"):
+    if path_taken == "gemv" and args.dtype in ("int8", "int4", "int2"):
+        compute = "s8 digits x s8 -> s32 (exact sums of 28-bit fixed-point activations)"
+    elif path_taken in ("gemv", "wstream"):
         compute = "bf16 terms x bf16 -> f32 (exact products)"
     line = {
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -380,7 +382,10 @@ def main():
                             "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "kernel": "spg_gemv_kernel",
                             "launches": int(k_cnt), "kernel_ms_per_step": k_ms / args.steps,
                             "algorithmic_bytes_per_step": nbytes, "peak_source": pk["source"] + " copy bandwidth",
-                            "whole_step_frac": nbytes / (dev_ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+                            "whole_step_frac": nbytes / (dev_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                            "note": "frac: event pairs around each layer kernel in a separate pass (events keep a layer from "
+                                    "prefetching weights under the previous one); whole_step_frac: algorithmic bytes / ms_per_step "
+                                    "of the timed loop, staging and softmax included"}
     if args.all_dtypes:
         per = {}
         for dt in PRECS:

@@ -140,10 +140,13 @@ SPGK_API int spgk_split16_rows(const float *x, uint32_t ldx, const uint32_t *row
 
 /* ---- K1: small-batch fused dequant-GEMV ----------------------------------
  * Whole layer for 1 <= N <= SPGK_GEMV_MAX_BATCH rows: streams the packed
- * weights once with 128-bit loads, dequantises in registers, multiplies on
- * the warp-level tensor path against a two/three-term bf16 split of x (all
- * products exact, fp32 accumulation), reduces the K splits, applies bias +
- * activation (not softmax).  Memory-bound by design.
+ * weights once (TMA boxes into a shared-memory ring), unpacks them in registers
+ * and multiplies on the warp-level tensor path -- integer files against base-128
+ * digits of a fixed-point x with exact s32 accumulation, float files against a
+ * two/three-term bf16 split of x with fp32 accumulation -- then applies bias and
+ * activation; a softmax layer is completed by the CTA that finishes last when N == 1
+ * (spgk_gemv_applies_softmax(N) == 1) and left as logits for spgk_softmax_rows otherwise.
+ * Memory-bound by design.
  * Needs 16-byte aligned packed rows of at least 64 bytes (TMA boxes of the packed
  * matrix); returns SPGK_E_UNSUPPORTED otherwise so the caller can use spgk_layer_simt.
  * scratch: dev, at least spgk_gemv_scratch_bytes(L, N) bytes, ZERO-FILLED before
@@ -152,6 +155,7 @@ SPGK_API int spgk_split16_rows(const float *x, uint32_t ldx, const uint32_t *row
  * Does forward()'s layer step, reference Network.c:218-247 / SIMD.c:190-240. */
 #define SPGK_GEMV_MAX_BATCH 8
 SPGK_API size_t spgk_gemv_scratch_bytes(const spgk_layer *L, uint32_t N);
+SPGK_API int spgk_gemv_applies_softmax(uint32_t N);
 SPGK_API int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx,
                              float *y, uint32_t ldy, uint32_t N,
                              void *scratch, void *stream);

@@ -95,6 +95,7 @@ struct GemvParams {
     const uint8_t *in_head;                 // integer path: head of this layer's staged input
     uint8_t *out_head;                      // integer path: head of the next layer's staged input (or NULL)
     float bias_absmax;                      // integer path: caller's bound of |bias|, checked against every bias used
+    int softmax;                            // the layer ends in a row softmax: the CTA that finishes last applies it
 };
 
 // elements covered by one 128-bit load, per stored precision
@@ -354,6 +355,49 @@ __device__ __forceinline__ void bulk_copy_1d(uint32_t dst, const void *src, uint
 // only arrives (does not wait), the side that needs it waits.
 __device__ __forceinline__ void handoff_arrive(uint32_t id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(HANDOFF_THREADS) : "memory"); }
 __device__ __forceinline__ void handoff_wait(uint32_t id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(HANDOFF_THREADS) : "memory"); }
+
+// Row softmax of a finished layer, run by the epilogue warp of the CTA that finishes last (a ticket next to the
+// status word tells which one): Activation.c:5-21 per row -- maximum from -FLT_MAX, expf(x - max), and the
+// scaling by 1/sum only when the sum is positive.
+__device__ __forceinline__ void gemv_final_softmax(const GemvParams &p, uint32_t lane)
+{
+    __threadfence();                                           // this CTA's outputs are visible before its ticket
+    uint32_t ticket = 0;
+    if (lane == 0) ticket = atomicAdd(reinterpret_cast<unsigned int *>(p.status + 1), 1u);
+    ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+    if (ticket != gridDim.x - 1) return;
+    __threadfence();
+    for (uint32_t n = 0; n < p.N; n++) {
+        float *r = p.y + (uint64_t)n * p.ldy;
+        if (p.out <= 1024) {
+            // the whole row in registers: one trip to L2 and back
+            float v[32];
+            float mx = -FLT_MAX;
+#pragma unroll
+            for (int j = 0; j < 32; j++) { const uint32_t i = j * 32 + lane; v[j] = i < p.out ? __ldcg(r + i) : -FLT_MAX; if (v[j] > mx) mx = v[j]; }
+            mx = spg_warp_max(mx);
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32; j++) { const uint32_t i = j * 32 + lane; v[j] = i < p.out ? expf(v[j] - mx) : 0.0f; sum += v[j]; }
+            sum = spg_warp_sum(sum);
+            const float inv = sum > 0.0f ? 1.0f / sum : 1.0f;
+#pragma unroll
+            for (int j = 0; j < 32; j++) { const uint32_t i = j * 32 + lane; if (i < p.out) r[i] = v[j] * inv; }
+            continue;
+        }
+        float mx = -FLT_MAX;
+        for (uint32_t i = lane; i < p.out; i += 32u) { const float v = __ldcg(r + i); if (v > mx) mx = v; }
+        mx = spg_warp_max(mx);
+        float sum = 0.0f;
+        for (uint32_t i = lane; i < p.out; i += 32u) { const float e = expf(__ldcg(r + i) - mx); r[i] = e; sum += e; }
+        sum = spg_warp_sum(sum);
+        if (sum > 0.0f) {
+            const float inv = 1.0f / sum;
+            for (uint32_t i = lane; i < p.out; i += 32u) r[i] *= inv;
+        }
+    }
+    if (lane == 0) p.status[1] = 0;                            // ready for the next launch
+}
 
 // One step of one warp: 16 rows x (4 lanes x EL elements).  ra / rbv are the lane's 128-bit pieces of rows
 // g and g+8; xb points at this lane's slot of the step's staged activations (CW columns per tile).
@@ -655,6 +699,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                     if (n < p.N) oparts[(uint64_t)blockIdx.x * 8 + n] = abs_run[u];
                 }
             }
+            if (p.softmax) gemv_final_softmax(p, lane);
         } else {
         constexpr int PER_LANE = ITEM_ROWS * MAX_BATCH / 32;
         for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
@@ -703,6 +748,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                         p.xout[staged_index(p.next_prec, cs, p.out + idx / cs, idx % cs)] = __float2bfloat16_rn(0.0f);
             }
         }
+        if (p.softmax) gemv_final_softmax(p, lane);
         }
         return;
     }
@@ -969,6 +1015,7 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
     GemvParams p{};
     p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out; p.bias_absmax = L->bias_absmax;
     p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
+    p.softmax = (L->act == SPG_ACT_SOFTMAX && N == 1) ? 1 : 0;     // one warp finishes one row quickly; more rows are left to the caller
     p.y = y; p.ldy = ldy;
     p.N = N; p.P = pl.P; p.C = pl.C;
     p.items = pl.items; p.nboxes = pl.nboxes; p.nchunks = pl.nchunks; p.spb = pl.spb; p.box_bytes = pl.box_bytes;
@@ -1027,6 +1074,9 @@ int spgk_gemv_chain_stages_next(const spgk_layer *L, const spgk_layer *next, uin
     const Plan a = make_plan(L, N), b = make_plan(next, N);
     return a.ok && b.ok && a.intp == b.intp ? 1 : 0;
 }
+
+// 1 if spgk_layer_gemv / spgk_layer_gemv_chain complete a softmax layer themselves at this batch (else they leave logits)
+int spgk_gemv_applies_softmax(uint32_t N) { return N == 1 ? 1 : 0; }
 
 int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx, float *y, uint32_t ldy, uint32_t N,
                     void *scratch, void *stream)

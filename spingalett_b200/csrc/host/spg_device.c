@@ -365,7 +365,9 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
             k = spgk_layer_simt(L, x, xld, y, L->out, N, n->stream);
         }
         if ((rc = spg_map_kernel_error(k, "layer (small batch)"))) return rc;
-        if (L->act == ACT_SOFTMAX && (rc = spg_map_kernel_error(spgk_softmax_rows(y, L->out, N, L->out, n->stream), "softmax"))) return rc;
+        /* at one row the GEMV applies the softmax itself (its last CTA to finish does it); otherwise the layer left logits */
+        if (L->act == ACT_SOFTMAX && !(used[0] == 'g' && spgk_gemv_applies_softmax(N)) &&
+            (rc = spg_map_kernel_error(spgk_softmax_rows(y, L->out, N, L->out, n->stream), "softmax"))) return rc;
         if (!path || used[0] == 's' || (used[0] == 'w' && path[0] == 'g')) path = used;    /* report the most general kernel used */
         x = y; xld = L->out;
     }

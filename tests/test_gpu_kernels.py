@@ -36,7 +36,12 @@ def _round16(x, t):
     return torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(dt).float().numpy()
 
 
-ACT = {1: lambda v: np.maximum(v, 0), 6: lambda v: v, 3: lambda v: np.where(v > 0, v, 0.01 * v),
+def _softmax(v):
+    e = np.exp(v - v.max(-1, keepdims=True))
+    return e / e.sum(-1, keepdims=True)
+
+
+ACT = {1: lambda v: np.maximum(v, 0), 6: lambda v: v, 3: lambda v: np.where(v > 0, v, 0.01 * v), 5: _softmax,
        2: np.tanh, 0: lambda v: 1 / (1 + np.exp(-v)),
        4: lambda v: np.where(v > 1, 1 + 0.01 * (v - 1), np.where(v < 0, 0.01 * v, v))}
 
@@ -159,7 +164,7 @@ def test_gemv_against_float64(spg, k, oracle, prec, int_path, out, inn, n):
     payload = torch.from_numpy(np.concatenate([raw[skip:], np.zeros(256, np.uint8)])).cuda()
     bias = rng.standard_normal(out).astype(np.float32) * 0.1
     bd = torch.from_numpy(bias).cuda()
-    act = [1, 6, 3, 2, 0, 4][(out + n) % 6]
+    act = [1, 6, 3, 2, 0, 4, 5][(out + n) % 7]                 # 5 = softmax, finished by the last CTA of the kernel
     L = spg.abi.KLayer(payload.data_ptr(), bd.data_ptr(), scale, inn, out, prec, act)
     x = rng.standard_normal((n, inn)).astype(np.float32)
     xd = torch.from_numpy(x).cuda()
@@ -174,7 +179,9 @@ def test_gemv_against_float64(spg, k, oracle, prec, int_path, out, inn, n):
         rc = k.spgk_layer_gemv(C.byref(L), xd.data_ptr(), inn, y.data_ptr(), out, n, scratch.data_ptr(), None)
         assert rc == 0, k.spgk_error_string()
         torch.cuda.synchronize()
-        want = ACT[act](x.astype(np.float64) @ dec.T + bias)
+        want = x.astype(np.float64) @ dec.T + bias
+        if act != 5 or n == 1:                # more than one row: a softmax layer is left as logits for spgk_softmax_rows
+            want = ACT[act](want)
         got = y.cpu().numpy()
         assert np.all(got[n] == -9.0)
         # bf16 path, one row: three bf16 terms (24 bits); more rows: two terms (16 bits) per activation
