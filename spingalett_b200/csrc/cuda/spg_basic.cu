@@ -308,6 +308,7 @@ spg_split16_kernel(const float *__restrict__ x, uint32_t ldx, uint32_t N, uint32
     }
 }
 
+
 thread_local const uint32_t *spg_tls_rows_limit = nullptr;
 thread_local uint32_t spg_tls_rows_expected = 0;
 thread_local float spg_tls_margin_theta = 0.0f;

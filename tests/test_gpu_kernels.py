@@ -358,3 +358,4 @@ def test_device_resident_row_count_with_gather_and_scatter(spg, k, cap, K, rows,
     touched = np.where((got != -3.0).any(1))[0]
     assert touched.tolist() == sorted(rows)
     assert np.abs(got[rows] - want).max() <= 2e-6
+
