@@ -75,7 +75,8 @@ def parse():
     ap.add_argument("--dtype", default=None, choices=PRECS)
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--math", default="auto", choices=["auto", "exact", "fast"])
-    ap.add_argument("--all-dtypes", action="store_true", help="also report every stored precision (fewer steps each)")
+    ap.add_argument("--all-dtypes", action="store_true", help="also report every stored precision (fewer steps each); on by default for the mlp workload")
+    ap.add_argument("--one-dtype", action="store_true", help="skip the per-dtype table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -386,12 +387,13 @@ def main():
                             "note": "frac: event pairs around each layer kernel in a separate pass (events keep a layer from "
                                     "prefetching weights under the previous one); whole_step_frac: algorithmic bytes / ms_per_step "
                                     "of the timed loop, staging and softmax included"}
-    if args.all_dtypes:
+    if (args.all_dtypes or args.workload == "mlp") and not args.one_dtype:
         per = {}
         for dt in PRECS:
             _, (d_ms, e_ms, km, kc, _, _), _ = run_dtype(dt, max(5, args.steps // 2), 3)
+            ktf = (flops_per_sample(topo) * batch * max(5, args.steps // 2) / (km * 1e-3) / 1e12) if kc else None
             per[dt] = {"value": batch * world / (d_ms * 1e-3), "e2e": batch * world / (e_ms * 1e-3),
-                       "kernel_tflops": (flops_per_sample(topo) * batch * max(5, args.steps // 2) / (km * 1e-3) / 1e12) if kc else None}
+                       "kernel_tflops": ktf, "roofline_frac": (ktf / pk["bf16_tflops"]) if ktf else None}
         line["per_dtype"] = per
     if rank == 0 and world == 1 and not args.no_cpu:
         sample = min(batch, 16384 if args.workload == "mlp" else 64)

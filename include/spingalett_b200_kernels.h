@@ -81,6 +81,10 @@ SPGK_API int spgk_event_create(void **event);
 SPGK_API int spgk_event_destroy(void *event);
 SPGK_API int spgk_event_record(void *event, void *stream);
 SPGK_API int spgk_event_elapsed_ms(void *start, void *stop, float *ms);
+/* a second (non-blocking) stream and cross-stream ordering, for copies that overlap compute */
+SPGK_API int spgk_stream_create(void **stream);
+SPGK_API int spgk_stream_destroy(void *stream);
+SPGK_API int spgk_stream_wait_event(void *stream, void *event);
 
 /* ---- K0: general layer, fp32 SIMT ---------------------------------------
  * y[n][j] = act(bias[j] + w_scale * sum_k q[j][k] * x[n][k]) for any
@@ -137,6 +141,13 @@ SPGK_API int spgk_split16(const float *x, uint32_t ldx, uint32_t N, uint32_t in,
 SPGK_API int spgk_split16_rows(const float *x, uint32_t ldx, const uint32_t *rows_idx, uint32_t N, uint32_t in,
                           void *dst, uint32_t ld16, uint64_t plane_elems,
                           int parts, int type, void *stream);
+
+/* ---- array encoders of the .nn format on the device -------------------------
+ * dst receives exactly the bytes write_array_compressed (Serialize.c:87-193) writes for src[0..count): fp32 copy,
+ * truncated fp16 / bf16 words, or [abs-max float][packed INT8 / INT4 / INT2].  dst: dev, spgk_encoded_bytes(count,
+ * precision) bytes, 4-byte aligned for the integer formats.  Stream-ordered, no host synchronisation. */
+SPGK_API size_t spgk_encoded_bytes(uint64_t count, int precision);
+SPGK_API int spgk_encode_array(const float *src, uint64_t count, int precision, uint8_t *dst, void *stream);
 
 /* ---- K1: small-batch fused dequant-GEMV ----------------------------------
  * Whole layer for 1 <= N <= SPGK_GEMV_MAX_BATCH rows: streams the packed

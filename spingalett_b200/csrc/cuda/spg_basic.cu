@@ -91,6 +91,9 @@ int spgk_event_create(void **event)
 }
 int spgk_event_destroy(void *event) { if (event) SPGK_CUDA(cudaEventDestroy((cudaEvent_t)event)); return SPGK_OK; }
 int spgk_event_record(void *event, void *stream) { SPGK_CUDA(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream)); return SPGK_OK; }
+int spgk_stream_create(void **stream) { cudaStream_t s; SPGK_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking)); *stream = s; return SPGK_OK; }
+int spgk_stream_destroy(void *stream) { if (stream) SPGK_CUDA(cudaStreamDestroy((cudaStream_t)stream)); return SPGK_OK; }
+int spgk_stream_wait_event(void *stream, void *event) { SPGK_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0)); return SPGK_OK; }
 int spgk_event_elapsed_ms(void *start, void *stop, float *ms) { SPGK_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop)); return SPGK_OK; }
 int spgk_is_device_pointer(const void *ptr)
 {

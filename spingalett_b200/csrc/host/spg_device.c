@@ -92,6 +92,8 @@ void spg_dev_release(spg_net *n)
     spgk_free(n->d_w16); n->d_w16 = NULL; n->w16_bytes = 0;
     spgk_free(n->d_head_w); n->d_head_w = NULL;
     spgk_host_free(n->h_count); n->h_count = NULL; n->count_pending = false; n->count_seen = false;
+    for (int i = 0; i <= SPG_PIPE_MAX; i++) { if (n->copy_ev[i]) spgk_event_destroy(n->copy_ev[i]); n->copy_ev[i] = NULL; }
+    spgk_stream_destroy(n->copy_stream); n->copy_stream = NULL;
     for (int t = 0; t < 2; t++) {
         if (n->d_w16c[t]) for (uint32_t l = 0; l < n->dev_layers; l++) spgk_free(n->d_w16c[t][l]);
         free(n->d_w16c[t]); n->d_w16c[t] = NULL;
@@ -212,7 +214,10 @@ uint32_t spingalett_last_repaired(NeuralNetwork *net)
     spg_net *n = spg_priv(net);
     if (n->count_pending) {                       /* the count was copied asynchronously: wait for it */
         n->count_pending = false;
-        if (spgk_stream_sync(n->stream) == 0 && n->h_count) n->last_repaired = *n->h_count;
+        if (spgk_stream_sync(n->stream) == 0 && n->h_count) {
+            n->last_repaired = 0;
+            for (uint32_t i = 0; i < n->count_slots_used; i++) n->last_repaired += n->h_count[i];
+        }
     }
     return n->last_repaired;
 }
@@ -589,11 +594,14 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
      * travels to pinned host memory for spingalett_last_repaired(). */
     if (!n->h_count) {
         void *h = NULL;
-        if ((rc = spg_map_kernel_error(spgk_host_alloc(&h, 64), "repair count (host)"))) return rc;
+        if ((rc = spg_map_kernel_error(spgk_host_alloc(&h, 256), "repair count (host)"))) return rc;
         n->h_count = h;
+        memset(h, 0, 256);
     }
-    const uint32_t expected = n->count_seen ? *(volatile uint32_t *)n->h_count : 0;    /* the count of the call before: a guide to tile shapes only */
-    if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(n->h_count, d_count, 4, n->stream), "repair count"))) return rc;
+    uint32_t *h_slot = n->h_count + n->count_slot;
+    const uint32_t expected = n->count_seen ? *(volatile uint32_t *)h_slot : 0;    /* the count of the call before: a guide to tile shapes only */
+    if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(h_slot, d_count, 4, n->stream), "repair count"))) return rc;
+    if (n->count_slot + 1 > n->count_slots_used) n->count_slots_used = n->count_slot + 1;
     n->count_pending = true; n->count_seen = true;
     if (Llast->act == ACT_SOFTMAX && Llast->out > spgk_gemm_tc_softmax_max()) {
         if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
@@ -648,10 +656,22 @@ float *forward_batch_struct_arguments(ForwardBatchArgs a)
 
     const float *d_x = a.inputs;
     const bool in_dev = spgk_is_device_pointer(a.inputs) == 1;
+    /* Large host batches are cut into chunks whose copies run on a second stream ahead of the compute: the
+     * call is bound by the host link, and this hides all compute but the last chunk's behind the copies. */
+    const uint32_t chunk_rows = 16384;
+    const uint32_t chunks = (N + chunk_rows - 1) / chunk_rows;
+    const bool pipelined = !in_dev && N >= 2 * chunk_rows && chunks <= SPG_PIPE_MAX;
     if (!in_dev) {
         if (reserve((void **)&n->d_in32, &n->in32_bytes, in_bytes, "forward_batch: input staging")) return NULL;
-        if (spg_map_kernel_error(spgk_memcpy_h2d(n->d_in32, a.inputs, in_bytes, n->stream), "forward_batch: input copy")) return NULL;
         d_x = n->d_in32;
+        if (pipelined) {
+            if (!n->copy_stream && spg_map_kernel_error(spgk_stream_create(&n->copy_stream), "forward_batch: copy stream")) return NULL;
+            for (uint32_t c = 0; c <= chunks; c++)
+                if (!n->copy_ev[c] && spg_map_kernel_error(spgk_event_create(&n->copy_ev[c]), "forward_batch: copy event")) return NULL;
+            /* the staging buffer may still be read by earlier work on the compute stream */
+            if (spg_map_kernel_error(spgk_event_record(n->copy_ev[0], n->stream), "forward_batch: pipeline") ||
+                spg_map_kernel_error(spgk_stream_wait_event(n->copy_stream, n->copy_ev[0]), "forward_batch: pipeline")) return NULL;
+        } else if (spg_map_kernel_error(spgk_memcpy_h2d(n->d_in32, a.inputs, in_bytes, n->stream), "forward_batch: input copy")) return NULL;
     }
 
     /* Up to 8 rows always take the weight-streaming chain; up to 512 rows do so (in groups of at most 128
@@ -673,7 +693,28 @@ float *forward_batch_struct_arguments(ForwardBatchArgs a)
             if (reserve((void **)&n->d_out32, &n->out32_bytes, out_bytes, "forward_batch: output staging")) return NULL;
             d_out = n->d_out32;
         }
-        if (spg_dev_forward_large(n, d_x, N, d_out)) return NULL;
+        n->count_slot = 0; n->count_slots_used = 0;
+        if (pipelined) {
+            /* compute on chunk c starts as soon as its copy has landed, while the copies of the later chunks go on */
+            /* copy c is queued before compute c-1 is launched, so a pageable source (whose copies block the host)
+             * overlaps as well as a pinned one */
+            for (uint32_t c = 0; c <= chunks; c++) {
+                if (c < chunks) {
+                    const size_t r0 = (size_t)c * chunk_rows, rows = N - r0 < chunk_rows ? N - r0 : chunk_rows;
+                    if (spg_map_kernel_error(spgk_memcpy_h2d(n->d_in32 + r0 * in0, a.inputs + r0 * in0, rows * in0 * sizeof(float), n->copy_stream),
+                                             "forward_batch: input copy") ||
+                        spg_map_kernel_error(spgk_event_record(n->copy_ev[c + 1], n->copy_stream), "forward_batch: pipeline")) return NULL;
+                }
+                if (c >= 1) {
+                    const uint32_t k = c - 1, r0 = k * chunk_rows, rows = N - r0 < chunk_rows ? N - r0 : chunk_rows;
+                    if (spg_map_kernel_error(spgk_stream_wait_event(n->stream, n->copy_ev[k + 1]), "forward_batch: pipeline")) return NULL;
+                    n->count_slot = k;
+                    const int rc = spg_dev_forward_large(n, d_x + (size_t)r0 * in0, rows, d_out + (size_t)r0 * outw);
+                    n->count_slot = 0;
+                    if (rc) return NULL;
+                }
+            }
+        } else if (spg_dev_forward_large(n, d_x, N, d_out)) return NULL;
         if (!out_dev && spg_map_kernel_error(spgk_memcpy_d2h(result, d_out, out_bytes, n->stream), "forward_batch: output copy")) return NULL;
     }
     /* device-to-device calls are stream-ordered like any CUDA library call: the caller

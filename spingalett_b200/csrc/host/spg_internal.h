@@ -13,6 +13,7 @@
 #include "spingalett_b200_kernels.h"
 #include <stdint.h>
 #include <stdbool.h>
+#define SPG_PIPE_MAX 16        /* most chunks a host-input batch is cut into */
 #include <stddef.h>
 
 #define SPG_ERRMSG_MAX 256
@@ -52,7 +53,9 @@ typedef struct {
     /* AUTO math mode: rows recomputed exactly after the one-term pass */
     uint32_t *d_rep_idx; size_t rep_idx_bytes; float *d_rep_in; size_t rep_in_bytes; float *d_rep_out; size_t rep_out_bytes;
     uint32_t last_repaired; bool auto_calibrated; float auto_theta;
-    uint32_t *h_count; bool count_pending, count_seen;      /* pinned copy of the repaired-row count of the last AUTO call */
+    uint32_t *h_count; bool count_pending, count_seen;      /* pinned: [slot] repaired-row counts of the last AUTO call (one slot per pipelined chunk) */
+    uint32_t count_slot, count_slots_used;
+    void *copy_stream; void *copy_ev[SPG_PIPE_MAX + 1];      /* host-input pipeline: copies run ahead of compute */
 
     /* large-batch workspace */
     float *d_in32;  size_t in32_bytes;      /* staging for host inputs */

@@ -151,9 +151,41 @@ fail:
     return NULL;
 }
 
-static bool write_array(FILE *f, const float *src, uint32_t count, PrecisionMode p, uint8_t *scratch)
+/* Arrays of a million elements or more are quantised on the GPU when one is there (upload, encode kernels, read
+ * the packed bytes back: the scalar host loops below take seconds on a half-billion-weight net); the bytes are
+ * the same either way, and without a device, with SPINGALETT_HOST_ENCODE set in the environment, or if anything on
+ * that route fails, the host encoder does the work. */
+#define SPG_DEV_ENCODE_MIN (1u << 20)
+typedef struct { float *d_src; uint8_t *d_dst; bool ok; } dev_encoder;
+
+static void dev_encoder_open(dev_encoder *de, uint32_t max_count)
 {
-    size_t n = spg_encode_array(src, count, p, scratch);
+    de->d_src = NULL; de->d_dst = NULL; de->ok = false;
+    int count = 0;
+    if (max_count < SPG_DEV_ENCODE_MIN || getenv("SPINGALETT_HOST_ENCODE") || spgk_device_count(&count) != 0 || count <= 0) return;
+    void *a = NULL, *b = NULL;
+    if (spgk_malloc(&a, (size_t)max_count * 4) == 0 && spgk_malloc(&b, (size_t)max_count * 4 + 16) == 0) {
+        de->d_src = a; de->d_dst = b; de->ok = true;
+    } else {
+        spgk_free(a); spgk_free(b);
+    }
+}
+
+static void dev_encoder_close(dev_encoder *de) { spgk_free(de->d_src); spgk_free(de->d_dst); de->ok = false; }
+
+static bool write_array(FILE *f, const float *src, uint32_t count, PrecisionMode p, uint8_t *scratch, dev_encoder *de)
+{
+    size_t n = 0;
+    if (de && de->ok && count >= SPG_DEV_ENCODE_MIN && p != PRECISION_FLOAT32) {
+        n = spgk_encoded_bytes(count, (int)p);
+        if (spgk_memcpy_h2d(de->d_src, src, (size_t)count * 4, NULL) || spgk_encode_array(de->d_src, count, (int)p, de->d_dst, NULL) ||
+            spgk_memcpy_d2h(scratch, de->d_dst, n, NULL) || spgk_stream_sync(NULL)) {
+            spg_log(LOG_DEBUG, "save: device encoder unavailable, using the host encoder");
+            de->ok = false;
+            n = 0;
+        }
+    }
+    if (!n) n = spg_encode_array(src, count, p, scratch);
     return fwrite(scratch, 1, n, f) == n;
 }
 
@@ -212,18 +244,21 @@ void save_spingalett_struct_arguments(SaveArgs a)
         free(scratch); free(zeros); fclose(f); free(path);
         return;
     }
+    dev_encoder de;
+    dev_encoder_open(&de, a.precision != PRECISION_FLOAT32 ? maxc : 0);
     for (uint32_t l = 0; l + 1 < n->layers && ok; l++) {
         uint32_t wc = n->topology[l] * n->topology[l + 1], bc = n->topology[l + 1];
         uint64_t wo = n->weight_offsets[l], bo = n->bias_offsets[l];
-        ok = write_array(f, n->weights + wo, wc, a.precision, scratch);
+        ok = write_array(f, n->weights + wo, wc, a.precision, scratch, &de);
         if (ok && has_opt)
-            ok = write_array(f, zeros ? zeros : n->opt_m_weights + wo, wc, a.precision, scratch) &&
-                 write_array(f, zeros ? zeros : n->opt_v_weights + wo, wc, a.precision, scratch);
-        if (ok) ok = write_array(f, n->biases + bo, bc, a.precision, scratch);
+            ok = write_array(f, zeros ? zeros : n->opt_m_weights + wo, wc, a.precision, scratch, &de) &&
+                 write_array(f, zeros ? zeros : n->opt_v_weights + wo, wc, a.precision, scratch, &de);
+        if (ok) ok = write_array(f, n->biases + bo, bc, a.precision, scratch, &de);
         if (ok && has_opt)
-            ok = write_array(f, zeros ? zeros : n->opt_m_biases + bo, bc, a.precision, scratch) &&
-                 write_array(f, zeros ? zeros : n->opt_v_biases + bo, bc, a.precision, scratch);
+            ok = write_array(f, zeros ? zeros : n->opt_m_biases + bo, bc, a.precision, scratch, &de) &&
+                 write_array(f, zeros ? zeros : n->opt_v_biases + bo, bc, a.precision, scratch, &de);
     }
+    dev_encoder_close(&de);
     free(scratch); free(zeros);
     if (fclose(f) != 0) ok = false;
     if (!ok) {

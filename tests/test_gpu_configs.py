@@ -78,3 +78,20 @@ def test_large_int4_mlp_batch_sweep(spg, l_net, n):
             lib.spgk_gemv_set_int_path(1)
         assert spg.last_path() == "gemv"
         assert np.abs(other - got).max() <= 2e-6, np.abs(other - got).max()
+
+
+@pytest.mark.parametrize("prec", ["fp16", "bf16", "int8", "int4", "int2"])
+def test_save_through_the_device_encoder_writes_the_same_file(spg, has_gpu, tmp_path, prec, monkeypatch):
+    """Arrays of a million elements or more are quantised on the GPU by save_spingalett; the file must equal the one
+    the host encoder writes."""
+    assert has_gpu
+    p = {"fp16": 1, "bf16": 2, "int8": 3, "int4": 4, "int2": 5}[prec]
+    # 1 134 100 weights in the first matrix: above the threshold, and an odd count for the 4- and 2-bit tails
+    net = spg.Network.build([1100, 1031, 10], [spg.abi.ACT_RELU, spg.abi.ACT_SOFTMAX], seed=99)
+    a, b = str(tmp_path / "dev.nn"), str(tmp_path / "host.nn")
+    net.save(a, p, with_optimizer=True)
+    monkeypatch.setenv("SPINGALETT_HOST_ENCODE", "1")
+    net.save(b, p, with_optimizer=True)
+    monkeypatch.delenv("SPINGALETT_HOST_ENCODE")
+    assert open(a, "rb").read() == open(b, "rb").read()
+    net.free()

@@ -359,3 +359,32 @@ def test_device_resident_row_count_with_gather_and_scatter(spg, k, cap, K, rows,
     assert touched.tolist() == sorted(rows)
     assert np.abs(got[rows] - want).max() <= 2e-6
 
+
+
+@pytest.mark.parametrize("prec", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("count", [1, 7, 1000, (1 << 20) + 3])
+def test_encode_array_matches_the_reference_bytes(spg, k, oracle, prec, count):
+    """Device-side array encoder vs the oracle's restatement of write_array_compressed (itself pinned to files the
+    reference wrote): byte for byte, for every precision, odd tails and awkward values."""
+    import torch
+    lib = k
+    vp = C.c_void_p
+    lib.spgk_encoded_bytes.argtypes = [C.c_uint64, C.c_int]
+    lib.spgk_encoded_bytes.restype = C.c_size_t
+    lib.spgk_encode_array.argtypes = [vp, C.c_uint64, C.c_int, vp, vp]
+    rng = np.random.default_rng(prec * 100 + count % 97)
+    x = (rng.standard_normal(count) * rng.choice([1e-3, 0.1, 1.0, 30.0])).astype(np.float32)
+    special = np.array([0.0, -0.0, 1e-8, -1e-8, 6.1e-5, 65504.0, 65520.0, 1e5, -1e5, 1e-40, 0.5, -0.5, 1.5, 2.5], np.float32)
+    if prec in (1, 2):                                   # the float formats also see non-finite values
+        special = np.concatenate([special, np.array([np.inf, -np.inf, np.nan], np.float32)])
+    m = min(count, len(special))
+    x[:m] = special[:m]
+    want = oracle.Oracle.encode(x, prec)
+    nbytes = lib.spgk_encoded_bytes(count, prec)
+    assert nbytes == len(want)
+    src = torch.from_numpy(x).cuda()
+    dst = torch.full((nbytes + 8,), 0xAB, dtype=torch.uint8, device="cuda")
+    assert lib.spgk_encode_array(src.data_ptr(), count, prec, dst.data_ptr(), None) == 0, lib.spgk_error_string()
+    got = dst.cpu().numpy()
+    assert np.all(got[nbytes:] == 0xAB)
+    assert np.array_equal(got[:nbytes], np.frombuffer(want.tobytes(), np.uint8))
