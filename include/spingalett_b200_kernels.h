@@ -181,6 +181,12 @@ SPGK_API int spgk_layer_gemv(const spgk_layer *L, const float *x, uint32_t ldx,
  *             for a layer whose `in` is `width`.
  * y (fp32) is always written as well. */
 SPGK_API size_t spgk_gemv_staged_bytes(uint32_t width, uint32_t N);
+/* The whole run of layers of a small-batch forward in ONE launch (the CTAs stay on their SMs, weights of the next layer
+ * stream in while a layer finishes, a device-wide counter orders only the staged inputs).  Returns SPGK_E_UNSUPPORTED
+ * unless every layer is eligible with the same stored precision and chunk geometry and only the last is a softmax
+ * layer: then call spgk_layer_gemv_chain layer by layer.  ys[l]: fp32 output of layer l, [N][out_l]. */
+SPGK_API int spgk_gemv_forward_chain(const spgk_layer *layers, uint32_t n, const float *x, uint32_t ldx, float *const *ys, uint32_t N,
+                                     void *staged_a, void *staged_b, void *scratch, void *stream);
 /* status word at the start of scratch: SPGK_E_TIMEOUT if a bounded wait inside the kernel gave up (synchronises) */
 SPGK_API int spgk_gemv_status(void *scratch, void *stream);
 SPGK_API int spgk_gemv_chain_stages_next(const spgk_layer *L, const spgk_layer *next, uint32_t N);

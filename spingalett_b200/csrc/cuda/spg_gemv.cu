@@ -98,6 +98,17 @@ struct GemvParams {
     int softmax;                            // the layer ends in a row softmax: the CTA that finishes last applies it
 };
 
+// One launch may run a whole run of layers (same stored precision, same batch, each feeding the next): the CTAs
+// keep streaming weights across the layer boundaries and only the staged input of a layer waits for the layer
+// before it (a device-wide counter the epilogue warps bump when their share of a layer is done).
+constexpr uint32_t MAX_CHAIN = 8;
+struct ChainMaps { CUtensorMap m[MAX_CHAIN]; };
+struct ChainParams {
+    GemvParams L[MAX_CHAIN];
+    uint32_t n;                             // layers in this launch (1 = the plain single-layer call)
+    int32_t *sync;                          // [MAX_CHAIN] layer-done counters + [1] exit ticket, all zero between launches
+};
+
 // elements covered by one 128-bit load, per stored precision
 template <int PREC> struct Fmt;
 template <> struct Fmt<SPG_P_I4>   { static constexpr int EL = 32; };
@@ -356,18 +367,36 @@ __device__ __forceinline__ void bulk_copy_1d(uint32_t dst, const void *src, uint
 __device__ __forceinline__ void handoff_arrive(uint32_t id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(HANDOFF_THREADS) : "memory"); }
 __device__ __forceinline__ void handoff_wait(uint32_t id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(HANDOFF_THREADS) : "memory"); }
 
-// Row softmax of a finished layer, run by the epilogue warp of the CTA that finishes last (a ticket next to the
-// status word tells which one): Activation.c:5-21 per row -- maximum from -FLT_MAX, expf(x - max), and the
-// scaling by 1/sum only when the sum is positive.
-__device__ __forceinline__ void gemv_final_softmax(const GemvParams &p, uint32_t lane)
+// Bounded wait until `target` CTAs have finished a layer (device-scope acquire on the layer's counter).
+__device__ __forceinline__ bool grid_wait(const int32_t *counter, uint32_t target, volatile int *abort_flag, int32_t *status, int code)
 {
+    if (*abort_flag) return false;
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if ((uint32_t)v >= target) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
+        __nanosleep(64);
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+// End of the launch, epilogue warp: the CTA that finishes last (an exit ticket) applies the row softmax of a
+// final softmax layer (Activation.c:5-21 per row -- maximum from -FLT_MAX, expf(x - max), scaling by 1/sum only
+// when the sum is positive) and puts the layer counters and the ticket back to zero for the next launch.
+__device__ __forceinline__ void chain_finish(const ChainParams &ch, uint32_t lane)
+{
+    const GemvParams &p = ch.L[ch.n - 1];
+    if (!p.softmax && ch.n == 1) return;
     __threadfence();                                           // this CTA's outputs are visible before its ticket
     uint32_t ticket = 0;
-    if (lane == 0) ticket = atomicAdd(reinterpret_cast<unsigned int *>(p.status + 1), 1u);
+    if (lane == 0) ticket = atomicAdd(reinterpret_cast<unsigned int *>(ch.sync + MAX_CHAIN), 1u);
     ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
     if (ticket != gridDim.x - 1) return;
     __threadfence();
-    for (uint32_t n = 0; n < p.N; n++) {
+    for (uint32_t n = 0; p.softmax && n < p.N; n++) {
         float *r = p.y + (uint64_t)n * p.ldy;
         if (p.out <= 1024) {
             // the whole row in registers: one trip to L2 and back
@@ -396,7 +425,7 @@ __device__ __forceinline__ void gemv_final_softmax(const GemvParams &p, uint32_t
             for (uint32_t i = lane; i < p.out; i += 32u) r[i] *= inv;
         }
     }
-    if (lane == 0) p.status[1] = 0;                            // ready for the next launch
+    if (lane <= MAX_CHAIN) ch.sync[lane] = 0;                  // ready for the next launch
 }
 
 // One step of one warp: 16 rows x (4 lanes x EL elements).  ra / rbv are the lane's 128-bit pieces of rows
@@ -526,12 +555,13 @@ __device__ __forceinline__ void gemv_step_int(const uint4 &ra, const uint4 &rbv,
 
 template <int PREC, int T, int CW, bool INTP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
-spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
+spg_gemv_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ ChainParams ch)
 {
     using F = Fmt<PREC>;
     constexpr uint32_t EL = F::EL, NB = EL / 4;                // per warp step: 4 lanes x EL elements; NB B-blocks per load
     constexpr uint32_t STEP_SLOTS = (INTP ? EL / 8 : NB) * T * 4 * CW;   // uint2 slots of staged input per step
     constexpr uint32_t CPAD = 8 * T;
+    const GemvParams &p0 = ch.L[0];                             // chunk geometry, ring depth and batch are the same for every layer
 
     extern __shared__ uint8_t gemv_smem_raw[];
     const uint32_t raw = gsmem_u32(gemv_smem_raw);
@@ -539,55 +569,81 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
     uint8_t *smem = gemv_smem_raw + (base - raw);
     // layout: ring of chunks, each = [16 rows x 8 warp slices of packed weights | staged input of the same K range];
     // then the reduction buffer, the barriers and the abort flag
-    const uint32_t wchunk_bytes = 8 * p.box_bytes;
-    const uint32_t slot_bytes = wchunk_bytes + p.xchunk_bytes;
-    const uint32_t red_off = p.ring * slot_bytes;
+    const uint32_t wchunk_bytes = 8 * p0.box_bytes;
+    const uint32_t slot_bytes = wchunk_bytes + p0.xchunk_bytes;
+    const uint32_t ring = p0.ring;
+    const uint32_t red_off = ring * slot_bytes;
     constexpr uint32_t RED_FLOATS = (INTP ? 1 : CONSUMER_WARPS) * ITEM_ROWS * CPAD;   // integer path: one shared buffer of sums
     const uint32_t bar_off = red_off + 2 * RED_FLOATS * 4;       // two reduction buffers, used alternately
-    const uint32_t full0 = base + bar_off, empty0 = full0 + 8 * p.ring;
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + bar_off + 16 * p.ring);
+    const uint32_t full0 = base + bar_off, empty0 = full0 + 8 * ring;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + bar_off + 16 * ring);
     float *red = reinterpret_cast<float *>(smem + red_off);
+    int32_t *status = p0.status;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     if (INTP) for (uint32_t i = tid; i < 2 * RED_FLOATS; i += GEMV_THREADS) red[i] = 0.0f;      // integer zero too
     if (tid == 0) {
-        for (uint32_t s = 0; s < p.ring; s++) { gbar_init(full0 + 8 * s, 1); gbar_init(empty0 + 8 * s, CONSUMER_WARPS); }
+        for (uint32_t s = 0; s < ring; s++) { gbar_init(full0 + 8 * s, 1); gbar_init(empty0 + 8 * s, CONSUMER_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
+        for (uint32_t l = 0; l < ch.n; l++) asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.m[l]) : "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel may start on SMs this grid leaves
     }
     __syncthreads();
+    // items of this CTA over all layers (the consumer <-> epilogue hand-off counts them through)
+    uint32_t my_total = 0;
+    for (uint32_t l = 0; l < ch.n; l++) my_total += ch.L[l].items > blockIdx.x ? (ch.L[l].items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------ producer: two copies per chunk -------------------
-        // The weights do not depend on the layer before this one, the staged input does: the first ring of
-        // weight boxes is requested at once, and only then does the thread wait for the preceding kernel in
-        // the stream (programmatic dependent launch), so the start of this layer overlaps the end of the last.
+        // The weights of a layer depend on nothing that runs before it, its staged input does: on the kernel before
+        // this one in the stream (layer 0, programmatic dependent launch) or on every CTA's share of the layer
+        // before (a device-wide counter).  So weight boxes are requested as far ahead as the ring allows, the
+        // input copies of the chunks issued meanwhile are held back, and only when nothing else can be done does
+        // the thread wait for the input to exist.  The HBM stream therefore runs through layer boundaries.
         if (lane == 0) {
-            const uint32_t my_items = p.items > blockIdx.x ? (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-            const uint32_t total = my_items * p.nchunks;
-            const uint32_t head = total < p.ring ? total : p.ring;
-            for (uint32_t q = 0; q < head; q++) {                       // slots are free at the start: no wait needed
-                const uint32_t item = blockIdx.x + (q / p.nchunks) * gridDim.x, c = q % p.nchunks;
-                gbar_expect_tx(full0 + 8 * q, slot_bytes);
-                tma_box_2d(base + q * slot_bytes, &wmap, full0 + 8 * q, (int)(c * (wchunk_bytes / ITEM_ROWS / 8)), (int)(item * ITEM_ROWS));
-            }
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (uint32_t q = 0; q < head; q++) {
-                const uint32_t c = q % p.nchunks;
-                bulk_copy_1d(base + q * slot_bytes + wchunk_bytes,
-                             reinterpret_cast<const uint8_t *>(p.xin) + (size_t)c * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * q);
-            }
-            uint32_t s = head == p.ring ? 0 : head, ph = head == p.ring ? 0 : 1;
-            for (uint32_t q = head; q < total; q++) {
-                const uint32_t item = blockIdx.x + (q / p.nchunks) * gridDim.x, c = q % p.nchunks;
-                if (!gbar_wait(empty0 + 8 * s, ph, abort_flag, p.status, 1)) break;
-                gbar_expect_tx(full0 + 8 * s, slot_bytes);
-                tma_box_2d(base + s * slot_bytes, &wmap, full0 + 8 * s, (int)(c * (wchunk_bytes / ITEM_ROWS / 8)), (int)(item * ITEM_ROWS));
-                bulk_copy_1d(base + s * slot_bytes + wchunk_bytes,
-                             reinterpret_cast<const uint8_t *>(p.xin) + (size_t)c * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * s);
-                if (++s == p.ring) { s = 0; ph ^= 1u; }
+            uint32_t s = 0, ph = 1, q = 0, npend = 0;
+            uint32_t pend_slot[8], pend_c[8];
+            bool alive = true;
+            for (uint32_t l = 0; l < ch.n && alive; l++) {
+                const GemvParams &p = ch.L[l];
+                bool x_ready = false;
+                auto make_ready = [&]() -> bool {
+                    if (l == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+                    else if (!grid_wait(ch.sync + (l - 1), gridDim.x, abort_flag, status, 7)) return false;
+                    for (uint32_t i = 0; i < npend; i++)
+                        bulk_copy_1d(base + pend_slot[i] * slot_bytes + wchunk_bytes,
+                                     reinterpret_cast<const uint8_t *>(p.xin) + (size_t)pend_c[i] * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * pend_slot[i]);
+                    npend = 0;
+                    x_ready = true;
+                    return true;
+                };
+                for (uint32_t item = blockIdx.x; item < p.items && alive; item += gridDim.x) {
+                    for (uint32_t c = 0; c < p.nchunks; c++, q++) {
+                        if (q >= ring) {
+                            // a held-back input copy keeps its slot from ever filling: settle those before blocking on a slot
+                            if (!x_ready && (npend == ring || npend == 8) && !make_ready()) { alive = false; break; }
+                            if (!x_ready) {
+                                uint32_t ok;
+                                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                             : "=r"(ok) : "r"(empty0 + 8 * s), "r"(ph) : "memory");
+                                if (!ok && !make_ready()) { alive = false; break; }
+                            }
+                            if (!gbar_wait(empty0 + 8 * s, ph, abort_flag, status, 1)) { alive = false; break; }
+                        }
+                        gbar_expect_tx(full0 + 8 * s, slot_bytes);
+                        tma_box_2d(base + s * slot_bytes, &maps.m[l], full0 + 8 * s, (int)(c * (wchunk_bytes / ITEM_ROWS / 8)), (int)(item * ITEM_ROWS));
+                        if (x_ready) {
+                            bulk_copy_1d(base + s * slot_bytes + wchunk_bytes,
+                                         reinterpret_cast<const uint8_t *>(p.xin) + (size_t)c * p.xchunk_bytes, p.xchunk_bytes, full0 + 8 * s);
+                        } else {
+                            pend_slot[npend] = s; pend_c[npend] = c; npend++;
+                            if (npend == 8 && !make_ready()) { alive = false; break; }
+                        }
+                        if (++s == ring) { s = 0; ph ^= 1u; }
+                    }
+                }
+                if (alive && npend && !make_ready()) alive = false;        // every chunk of the layer went out before its input existed
             }
         }
         return;
@@ -597,9 +653,28 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
         // ------------------------------ epilogue warp ------------------------------
         // Sums the sixteen K slices and the activation terms of each finished item, applies scale, bias and
         // activation, writes y and stages the next layer's input, while the consumers stream the next item.
-        const uint32_t cs = CW * T, spare = cs - p.C;
         uint32_t n_item = 0;
-        asm volatile("griddepcontrol.wait;" ::: "memory");       // everything this warp reads or writes is ordered after the kernel before
+        bool dead = false;                                      // a bounded wait gave up: keep the hand-offs going, do no work
+        for (uint32_t l = 0; l < ch.n; l++) {
+        const GemvParams &p = ch.L[l];
+        const uint32_t cs = CW * T, spare = cs - p.C;
+        // everything this warp reads or writes is ordered after the kernel before (first layer) or after every
+        // CTA's share of the layer before
+        if (l == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+        else if (!dead) {
+            bool ok = true;
+            if (lane == 0) ok = grid_wait(ch.sync + (l - 1), gridDim.x, abort_flag, status, 8);
+            if (!__shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0)) dead = true;
+            __threadfence();
+        }
+        if (dead) {
+            // the consumers still arrive at and wait on the named barriers: answer them so that nobody hangs
+            for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
+                handoff_wait(1 + (n_item & 1u));
+                if (n_item + 2 < my_total) handoff_arrive(3 + (n_item & 1u));
+            }
+            continue;
+        }
         if constexpr (INTP) {
             // ---- integer path: exact integer dot products; scales and the next layer's range bound first ----
             __shared__ float e_sc[MAX_BATCH], e_inv[MAX_BATCH];
@@ -607,11 +682,14 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
             const long long *iparts = reinterpret_cast<const long long *>(p.in_head + 256);
             const float bmax = p.bias_absmax;
             for (uint32_t n = 0; n < p.N; n++) {
-                const float S = ih->S[n];
+                // the head was written by other CTAs earlier in this launch (or by the kernel before): read it past L1,
+                // which may still hold this buffer's lines from two layers ago
+                const float S = __ldcg(&ih->S[n]);
                 float inv_next = 0.0f;
                 if (p.xout) {
                     long long l1 = 0;
-                    for (uint32_t i = lane; i < ih->nparts; i += 32) l1 += iparts[(uint64_t)i * 8 + n];
+                    const uint32_t nparts = __ldcg(&ih->nparts);
+                    for (uint32_t i = lane; i < nparts; i += 32) l1 += __ldcg(iparts + (uint64_t)i * 8 + n);
                     for (int o = 16; o > 0; o >>= 1) l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
                     // |y| <= max|bias| + |scale| * max|q| * sum|x'|, x' = V * S / DIGIT_FULL the values the MMAs really see
                     double bound = (double)bmax + fabs((double)p.scale) * IntFmt<PREC>::QMAX * ((double)S / DIGIT_FULL) * (double)l1;
@@ -637,14 +715,21 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
             long long abs_run[PER_LANE];                                // this CTA's sum of |V| per batch row (lanes 0 and 16 hold it)
 #pragma unroll
             for (int u = 0; u < PER_LANE; u++) abs_run[u] = 0;
+            // the biases of an item's rows are fetched one item ahead, so their latency never sits between two items
+            float bias_nx[PER_LANE];
+#pragma unroll
+            for (int u = 0; u < PER_LANE; u++) {
+                const uint32_t idx = u * 32 + lane, row = blockIdx.x * ITEM_ROWS + idx % ITEM_ROWS;
+                bias_nx[u] = (idx < ITEM_ROWS * p.N && row < p.out) ? p.bias[row] : 0.0f;
+            }
             for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
                 const uint32_t rbuf = n_item & 1u;
-                // what does not depend on the consumers comes first: the biases of this item's rows
                 float bias_r[PER_LANE];
 #pragma unroll
                 for (int u = 0; u < PER_LANE; u++) {
-                    const uint32_t idx = u * 32 + lane, row = item * ITEM_ROWS + idx % ITEM_ROWS;
-                    bias_r[u] = (idx < ITEM_ROWS * p.N && row < p.out) ? p.bias[row] : 0.0f;
+                    bias_r[u] = bias_nx[u];
+                    const uint32_t idx = u * 32 + lane, row = (item + gridDim.x) * ITEM_ROWS + idx % ITEM_ROWS;
+                    bias_nx[u] = (idx < ITEM_ROWS * p.N && row < p.out) ? p.bias[row] : 0.0f;
                     if (xo && !(fabsf(bias_r[u]) <= bmax)) atomicCAS(p.status, 0, 9);       // the caller's bound is wrong
                 }
                 handoff_wait(1 + rbuf);
@@ -661,7 +746,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                     }
                 }
                 __syncwarp();
-                if (n_item + 2 < (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x) handoff_arrive(3 + rbuf);   // the buffer is free again
+                if (n_item + 2 < my_total) handoff_arrive(3 + rbuf);   // the buffer is free again
 #pragma unroll
                 for (int u = 0; u < PER_LANE; u++) {
                     const uint32_t idx = u * 32 + lane, n = idx / ITEM_ROWS, rl = idx % ITEM_ROWS, row = item * ITEM_ROWS + rl;
@@ -699,7 +784,6 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                     if (n < p.N) oparts[(uint64_t)blockIdx.x * 8 + n] = abs_run[u];
                 }
             }
-            if (p.softmax) gemv_final_softmax(p, lane);
         } else {
         constexpr int PER_LANE = ITEM_ROWS * MAX_BATCH / 32;
         for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
@@ -728,7 +812,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                 sum_r[u] = sum;
             }
             __syncwarp();
-            if (n_item + 2 < (p.items - blockIdx.x + gridDim.x - 1) / gridDim.x) handoff_arrive(3 + rbuf);   // only if a later item will wait for it
+            if (n_item + 2 < my_total) handoff_arrive(3 + rbuf);   // only if a later item will wait for it
 #pragma unroll
             for (int u = 0; u < PER_LANE; u++) {
                 const uint32_t idx = u * 32 + lane, n = idx / ITEM_ROWS, row = item * ITEM_ROWS + idx % ITEM_ROWS;
@@ -748,15 +832,24 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                         p.xout[staged_index(p.next_prec, cs, p.out + idx / cs, idx % cs)] = __float2bfloat16_rn(0.0f);
             }
         }
-        if (p.softmax) gemv_final_softmax(p, lane);
         }
+        // this CTA's share of the layer is done (outputs, staged input of the next layer, partial sums): tell the others
+        if (l + 1 < ch.n) {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(ch.sync + l, 1);
+        }
+        }
+        chain_finish(ch, lane);
         return;
     }
 
     // ------------------------------ consumers --------------------------------------
     const bool col_live = g < CW;                              // with 4 kept columns only lanes of columns 0..3 load
-    const uint32_t row_pitch = 8 * p.spb * 64u;                // bytes of one chunk row (8 warp slices)
     uint32_t s = 0, ph = 0, n_item = 0;
+    for (uint32_t l = 0; l < ch.n; l++) {
+    const GemvParams &p = ch.L[l];
+    const uint32_t row_pitch = 8 * p.spb * 64u;                // bytes of one chunk row (8 warp slices)
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, n_item++) {
         // two accumulator sets (even / odd steps) keep two independent MMA chains in flight
         float acc[2][T][4], acc_hi[2][T][4];                   // acc_hi: INT8 only (the high-nibble term)
@@ -769,7 +862,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
                 for (int j = 0; j < 4; j++) { acc[e][i][j] = 0.0f; acc_hi[e][i][j] = 0.0f; iacc[e][i][j] = 0; }
 
         for (uint32_t c = 0; c < p.nchunks; c++) {
-            const bool ok = gbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 2);
+            const bool ok = gbar_wait(full0 + 8 * s, ph, abort_flag, status, 2);
             const uint32_t slice = warp & 7u, sub = warp >> 3;             // which 8th of the chunk's K range, which half of its steps
             const uint32_t per_sub = p.spb > 1 ? p.spb / 2 : 1;
             if (ok && c * 8u + slice < p.nboxes && sub * per_sub < p.spb) {
@@ -790,7 +883,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
             }
             __syncwarp();
             if (lane == 0) gbar_arrive(empty0 + 8 * s);
-            if (++s == p.ring) { s = 0; ph ^= 1u; }
+            if (++s == ring) { s = 0; ph ^= 1u; }
         }
 
         // ---- the sixteen partial sums go to shared memory [warp][row][column]; the epilogue warp takes over ----
@@ -822,6 +915,7 @@ spg_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p)
         }
         __threadfence_block();
         handoff_arrive(1 + rbuf);                              // no waiting: on to the next item
+    }
     }
 }
 
@@ -935,7 +1029,7 @@ int weight_map(const spgk_layer *L, uint32_t box_row_bytes, CUtensorMap *out_map
 }
 
 template <int PREC, int T, int CW, bool INTP>
-int launch(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
+int launch(const ChainMaps &maps, const ChainParams &ch, uint32_t grid_items, const Plan &pl, cudaStream_t s)
 {
     static bool attr_done = false;
     static int sms = 0;
@@ -946,35 +1040,86 @@ int launch(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStre
         SPGK_CUDA(cudaFuncSetAttribute(spg_gemv_kernel<PREC, T, CW, INTP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         attr_done = true;
     }
-    const uint32_t grid = pl.items < (uint32_t)sms ? pl.items : (uint32_t)sms;
+    // one CTA per SM at most (the shared-memory ring fills an SM), so all CTAs of a launch are resident together
+    const uint32_t grid = grid_items < (uint32_t)sms ? grid_items : (uint32_t)sms;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMV_THREADS); cfg.dynamicSmemBytes = pl.smem; cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    SPGK_CUDA(cudaLaunchKernelEx(&cfg, spg_gemv_kernel<PREC, T, CW, INTP>, map, p));
+    SPGK_CUDA(cudaLaunchKernelEx(&cfg, spg_gemv_kernel<PREC, T, CW, INTP>, maps, ch));
     return spgk_check_launch("spg_gemv_kernel");
 }
 
 template <int PREC>
-int launch_t(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
+int launch_t(const ChainMaps &maps, const ChainParams &ch, uint32_t grid_items, const Plan &pl, cudaStream_t s)
 {
-    if (pl.cs == 4) return launch<PREC, 1, 4, false>(map, p, pl, s);
-    if (pl.cs == 8) return launch<PREC, 1, 8, false>(map, p, pl, s);
-    return launch<PREC, 2, 8, false>(map, p, pl, s);
+    if (pl.cs == 4) return launch<PREC, 1, 4, false>(maps, ch, grid_items, pl, s);
+    if (pl.cs == 8) return launch<PREC, 1, 8, false>(maps, ch, grid_items, pl, s);
+    return launch<PREC, 2, 8, false>(maps, ch, grid_items, pl, s);
 }
 
 template <int PREC>
-int launch_int(const CUtensorMap &map, const GemvParams &p, const Plan &pl, cudaStream_t s)
+int launch_int(const ChainMaps &maps, const ChainParams &ch, uint32_t grid_items, const Plan &pl, cudaStream_t s)
 {
     switch (pl.cs) {
-        case 4:  return launch<PREC, 1, 4, true>(map, p, pl, s);
-        case 8:  return launch<PREC, 1, 8, true>(map, p, pl, s);
-        case 16: return launch<PREC, 2, 8, true>(map, p, pl, s);
-        case 24: return launch<PREC, 3, 8, true>(map, p, pl, s);
-        default: return launch<PREC, 4, 8, true>(map, p, pl, s);
+        case 4:  return launch<PREC, 1, 4, true>(maps, ch, grid_items, pl, s);
+        case 8:  return launch<PREC, 1, 8, true>(maps, ch, grid_items, pl, s);
+        case 16: return launch<PREC, 2, 8, true>(maps, ch, grid_items, pl, s);
+        case 24: return launch<PREC, 3, 8, true>(maps, ch, grid_items, pl, s);
+        default: return launch<PREC, 4, 8, true>(maps, ch, grid_items, pl, s);
     }
+}
+
+int launch_any(int precision, const ChainMaps &maps, const ChainParams &ch, uint32_t grid_items, const Plan &pl, cudaStream_t s)
+{
+    if (pl.intp) {
+        switch (precision) {
+            case SPG_P_I4: return launch_int<SPG_P_I4>(maps, ch, grid_items, pl, s);
+            case SPG_P_I2: return launch_int<SPG_P_I2>(maps, ch, grid_items, pl, s);
+            default:       return launch_int<SPG_P_I8>(maps, ch, grid_items, pl, s);
+        }
+    }
+    switch (precision) {
+        case SPG_P_I4:   return launch_t<SPG_P_I4>(maps, ch, grid_items, pl, s);
+        case SPG_P_I2:   return launch_t<SPG_P_I2>(maps, ch, grid_items, pl, s);
+        case SPG_P_I8:   return launch_t<SPG_P_I8>(maps, ch, grid_items, pl, s);
+        case SPG_P_BF16: return launch_t<SPG_P_BF16>(maps, ch, grid_items, pl, s);
+        case SPG_P_F16:  return launch_t<SPG_P_F16>(maps, ch, grid_items, pl, s);
+        default:         return launch_t<SPG_P_F32>(maps, ch, grid_items, pl, s);
+    }
+}
+
+// Everything of one layer's parameters that does not depend on where its input comes from or its output goes.
+void layer_params(const spgk_layer *L, const Plan &pl, uint32_t N, float *y, uint32_t ldy, void *scratch, GemvParams &p)
+{
+    p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out; p.bias_absmax = L->bias_absmax;
+    p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
+    p.softmax = (L->act == SPG_ACT_SOFTMAX && N == 1) ? 1 : 0;     // one warp finishes one row quickly; more rows are left to the caller
+    p.y = y; p.ldy = ldy;
+    p.N = N; p.P = pl.P; p.C = pl.C;
+    p.items = pl.items; p.nboxes = pl.nboxes; p.nchunks = pl.nchunks; p.spb = pl.spb; p.box_bytes = pl.box_bytes;
+    p.ring = pl.ring; p.xdepth = pl.xdepth; p.xchunk_bytes = pl.xchunk_bytes;
+    p.status = reinterpret_cast<int32_t *>(scratch);
+    p.xout = nullptr; p.out_head = nullptr; p.next_prec = 0; p.next_kpad = 0;
+}
+
+// Stages x for the first layer of a launch into the scratch buffer's own staged area; returns its head.
+int stage_first(const spgk_layer *L, const Plan &pl, const float *x, uint32_t ldx, uint32_t N, void *scratch, cudaStream_t s, GemvParams &p)
+{
+    uint8_t *base = reinterpret_cast<uint8_t *>(scratch);
+    uint8_t *own_head = base + HEAD_BYTES, *own = own_head + staged_head_bytes(L->in);
+    if (pl.intp)
+        spg_gemv_stage_int_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, L->in, pl.kpad, L->precision, pl.cs, own_head, own);
+    else
+        spg_gemv_stage_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.kpad, L->precision, pl.cs,
+                                                                  reinterpret_cast<__nv_bfloat16 *>(own));
+    int rc = spgk_check_launch("spg_gemv_stage_kernel");
+    if (rc) return rc;
+    p.in_head = own_head;
+    p.xin = reinterpret_cast<const uint4 *>(own);
+    return SPGK_OK;
 }
 
 }  // namespace
@@ -1009,39 +1154,20 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
     if (!pl.ok) return SPGK_E_UNSUPPORTED;
     if (!scratch) { spgk_set_error("spgk_layer_gemv", "scratch is NULL"); return SPGK_E_ARG; }
     cudaStream_t s = (cudaStream_t)stream;
-    CUtensorMap map;
-    int rc = weight_map(L, 8 * pl.spb * 64, &map);
+    ChainMaps maps;
+    int rc = weight_map(L, 8 * pl.spb * 64, &maps.m[0]);
     if (rc) return rc;
-    GemvParams p{};
-    p.bias = L->bias; p.scale = L->w_scale; p.in = L->in; p.out = L->out; p.bias_absmax = L->bias_absmax;
-    p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
-    p.softmax = (L->act == SPG_ACT_SOFTMAX && N == 1) ? 1 : 0;     // one warp finishes one row quickly; more rows are left to the caller
-    p.y = y; p.ldy = ldy;
-    p.N = N; p.P = pl.P; p.C = pl.C;
-    p.items = pl.items; p.nboxes = pl.nboxes; p.nchunks = pl.nchunks; p.spb = pl.spb; p.box_bytes = pl.box_bytes;
-    p.ring = pl.ring; p.xdepth = pl.xdepth; p.xchunk_bytes = pl.xchunk_bytes;
-    uint8_t *base = reinterpret_cast<uint8_t *>(scratch);
-    p.status = reinterpret_cast<int32_t *>(base);
-    const size_t in_head_bytes = staged_head_bytes(L->in);
+    ChainParams ch{};
+    ch.n = 1;
+    ch.sync = reinterpret_cast<int32_t *>(scratch) + 8;
+    GemvParams &p = ch.L[0];
+    layer_params(L, pl, N, y, ldy, scratch, p);
     if (staged_in) {
         p.in_head = reinterpret_cast<const uint8_t *>(staged_in);
-        p.xin = reinterpret_cast<const uint4 *>(p.in_head + in_head_bytes);
-    } else {
-        // put x into the form and order this layer's weight loads consume
-        uint8_t *own_head = base + HEAD_BYTES, *own = own_head + in_head_bytes;
-        if (pl.intp)
-            spg_gemv_stage_int_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, L->in, pl.kpad, L->precision, pl.cs, own_head, own);
-        else
-            spg_gemv_stage_kernel<<<(pl.kpad + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.kpad, L->precision, pl.cs,
-                                                                      reinterpret_cast<__nv_bfloat16 *>(own));
-        rc = spgk_check_launch("spg_gemv_stage_kernel");
-        if (rc) return rc;
-        p.in_head = own_head;
-        p.xin = reinterpret_cast<const uint4 *>(own);
-    }
+        p.xin = reinterpret_cast<const uint4 *>(p.in_head + staged_head_bytes(L->in));
+    } else if ((rc = stage_first(L, pl, x, ldx, N, scratch, s, p))) return rc;
     // The epilogue can stage the next layer's input directly, when that layer will also run here on the same
     // path and this layer's output needs no further pass (softmax) first.
-    p.xout = nullptr; p.out_head = nullptr; p.next_prec = 0; p.next_kpad = 0;
     if (next && staged_out && L->act != SPG_ACT_SOFTMAX && next->in == L->out) {
         Plan np = make_plan(next, N);
         if (np.ok && np.intp == pl.intp) {
@@ -1050,21 +1176,58 @@ int spgk_layer_gemv_chain(const spgk_layer *L, const spgk_layer *next, const voi
             p.next_prec = next->precision; p.next_kpad = np.kpad;
         }
     }
-    if (pl.intp) {
-        switch (L->precision) {
-            case SPG_P_I4: return launch_int<SPG_P_I4>(map, p, pl, s);
-            case SPG_P_I2: return launch_int<SPG_P_I2>(map, p, pl, s);
-            default:       return launch_int<SPG_P_I8>(map, p, pl, s);
+    return launch_any(L->precision, maps, ch, pl.items, pl, s);
+}
+
+// A whole run of layers in ONE launch: layer l's CTAs never leave the SMs, weights of layer l+1 are already on
+// their way while layer l finishes, and only the staged input of l+1 waits for l (see the kernel).  All layers must
+// be eligible for the kernel on the same path with the same chunk geometry (same stored precision), each feed the
+// next, and only the last may be a softmax layer; otherwise SPGK_E_UNSUPPORTED and the caller goes layer by layer.
+// ys[l] receives layer l's fp32 output [N][out_l]; staged_a / staged_b are the two ping-pong staged-input buffers
+// (spgk_gemv_staged_bytes of the widest layer each).
+int spgk_gemv_forward_chain(const spgk_layer *layers, uint32_t n, const float *x, uint32_t ldx, float *const *ys, uint32_t N,
+                            void *staged_a, void *staged_b, void *scratch, void *stream)
+{
+    if (!layers || n == 0 || !x || !ys || !scratch || !staged_a || !staged_b) { spgk_set_error("spgk_gemv_forward_chain", "bad argument"); return SPGK_E_ARG; }
+    if (n > MAX_CHAIN) return SPGK_E_UNSUPPORTED;
+    Plan pls[MAX_CHAIN];
+    uint32_t max_items = 0;
+    for (uint32_t l = 0; l < n; l++) {
+        const spgk_layer *L = &layers[l];
+        if (!L->w || !L->bias || !ys[l]) { spgk_set_error("spgk_gemv_forward_chain", "bad argument"); return SPGK_E_ARG; }
+        pls[l] = make_plan(L, N);
+        if (!pls[l].ok) return SPGK_E_UNSUPPORTED;
+        if (l > 0 && (L->in != layers[l - 1].out || L->precision != layers[0].precision || pls[l].intp != pls[0].intp || pls[l].spb != pls[0].spb ||
+                      pls[l].box_bytes != pls[0].box_bytes || pls[l].xchunk_bytes != pls[0].xchunk_bytes || pls[l].ring != pls[0].ring ||
+                      pls[l].cs != pls[0].cs || pls[l].smem != pls[0].smem)) return SPGK_E_UNSUPPORTED;
+        if (l + 1 < n && L->act == SPG_ACT_SOFTMAX) return SPGK_E_UNSUPPORTED;
+        if (pls[l].items > max_items) max_items = pls[l].items;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    ChainMaps maps;
+    ChainParams ch{};
+    ch.n = n;
+    ch.sync = reinterpret_cast<int32_t *>(scratch) + 8;
+    void *stg[2] = { staged_a, staged_b };
+    for (uint32_t l = 0; l < n; l++) {
+        const spgk_layer *L = &layers[l];
+        int rc = weight_map(L, 8 * pls[l].spb * 64, &maps.m[l]);
+        if (rc) return rc;
+        GemvParams &p = ch.L[l];
+        layer_params(L, pls[l], N, ys[l], L->out, scratch, p);
+        if (l == 0) {
+            if ((rc = stage_first(L, pls[0], x, ldx, N, scratch, s, p))) return rc;
+        } else {
+            p.in_head = reinterpret_cast<const uint8_t *>(stg[l & 1]);
+            p.xin = reinterpret_cast<const uint4 *>(p.in_head + staged_head_bytes(L->in));
+        }
+        if (l + 1 < n) {
+            p.out_head = reinterpret_cast<uint8_t *>(stg[(l + 1) & 1]);
+            p.xout = reinterpret_cast<__nv_bfloat16 *>(p.out_head + staged_head_bytes(layers[l + 1].in));
+            p.next_prec = layers[l + 1].precision; p.next_kpad = pls[l + 1].kpad;
         }
     }
-    switch (L->precision) {
-        case SPG_P_I4:   return launch_t<SPG_P_I4>(map, p, pl, s);
-        case SPG_P_I2:   return launch_t<SPG_P_I2>(map, p, pl, s);
-        case SPG_P_I8:   return launch_t<SPG_P_I8>(map, p, pl, s);
-        case SPG_P_BF16: return launch_t<SPG_P_BF16>(map, p, pl, s);
-        case SPG_P_F16:  return launch_t<SPG_P_F16>(map, p, pl, s);
-        default:         return launch_t<SPG_P_F32>(map, p, pl, s);
-    }
+    return launch_any(layers[0].precision, maps, ch, max_items, pls[0], s);
 }
 
 // 1 if the call above staged (or would stage) `next`'s input: lets the caller know whether to pass it on
@@ -1093,14 +1256,14 @@ int spgk_gemv_status(void *scratch, void *stream)
     SPGK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (h == 9) {
         spgk_set_error("spg_gemv_kernel", "spgk_layer.bias_absmax is smaller than a bias of the layer");
-        SPGK_CUDA(cudaMemsetAsync(scratch, 0, sizeof h, (cudaStream_t)stream));
+        SPGK_CUDA(cudaMemsetAsync(scratch, 0, HEAD_BYTES, (cudaStream_t)stream));
         return SPGK_E_ARG;
     }
     if (h != 0) {
         char msg[96];
         snprintf(msg, sizeof msg, "bounded wait %d gave up inside the GEMV kernel", (int)h);
         spgk_set_error("spg_gemv_kernel", msg);
-        SPGK_CUDA(cudaMemsetAsync(scratch, 0, sizeof h, (cudaStream_t)stream));
+        SPGK_CUDA(cudaMemsetAsync(scratch, 0, HEAD_BYTES, (cudaStream_t)stream));      // status word, layer counters, exit ticket
         return SPGK_E_TIMEOUT;
     }
     return SPGK_OK;

@@ -343,6 +343,26 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
     uint32_t xld = d_x ? ldx : p->topology[0];
     const char *path = NULL;
     const void *staged = NULL, *operand = NULL;      /* input of the layer in flight, already in a kernel's own order */
+    if (N <= SPGK_GEMV_MAX_BATCH && n->dev_layers <= 8 && n->d_staged[0] && n->d_staged[1] && n->d_gemv_scratch) {
+        /* every layer in one launch when the kernel takes them all: the weight stream then runs through the layer boundaries */
+        float *ys[8];
+        for (uint32_t l = 0; l < n->dev_layers; l++)
+            ys[l] = (d_final && l + 1 == n->dev_layers) ? d_final : n->d_small + (size_t)N * p->neuron_offsets[l + 1];
+        prof_mark(n);
+        int k = spgk_gemv_forward_chain(n->klayers, n->dev_layers, x, xld, ys, N, n->d_staged[0], n->d_staged[1], n->d_gemv_scratch, n->stream);
+        prof_mark(n);
+        if (k == SPGK_OK) {
+            n->gemv_pending = true;
+            const spgk_layer *Ll = &n->klayers[n->dev_layers - 1];
+            if (Ll->act == ACT_SOFTMAX && !spgk_gemv_applies_softmax(N) &&
+                (rc = spg_map_kernel_error(spgk_softmax_rows(ys[n->dev_layers - 1], Ll->out, N, Ll->out, n->stream), "softmax"))) return rc;
+            spg_note_path("gemv");
+            *d_last = ys[n->dev_layers - 1];
+            return SPINGALETT_OK;
+        }
+        if (n->prof_used >= 2) n->prof_used -= 2;          /* nothing was launched between the two marks */
+        if (k != SPGK_E_UNSUPPORTED && (rc = spg_map_kernel_error(k, "layers (small batch)"))) return rc;
+    }
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
         const spgk_layer *next = l + 1 < n->dev_layers ? &n->klayers[l + 1] : NULL;
