@@ -73,7 +73,7 @@ constexpr uint32_t INT_PATH_MAX_K = 131072;              // 127 * 128 * K must s
 struct StagedHead { float S[8]; uint32_t nparts; uint32_t pad[7]; };
 __host__ __device__ inline size_t staged_head_bytes(uint32_t width)
 {
-    const size_t parts = (size_t)(width + 15) / 16 + 33;
+    const size_t parts = (size_t)(width + 15) / 16 + 33 + 160;      // staging blocks of the first layer, or one entry per CTA of a launch (at most one CTA per SM)
     return 256 + ((parts * 64 + 255) & ~(size_t)255);
 }
 
@@ -135,8 +135,6 @@ __device__ __forceinline__ void frag_pos(int prec, uint32_t e, uint32_t &block, 
         block = e >> 2; r = e & 3u;
     }
 }
-
-__host__ __device__ inline uint32_t elems_per_load(int prec) { return 128u / spg_bits_per_elem(prec); }
 
 // Index (in bf16 units) of activation element k, column `col`, inside a staged-input buffer laid out as
 // [step][block][tile][t][cw columns][4]: the order in which the weight loads of a layer stored in

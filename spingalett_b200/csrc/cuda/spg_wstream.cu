@@ -33,7 +33,7 @@ namespace {
 using namespace spgtc;
 
 constexpr uint32_t WS_THREADS = 448;        // 14 warps
-constexpr uint32_t CONV_WARPS = 8, CONV_THREADS = 32 * CONV_WARPS, CONV_WARP0 = 6;
+constexpr uint32_t CONV_WARPS = 8, CONV_WARP0 = 6;
 constexpr uint32_t TILE_ROWS = 128;
 constexpr uint32_t RAW_BYTES = 128 * TILE_ROWS;          // one raw box
 constexpr uint32_t A_TILE = 128 * TILE_ROWS;             // one bf16 operand tile (64 k)
