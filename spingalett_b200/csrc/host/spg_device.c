@@ -697,8 +697,13 @@ float *forward_batch_struct_arguments(ForwardBatchArgs a)
     /* Up to 8 rows always take the weight-streaming chain; up to 512 rows do so (in groups of at most 128
      * rows, each group streaming the packed weights once) when every layer is eligible for the tensor-core
      * streaming kernel; everything else is the large-batch GEMM chain. */
-    const uint32_t group = N <= SPGK_GEMV_MAX_BATCH ? N : 128u;
-    if (N <= SPGK_GEMV_MAX_BATCH || (N <= 512 && all_wstream(n, N < group ? N : group))) {
+    /* 9 to 24 rows on a net the GEMV takes whole: groups of 8 rows through the GEMV (0.2 ms per group on the large
+     * INT4 net) beat one pass of the tensor-core streaming kernel (0.7 - 0.8 ms there) */
+    bool gemv_groups = N > SPGK_GEMV_MAX_BATCH && N <= 3 * SPGK_GEMV_MAX_BATCH;
+    for (uint32_t l = 0; l < n->dev_layers && gemv_groups; l++)
+        if (!spgk_gemv_scratch_bytes(&n->klayers[l], SPGK_GEMV_MAX_BATCH)) gemv_groups = false;
+    const uint32_t group = N <= SPGK_GEMV_MAX_BATCH ? N : (gemv_groups ? SPGK_GEMV_MAX_BATCH : 128u);
+    if (N <= SPGK_GEMV_MAX_BATCH || gemv_groups || (N <= 512 && all_wstream(n, N < group ? N : group))) {
         for (uint32_t r0 = 0; r0 < N; r0 += group) {
             const uint32_t rows = N - r0 < group ? N - r0 : group;
             float *d_last = NULL;

@@ -53,13 +53,13 @@ def test_wide_bf16_mlp_batch_16384(spg, w_net):
     assert np.abs(again - got[rows]).max() <= 2e-6
 
 
-@pytest.mark.parametrize("n", [1, 8, 64, 256])
+@pytest.mark.parametrize("n", [1, 8, 20, 64, 256])
 def test_large_int4_mlp_batch_sweep(spg, l_net, n):
     net, onet = l_net
     x = nets.normal_inputs(n, nets.L_TOPO[0], seed=100 + n)
     spg.set_math_mode(spg.abi.MATH_EXACT)
     got = net.forward_batch(x)
-    assert spg.last_path() == ("gemv" if n <= 8 else "wstream")
+    assert spg.last_path() == ("gemv" if n <= 24 else "wstream")      # 9..24 rows: GEMV in groups of 8
     rows = np.arange(n) if n <= 64 else np.random.default_rng(2).choice(n, 64, replace=False)
     want = onet.forward_batch(x[rows])
     agree, err = nets.parity(got[rows], want)
@@ -68,7 +68,7 @@ def test_large_int4_mlp_batch_sweep(spg, l_net, n):
     if n == 1:
         one = net.forward(x[0])                                  # the reference's single-sample entry point
         assert np.abs(one - want[0]).max() <= 2e-5
-    if n <= 8:
+    if n <= 24:
         # the integer-digit GEMV (default for integer files) against the bf16-term GEMV on the whole chain
         lib = spg.lib()
         lib.spgk_gemv_set_int_path(0)
