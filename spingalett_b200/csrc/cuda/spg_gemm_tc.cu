@@ -828,9 +828,9 @@ static int gemm_launch(const spgk_layer *L,
     } else {
         p.stg_bytes = STG_BYTES;
     }
-    const size_t fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 8) + 64 + p.stg_bytes;
+    const size_t fixed = 1024 /*alignment slack*/ + 8 * (2 * 12 + 8) + 64 + p.stg_bytes;
     uint32_t stages = (uint32_t)((smem_max - fixed) / stage_bytes);
-    if (stages > 8) stages = 8;
+    if (stages > 12) stages = 12;
     if (stages < 2) { spgk_set_error("spgk_layer_gemm_tc", "not enough shared memory"); return SPGK_E_UNSUPPORTED; }
     p.stages = stages;
     p.m_tiles = (N + BM - 1) / BM;
