@@ -95,3 +95,22 @@ def test_save_through_the_device_encoder_writes_the_same_file(spg, has_gpu, tmp_
     monkeypatch.delenv("SPINGALETT_HOST_ENCODE")
     assert open(a, "rb").read() == open(b, "rb").read()
     net.free()
+
+
+def test_non_finite_input_rows_poison_only_themselves(spg, l_net):
+    """An infinity or a NaN in one input row: that row's outputs are not finite (the reference's would not be either),
+    every other row of the batch is what it is without the bad row.  Small batch = integer-digit GEMV (the row's
+    fixed-point scale becomes NaN), larger batches = the streaming and tensor-core chains."""
+    net, _ = l_net
+    spg.set_math_mode(spg.abi.MATH_AUTO)
+    for n, bad in ((2, 1), (8, 3), (40, 17), (1024, 500)):
+        x = nets.normal_inputs(n, nets.L_TOPO[0], seed=300 + n)
+        clean = net.forward_batch(x)
+        y = x.copy()
+        y[bad, 5] = np.inf
+        y[bad, 77] = np.nan
+        got = net.forward_batch(y)
+        good = np.arange(n) != bad
+        assert not np.any(np.isfinite(got[bad])), (n, spg.last_path(), got[bad][:4])
+        assert np.all(np.isfinite(got[good]))
+        assert np.abs(got[good] - clean[good]).max() <= 2e-6, (n, spg.last_path())
