@@ -149,3 +149,32 @@ def test_two_rank_data_parallel_step(spg, tmp_path):
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "DIST_TRAIN_OK" in r.stdout
+
+
+def test_checkpoint_and_resume_through_the_file(spg, tmp_path):
+    """Train, save with the optimiser sections, load: the loaded network carries the same weights, Adam moments and
+    step counter, and training it further gives bit for bit what training the original further gives."""
+    rng = np.random.default_rng(7)
+    n = 512
+    x = rng.random((n, 64), dtype=np.float32)
+    t = np.zeros((n, 5), np.float32)
+    t[np.arange(n), rng.integers(0, 5, n)] = 1.0
+    net = spg.Network.build([64, 48, 5], [spg.abi.ACT_RELU, spg.abi.ACT_SOFTMAX], spg.abi.WEIGHT_INITIALIZATION_HE, seed=11)
+    kw = dict(batch_size=n, strategy=spg.abi.STRATEGY_FULL_BATCH, learning_rate=1e-2)
+    net.train(x, t, epochs=5, **kw)
+    path = str(tmp_path / "ckpt.nn")
+    net.save(path, spg.abi.PRECISION_FLOAT32, with_optimizer=True)
+    back = spg.Network.load(path)
+    assert back.c.time_step == net.c.time_step == 5
+    assert np.array_equal(back.weights, net.weights) and np.array_equal(back.biases, net.biases)
+    tw = int(net.c.total_weights)
+    for name in ("opt_m_weights", "opt_v_weights"):
+        a = np.ctypeslib.as_array(getattr(net.c, name), (tw,))
+        b = np.ctypeslib.as_array(getattr(back.c, name), (tw,))
+        assert np.array_equal(a, b) and np.any(a != 0), name
+    net.train(x, t, epochs=4, **kw)
+    back.train(x, t, epochs=4, **kw)
+    assert back.c.time_step == net.c.time_step == 9
+    assert np.array_equal(back.weights, net.weights) and np.array_equal(back.biases, net.biases)
+    net.free()
+    back.free()
