@@ -18,53 +18,102 @@
 
 namespace {
 
-constexpr int TM = 64, TN = 64, TK = 16;      // CTA tile; 256 threads, 4x4 outputs each
+constexpr int TK = 16;      // k depth of a staged tile; the CTA tile is TS x TS, (TS/4)^2 threads with 4x4 outputs each
 
 enum { GEMM_FWD = 0, GEMM_DELTA = 1, GEMM_GRAD = 2 };
+
+// Four consecutive floats at `base`: one 128-bit load when `vec`, else element-wise with zeros where the row is
+// outside the matrix (`row_ok` false) or the element index first+j reaches `limit`.
+__device__ __forceinline__ float4 train_load4(const float *base, bool vec, bool row_ok, uint32_t first, uint32_t limit)
+{
+    if (vec) return *reinterpret_cast<const float4 *>(base);
+    float4 v;
+    v.x = row_ok && first < limit ? base[0] : 0.0f;
+    v.y = row_ok && first + 1 < limit ? base[1] : 0.0f;
+    v.z = row_ok && first + 2 < limit ? base[2] : 0.0f;
+    v.w = row_ok && first + 3 < limit ? base[3] : 0.0f;
+    return v;
+}
 
 // MODE 0: C[M][N] = act(A[M][K] . B[N][K]^T + bias[N])        (A = activations, B = weights [out][in])
 // MODE 1: C[M][N] = (A[M][K] . B[K][N]) * act'(aux[M][N])      (A = delta_{l+1}, B = weights [next][cur])
 // MODE 2: C[M][N] = alpha * A[K][M]^T . B[K][N]                 (A = delta [rows][out], B = activations [rows][in])
-template <int MODE>
-__global__ void __launch_bounds__(256)
+// The A tile is staged as As[k][m] and the B tile as Bs[k][n].  Every thread owns R groups of four elements of each
+// operand, consecutive along that operand's contiguous axis; the groups of the next k-tile are loaded into registers
+// before the products of the current one are formed, so the global-memory latency hides behind the arithmetic.
+template <int MODE, int TS>
+__global__ void __launch_bounds__((TS / 4) * (TS / 4))
 spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__restrict__ B, uint32_t ldb,
                       float *__restrict__ C, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K,
                       float alpha, const float *__restrict__ bias, const float *__restrict__ aux, uint32_t ldaux, int act)
 {
-    __shared__ float As[TK][TM + 4];
-    __shared__ float Bs[TK][TN + 4];
-    const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
+    constexpr int TM = TS, TN = TS, NT = (TS / 4) * (TS / 4), Q = TS / 4;     // Q: groups of four per tile row along m or n
+    constexpr int R = TS * TK / 4 / NT;                                       // groups per thread per operand
+    constexpr bool a_km = MODE == GEMM_GRAD;                    // A stored [K][M] (contiguous in m); otherwise [M][K]
+    constexpr bool b_nk = MODE == GEMM_FWD;                     // B stored [N][K] (contiguous in k); otherwise [K][N]
+    __shared__ __align__(16) float As[TK][TM + 4];
+    __shared__ __align__(16) float Bs[TK][TN + 4];
+    const uint32_t tid = threadIdx.x, tx = tid % Q, ty = tid / Q;
     const uint32_t m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    const bool a_al = (lda & 3u) == 0 && (reinterpret_cast<uintptr_t>(A) & 15u) == 0 && m0 + TM <= M;
+    const bool b_al = (ldb & 3u) == 0 && (reinterpret_cast<uintptr_t>(B) & 15u) == 0 && n0 + TN <= N;
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    float4 ra[R], rb[R];
 
+    auto fetch = [&](uint32_t k0) {
+        const bool whole = k0 + TK <= K;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const uint32_t i = tid + r * NT;
+            if (a_km) {
+                const uint32_t k = i / Q, m = (i % Q) * 4;
+                ra[r] = train_load4(A + (uint64_t)(k0 + k) * lda + m0 + m, a_al && whole, k0 + k < K, m0 + m, M);
+            } else {
+                const uint32_t m = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                ra[r] = train_load4(A + (uint64_t)(m0 + m) * lda + k0 + k, a_al && whole, m0 + m < M, k0 + k, K);
+            }
+            if (b_nk) {
+                const uint32_t n = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                rb[r] = train_load4(B + (uint64_t)(n0 + n) * ldb + k0 + k, b_al && whole, n0 + n < N, k0 + k, K);
+            } else {
+                const uint32_t k = i / Q, n = (i % Q) * 4;
+                rb[r] = train_load4(B + (uint64_t)(k0 + k) * ldb + n0 + n, b_al && whole, k0 + k < K, n0 + n, N);
+            }
+        }
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const uint32_t i = tid + r * NT;
+            if (a_km) {
+                *reinterpret_cast<float4 *>(&As[i / Q][(i % Q) * 4]) = ra[r];
+            } else {
+                const uint32_t m = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                As[k][m] = ra[r].x; As[k + 1][m] = ra[r].y; As[k + 2][m] = ra[r].z; As[k + 3][m] = ra[r].w;
+            }
+            if (b_nk) {
+                const uint32_t n = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                Bs[k][n] = rb[r].x; Bs[k + 1][n] = rb[r].y; Bs[k + 2][n] = rb[r].z; Bs[k + 3][n] = rb[r].w;
+            } else {
+                *reinterpret_cast<float4 *>(&Bs[i / Q][(i % Q) * 4]) = rb[r];
+            }
+        }
+    };
+
+    fetch(0);
     for (uint32_t k0 = 0; k0 < K; k0 += TK) {
-        // stage A tile as As[k][m] and B tile as Bs[k][n]
-        for (uint32_t i = tid; i < TM * TK; i += 256) {
-            uint32_t m, k;
-            float v = 0.0f;
-            if (MODE == GEMM_GRAD) { m = i % TM; k = i / TM; if (m0 + m < M && k0 + k < K) v = A[(uint64_t)(k0 + k) * lda + m0 + m]; }
-            else { k = i % TK; m = i / TK; if (m0 + m < M && k0 + k < K) v = A[(uint64_t)(m0 + m) * lda + k0 + k]; }
-            As[k][m] = v;
-        }
-        for (uint32_t i = tid; i < TN * TK; i += 256) {
-            uint32_t n, k;
-            float v = 0.0f;
-            if (MODE == GEMM_FWD) { k = i % TK; n = i / TK; if (n0 + n < N && k0 + k < K) v = B[(uint64_t)(n0 + n) * ldb + k0 + k]; }
-            else { n = i % TN; k = i / TN; if (n0 + n < N && k0 + k < K) v = B[(uint64_t)(k0 + k) * ldb + n0 + n]; }
-            Bs[k][n] = v;
-        }
+        stage();
         __syncthreads();
+        if (k0 + TK < K) fetch(k0 + TK);
 #pragma unroll
         for (int k = 0; k < TK; k++) {
-            float a[4], b[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) a[i] = As[k][ty * 4 + i];
-#pragma unroll
-            for (int j = 0; j < 4; j++) b[j] = Bs[k][tx * 4 + j];
+            const float4 av = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
+            const float4 bv = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4]);
+            const float a[4] = { av.x, av.y, av.z, av.w }, b[4] = { bv.x, bv.y, bv.z, bv.w };
 #pragma unroll
             for (int i = 0; i < 4; i++)
 #pragma unroll
@@ -227,13 +276,19 @@ int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint
         spgk_set_error("spgk_train_gemm", "bad argument");
         return SPGK_E_ARG;
     }
-    dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     cudaStream_t s = (cudaStream_t)stream;
     if (act == SPG_ACT_SOFTMAX && mode == GEMM_FWD) act = SPG_ACT_NONE;      // softmax rows are finished separately
-    if (mode == GEMM_FWD) spg_train_gemm_kernel<GEMM_FWD><<<grid, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act);
-    else if (mode == GEMM_DELTA) spg_train_gemm_kernel<GEMM_DELTA><<<grid, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act);
-    else if (mode == GEMM_GRAD) spg_train_gemm_kernel<GEMM_GRAD><<<grid, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act);
-    else { spgk_set_error("spgk_train_gemm", "unknown mode"); return SPGK_E_ARG; }
+    if (mode != GEMM_FWD && mode != GEMM_DELTA && mode != GEMM_GRAD) { spgk_set_error("spgk_train_gemm", "unknown mode"); return SPGK_E_ARG; }
+    // 64 x 64 tiles when they give each of the 148 SMs a CTA; 32 x 32 tiles (four times the CTAs) otherwise, which on a
+    // 256-row step of a 784-512-1000-10 network is every product
+#define SPG_TRAIN_LAUNCH(MODEV, TSV) \
+    spg_train_gemm_kernel<MODEV, TSV><<<dim3((N + TSV - 1) / TSV, (M + TSV - 1) / TSV), (TSV / 4) * (TSV / 4), 0, s>>>( \
+        A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act)
+    const bool small = ((N + 63) / 64) * ((M + 63) / 64) < 148u;
+    if (mode == GEMM_FWD) { if (small) SPG_TRAIN_LAUNCH(GEMM_FWD, 32); else SPG_TRAIN_LAUNCH(GEMM_FWD, 64); }
+    else if (mode == GEMM_DELTA) { if (small) SPG_TRAIN_LAUNCH(GEMM_DELTA, 32); else SPG_TRAIN_LAUNCH(GEMM_DELTA, 64); }
+    else { if (small) SPG_TRAIN_LAUNCH(GEMM_GRAD, 32); else SPG_TRAIN_LAUNCH(GEMM_GRAD, 64); }
+#undef SPG_TRAIN_LAUNCH
     return spgk_check_launch("spg_train_gemm_kernel");
 }
 
