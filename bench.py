@@ -296,7 +296,7 @@ def measure(spg, net, torch, x_dev, y_dev, x_pin, y_pin, batch, steps, warmup, d
 def run_train(args):
     """Training configuration: MLP 784-512-1000-10, fp32, 256 rows per GPU per step, cross-entropy, Adam lr 1e-3; with more
     than one rank the flat gradient is all-reduced over NCCL every step.  One train() call runs `steps` optimiser steps
-    (10 epochs over steps/10*256 rows in shuffled mini-batches of 256); CUDA events on the library's stream bracket the call,
+    (100 epochs over 20*256 rows in shuffled mini-batches of 256, so that the per-call costs - allocation, upload, read-back - weigh a few percent); CUDA events on the library's stream bracket the call,
     the upload of the host arrays and the read-back of weights and optimiser state included."""
     import torch
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -320,10 +320,10 @@ def run_train(args):
     topo = [784, 512, 1000, 10]
     net = spg.Network.build(topo, [spg.abi.ACT_RELU, spg.abi.ACT_RELU, spg.abi.ACT_SOFTMAX], spg.abi.WEIGHT_INITIALIZATION_HE, seed=1234)
     net.set_stream(torch.cuda.current_stream().cuda_stream)
-    steps = max(args.steps, 20) * 10
+    epochs = max(args.steps, 20) * 5
+    steps = epochs * 20
     rng = np.random.default_rng(100 + rank)
-    epochs = 10
-    rows = 256 * steps // epochs
+    rows = 256 * 20
     x = rng.random((rows, 784), dtype=np.float32)
     tg = np.zeros((rows, 10), np.float32)
     tg[np.arange(rows), rng.integers(0, 10, rows)] = 1.0
@@ -348,7 +348,7 @@ def run_train(args):
         print(json.dumps({"metric": "mlp_train_samples_per_sec", "value": 256 * steps * world / (ms * 1e-3), "unit": "samples/s", "n_gpus": world,
                           "steps": steps, "warmup": 8, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                           "dtype": "f32", "data": "synthetic",
-                          "config": {"workload": "MLP 784-512-1000-10 training, 256 rows per GPU per step, cross-entropy, Adam lr 1e-3, one train() call of 10 epochs "
+                          "config": {"workload": "MLP 784-512-1000-10 training, 256 rows per GPU per step, cross-entropy, Adam lr 1e-3, one train() call of %d epochs over 5120 rows " % epochs +
                                                  "(host arrays in, weights and optimiser state back to the host at the end)",
                                      "collective": "NCCL all-reduce of 924930 fp32 gradients per step" if world > 1 else "none"},
                           "gpu_launches": int(launches)}))
