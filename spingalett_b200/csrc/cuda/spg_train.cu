@@ -41,8 +41,11 @@ __device__ __forceinline__ float4 train_load4(const float *base, bool vec, bool 
 // The A tile is staged as As[k][m] and the B tile as Bs[k][n].  Every thread owns R groups of four elements of each
 // operand, consecutive along that operand's contiguous axis; the groups of the next k-tile are loaded into registers
 // before the products of the current one are formed, so the global-memory latency hides behind the arithmetic.
-template <int MODE, int TS>
-__global__ void __launch_bounds__((TS / 4) * (TS / 4))
+// KS > 1 puts KS such thread groups ("slices") in the CTA: slice s takes the k-tiles s, s+KS, ... and the partial sums are
+// added in slice order through shared memory at the end, so the result does not depend on timing.  It is what keeps an SM
+// busy when the whole product has fewer tiles than the GPU has SMs and a CTA would otherwise be two warps waiting on loads.
+template <int MODE, int TS, int KS>
+__global__ void __launch_bounds__((TS / 4) * (TS / 4) * KS)
 spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__restrict__ B, uint32_t ldb,
                       float *__restrict__ C, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K,
                       float alpha, const float *__restrict__ bias, const float *__restrict__ aux, uint32_t ldaux, int act)
@@ -51,9 +54,11 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
     constexpr int R = TS * TK / 4 / NT;                                       // groups per thread per operand
     constexpr bool a_km = MODE == GEMM_GRAD;                    // A stored [K][M] (contiguous in m); otherwise [M][K]
     constexpr bool b_nk = MODE == GEMM_FWD;                     // B stored [N][K] (contiguous in k); otherwise [K][N]
-    __shared__ __align__(16) float As[TK][TM + 4];
-    __shared__ __align__(16) float Bs[TK][TN + 4];
-    const uint32_t tid = threadIdx.x, tx = tid % Q, ty = tid / Q;
+    static_assert(KS == 1 || (KS - 1) * NT * 16 <= KS * 2 * TK * (TS + 4), "the partial sums reuse the staging memory");
+    __shared__ __align__(16) float sm[KS][2][TK][TS + 4];
+    const uint32_t slice = threadIdx.x / NT, tid = threadIdx.x % NT, tx = tid % Q, ty = tid / Q;
+    float (*As)[TS + 4] = sm[slice][0];
+    float (*Bs)[TS + 4] = sm[slice][1];
     const uint32_t m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
     const bool a_al = (lda & 3u) == 0 && (reinterpret_cast<uintptr_t>(A) & 15u) == 0 && m0 + TM <= M;
     const bool b_al = (ldb & 3u) == 0 && (reinterpret_cast<uintptr_t>(B) & 15u) == 0 && n0 + TN <= N;
@@ -104,11 +109,12 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
         }
     };
 
-    fetch(0);
-    for (uint32_t k0 = 0; k0 < K; k0 += TK) {
+    // every slice runs the same number of rounds (a tile beyond K loads as zeros), so the CTA-wide barriers line up
+    fetch(slice * TK);
+    for (uint32_t kb = 0; kb < K; kb += KS * TK) {
         stage();
         __syncthreads();
-        if (k0 + TK < K) fetch(k0 + TK);
+        if (kb + KS * TK < K) fetch(kb + (KS + slice) * TK);
 #pragma unroll
         for (int k = 0; k < TK; k++) {
             const float4 av = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
@@ -120,6 +126,18 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
                 for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
         __syncthreads();
+    }
+    if (KS > 1) {
+        float *red = &sm[0][0][0][0];
+        if (slice > 0) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) red[((slice - 1) * 16 + i) * NT + tid] = acc[i >> 2][i & 3];
+        }
+        __syncthreads();
+        if (slice > 0) return;
+        for (int sl = 0; sl < KS - 1; sl++)
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i >> 2][i & 3] += red[(sl * 16 + i) * NT + tid];
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -279,15 +297,21 @@ int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint
     cudaStream_t s = (cudaStream_t)stream;
     if (act == SPG_ACT_SOFTMAX && mode == GEMM_FWD) act = SPG_ACT_NONE;      // softmax rows are finished separately
     if (mode != GEMM_FWD && mode != GEMM_DELTA && mode != GEMM_GRAD) { spgk_set_error("spgk_train_gemm", "unknown mode"); return SPGK_E_ARG; }
-    // 64 x 64 tiles when they give each of the 148 SMs a CTA; 32 x 32 tiles (four times the CTAs) otherwise, which on a
-    // 256-row step of a 784-512-1000-10 network is every product
-#define SPG_TRAIN_LAUNCH(MODEV, TSV) \
-    spg_train_gemm_kernel<MODEV, TSV><<<dim3((N + TSV - 1) / TSV, (M + TSV - 1) / TSV), (TSV / 4) * (TSV / 4), 0, s>>>( \
+    // 64 x 64 tiles when they give each of the 148 SMs a CTA; otherwise 32 x 32 tiles (four times the CTAs) with the k
+    // range of each tile split over four thread groups of the CTA, eight when there are at most 32 tiles - on a 256-row
+    // step of a 784-512-1000-10 network that is every product
+    const uint32_t tiles64 = ((N + 63) / 64) * ((M + 63) / 64), tiles32 = ((N + 31) / 32) * ((M + 31) / 32);
+    const int shape = tiles64 >= 148u ? 0 : tiles32 > 32u ? 1 : 2;
+#define SPG_TRAIN_LAUNCH(MODEV, TSV, KSV) \
+    spg_train_gemm_kernel<MODEV, TSV, KSV><<<dim3((N + TSV - 1) / TSV, (M + TSV - 1) / TSV), (TSV / 4) * (TSV / 4) * KSV, 0, s>>>( \
         A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act)
-    const bool small = ((N + 63) / 64) * ((M + 63) / 64) < 148u;
-    if (mode == GEMM_FWD) { if (small) SPG_TRAIN_LAUNCH(GEMM_FWD, 32); else SPG_TRAIN_LAUNCH(GEMM_FWD, 64); }
-    else if (mode == GEMM_DELTA) { if (small) SPG_TRAIN_LAUNCH(GEMM_DELTA, 32); else SPG_TRAIN_LAUNCH(GEMM_DELTA, 64); }
-    else { if (small) SPG_TRAIN_LAUNCH(GEMM_GRAD, 32); else SPG_TRAIN_LAUNCH(GEMM_GRAD, 64); }
+#define SPG_TRAIN_SHAPES(MODEV) \
+    do { if (shape == 0) SPG_TRAIN_LAUNCH(MODEV, 64, 1); else if (shape == 1) SPG_TRAIN_LAUNCH(MODEV, 32, 4); \
+         else SPG_TRAIN_LAUNCH(MODEV, 32, 8); } while (0)
+    if (mode == GEMM_FWD) SPG_TRAIN_SHAPES(GEMM_FWD);
+    else if (mode == GEMM_DELTA) SPG_TRAIN_SHAPES(GEMM_DELTA);
+    else SPG_TRAIN_SHAPES(GEMM_GRAD);
+#undef SPG_TRAIN_SHAPES
 #undef SPG_TRAIN_LAUNCH
     return spgk_check_launch("spg_train_gemm_kernel");
 }

@@ -36,6 +36,18 @@ typedef struct {
 /* process-wide communicator for the gradient exchange */
 static void *s_comm = NULL;
 static int s_rank = 0, s_world = 1;
+/* the exchange runs on a stream of its own so that one layer's gradients cross NVLink while the next layer's are computed:
+   s_ev_ready orders it after the gradient kernels, s_ev_done orders the optimiser after it */
+static void *s_ar_stream = NULL, *s_ev_ready = NULL, *s_ev_done = NULL;
+
+static void dist_release(void)
+{
+    if (s_ev_ready) spgk_event_destroy(s_ev_ready);
+    if (s_ev_done) spgk_event_destroy(s_ev_done);
+    if (s_ar_stream) spgk_stream_destroy(s_ar_stream);
+    if (s_comm) spgk_nccl_destroy(s_comm);
+    s_ev_ready = s_ev_done = s_ar_stream = s_comm = NULL;
+}
 
 int spingalett_dist_unique_id(void *id128)
 {
@@ -48,16 +60,21 @@ int spingalett_dist_init(int rank, int world, const void *id128)
         spg_set_error(SPINGALETT_ERR_INVALID, "dist_init: bad rank/world/id");
         return SPINGALETT_ERR_INVALID;
     }
-    if (s_comm) { spgk_nccl_destroy(s_comm); s_comm = NULL; }
+    dist_release();
     s_rank = rank; s_world = world;
     if (world == 1) return SPINGALETT_OK;
-    return spg_map_kernel_error(spgk_nccl_init(&s_comm, rank, world, id128), "dist_init");
+    int rc = spgk_nccl_init(&s_comm, rank, world, id128);
+    if (rc == SPGK_OK) rc = spgk_stream_create(&s_ar_stream);
+    if (rc == SPGK_OK) rc = spgk_event_create(&s_ev_ready);
+    if (rc == SPGK_OK) rc = spgk_event_create(&s_ev_done);
+    if (rc != SPGK_OK) { dist_release(); s_rank = 0; s_world = 1; }
+    return spg_map_kernel_error(rc, "dist_init");
 }
 
 void spingalett_dist_shutdown(void)
 {
-    if (s_comm) spgk_nccl_destroy(s_comm);
-    s_comm = NULL; s_rank = 0; s_world = 1;
+    dist_release();
+    s_rank = 0; s_world = 1;
 }
 
 int spingalett_dist_world(void) { return s_world; }
@@ -222,25 +239,33 @@ void train_struct_arguments(TrainArgs a)
             float *d_last = t->deltas + (size_t)cur * p->neuron_offsets[last];
             DEV(spgk_ce_delta(t->acts + (size_t)cur * p->neuron_offsets[last], bt, d_last, (uint64_t)cur * outw,
                               need_loss ? t->loss : NULL, out_act == ACT_SIGMOID, st), "train: output delta");
-            /* hidden deltas */
-            for (uint32_t l = last - 1; l > 0; l--) {
-                const uint32_t cw = p->topology[l], nw = p->topology[l + 1];
-                DEV(spgk_train_gemm(1, t->deltas + (size_t)cur * p->neuron_offsets[l + 1], nw,
-                                    t->params + p->weight_offsets[l], cw, t->deltas + (size_t)cur * p->neuron_offsets[l], cw,
-                                    cur, cw, nw, 1.0f, NULL, t->acts + (size_t)cur * p->neuron_offsets[l], cw,
-                                    (int)p->act_func[l - 1], st), "train: delta");
-            }
-            /* gradients straight into the flat buffer */
+            /* backwards through the layers: the gradients of layer l (from delta l+1 and activation l) go into the flat
+               buffer and, with several replicas, start their all-reduce on the exchange stream at once, so that it runs
+               under the delta and gradient products of the layers below */
             const float gs = 1.0f / (float)cur;
-            for (uint32_t l = 0; l < last; l++) {
+            for (uint32_t l = last; l-- > 0;) {
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 const float *dl = t->deltas + (size_t)cur * p->neuron_offsets[l + 1];
                 const float *al = l == 0 ? bx : t->acts + (size_t)cur * p->neuron_offsets[l];
                 DEV(spgk_train_gemm(2, dl, fo, al, fi, t->grads + p->weight_offsets[l], fi, fo, fi, cur, gs, NULL, NULL, 0, 0, st),
                     "train: weight gradient");
                 DEV(spgk_col_sums(dl, cur, fo, gs, t->grads + tw + p->bias_offsets[l], st), "train: bias gradient");
+                if (s_world > 1) {
+                    DEV(spgk_event_record(s_ev_ready, st), "train: exchange order");
+                    DEV(spgk_stream_wait_event(s_ar_stream, s_ev_ready), "train: exchange order");
+                    DEV(spgk_nccl_allreduce_sum(s_comm, t->grads + p->weight_offsets[l], (uint64_t)fi * fo, s_ar_stream),
+                        "train: all-reduce");
+                    if (l == 0) DEV(spgk_nccl_allreduce_sum(s_comm, t->grads + tw, tb, s_ar_stream), "train: all-reduce");
+                }
+                if (l > 0)
+                    DEV(spgk_train_gemm(1, dl, fo, t->params + p->weight_offsets[l], fi,
+                                        t->deltas + (size_t)cur * p->neuron_offsets[l], fi, cur, fi, fo, 1.0f, NULL,
+                                        t->acts + (size_t)cur * p->neuron_offsets[l], fi, (int)p->act_func[l - 1], st), "train: delta");
             }
-            if (s_world > 1) DEV(spgk_nccl_allreduce_sum(s_comm, t->grads, np, st), "train: all-reduce");
+            if (s_world > 1) {
+                DEV(spgk_event_record(s_ev_done, s_ar_stream), "train: exchange order");
+                DEV(spgk_stream_wait_event(st, s_ev_done), "train: exchange order");
+            }
             p->time_step++;
             b1pow *= a.beta1;
             b2pow *= a.beta2;
