@@ -287,6 +287,8 @@ SPGK_API int spgk_gemm_tc_status(int32_t *status, void *stream);
  * spgk_ce_delta: delta = a - t (cross-entropy over softmax or sigmoid, Training.c:366-371); if
  *   loss != NULL the batch's summed cross-entropy (SIMD.c:533-549) is added to *loss.
  * spgk_col_sums: out[j] = scale * sum_rows d[row][j]   bias gradient (Training.c:413-417).
+ * spgk_train_grad: both gradients of one layer in one launch (Training.c:405-417):
+ *   gw[out][in] = scale * delta[rows][out]^T a[rows][in],  gb[out] = scale * sum_rows delta[row][out].
  * spgk_gather_rows: dst[i] = src[idx[i]]                mini-batch assembly (Training.c:759-767).
  * spgk_adam: one fused pass over a flat parameter buffer; g is scaled by gscale first
  *   (1/ranks after a sum all-reduce); epsilon inside the square root (SIMD.c:279-328).
@@ -297,6 +299,8 @@ SPGK_API int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float
 SPGK_API int spgk_ce_delta(const float *a, const float *t, float *delta, uint64_t count, float *loss,
                            int sigmoid_output, void *stream);
 SPGK_API int spgk_col_sums(const float *d, uint32_t rows, uint32_t cols, float scale, float *out, void *stream);
+SPGK_API int spgk_train_grad(const float *delta, uint32_t ldd, const float *a, uint32_t lda, float *gw, uint32_t ldg,
+                             float *gb, uint32_t out, uint32_t in, uint32_t rows, float scale, void *stream);
 SPGK_API int spgk_gather_rows(const float *src, const uint32_t *idx, float *dst, uint32_t rows, uint32_t width,
                               void *stream);
 SPGK_API int spgk_adam(float *w, float *m, float *v, const float *g, uint64_t n, float lr, float b1, float b2,

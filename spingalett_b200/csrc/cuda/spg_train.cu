@@ -48,13 +48,14 @@ template <int MODE, int TS, int KS>
 __global__ void __launch_bounds__((TS / 4) * (TS / 4) * KS)
 spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__restrict__ B, uint32_t ldb,
                       float *__restrict__ C, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K,
-                      float alpha, const float *__restrict__ bias, const float *__restrict__ aux, uint32_t ldaux, int act)
+                      float alpha, const float *__restrict__ bias, const float *__restrict__ aux, uint32_t ldaux, int act,
+                      float *__restrict__ colsum)
 {
     constexpr int TM = TS, TN = TS, NT = (TS / 4) * (TS / 4), Q = TS / 4;     // Q: groups of four per tile row along m or n
     constexpr int R = TS * TK / 4 / NT;                                       // groups per thread per operand
     constexpr bool a_km = MODE == GEMM_GRAD;                    // A stored [K][M] (contiguous in m); otherwise [M][K]
     constexpr bool b_nk = MODE == GEMM_FWD;                     // B stored [N][K] (contiguous in k); otherwise [K][N]
-    static_assert(KS == 1 || (KS - 1) * NT * 16 <= KS * 2 * TK * (TS + 4), "the partial sums reuse the staging memory");
+    static_assert(KS == 1 || (KS - 1) * NT * 20 <= KS * 2 * TK * (TS + 4), "the partial sums reuse the staging memory");
     __shared__ __align__(16) float sm[KS][2][TK][TS + 4];
     const uint32_t slice = threadIdx.x / NT, tid = threadIdx.x % NT, tx = tid % Q, ty = tid / Q;
     float (*As)[TS + 4] = sm[slice][0];
@@ -68,6 +69,10 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
     float4 ra[R], rb[R];
+    // MODE 2 with `colsum`: the CTAs of the first tile column also sum their A tile over k, colsum[m] = alpha * sum_k A[k][m]
+    // (the bias gradient beside the weight gradient); one thread per group of four m carries those sums
+    const bool cs = MODE == GEMM_GRAD && colsum != nullptr && blockIdx.x == 0 && tx == 0;
+    float bs[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
 
     auto fetch = [&](uint32_t k0) {
         const bool whole = k0 + TK <= K;
@@ -124,6 +129,10 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
             for (int i = 0; i < 4; i++)
 #pragma unroll
                 for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            if (cs) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) bs[i] += a[i];
+            }
         }
         __syncthreads();
     }
@@ -131,13 +140,27 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
         float *red = &sm[0][0][0][0];
         if (slice > 0) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) red[((slice - 1) * 16 + i) * NT + tid] = acc[i >> 2][i & 3];
+            for (int i = 0; i < 16; i++) red[((slice - 1) * 20 + i) * NT + tid] = acc[i >> 2][i & 3];
+            if (cs) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) red[((slice - 1) * 20 + 16 + i) * NT + tid] = bs[i];
+            }
         }
         __syncthreads();
         if (slice > 0) return;
-        for (int sl = 0; sl < KS - 1; sl++)
+        for (int sl = 0; sl < KS - 1; sl++) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) acc[i >> 2][i & 3] += red[(sl * 16 + i) * NT + tid];
+            for (int i = 0; i < 16; i++) acc[i >> 2][i & 3] += red[(sl * 20 + i) * NT + tid];
+            if (cs) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) bs[i] += red[(sl * 20 + 16 + i) * NT + tid];
+            }
+        }
+    }
+    if (cs) {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (m0 + ty * 4 + i < M) colsum[m0 + ty * 4 + i] = alpha * bs[i];
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -286,9 +309,9 @@ int nccl_check(int rc, const char *what)
 
 extern "C" {
 
-int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint32_t ldb, float *C, uint32_t ldc,
-                    uint32_t M, uint32_t N, uint32_t K, float alpha, const float *bias, const float *aux, uint32_t ldaux,
-                    int act, void *stream)
+static int train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint32_t ldb, float *C, uint32_t ldc,
+                      uint32_t M, uint32_t N, uint32_t K, float alpha, const float *bias, const float *aux, uint32_t ldaux,
+                      int act, float *colsum, void *stream)
 {
     if (!A || !B || !C || M == 0 || N == 0 || K == 0 || (mode == GEMM_FWD && !bias) || (mode == GEMM_DELTA && !aux)) {
         spgk_set_error("spgk_train_gemm", "bad argument");
@@ -304,7 +327,7 @@ int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint
     const int shape = tiles64 >= 148u ? 0 : tiles32 > 32u ? 1 : 2;
 #define SPG_TRAIN_LAUNCH(MODEV, TSV, KSV) \
     spg_train_gemm_kernel<MODEV, TSV, KSV><<<dim3((N + TSV - 1) / TSV, (M + TSV - 1) / TSV), (TSV / 4) * (TSV / 4) * KSV, 0, s>>>( \
-        A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act)
+        A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act, colsum)
 #define SPG_TRAIN_SHAPES(MODEV) \
     do { if (shape == 0) SPG_TRAIN_LAUNCH(MODEV, 64, 1); else if (shape == 1) SPG_TRAIN_LAUNCH(MODEV, 32, 4); \
          else SPG_TRAIN_LAUNCH(MODEV, 32, 8); } while (0)
@@ -314,6 +337,20 @@ int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint
 #undef SPG_TRAIN_SHAPES
 #undef SPG_TRAIN_LAUNCH
     return spgk_check_launch("spg_train_gemm_kernel");
+}
+
+int spgk_train_gemm(int mode, const float *A, uint32_t lda, const float *B, uint32_t ldb, float *C, uint32_t ldc,
+                    uint32_t M, uint32_t N, uint32_t K, float alpha, const float *bias, const float *aux, uint32_t ldaux,
+                    int act, void *stream)
+{
+    return train_gemm(mode, A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act, nullptr, stream);
+}
+
+int spgk_train_grad(const float *delta, uint32_t ldd, const float *a, uint32_t lda, float *gw, uint32_t ldg, float *gb,
+                    uint32_t out, uint32_t in, uint32_t rows, float scale, void *stream)
+{
+    if (!gb) { spgk_set_error("spgk_train_grad", "bad argument"); return SPGK_E_ARG; }
+    return train_gemm(GEMM_GRAD, delta, ldd, a, lda, gw, ldg, out, in, rows, scale, nullptr, nullptr, 0, 0, gb, stream);
 }
 
 int spgk_ce_delta(const float *a, const float *t, float *delta, uint64_t count, float *loss, int sigmoid_output, void *stream)

@@ -247,9 +247,8 @@ void train_struct_arguments(TrainArgs a)
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 const float *dl = t->deltas + (size_t)cur * p->neuron_offsets[l + 1];
                 const float *al = l == 0 ? bx : t->acts + (size_t)cur * p->neuron_offsets[l];
-                DEV(spgk_train_gemm(2, dl, fo, al, fi, t->grads + p->weight_offsets[l], fi, fo, fi, cur, gs, NULL, NULL, 0, 0, st),
-                    "train: weight gradient");
-                DEV(spgk_col_sums(dl, cur, fo, gs, t->grads + tw + p->bias_offsets[l], st), "train: bias gradient");
+                DEV(spgk_train_grad(dl, fo, al, fi, t->grads + p->weight_offsets[l], fi, t->grads + tw + p->bias_offsets[l],
+                                    fo, fi, cur, gs, st), "train: gradients");
                 if (s_world > 1) {
                     DEV(spgk_event_record(s_ev_ready, st), "train: exchange order");
                     DEV(spgk_stream_wait_event(s_ar_stream, s_ev_ready), "train: exchange order");

@@ -178,3 +178,47 @@ def test_checkpoint_and_resume_through_the_file(spg, tmp_path):
     assert np.array_equal(back.weights, net.weights) and np.array_equal(back.biases, net.biases)
     net.free()
     back.free()
+
+
+@pytest.mark.parametrize("rows,fi,fo", [(256, 784, 512), (256, 1000, 10), (37, 53, 29), (1024, 1031, 640), (300, 20, 1000)])
+def test_training_products_match_float64(spg, rows, fi, fo):
+    """The three products of a training step and the one-launch weight+bias gradient against float64 numpy, on shapes
+    that take each tile shape (64x64, 32x32 with four k-slices, 32x32 with eight) and on ragged, unaligned ones."""
+    import torch
+    lib = spg.lib()
+    vp, u32, f32 = C.c_void_p, C.c_uint32, C.c_float
+    lib.spgk_train_gemm.argtypes = [C.c_int, vp, u32, vp, u32, vp, u32, u32, u32, u32, f32, vp, vp, u32, C.c_int, vp]
+    lib.spgk_train_grad.argtypes = [vp, u32, vp, u32, vp, u32, vp, u32, u32, u32, f32, vp]
+    rng = np.random.default_rng(rows * 7 + fi)
+    x = rng.standard_normal((rows, fi)).astype(np.float32)
+    w = (rng.standard_normal((fo, fi)) / np.sqrt(fi)).astype(np.float32)
+    b = rng.standard_normal(fo).astype(np.float32)
+    d = rng.standard_normal((rows, fo)).astype(np.float32)
+    dx, dw, db, dd = (torch.from_numpy(a).cuda() for a in (x, w, b, d))
+    tol = lambda ref: 2e-6 * max(1.0, float(np.abs(ref).max())) * np.sqrt(max(rows, fi, fo))
+    # forward with ReLU
+    y = torch.empty(rows, fo, device="cuda")
+    assert lib.spgk_train_gemm(0, dx.data_ptr(), fi, dw.data_ptr(), fi, y.data_ptr(), fo, rows, fo, fi, 1.0, db.data_ptr(), None, 0,
+                               spg.abi.ACT_RELU, None) == 0
+    ref = np.maximum(x.astype(np.float64) @ w.astype(np.float64).T + b, 0.0)
+    assert np.abs(y.cpu().numpy() - ref).max() <= tol(ref)
+    # delta back through the layer, times the ReLU derivative of the layer input's activation
+    act_in = np.maximum(x, 0.0)
+    da = torch.from_numpy(act_in).cuda()
+    dprev = torch.empty(rows, fi, device="cuda")
+    assert lib.spgk_train_gemm(1, dd.data_ptr(), fo, dw.data_ptr(), fi, dprev.data_ptr(), fi, rows, fi, fo, 1.0, None, da.data_ptr(), fi,
+                               spg.abi.ACT_RELU, None) == 0
+    ref = (d.astype(np.float64) @ w.astype(np.float64)) * (act_in > 0)
+    assert np.abs(dprev.cpu().numpy() - ref).max() <= tol(ref)
+    # gradients: the product alone, then product + column sums in one launch; the product must not change
+    gs = 1.0 / rows
+    gw0 = torch.empty(fo, fi, device="cuda")
+    gw1 = torch.empty(fo, fi, device="cuda")
+    gb = torch.full((fo,), 7.0, device="cuda")
+    assert lib.spgk_train_gemm(2, dd.data_ptr(), fo, dx.data_ptr(), fi, gw0.data_ptr(), fi, fo, fi, rows, gs, None, None, 0, 0, None) == 0
+    assert lib.spgk_train_grad(dd.data_ptr(), fo, dx.data_ptr(), fi, gw1.data_ptr(), fi, gb.data_ptr(), fo, fi, rows, gs, None) == 0
+    ref = gs * (d.astype(np.float64).T @ x.astype(np.float64))
+    assert np.abs(gw0.cpu().numpy() - ref).max() <= tol(ref)
+    assert torch.equal(gw0, gw1)
+    refb = gs * d.astype(np.float64).sum(axis=0)
+    assert np.abs(gb.cpu().numpy() - refb).max() <= tol(refb)
