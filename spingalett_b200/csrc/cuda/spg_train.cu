@@ -179,6 +179,52 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
     }
 }
 
+// Forward product of a narrow layer (N <= 16 outputs, e.g. the class scores): one warp per row of A, the lanes striding
+// over k, every lane keeping N partial sums that a shuffle tree adds at the end.  The N rows of B are read by every warp
+// and stay in L1.  C[m][n] = act(sum_k A[m][k] B[n][k] + bias[n]).
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+spg_train_fwd_narrow_kernel(const float *__restrict__ A, uint32_t lda, const float *__restrict__ B, uint32_t ldb,
+                            float *__restrict__ C, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K,
+                            const float *__restrict__ bias, int act)
+{
+    const uint32_t lane = threadIdx.x & 31u, m = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (m >= M) return;
+    const float *a = A + (uint64_t)m * lda;
+    float acc[16];
+#pragma unroll
+    for (int n = 0; n < 16; n++) acc[n] = 0.0f;
+    if (VEC) {
+        for (uint32_t k = lane * 4u; k < K; k += 128u) {
+            const float4 av = *reinterpret_cast<const float4 *>(a + k);
+#pragma unroll
+            for (int n = 0; n < 16; n++) {
+                if ((uint32_t)n < N) {
+                    const float4 bv = __ldg(reinterpret_cast<const float4 *>(B + (uint64_t)n * ldb + k));
+                    acc[n] = fmaf(av.x, bv.x, fmaf(av.y, bv.y, fmaf(av.z, bv.z, fmaf(av.w, bv.w, acc[n]))));
+                }
+            }
+        }
+    } else {
+        for (uint32_t k = lane; k < K; k += 32u) {
+            const float av = a[k];
+#pragma unroll
+            for (int n = 0; n < 16; n++)
+                if ((uint32_t)n < N) acc[n] = fmaf(av, __ldg(B + (uint64_t)n * ldb + k), acc[n]);
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < 16; n++) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[n] += __shfl_xor_sync(0xffffffffu, acc[n], o);
+    }
+    float v = 0.0f;
+#pragma unroll
+    for (int n = 0; n < 16; n++)
+        if (lane == (uint32_t)n) v = acc[n];
+    if (lane < N) C[(uint64_t)m * ldc + lane] = spg_activate(v + bias[lane], act);
+}
+
 // delta = a - t over `count` elements; optionally adds the cross-entropy of each row to *loss
 // (softmax output: -sum t*log(max(o,1e-9)); sigmoid output: the two-sided form, SIMD.c:533-549).
 __global__ void __launch_bounds__(256)
@@ -320,6 +366,13 @@ static int train_gemm(int mode, const float *A, uint32_t lda, const float *B, ui
     cudaStream_t s = (cudaStream_t)stream;
     if (act == SPG_ACT_SOFTMAX && mode == GEMM_FWD) act = SPG_ACT_NONE;      // softmax rows are finished separately
     if (mode != GEMM_FWD && mode != GEMM_DELTA && mode != GEMM_GRAD) { spgk_set_error("spgk_train_gemm", "unknown mode"); return SPGK_E_ARG; }
+    if (mode == GEMM_FWD && N <= 16u) {
+        const bool vec = (K & 3u) == 0 && (lda & 3u) == 0 && (ldb & 3u) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15u) == 0;
+        if (vec) spg_train_fwd_narrow_kernel<true><<<(M + 7) / 8, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, bias, act);
+        else spg_train_fwd_narrow_kernel<false><<<(M + 7) / 8, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, bias, act);
+        return spgk_check_launch("spg_train_fwd_narrow_kernel");
+    }
     // 64 x 64 tiles when they give each of the 148 SMs a CTA; otherwise 32 x 32 tiles (four times the CTAs) with the k
     // range of each tile split over four thread groups of the CTA, eight when there are at most 32 tiles - on a 256-row
     // step of a 784-512-1000-10 network that is every product
