@@ -179,6 +179,151 @@ spg_train_gemm_kernel(const float *__restrict__ A, uint32_t lda, const float *__
     }
 }
 
+// ---- the same three products on the tensor cores, with fp32-level error -------------------------------------------------
+// An fp32 value x is split into hi = tf32(x) and lo = tf32(x - hi); a*b is formed as a_lo*b_hi + a_hi*b_lo + a_hi*b_hi by
+// three mma.m16n8k8.tf32 with fp32 accumulation (the dropped a_lo*b_lo term is below 2^-22 of the product).  CTA tile
+// 32 x 32, KS k-slices of two warps each (a warp owns 16 rows x 32 columns of the slice's partial sum); staging, slice
+// order and the fixed-order addition of the partial sums are those of spg_train_gemm_kernel.  The staged tiles have a
+// pitch of 40 floats, which makes the fragment reads As[k][m], k = lane%4 (+4), m = lane/4 (+8), conflict-free.
+__device__ __forceinline__ void tf32_split(float x, uint32_t &hi, uint32_t &lo)
+{
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(x - __uint_as_float(hi)));
+}
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int MODE, int KS>
+__global__ void __launch_bounds__(64 * KS)
+spg_train_mma_kernel(const float *__restrict__ A, uint32_t lda, const float *__restrict__ B, uint32_t ldb,
+                     float *__restrict__ C, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K,
+                     float alpha, const float *__restrict__ bias, const float *__restrict__ aux, uint32_t ldaux, int act,
+                     float *__restrict__ colsum)
+{
+    constexpr int TS = 32, NT = 64, Q = 8, R = 2, P = TS + 8;
+    constexpr bool a_km = MODE == GEMM_GRAD;
+    constexpr bool b_nk = MODE == GEMM_FWD;
+    static_assert((KS - 1) * (NT * 16 + TS) <= KS * 2 * TK * P, "the partial sums reuse the staging memory");
+    __shared__ __align__(16) float sm[KS][2][TK][P];
+    const uint32_t slice = threadIdx.x / NT, tid = threadIdx.x % NT, lane = tid & 31u, mh = tid >> 5, g = lane >> 2, t = lane & 3u;
+    float (*As)[P] = sm[slice][0];
+    float (*Bs)[P] = sm[slice][1];
+    const uint32_t m0 = blockIdx.y * TS, n0 = blockIdx.x * TS;
+    const bool a_al = (lda & 3u) == 0 && (reinterpret_cast<uintptr_t>(A) & 15u) == 0 && m0 + TS <= M;
+    const bool b_al = (ldb & 3u) == 0 && (reinterpret_cast<uintptr_t>(B) & 15u) == 0 && n0 + TS <= N;
+    float acc[4][4];                                            // [8-column block][fragment register]
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    float4 ra[R], rb[R];
+    const bool cs = MODE == GEMM_GRAD && colsum != nullptr && blockIdx.x == 0 && tid < (uint32_t)TS;    // thread tid sums column m0+tid
+    float bsum = 0.0f;
+
+    auto fetch = [&](uint32_t k0) {
+        const bool whole = k0 + TK <= K;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const uint32_t i = tid + r * NT;
+            if (a_km) {
+                const uint32_t k = i / Q, m = (i % Q) * 4;
+                ra[r] = train_load4(A + (uint64_t)(k0 + k) * lda + m0 + m, a_al && whole, k0 + k < K, m0 + m, M);
+            } else {
+                const uint32_t m = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                ra[r] = train_load4(A + (uint64_t)(m0 + m) * lda + k0 + k, a_al && whole, m0 + m < M, k0 + k, K);
+            }
+            if (b_nk) {
+                const uint32_t n = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                rb[r] = train_load4(B + (uint64_t)(n0 + n) * ldb + k0 + k, b_al && whole, n0 + n < N, k0 + k, K);
+            } else {
+                const uint32_t k = i / Q, n = (i % Q) * 4;
+                rb[r] = train_load4(B + (uint64_t)(k0 + k) * ldb + n0 + n, b_al && whole, k0 + k < K, n0 + n, N);
+            }
+        }
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const uint32_t i = tid + r * NT;
+            if (a_km) {
+                *reinterpret_cast<float4 *>(&As[i / Q][(i % Q) * 4]) = ra[r];
+            } else {
+                const uint32_t m = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                As[k][m] = ra[r].x; As[k + 1][m] = ra[r].y; As[k + 2][m] = ra[r].z; As[k + 3][m] = ra[r].w;
+            }
+            if (b_nk) {
+                const uint32_t n = i / (TK / 4), k = (i % (TK / 4)) * 4;
+                Bs[k][n] = rb[r].x; Bs[k + 1][n] = rb[r].y; Bs[k + 2][n] = rb[r].z; Bs[k + 3][n] = rb[r].w;
+            } else {
+                *reinterpret_cast<float4 *>(&Bs[i / Q][(i % Q) * 4]) = rb[r];
+            }
+        }
+    };
+
+    fetch(slice * TK);
+    for (uint32_t kb = 0; kb < K; kb += KS * TK) {
+        stage();
+        __syncthreads();
+        if (kb + KS * TK < K) fetch(kb + (KS + slice) * TK);
+#pragma unroll
+        for (int ks = 0; ks < TK; ks += 8) {
+            uint32_t ah[4], al[4];
+            tf32_split(As[ks + t][mh * 16 + g], ah[0], al[0]);
+            tf32_split(As[ks + t][mh * 16 + g + 8], ah[1], al[1]);
+            tf32_split(As[ks + t + 4][mh * 16 + g], ah[2], al[2]);
+            tf32_split(As[ks + t + 4][mh * 16 + g + 8], ah[3], al[3]);
+#pragma unroll
+            for (int nb = 0; nb < 4; nb++) {
+                uint32_t bh0, bl0, bh1, bl1;
+                tf32_split(Bs[ks + t][nb * 8 + g], bh0, bl0);
+                tf32_split(Bs[ks + t + 4][nb * 8 + g], bh1, bl1);
+                mma_tf32(acc[nb], al, bh0, bh1);
+                mma_tf32(acc[nb], ah, bl0, bl1);
+                mma_tf32(acc[nb], ah, bh0, bh1);
+            }
+        }
+        if (cs) {
+#pragma unroll
+            for (int k = 0; k < TK; k++) bsum += As[k][tid];
+        }
+        __syncthreads();
+    }
+    {
+        float *red = &sm[0][0][0][0];
+        if (slice > 0) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) red[(slice - 1) * (NT * 16 + TS) + i * NT + tid] = acc[i >> 2][i & 3];
+            if (cs) red[(slice - 1) * (NT * 16 + TS) + NT * 16 + tid] = bsum;
+        }
+        __syncthreads();
+        if (slice > 0) return;
+        for (int sl = 0; sl < KS - 1; sl++) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i >> 2][i & 3] += red[sl * (NT * 16 + TS) + i * NT + tid];
+            if (cs) bsum += red[sl * (NT * 16 + TS) + NT * 16 + tid];
+        }
+    }
+    if (cs && m0 + tid < M) colsum[m0 + tid] = alpha * bsum;
+#pragma unroll
+    for (int nb = 0; nb < 4; nb++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const uint32_t m = m0 + mh * 16 + g + (c >> 1) * 8, n = n0 + nb * 8 + 2 * t + (c & 1);
+            if (m >= M || n >= N) continue;
+            float v = acc[nb][c];
+            if (MODE == GEMM_FWD) v = spg_activate(v + bias[n], act);
+            else if (MODE == GEMM_DELTA) v *= spg_derivative(aux[(uint64_t)m * ldaux + n], act);
+            else v *= alpha;
+            C[(uint64_t)m * ldc + n] = v;
+        }
+    }
+}
+
 // Forward product of a narrow layer (N <= 16 outputs, e.g. the class scores): one warp per row of A, the lanes striding
 // over k, every lane keeping N partial sums that a shuffle tree adds at the end.  The N rows of B are read by every warp
 // and stay in L1.  C[m][n] = act(sum_k A[m][k] B[n][k] + bias[n]).
@@ -373,22 +518,22 @@ static int train_gemm(int mode, const float *A, uint32_t lda, const float *B, ui
         else spg_train_fwd_narrow_kernel<false><<<(M + 7) / 8, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, bias, act);
         return spgk_check_launch("spg_train_fwd_narrow_kernel");
     }
-    // 64 x 64 tiles when they give each of the 148 SMs a CTA; otherwise 32 x 32 tiles (four times the CTAs) with the k
-    // range of each tile split over four thread groups of the CTA, eight when there are at most 32 tiles - on a 256-row
-    // step of a 784-512-1000-10 network that is every product
+    // Products of at least 148 64 x 64 tiles: the SIMT kernel with that tile.  Smaller ones - on a 256-row step of a
+    // 784-512-1000-10 network that is every product - take 32 x 32 tiles on the tensor cores with the k range of a tile
+    // split over four two-warp slices of the CTA, eight when there are at most 32 tiles.
     const uint32_t tiles64 = ((N + 63) / 64) * ((M + 63) / 64), tiles32 = ((N + 31) / 32) * ((M + 31) / 32);
     const int shape = tiles64 >= 148u ? 0 : tiles32 > 32u ? 1 : 2;
-#define SPG_TRAIN_LAUNCH(MODEV, TSV, KSV) \
-    spg_train_gemm_kernel<MODEV, TSV, KSV><<<dim3((N + TSV - 1) / TSV, (M + TSV - 1) / TSV), (TSV / 4) * (TSV / 4) * KSV, 0, s>>>( \
-        A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act, colsum)
+#define SPG_TRAIN_ARGS A, lda, B, ldb, C, ldc, M, N, K, alpha, bias, aux, ldaux, act, colsum
 #define SPG_TRAIN_SHAPES(MODEV) \
-    do { if (shape == 0) SPG_TRAIN_LAUNCH(MODEV, 64, 1); else if (shape == 1) SPG_TRAIN_LAUNCH(MODEV, 32, 4); \
-         else SPG_TRAIN_LAUNCH(MODEV, 32, 8); } while (0)
+    do { const dim3 g32((N + 31) / 32, (M + 31) / 32); \
+         if (shape == 0) spg_train_gemm_kernel<MODEV, 64, 1><<<dim3((N + 63) / 64, (M + 63) / 64), 256, 0, s>>>(SPG_TRAIN_ARGS); \
+         else if (shape == 1) spg_train_mma_kernel<MODEV, 4><<<g32, 256, 0, s>>>(SPG_TRAIN_ARGS); \
+         else spg_train_mma_kernel<MODEV, 8><<<g32, 512, 0, s>>>(SPG_TRAIN_ARGS); } while (0)
     if (mode == GEMM_FWD) SPG_TRAIN_SHAPES(GEMM_FWD);
     else if (mode == GEMM_DELTA) SPG_TRAIN_SHAPES(GEMM_DELTA);
     else SPG_TRAIN_SHAPES(GEMM_GRAD);
 #undef SPG_TRAIN_SHAPES
-#undef SPG_TRAIN_LAUNCH
+#undef SPG_TRAIN_ARGS
     return spgk_check_launch("spg_train_gemm_kernel");
 }
 
