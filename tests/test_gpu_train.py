@@ -180,11 +180,12 @@ def test_checkpoint_and_resume_through_the_file(spg, tmp_path):
     back.free()
 
 
-@pytest.mark.parametrize("rows,fi,fo", [(256, 784, 512), (256, 1000, 10), (37, 53, 29), (37, 53, 7), (1024, 1031, 640), (300, 20, 1000)])
+@pytest.mark.parametrize("rows,fi,fo", [(256, 784, 512), (256, 1000, 10), (37, 53, 29), (37, 53, 7), (1024, 1031, 640), (300, 20, 1000),
+                                        (37, 64, 48), (256, 512, 1000)])
 def test_training_products_match_float64(spg, rows, fi, fo):
     """The three products of a training step and the one-launch weight+bias gradient against float64 numpy, on shapes
-    that take each tile shape (64x64, 32x32 with four k-slices, 32x32 with eight), the narrow-layer forward kernel
-    (at most 16 outputs, aligned and not) and ragged, unaligned ones."""
+    that take each kernel (64x64 SIMT tiles; 32x32 tensor-core tiles with four or eight k-slices; the narrow-layer
+    forward kernel, aligned and not) with whole and ragged tiles, aligned and unaligned operands."""
     import torch
     lib = spg.lib()
     vp, u32, f32 = C.c_void_p, C.c_uint32, C.c_float
