@@ -290,6 +290,10 @@ SPGK_API int spgk_gemm_tc_status(int32_t *status, void *stream);
  * spgk_train_grad: both gradients of one layer in one launch (Training.c:405-417):
  *   gw[out][in] = scale * delta[rows][out]^T a[rows][in],  gb[out] = scale * sum_rows delta[row][out].
  * spgk_gather_rows: dst[i] = src[idx[i]]                mini-batch assembly (Training.c:759-767).
+ * spgk_gather_rows2: the same rows of two tables (inputs and targets) in one launch.
+ * spgk_train_output: the output end of a step in one launch, for an output layer of at most 16 units:
+ *   y = softmax (or sigmoid) of x w^T + bias, delta = y - t, *loss += cross-entropy of the rows (loss may be NULL);
+ *   replaces mode 0 + spgk_softmax_rows + spgk_ce_delta (Training.c:327-343, :366-371).
  * spgk_adam: one fused pass over a flat parameter buffer; g is scaled by gscale first
  *   (1/ranks after a sum all-reduce); epsilon inside the square root (SIMD.c:279-328).
  * spgk_nonfinite: sets *flag_dev to 1 if any element is NaN/Inf (Training.c:11-19). */
@@ -303,6 +307,11 @@ SPGK_API int spgk_train_grad(const float *delta, uint32_t ldd, const float *a, u
                              float *gb, uint32_t out, uint32_t in, uint32_t rows, float scale, void *stream);
 SPGK_API int spgk_gather_rows(const float *src, const uint32_t *idx, float *dst, uint32_t rows, uint32_t width,
                               void *stream);
+SPGK_API int spgk_gather_rows2(const float *src_a, uint32_t width_a, float *dst_a, const float *src_b, uint32_t width_b,
+                               float *dst_b, const uint32_t *idx, uint32_t rows, void *stream);
+SPGK_API int spgk_train_output(const float *x, uint32_t ldx, const float *w, uint32_t ldw, const float *bias, float *y,
+                               const float *t, float *delta, float *loss, uint32_t rows, uint32_t out, uint32_t in,
+                               int sigmoid_output, void *stream);
 SPGK_API int spgk_adam(float *w, float *m, float *v, const float *g, uint64_t n, float lr, float b1, float b2,
                        float mf, float vf, float eps, float gscale, void *stream);
 SPGK_API int spgk_nonfinite(const float *w, uint64_t n, int *flag_dev, void *stream);

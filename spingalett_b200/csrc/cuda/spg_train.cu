@@ -327,11 +327,15 @@ spg_train_mma_kernel(const float *__restrict__ A, uint32_t lda, const float *__r
 // Forward product of a narrow layer (N <= 16 outputs, e.g. the class scores): one warp per row of A, the lanes striding
 // over k, every lane keeping N partial sums that a shuffle tree adds at the end.  The N rows of B are read by every warp
 // and stay in L1.  C[m][n] = act(sum_k A[m][k] B[n][k] + bias[n]).
-template <bool VEC>
+// FUSE 1 / 2 make it the whole output end of a training step in one launch: the row's softmax (1) or sigmoid (2) is formed
+// in the warp, C gets the activation, delta[m][n] = C[m][n] - T[m][n], and the row's cross-entropy is added to *loss when
+// loss is not null (same formulas as spg_softmax_rows_kernel and spg_ce_delta_kernel).
+template <bool VEC, int FUSE>
 __global__ void __launch_bounds__(256)
 spg_train_fwd_narrow_kernel(const float *__restrict__ A, uint32_t lda, const float *__restrict__ B, uint32_t ldb,
                             float *__restrict__ C, uint32_t ldc, uint32_t M, uint32_t N, uint32_t K,
-                            const float *__restrict__ bias, int act)
+                            const float *__restrict__ bias, int act, const float *__restrict__ T, float *__restrict__ delta,
+                            float *loss)
 {
     const uint32_t lane = threadIdx.x & 31u, m = blockIdx.x * 8u + (threadIdx.x >> 5);
     if (m >= M) return;
@@ -367,7 +371,39 @@ spg_train_fwd_narrow_kernel(const float *__restrict__ A, uint32_t lda, const flo
 #pragma unroll
     for (int n = 0; n < 16; n++)
         if (lane == (uint32_t)n) v = acc[n];
-    if (lane < N) C[(uint64_t)m * ldc + lane] = spg_activate(v + bias[lane], act);
+    const bool mine = lane < N;
+    const float z = mine ? v + bias[lane] : 0.0f;
+    if (FUSE == 0) {
+        if (mine) C[(uint64_t)m * ldc + lane] = spg_activate(z, act);
+        return;
+    }
+    float o;
+    if (FUSE == 1) {
+        const float mx = spg_warp_max(mine ? z : -FLT_MAX);
+        const float e = mine ? expf(z - mx) : 0.0f;
+        const float sum = spg_warp_sum(e);
+        o = sum > 0.0f ? e * (1.0f / sum) : e;
+    } else {
+        o = spg_activate(z, SPG_ACT_SIGMOID);
+    }
+    float local = 0.0f;
+    if (mine) {
+        const float tg = T[(uint64_t)m * N + lane];
+        C[(uint64_t)m * ldc + lane] = o;
+        delta[(uint64_t)m * N + lane] = o - tg;
+        if (loss) {
+            if (FUSE == 2) {
+                const float c = fminf(fmaxf(o, 1e-9f), 1.0f - 1e-9f);
+                local = -(tg * logf(c) + (1.0f - tg) * logf(1.0f - c));
+            } else {
+                local = -tg * logf(fmaxf(o, 1e-9f));
+            }
+        }
+    }
+    if (loss) {
+        local = spg_warp_sum(local);
+        if (lane == 0) atomicAdd(loss, local);
+    }
 }
 
 // delta = a - t over `count` elements; optionally adds the cross-entropy of each row to *loss
@@ -426,6 +462,21 @@ spg_gather_rows_kernel(const float *__restrict__ src, const uint32_t *__restrict
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t r = (uint32_t)(i / width), c = (uint32_t)(i % width);
         dst[i] = src[(uint64_t)idx[r] * width + c];
+    }
+}
+
+// gather the same rows of two tables (a mini-batch's inputs and targets) in one launch
+__global__ void __launch_bounds__(256)
+spg_gather_rows2_kernel(const float *__restrict__ src_a, uint32_t wa, float *__restrict__ dst_a, const float *__restrict__ src_b,
+                        uint32_t wb, float *__restrict__ dst_b, const uint32_t *__restrict__ idx, uint32_t rows)
+{
+    const uint32_t w = wa + wb;
+    const uint64_t total = (uint64_t)rows * w;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t r = (uint32_t)(i / w), c = (uint32_t)(i % w);
+        const uint64_t from = idx[r];
+        if (c < wa) dst_a[(uint64_t)r * wa + c] = src_a[from * wa + c];
+        else dst_b[(uint64_t)r * wb + (c - wa)] = src_b[from * wb + (c - wa)];
     }
 }
 
@@ -514,8 +565,8 @@ static int train_gemm(int mode, const float *A, uint32_t lda, const float *B, ui
     if (mode == GEMM_FWD && N <= 16u) {
         const bool vec = (K & 3u) == 0 && (lda & 3u) == 0 && (ldb & 3u) == 0 &&
                          ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15u) == 0;
-        if (vec) spg_train_fwd_narrow_kernel<true><<<(M + 7) / 8, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, bias, act);
-        else spg_train_fwd_narrow_kernel<false><<<(M + 7) / 8, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, bias, act);
+        if (vec) spg_train_fwd_narrow_kernel<true, 0><<<(M + 7) / 8, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, bias, act, nullptr, nullptr, nullptr);
+        else spg_train_fwd_narrow_kernel<false, 0><<<(M + 7) / 8, 256, 0, s>>>(A, lda, B, ldb, C, ldc, M, N, K, bias, act, nullptr, nullptr, nullptr);
         return spgk_check_launch("spg_train_fwd_narrow_kernel");
     }
     // Products of at least 148 64 x 64 tiles: the SIMT kernel with that tile.  Smaller ones - on a 256-row step of a
@@ -549,6 +600,35 @@ int spgk_train_grad(const float *delta, uint32_t ldd, const float *a, uint32_t l
 {
     if (!gb) { spgk_set_error("spgk_train_grad", "bad argument"); return SPGK_E_ARG; }
     return train_gemm(GEMM_GRAD, delta, ldd, a, lda, gw, ldg, out, in, rows, scale, nullptr, nullptr, 0, 0, gb, stream);
+}
+
+int spgk_train_output(const float *x, uint32_t ldx, const float *w, uint32_t ldw, const float *bias, float *y, const float *t,
+                      float *delta, float *loss, uint32_t rows, uint32_t out, uint32_t in, int sigmoid_output, void *stream)
+{
+    if (!x || !w || !bias || !y || !t || !delta || rows == 0 || in == 0 || out == 0 || out > 16u) {
+        spgk_set_error("spgk_train_output", "bad argument");
+        return SPGK_E_ARG;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = (in & 3u) == 0 && (ldx & 3u) == 0 && (ldw & 3u) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0;
+    const dim3 grid((rows + 7) / 8);
+#define SPG_OUT_LAUNCH(VECV, FUSEV) \
+    spg_train_fwd_narrow_kernel<VECV, FUSEV><<<grid, 256, 0, s>>>(x, ldx, w, ldw, y, out, rows, out, in, bias, 0, t, delta, loss)
+    if (sigmoid_output) { if (vec) SPG_OUT_LAUNCH(true, 2); else SPG_OUT_LAUNCH(false, 2); }
+    else { if (vec) SPG_OUT_LAUNCH(true, 1); else SPG_OUT_LAUNCH(false, 1); }
+#undef SPG_OUT_LAUNCH
+    return spgk_check_launch("spg_train_fwd_narrow_kernel");
+}
+
+int spgk_gather_rows2(const float *src_a, uint32_t width_a, float *dst_a, const float *src_b, uint32_t width_b, float *dst_b,
+                      const uint32_t *idx, uint32_t rows, void *stream)
+{
+    if (!src_a || !dst_a || !src_b || !dst_b || !idx) { spgk_set_error("spgk_gather_rows2", "bad argument"); return SPGK_E_ARG; }
+    if (rows == 0 || width_a + width_b == 0) return SPGK_OK;
+    spg_gather_rows2_kernel<<<blocks_for((uint64_t)rows * (width_a + width_b)), 256, 0, (cudaStream_t)stream>>>(
+        src_a, width_a, dst_a, src_b, width_b, dst_b, idx, rows);
+    return spgk_check_launch("spg_gather_rows2_kernel");
 }
 
 int spgk_ce_delta(const float *a, const float *t, float *delta, uint64_t count, float *loss, int sigmoid_output, void *stream)

@@ -221,24 +221,33 @@ void train_struct_arguments(TrainArgs a)
             const uint32_t cur = start + batch > a.sample_count ? a.sample_count - start : batch;
             const float *bx = t->data_x, *bt = t->data_t;
             if (mini) {
-                DEV(spgk_gather_rows(t->data_x, t->idx + start, t->batch_x, cur, in0, st), "train: gather inputs");
-                DEV(spgk_gather_rows(t->data_t, t->idx + start, t->batch_t, cur, outw, st), "train: gather targets");
+                DEV(spgk_gather_rows2(t->data_x, in0, t->batch_x, t->data_t, outw, t->batch_t, t->idx + start, cur, st),
+                    "train: gather mini-batch");
                 bx = t->batch_x; bt = t->batch_t;
             }
-            /* forward: activations of layer l live at acts + cur*neuron_offsets[l], [cur][width] */
+            /* forward: activations of layer l live at acts + cur*neuron_offsets[l], [cur][width].  An output layer of at
+               most 16 units is finished in one launch: product, softmax or sigmoid, delta and (when someone will read
+               it) the loss; otherwise product, softmax rows and the delta kernel follow one another */
+            float *d_last = t->deltas + (size_t)cur * p->neuron_offsets[last];
+            const bool fused_out = outw <= 16;
             const float *x = bx;
             for (uint32_t l = 0; l < last; l++) {
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 float *y = t->acts + (size_t)cur * p->neuron_offsets[l + 1];
+                if (l + 1 == last && fused_out) {
+                    DEV(spgk_train_output(x, fi, t->params + p->weight_offsets[l], fi, t->params + tw + p->bias_offsets[l], y, bt,
+                                          d_last, need_loss ? t->loss : NULL, cur, fo, fi, out_act == ACT_SIGMOID, st),
+                        "train: output layer");
+                    break;
+                }
                 DEV(spgk_train_gemm(0, x, fi, t->params + p->weight_offsets[l], fi, y, fo, cur, fo, fi, 1.0f,
                                     t->params + tw + p->bias_offsets[l], NULL, 0, (int)p->act_func[l], st), "train: forward");
                 if (p->act_func[l] == ACT_SOFTMAX) DEV(spgk_softmax_rows(y, fo, cur, fo, st), "train: softmax");
                 x = y;
             }
-            /* output delta (+ loss when someone will read it) */
-            float *d_last = t->deltas + (size_t)cur * p->neuron_offsets[last];
-            DEV(spgk_ce_delta(t->acts + (size_t)cur * p->neuron_offsets[last], bt, d_last, (uint64_t)cur * outw,
-                              need_loss ? t->loss : NULL, out_act == ACT_SIGMOID, st), "train: output delta");
+            if (!fused_out)
+                DEV(spgk_ce_delta(t->acts + (size_t)cur * p->neuron_offsets[last], bt, d_last, (uint64_t)cur * outw,
+                                  need_loss ? t->loss : NULL, out_act == ACT_SIGMOID, st), "train: output delta");
             /* backwards through the layers: the gradients of layer l (from delta l+1 and activation l) go into the flat
                buffer and, with several replicas, start their all-reduce on the exchange stream at once, so that it runs
                under the delta and gradient products of the layers below */

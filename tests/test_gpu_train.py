@@ -112,6 +112,27 @@ def test_sigmoid_output_and_ragged_last_batch(spg, oracle):
     net.free()
 
 
+@pytest.mark.parametrize("outw,act", [(24, "softmax"), (20, "sigmoid"), (7, "softmax")])
+def test_wide_and_narrow_output_layers_match_oracle_gradients(spg, oracle, outw, act):
+    """An output layer of more than 16 units takes product + softmax rows + delta kernel, a narrower one the one-launch
+    output kernel: both give the oracle's gradients, and the loss that train() reports is finite."""
+    out_act = spg.abi.ACT_SOFTMAX if act == "softmax" else spg.abi.ACT_SIGMOID
+    net = spg.Network.build([16, 40, outw], [spg.abi.ACT_RELU, out_act], spg.abi.WEIGHT_INITIALIZATION_HE, seed=11)
+    onet = oracle.OracleNet.from_arrays(net.topology, net.acts, net.weights, net.biases)
+    rng = np.random.default_rng(outw)
+    x = rng.random((48, 16), dtype=np.float32)
+    if act == "softmax":
+        t = np.zeros((48, outw), np.float32)
+        t[np.arange(48), rng.integers(0, outw, 48)] = 1.0
+    else:
+        t = (rng.random((48, outw)) > 0.5).astype(np.float32)
+    net.train(x, t, epochs=1, strategy=spg.abi.STRATEGY_FULL_BATCH, learning_rate=1e-3)
+    grads = _flat(net.c, "grad_weights", "grad_biases")
+    og = onet.gradients(x, t, 1.0 / 48)
+    assert np.linalg.norm(grads - og) / np.linalg.norm(og) <= 1e-5
+    net.free()
+
+
 def test_unsupported_training_requests_are_refused(spg):
     lib, a = spg.lib(), spg.abi
     net = spg.Network.build([4, 3, 2], [a.ACT_RELU, a.ACT_SOFTMAX], a.WEIGHT_INITIALIZATION_HE, seed=1)
