@@ -322,6 +322,9 @@ SPGK_API int spgk_nonfinite(const float *w, uint64_t n, int *flag_dev, void *str
 SPGK_API int spgk_nccl_unique_id(void *id128);
 SPGK_API int spgk_nccl_init(void **comm, int rank, int world, const void *id128);
 SPGK_API int spgk_nccl_allreduce_sum(void *comm, float *buf, uint64_t count, void *stream);
+/* two buffers summed in one grouped NCCL launch */
+SPGK_API int spgk_nccl_allreduce_sum2(void *comm, float *buf_a, uint64_t count_a, float *buf_b, uint64_t count_b,
+                                     void *stream);
 SPGK_API int spgk_nccl_destroy(void *comm);
 
 /* ---- K2 without allocations ----------------------------------------------

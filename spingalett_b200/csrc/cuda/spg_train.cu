@@ -516,6 +516,8 @@ struct NcclApi {
     int (*CommInitRank)(nccl_comm *, int, nccl_uid, int);
     int (*AllReduce)(const void *, void *, size_t, int, int, nccl_comm, cudaStream_t);
     int (*CommDestroy)(nccl_comm);
+    int (*GroupStart)(void);
+    int (*GroupEnd)(void);
     const char *(*GetErrorString)(int);
 };
 NcclApi g_nccl;
@@ -532,7 +534,9 @@ int nccl_load()
     g_nccl.AllReduce = (int (*)(const void *, void *, size_t, int, int, nccl_comm, cudaStream_t))dlsym(h, "ncclAllReduce");
     g_nccl.CommDestroy = (int (*)(nccl_comm))dlsym(h, "ncclCommDestroy");
     g_nccl.GetErrorString = (const char *(*)(int))dlsym(h, "ncclGetErrorString");
-    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.CommDestroy) {
+    g_nccl.GroupStart = (int (*)(void))dlsym(h, "ncclGroupStart");
+    g_nccl.GroupEnd = (int (*)(void))dlsym(h, "ncclGroupEnd");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.CommDestroy || !g_nccl.GroupStart || !g_nccl.GroupEnd) {
         spgk_set_error("libnccl", "missing symbols");
         return SPGK_E_CUDA;
     }
@@ -700,6 +704,18 @@ int spgk_nccl_allreduce_sum(void *comm, float *buf, uint64_t count, void *stream
     if (!comm || !g_nccl.handle) { spgk_set_error("spgk_nccl_allreduce_sum", "no communicator"); return SPGK_E_ARG; }
     return nccl_check(g_nccl.AllReduce(buf, buf, (size_t)count, 7 /* ncclFloat32 */, 0 /* ncclSum */, comm, (cudaStream_t)stream),
                       "ncclAllReduce");
+}
+
+int spgk_nccl_allreduce_sum2(void *comm, float *buf_a, uint64_t count_a, float *buf_b, uint64_t count_b, void *stream)
+{
+    if (!comm || !g_nccl.handle) { spgk_set_error("spgk_nccl_allreduce_sum2", "no communicator"); return SPGK_E_ARG; }
+    int rc = nccl_check(g_nccl.GroupStart(), "ncclGroupStart");
+    if (rc != SPGK_OK) return rc;
+    int ra = g_nccl.AllReduce(buf_a, buf_a, (size_t)count_a, 7 /* ncclFloat32 */, 0 /* ncclSum */, comm, (cudaStream_t)stream);
+    int rb = g_nccl.AllReduce(buf_b, buf_b, (size_t)count_b, 7, 0, comm, (cudaStream_t)stream);
+    int re = g_nccl.GroupEnd();                     // always closed, so that a failed call does not leave the group open
+    if ((rc = nccl_check(ra, "ncclAllReduce")) != SPGK_OK || (rc = nccl_check(rb, "ncclAllReduce")) != SPGK_OK) return rc;
+    return nccl_check(re, "ncclGroupEnd");
 }
 
 int spgk_nccl_destroy(void *comm)

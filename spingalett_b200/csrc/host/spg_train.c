@@ -261,9 +261,12 @@ void train_struct_arguments(TrainArgs a)
                 if (s_world > 1) {
                     DEV(spgk_event_record(s_ev_ready, st), "train: exchange order");
                     DEV(spgk_stream_wait_event(s_ar_stream, s_ev_ready), "train: exchange order");
-                    DEV(spgk_nccl_allreduce_sum(s_comm, t->grads + p->weight_offsets[l], (uint64_t)fi * fo, s_ar_stream),
-                        "train: all-reduce");
-                    if (l == 0) DEV(spgk_nccl_allreduce_sum(s_comm, t->grads + tw, tb, s_ar_stream), "train: all-reduce");
+                    if (l == 0)             /* the bias gradients of every layer are complete now: one launch for both */
+                        DEV(spgk_nccl_allreduce_sum2(s_comm, t->grads + p->weight_offsets[l], (uint64_t)fi * fo, t->grads + tw, tb,
+                                                     s_ar_stream), "train: all-reduce");
+                    else
+                        DEV(spgk_nccl_allreduce_sum(s_comm, t->grads + p->weight_offsets[l], (uint64_t)fi * fo, s_ar_stream),
+                            "train: all-reduce");
                 }
                 if (l > 0)
                     DEV(spgk_train_gemm(1, dl, fo, t->params + p->weight_offsets[l], fi,
