@@ -351,6 +351,10 @@ def run_train(args):
                           "config": {"workload": "MLP 784-512-1000-10 training, 256 rows per GPU per step, cross-entropy, Adam lr 1e-3, one train() call of %d epochs over 5120 rows " % epochs +
                                                  "(host arrays in, weights and optimiser state back to the host at the end)",
                                      "collective": "NCCL all-reduce of 924930 fp32 gradients per step" if world > 1 else "none"},
+                          "e2e": {"value": 256 * steps * world / (ms * 1e-3), "unit": "samples/s",
+                                  "h2d_bytes_per_step": int((x.nbytes + tg.nbytes + 3 * 924930 * 4) // steps),
+                                  "d2h_bytes_per_step": int((4 * 924930 * 4) // steps),
+                                  "note": "train() takes host arrays and returns host arrays: the timed region is the call"},
                           "gpu_launches": int(launches)}))
     if world > 1:
         lib.spingalett_dist_shutdown()
