@@ -36,7 +36,6 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 TOPO = [784, 512, 1000, 10]
 FLOP_PER_SAMPLE = 2 * (784 * 512 + 512 * 1000 + 1000 * 10)       # 1 846 816
@@ -169,7 +168,7 @@ class ClockSampler:
 
 
 def make_net_file(spg, dtype, tmpdir, workload="mlp"):
-    import nets
+    from spingalett_b200 import configs as nets
     if workload == "mlp":
         return nets.make_net_file(spg, os.path.join(tmpdir, f"mlp_{dtype}.nn"), nets.A_TOPO, nets.A_ACTS,
                                   spg.abi.PRECISION_NAMES[dtype], seed=1234, reference_rng=True)
@@ -179,7 +178,7 @@ def make_net_file(spg, dtype, tmpdir, workload="mlp"):
 
 
 def make_inputs(workload, batch, width, seed):
-    import nets
+    from spingalett_b200 import configs as nets
     return nets.uniform_inputs(batch, width, seed) if WORKLOADS[workload][5] == "uniform" else nets.normal_inputs(batch, width, seed)
 
 
@@ -220,22 +219,53 @@ def cpu_arm(path, x, steps, warmup, sample_rows):
             "sample": f"{sample_rows} rows x {steps} steps of the same batch; {how}", "ms_per_step": dt / steps * 1e3}
 
 
+def workload_name(args):
+    """One description of the configuration, shared by both arms."""
+    dist_name = "U[0,1)" if WORKLOADS[args.workload][5] == "uniform" else "N(0,1)"
+    return (f"MLP {'-'.join(map(str, args.topo))} forward, weights stored {args.dtype} (.nn), batch {args.batch} per GPU, "
+            f"{dist_name} fp32 inputs")
+
+
+def reference_net_file(dtype, tmpdir, workload):
+    """The same .nn file as make_net_file(), written by the reference library itself (its own generator stream after
+    rng_seed for the benchmark MLP, the same numpy draws for the two large nets, its own save_spingalett), so the
+    reference arm never loads this repository's library."""
+    from oracle import Reference as R
+    from spingalett_b200 import abi, configs
+    path = os.path.join(tmpdir, f"{workload}_{dtype}_ref.nn")
+    if workload == "mlp":
+        net = R.build_net(configs.A_TOPO, configs.A_ACTS, abi.WEIGHT_INITIALIZATION_HE, seed=1234)
+    else:
+        topo, acts = (configs.W_TOPO, configs.W_ACTS) if workload == "wide" else (configs.L_TOPO, configs.L_ACTS)
+        net = R.build_net(topo, acts, abi.WEIGHT_INITIALIZATION_NONE)
+
+        class _View:                      # what configs.fill_normal writes into
+            weights, biases = R.weights(net), R.biases(net)
+        configs.fill_normal(_View, topo, WORKLOADS[workload][4], 77)
+    R.save(net, path, abi.PRECISION_NAMES[dtype])
+    R.free(net)
+    return path
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import spingalett_b200 as spg          # only to write the .nn file the reference then loads itself
-    spg.lib().spingalett_set_verbose(False)
-    import nets
+    from oracle import Reference
     tmpdir = tempfile.mkdtemp(prefix="spg_bench_")
-    path = make_net_file(spg, args.dtype, tmpdir, args.workload)
+    if Reference.available():
+        path = reference_net_file(args.dtype, tmpdir, args.workload)
+    else:
+        import spingalett_b200 as spg      # no reference build here: the oracle port reads a file this library writes
+        spg.lib().spingalett_set_verbose(False)
+        path = make_net_file(spg, args.dtype, tmpdir, args.workload)
     x = make_inputs(args.workload, args.batch, args.topo[0], 4321)
     r = cpu_arm(path, x, args.steps, args.warmup, args.batch)
     line = {"metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": f"MLP {'-'.join(map(str, args.topo))}, {args.dtype} .nn file (dequantised to fp32 at load), batch {args.batch}",
-                       "batch_per_gpu": args.batch},
+            "config": {"workload": workload_name(args), "batch_per_gpu": args.batch,
+                       "note": "the reference dequantises the file to fp32 at load and computes in fp32 (OpenBLAS sgemm)"},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -305,7 +335,6 @@ def run_train(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("gloo")
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
     import spingalett_b200 as spg
     lib = spg.lib()
     lib.spingalett_set_verbose(False)
@@ -377,14 +406,11 @@ def main():
     torch.cuda.set_device(local_rank)
     dist = None
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
-            os.environ["NCCL_DEBUG"] = "WARN"          # keep stdout to the one JSON line
         import torch.distributed as dist_mod
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist = dist_mod
 
     import spingalett_b200 as spg
-    import nets
     lib = spg.lib()
     lib.spingalett_set_verbose(False)
     assert lib.spingalett_set_device(local_rank) == 0
@@ -422,9 +448,7 @@ def main():
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": compute, "data": "synthetic",
-        "config": {"workload": f"MLP {'-'.join(map(str, topo))} forward, weights stored {args.dtype} (.nn), batch {batch} per GPU, "
-                               f"{'U[0,1)' if WORKLOADS[args.workload][5] == 'uniform' else 'N(0,1)'} fp32 inputs",
-                   "batch_per_gpu": batch, "math_mode": args.math, "path": path_taken,
+        "config": {"workload": workload_name(args), "batch_per_gpu": batch, "math_mode": args.math, "path": path_taken,
                    "l2": ("inputs (205 MB per batch) and activations exceed the 126 MB L2; no explicit flush" if args.workload == "mlp"
                           else "the stored weights streamed every step (>= 136 MB) exceed the 126 MB L2; no explicit flush"),
                    "sharding": "rows across ranks, weights replicated, no collective"},

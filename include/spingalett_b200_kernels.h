@@ -277,6 +277,51 @@ SPGK_API int spgk_layer_gemm_tc_head(const spgk_layer *L,
                                      uint32_t N, int32_t *status, void *stream);
 SPGK_API int spgk_gemm_tc_status(int32_t *status, void *stream);
 
+/* ---- K2f: a three-layer MLP in one launch (large batches) ----------------------
+ * out[N][L3->out] = head(act2(L2(act1(L1(x))))) for a net of exactly three weight layers whose last
+ * layer ("head") has at most 16 outputs -- the whole layer loop of batch_forward (reference
+ * Training.c:313-345) in ONE persistent tcgen05 kernel: the fp32 input rows are rounded to the 16-bit
+ * operand type inside the kernel, the first hidden matrix lives only in shared memory (as the A
+ * operand of layer 2), the second only in registers (rounded to 16 bits and multiplied into the head's sums
+ * by warp-level MMAs whose A fragments come straight from tensor memory),
+ * and bias / activation / row softmax (Activation.c:5-38) are applied on the way.  No activation
+ * matrix is written to or read from HBM.
+ *   w1_16 / w2_16: the 16-bit K-major weight operands of layers 1 and 2 ([out][ldw], flavour type16):
+ *     the stored payload itself for FP16/BF16 files (spgk_weights16_direct), else spgk_dequant16 output.
+ *   params: spgk_mlp3_params_bytes() bytes filled once per net and 16-bit flavour by spgk_mlp3_params
+ *     (padded biases, and the head's weights as a 16-bit operand: exact for INT8/INT4/INT2/FP16/BF16 files).
+ *   x: dev fp32 rows, 16-byte aligned, ldx a multiple of 4.  rows_idx (optional, dev): logical row r
+ *     reads input row rows_idx[r] and writes output row rows_idx[r].  rows_limit (optional, dev): the
+ *     kernel works on min(N, *rows_limit) rows, read when it runs; rows_expected is the caller's
+ *     guess of that count (0 = none) and only sizes the grid.
+ *   pairs != 0: every row is computed from a two-term split (16-bit rounding + scaled remainder) of the
+ *     input and of the hidden activations, carried as two adjacent rows of the same one-term tensor
+ *     pass and recombined in the epilogue: exact products for INT8/INT4/INT2/FP16/BF16 files at twice
+ *     the tensor work per row.
+ *   margin_idx / margin_count (optional, dev; pairs == 0, softmax head): rows whose two largest logits
+ *     are within theta are appended to margin_idx and counted in *margin_count (the caller zeroes it).
+ *   status: dev int32, as for spgk_layer_gemm_tc (read with spgk_gemm_tc_status).
+ * spgk_mlp3_supported() == 0 (other depths, hidden width above 512, head wider than 16, unaligned
+ * input rows) means: run the layers one by one with spgk_layer_gemm_tc. */
+SPGK_API int spgk_mlp3_supported(const spgk_layer *L1, const spgk_layer *L2, const spgk_layer *L3, uint32_t ldx);
+SPGK_API size_t spgk_mlp3_params_bytes(const spgk_layer *L1, const spgk_layer *L2, const spgk_layer *L3);
+SPGK_API int spgk_mlp3_params(const spgk_layer *L1, const spgk_layer *L2, const spgk_layer *L3, int type16, float *dst, void *stream);
+SPGK_API int spgk_mlp3_forward(const spgk_layer *L1, const void *w1_16, uint32_t ldw1,
+                               const spgk_layer *L2, const void *w2_16, uint32_t ldw2,
+                               const spgk_layer *L3, const float *params, int type16,
+                               const float *x, uint32_t ldx, const uint32_t *rows_idx, const uint32_t *rows_limit,
+                               uint32_t rows_expected, int pairs, float *out, uint32_t ldo, uint32_t N,
+                               float theta, uint32_t *margin_idx, uint32_t *margin_count,
+                               int32_t *status, void *stream);
+
+/* Profiling hook of the one-launch MLP (no reference counterpart): after spgk_mlp3_set_trace(buf) the
+ * spgk_mlp3_forward calls of this thread make CTA 0 write cycle counters of its four roles into buf (dev, 32
+ * uint64: [0..4] MMA issuer total / waits for accumulator, input tile, hidden tile, weight tile; [8..12] one
+ * epilogue warp total / wait for accumulator / layer-1 work / layer-2 work / exchange wait; [16..18] one
+ * converter warp total / wait for a free slot / work; [24..25] weight producer total / wait for a free slot).
+ * NULL switches it off. */
+SPGK_API void spgk_mlp3_set_trace(unsigned long long *trace32);
+
 /* ---- training step (fp32, as the reference) -------------------------------
  * spgk_train_gemm modes:
  *   0  C[M][N] = act(A[M][K] B[N][K]^T + bias[N])      forward, batch_forward (Training.c:327-343);

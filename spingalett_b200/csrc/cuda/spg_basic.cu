@@ -21,7 +21,46 @@ int spgk_check_launch(const char *kernel_name)
     return SPGK_OK;
 }
 
+int spg_device_props(SpgDeviceProps *out)
+{
+    static SpgDeviceProps table[SPG_MAX_DEVICES];
+    static SpgOncePerDevice once;
+    int dev = 0;
+    SPGK_CUDA(cudaGetDevice(&dev));
+    const int rc = once.run(dev, [&]() -> int {
+        int sms = 0, optin = 0, major = 0, minor = 0;
+        SPGK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        SPGK_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        SPGK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        SPGK_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+        table[dev].cc = major * 10 + minor; table[dev].sm_count = sms; table[dev].smem_optin = (size_t)optin;
+        return SPGK_OK;
+    });
+    if (rc) return rc;
+    *out = table[dev];
+    return SPGK_OK;
+}
+
 extern "C" {
+
+// Host-only check of the once-per-device bookkeeping the launchers use (no CUDA call): `calls` rounds over
+// `devices` fake device indices, the set-up of device `fail_first` failing on its first attempt.  Returns the
+// number of set-ups that ran, or -1 if an out-of-range index was accepted.
+int spgk_selftest_once_per_device(int devices, int calls, int fail_first)
+{
+    SpgOncePerDevice once;
+    int ran = 0;
+    bool failed_once = false;
+    for (int c = 0; c < calls; c++)
+        for (int d = 0; d < devices; d++)
+            once.run(d, [&]() -> int {
+                ran++;
+                if (d == fail_first && !failed_once) { failed_once = true; return SPGK_E_CUDA; }
+                return SPGK_OK;
+            });
+    if (once.run(-1, [] { return SPGK_OK; }) == SPGK_OK || once.run(SPG_MAX_DEVICES, [] { return SPGK_OK; }) == SPGK_OK) return -1;
+    return ran;
+}
 
 const char *spgk_error_string(void) { return g_err; }
 uint64_t spgk_launch_count(void) { return g_launches.load(); }

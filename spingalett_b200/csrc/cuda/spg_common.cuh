@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <float.h>
+#include <mutex>
 #include "spingalett_b200_kernels.h"
 
 // enum values of the public header (ActivationFunction / PrecisionMode)
@@ -26,6 +27,30 @@ int  spgk_check_launch(const char *kernel_name);
             return e__ == cudaErrorMemoryAllocation ? SPGK_E_NOMEM : SPGK_E_CUDA; \
         }                                                                        \
     } while (0)
+
+// ---- per-device launcher state ----------------------------------------------
+// SM count, compute capability and the opt-in shared-memory limit of a device, looked up once per
+// device (a process may use several: spingalett_set_device, per-net device binding).
+#define SPG_MAX_DEVICES 64
+struct SpgDeviceProps { int cc; int sm_count; size_t smem_optin; };
+// properties of the CURRENT device (cached per device under a mutex); SPGK_OK or an error code
+int spg_device_props(SpgDeviceProps *out);
+
+// Work that has to happen once per device and per kernel -- cudaFuncSetAttribute is per device -- keyed by
+// the device index: `fn` runs the first time `device` is seen (and again if it failed), under a mutex.
+struct SpgOncePerDevice {
+    std::mutex lock;
+    uint64_t done = 0;
+    template <typename Fn> int run(int device, Fn fn)
+    {
+        if (device < 0 || device >= SPG_MAX_DEVICES) { spgk_set_error("device table", "device index out of range"); return SPGK_E_ARG; }
+        std::lock_guard<std::mutex> g(lock);
+        if ((done >> device) & 1u) return SPGK_OK;
+        const int rc = fn();
+        if (rc == SPGK_OK) done |= (uint64_t)1 << device;
+        return rc;
+    }
+};
 
 // Scalar activation, same comparisons as the reference (Activation.c:23-38):
 // strict > and <, so ReLU(0)=0, FOO52(0)=0, FOO52(1)=1.  Softmax and "none"

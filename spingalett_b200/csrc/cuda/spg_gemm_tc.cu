@@ -18,6 +18,7 @@
 // code in `status`, raises a shared abort flag that all roles poll, drains, frees
 // its tensor memory and returns; the launcher turns that into SPGK_E_TIMEOUT.
 #include "spg_common.cuh"
+#include "spg_tc.cuh"
 #include <cuda.h>
 #include <cstdio>
 #include <mutex>
@@ -64,42 +65,18 @@ struct GemmParams {
 
 struct RowLimit { uint32_t m_tiles, group_m; };   // tile counts for the rows actually present (<= the launch's capacity)
 
-// ---- raw PTX wrappers -------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// ---- PTX wrappers: the shared ones of spg_tc.cuh, plus what only this kernel uses -----------------
+using spgtc::smem_u32; using spgtc::mbar_init; using spgtc::mbar_arrive; using spgtc::tc_fence_before; using spgtc::tc_fence_after;
+using spgtc::umma_f16; using spgtc::umma_commit; using spgtc::tmem_ld16; using spgtc::tmem_ld_wait; using spgtc::fence_async_smem;
+using spgtc::mbar_wait_uniform; using spgtc::elect_one;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok;
-}
-// Bounded wait.  Returns false when the abort flag is up or the bound was hit
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) { spgtc::mbar_expect_tx(bar, bytes); }
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) { return spgtc::smem_desc_sw128(saddr); }
+// Bounded wait of the epilogue warps.  Returns false when the abort flag is up or the bound was hit
 // (in which case it raises the flag and records `code`).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *status, int code)
 {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicCAS(status, 0, code);
-    return false;
+    return spgtc::mbar_wait(bar, parity, abort_flag, status, code, WAIT_LIMIT);
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
@@ -107,45 +84,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major, 128-byte-swizzled shared-memory operand descriptor: rows of 128
-// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), tile base
-// 1024-byte aligned; version 1; layout type 2 = SWIZZLE_128B.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address
-    d |= (uint64_t)1u << 16;                           // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024u >> 4) << 32;                 // stride byte offset
-    d |= (uint64_t)1u << 46;                           // descriptor version
-    d |= (uint64_t)2u << 61;                           // 128-byte swizzle
-    return d;
 }
 
 __device__ __forceinline__ void tile_coords(const GemmParams &p, const RowLimit &rl, uint32_t t, uint32_t &m_tile, uint32_t &n_tile)
@@ -233,8 +171,6 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t sr
                  ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-// generic-proxy writes to shared memory -> visible to the bulk-copy (async) proxy
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
@@ -503,7 +439,9 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     uint8_t *stage = smem + stg_off;
 
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    // the warp index through a shuffle: provably warp-uniform, so the role code below keeps uniform values in uniform registers
+    const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31u;
+    const uint32_t abort_addr = smem_u32(const_cast<int *>(abort_flag));
     const uint32_t tmem_cols = 2 * p.BN < 32 ? 32 : 2 * p.BN;       // power of two: BN in {16,32,64,128,256}
 
     if (threadIdx.x == 0) {
@@ -551,51 +489,54 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool alive = true;
-            for (uint32_t ti = 0; ti < ntile && alive; ti++) {
-                uint32_t mt, nt;
-                my_tile(p, rl, ti, mt, nt);
-                for (uint32_t ps = 0; ps < p.npass && alive; ps++) {
-                    for (uint32_t kb = 0; kb < p.kblocks; kb++, it++) {
-                        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
-                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
+        // The whole warp walks the loops convergently and one elected lane issues: every operand of the bulk-tensor
+        // copies then stays warp-uniform (uniform registers) instead of being moved over per instruction.
+        uint32_t it = 0;
+        for (uint32_t ti = 0; ti < ntile; ti++) {
+            uint32_t mt, nt;
+            my_tile(p, rl, ti, mt, nt);
+            for (uint32_t ps = 0; ps < p.npass; ps++) {
+                for (uint32_t kb = 0; kb < p.kblocks; kb++, it++) {
+                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    mbar_wait_uniform(empty0 + 8 * s, ph ^ 1u, abort_addr, p.status, 1, WAIT_LIMIT);
+                    if (elect_one()) {
                         mbar_arrive_expect_tx(full0 + 8 * s, A_TILE_BYTES + b_tile_bytes);
                         tma_load_3d(base + a_off + s * A_TILE_BYTES, &map_a, full0 + 8 * s,
                                     (int)(kb * BK), (int)(mt * BM), (int)p.pass_a[ps]);
                         tma_load_3d(base + b_off + s * b_tile_bytes, &map_w, full0 + 8 * s,
                                     (int)(kb * BK), (int)(nt * p.BN), (int)p.pass_w[ps]);
                     }
+                    __syncwarp();
                 }
             }
         }
-        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool alive = true;
-            for (uint32_t tcount = 0; tcount < ntile && alive; tcount++) {
-                const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
-                if (!mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1u, abort_flag, p.status, 2)) break;
+        // Convergent like the producer: descriptors, addresses and counters stay in uniform registers, which is
+        // where tcgen05.mma takes them from.  A wait that gives up only raises the abort flag (every later wait then
+        // ends at once); the MMAs issued after that work on stale tiles, and the host discards the launch.
+        uint32_t it = 0;
+        for (uint32_t tcount = 0; tcount < ntile; tcount++) {
+            const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+            mbar_wait_uniform(tempty0 + 8 * acc, acc_ph ^ 1u, abort_addr, p.status, 2, WAIT_LIMIT);
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * p.BN;
+            for (uint32_t i = 0; i < iters_per_tile; i++, it++) {
+                const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                mbar_wait_uniform(full0 + 8 * s, ph, abort_addr, p.status, 3, WAIT_LIMIT);
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * p.BN;
-                for (uint32_t i = 0; i < iters_per_tile; i++, it++) {
-                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
-                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
-                    tc_fence_after();
-                    const uint64_t da = make_smem_desc(base + a_off + s * A_TILE_BYTES);
-                    const uint64_t db = make_smem_desc(base + b_off + s * b_tile_bytes);
+                const uint64_t da = make_smem_desc(base + a_off + s * A_TILE_BYTES);
+                const uint64_t db = make_smem_desc(base + b_off + s * b_tile_bytes);
+                if (elect_one()) {
 #pragma unroll
                     for (uint32_t k = 0; k < BK / UMMA_K; k++)
                         umma_f16(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (i | k) ? 1u : 0u);   // +32 bytes per K step
                     umma_commit(empty0 + 8 * s);          // frees the stage once these MMAs have read it
+                    if (i + 1 == iters_per_tile) umma_commit(tfull0 + 8 * acc);  // accumulator complete
                 }
-                if (alive) umma_commit(tfull0 + 8 * acc);  // accumulator complete
+                __syncwarp();
             }
         }
-        __syncwarp();
     } else {
         // ------------------------------ epilogue ----------------------------------
         // The activation is resolved once, outside every loop, so the per-element code is branch-free.
@@ -725,9 +666,9 @@ uint32_t spgk_gemm_tc_softmax_max(void) { return SOFTMAX_FUSE_MAX; }
 int spgk_gemm_tc_supported(const spgk_layer *L)
 {
     if (!L || L->in == 0 || L->out == 0) return 0;
-    static int cc = -1;
-    if (cc < 0) { int c = 0; if (spgk_device_info(&c, nullptr, nullptr) != SPGK_OK) return 0; cc = c; }
-    return cc == 100 ? 1 : 0;        // tcgen05 / TMEM exist on sm_100 only
+    SpgDeviceProps dp;
+    if (spg_device_props(&dp) != SPGK_OK) return 0;
+    return dp.cc == 100 ? 1 : 0;     // tcgen05 / TMEM exist on sm_100 only
 }
 
 int spgk_weights16_direct(const spgk_layer *L, int type16)
@@ -793,17 +734,22 @@ static int gemm_launch(const spgk_layer *L,
         return SPGK_E_ARG;
     }
     if (N == 0) return SPGK_OK;
-    static int sm_count = 0;
-    static size_t smem_max = 0;
-    if (!sm_count) {
-        int dev = 0, sms = 0, optin = 0;
+    SpgDeviceProps dp;
+    {
+        const int prc = spg_device_props(&dp);
+        if (prc) return prc;
+        // the opt-in for large dynamic shared memory is a per-device function attribute
+        static SpgOncePerDevice once;
+        int dev = 0;
         SPGK_CUDA(cudaGetDevice(&dev));
-        SPGK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        SPGK_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        SPGK_CUDA(cudaFuncSetAttribute(spg_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin));
-        smem_max = (size_t)optin;
-        sm_count = sms;
+        const int orc = once.run(dev, [&]() -> int {
+            SPGK_CUDA(cudaFuncSetAttribute(spg_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dp.smem_optin));
+            return SPGK_OK;
+        });
+        if (orc) return orc;
     }
+    const int sm_count = dp.sm_count;
+    const size_t smem_max = dp.smem_optin;
     GemmParams p{};
     p.M = N; p.N = L->out; p.K = L->in;
     p.BN = pick_bn(L->out);

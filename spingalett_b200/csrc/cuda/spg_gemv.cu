@@ -1029,15 +1029,18 @@ int weight_map(const spgk_layer *L, uint32_t box_row_bytes, CUtensorMap *out_map
 template <int PREC, int T, int CW, bool INTP>
 int launch(const ChainMaps &maps, const ChainParams &ch, uint32_t grid_items, const Plan &pl, cudaStream_t s)
 {
-    static bool attr_done = false;
-    static int sms = 0;
-    if (!attr_done) {
-        int dev = 0;
-        SPGK_CUDA(cudaGetDevice(&dev));
-        SPGK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // the opt-in for large dynamic shared memory is a per-device function attribute
+    static SpgOncePerDevice once;
+    int dev = 0;
+    SPGK_CUDA(cudaGetDevice(&dev));
+    int rc = once.run(dev, [&]() -> int {
         SPGK_CUDA(cudaFuncSetAttribute(spg_gemv_kernel<PREC, T, CW, INTP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        attr_done = true;
-    }
+        return SPGK_OK;
+    });
+    if (rc) return rc;
+    SpgDeviceProps dp;
+    if ((rc = spg_device_props(&dp))) return rc;
+    const int sms = dp.sm_count;
     // one CTA per SM at most (the shared-memory ring fills an SM), so all CTAs of a launch are resident together
     const uint32_t grid = grid_items < (uint32_t)sms ? grid_items : (uint32_t)sms;
     cudaLaunchConfig_t cfg = {};

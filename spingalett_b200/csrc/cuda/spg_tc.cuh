@@ -45,6 +45,54 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// The same bounded wait for a role whose whole warp runs convergently (the TMA and MMA warps): the loop lives inside
+// one asm block, so the compiler sees straight-line code and keeps warp-uniform values (descriptors, addresses,
+// counters) in uniform registers -- tcgen05.mma and the bulk-tensor copies take their operands from there, and a value
+// that has become "divergent" costs a register-to-uniform move per operand and instruction.  Nothing is returned:
+// when the abort flag is up (or the bound is hit, which raises it and records `code`) the wait simply ends and the
+// caller carries on; every later wait then ends at once, so the role runs out of its loops quickly.
+__device__ __forceinline__ void mbar_wait_uniform(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem, int32_t *status, int code,
+                                                  uint32_t limit = 1u << 22)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n, a;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "ld.volatile.shared.u32 a, [%2];\n\t"
+        "setp.ne.u32 q, a, 0;\n\t"
+        "@q bra SPG_WAIT_DONE;\n\t"
+        "SPG_WAIT_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "@p bra SPG_WAIT_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "and.b32 a, n, 255;\n\t"
+        "setp.ne.u32 q, a, 0;\n\t"
+        "@q bra SPG_WAIT_LOOP;\n\t"
+        "ld.volatile.shared.u32 a, [%2];\n\t"
+        "setp.ne.u32 q, a, 0;\n\t"
+        "@q bra SPG_WAIT_DONE;\n\t"
+        "setp.lt.u32 q, n, %5;\n\t"
+        "@q bra SPG_WAIT_LOOP;\n\t"
+        "st.volatile.shared.u32 [%2], 1;\n\t"
+        "atom.global.cas.b32 a, [%3], 0, %4;\n\t"
+        "SPG_WAIT_DONE:\n\t"
+        "}"
+        ::"r"(bar), "r"(parity), "r"(abort_flag_smem), "l"(status), "r"(code), "r"(limit) : "memory");
+}
+
+// one lane of a convergent warp (the same lane every time)
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
 {
     asm volatile(

@@ -537,22 +537,25 @@ int spgk_layer_wstream(const spgk_layer *L, const spgk_layer *next, const void *
     WsPlan pl = ws_plan(L, N);
     if (!pl.ok) return SPGK_E_UNSUPPORTED;
     if (!scratch) { spgk_set_error("spgk_layer_wstream", "scratch is NULL"); return SPGK_E_ARG; }
-    static int sms = 0, cc = 0;
-    if (!sms) {
+    SpgDeviceProps dp;
+    int rc;
+    if ((rc = spg_device_props(&dp))) return rc;
+    if (dp.cc != 100) return SPGK_E_UNSUPPORTED;                        // tcgen05 / TMEM exist on sm_100 only
+    const int sms = dp.sm_count;
+    {
+        // the opt-in for large dynamic shared memory is a per-device function attribute
+        static SpgOncePerDevice once;
         int dev = 0;
         SPGK_CUDA(cudaGetDevice(&dev));
-        SPGK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        int major = 0, minor = 0;
-        SPGK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
-        SPGK_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
-        cc = major * 10 + minor;
-        SPGK_CUDA(cudaFuncSetAttribute(spg_wstream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        rc = once.run(dev, [&]() -> int {
+            SPGK_CUDA(cudaFuncSetAttribute(spg_wstream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            return SPGK_OK;
+        });
+        if (rc) return rc;
     }
-    if (cc != 100) return SPGK_E_UNSUPPORTED;                           // tcgen05 / TMEM exist on sm_100 only
     cudaStream_t s = (cudaStream_t)stream;
     uint8_t *base = reinterpret_cast<uint8_t *>(scratch);
     const void *xop = operand_in;
-    int rc;
     if (!xop) {
         __nv_bfloat16 *own = reinterpret_cast<__nv_bfloat16 *>(base + WS_HEAD + pl.tickets_bytes + pl.partial_bytes);
         spg_ws_stage_kernel<<<(pl.ld + 255) / 256, 256, 0, s>>>(x, ldx, N, pl.P, L->in, pl.ld, pl.NC, L->precision, own);

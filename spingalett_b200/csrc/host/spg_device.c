@@ -91,6 +91,7 @@ void spg_dev_release(spg_net *n)
     spgk_free(n->d_status); n->d_status = NULL;
     spgk_free(n->d_w16); n->d_w16 = NULL; n->w16_bytes = 0;
     spgk_free(n->d_head_w); n->d_head_w = NULL;
+    spgk_free(n->d_fused_params); n->d_fused_params = NULL;
     spgk_host_free(n->h_count); n->h_count = NULL; n->count_pending = false; n->count_seen = false;
     for (int i = 0; i <= SPG_PIPE_MAX; i++) { if (n->copy_ev[i]) spgk_event_destroy(n->copy_ev[i]); n->copy_ev[i] = NULL; }
     spgk_stream_destroy(n->copy_stream); n->copy_stream = NULL;
@@ -441,6 +442,44 @@ static int large_simt(spg_net *n, const float *d_x, uint32_t N, float *d_out)
     return SPINGALETT_OK;
 }
 
+/* The 16-bit K-major operand of layer l in flavour `type` with `w_parts` planes: the stored payload itself when
+ * TMA can read it in place, else an expansion that is made once and kept with the net (while the whole net's
+ * expansions stay below SPG_W16_KEEP_MAX; `keep` says so), else *w16 = NULL and the caller expands per call. */
+static int kept_weight_operand(spg_net *n, int type, uint32_t l, int w_parts, bool keep, const void **w16, uint32_t *ldw, uint64_t *w_plane)
+{
+    const spgk_layer *L = &n->klayers[l];
+    int rc;
+    *w16 = NULL;
+    if (spgk_weights16_direct(L, type)) { *w16 = L->w; *ldw = L->in; *w_plane = 0; return SPINGALETT_OK; }
+    *ldw = round8(L->in);
+    *w_plane = (uint64_t)L->out * *ldw;
+    if (!keep) return SPINGALETT_OK;
+    if (!n->d_w16c[type]) {
+        n->d_w16c[type] = calloc(n->dev_layers, sizeof(void *));
+        n->w16c_parts[type] = calloc(n->dev_layers, 1);
+        if (!n->d_w16c[type] || !n->w16c_parts[type]) { spg_set_error(SPINGALETT_ERR_ALLOC, "weight operand table"); return SPINGALETT_ERR_ALLOC; }
+    }
+    if (n->d_w16c[type][l] && n->w16c_parts[type][l] != w_parts) { spgk_free(n->d_w16c[type][l]); n->d_w16c[type][l] = NULL; }
+    if (!n->d_w16c[type][l]) {
+        if ((rc = spg_map_kernel_error(spgk_malloc(&n->d_w16c[type][l], spgk_weights16_bytes(L, w_parts)), "kept weight operand"))) return rc;
+        n->w16c_parts[type][l] = (uint8_t)w_parts;
+        if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16c[type][l], *ldw, *w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
+    }
+    *w16 = n->d_w16c[type][l];
+    return SPINGALETT_OK;
+}
+
+/* whether the expanded 16-bit operands of the whole net (flavour `type`) are small enough to keep between calls */
+static bool weights_keepable(const spg_net *n, int type, bool exact)
+{
+    size_t wtotal = 0;
+    for (uint32_t l = 0; l < n->dev_layers; l++) {
+        const spgk_layer *L = &n->klayers[l];
+        if (!spgk_weights16_direct(L, type)) wtotal += spgk_weights16_bytes(L, (exact && L->precision == PRECISION_FLOAT32) ? 2 : 1);
+    }
+    return wtotal <= SPG_W16_KEEP_MAX;
+}
+
 static _Thread_local bool dynamic_rows = false;      /* true around the repair chain of the AUTO mode */
 static _Thread_local const uint32_t *repair_rows = NULL;   /* repair chain: input row i is row repair_rows[i] of d_x, and its result goes back there */
 
@@ -485,11 +524,6 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
     }
     const bool keep = wtotal && wtotal <= SPG_W16_KEEP_MAX;
     int rc;
-    if (keep && !n->d_w16c[type]) {
-        n->d_w16c[type] = calloc(n->dev_layers, sizeof(void *));
-        n->w16c_parts[type] = calloc(n->dev_layers, 1);
-        if (!n->d_w16c[type] || !n->w16c_parts[type]) { spg_set_error(SPINGALETT_ERR_ALLOC, "weight operand table"); return SPINGALETT_ERR_ALLOC; }
-    }
     if (!keep && wneed && (rc = reserve(&n->d_w16, &n->w16_bytes, wneed, "16-bit weight operand scratch"))) return rc;
     rc = spg_map_kernel_error(spgk_split16_rows(d_x, p->topology[0], repair_rows, N, p->topology[0], n->d_act16[0],
                                                 round8(p->topology[0]), plane, parts, type, n->stream), "input split");
@@ -500,26 +534,14 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
         bool fuse_sm = L->act == ACT_SOFTMAX && L->out <= spgk_gemm_tc_softmax_max();
         void *o16 = last ? NULL : n->d_act16[(l + 1) & 1];
         float *o32 = last ? d_out : NULL;
-        const void *w16 = L->w;
-        uint32_t ldw = L->in;
+        const void *w16 = NULL;
+        uint32_t ldw = 0;
         uint64_t w_plane = 0;
-        int w_parts = 1;
-        if (!spgk_weights16_direct(L, type)) {
-            w_parts = (exact && L->precision == PRECISION_FLOAT32) ? 2 : 1;
-            ldw = round8(L->in);
-            w_plane = (uint64_t)L->out * ldw;
-            if (keep) {
-                if (n->d_w16c[type][l] && n->w16c_parts[type][l] != w_parts) { spgk_free(n->d_w16c[type][l]); n->d_w16c[type][l] = NULL; }
-                if (!n->d_w16c[type][l]) {
-                    if ((rc = spg_map_kernel_error(spgk_malloc(&n->d_w16c[type][l], spgk_weights16_bytes(L, w_parts)), "kept weight operand"))) return rc;
-                    n->w16c_parts[type][l] = (uint8_t)w_parts;
-                    if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16c[type][l], ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
-                }
-                w16 = n->d_w16c[type][l];
-            } else {
-                w16 = n->d_w16;
-                if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16, ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
-            }
+        const int w_parts = (!spgk_weights16_direct(L, type) && exact && L->precision == PRECISION_FLOAT32) ? 2 : 1;
+        if ((rc = kept_weight_operand(n, type, l, w_parts, keep, &w16, &ldw, &w_plane))) return rc;
+        if (!w16) {
+            w16 = n->d_w16;
+            if ((rc = spg_map_kernel_error(spgk_dequant16(L, n->d_w16, ldw, w_plane, w_parts, type, n->stream), "weight operand"))) return rc;
         }
         /* Measured on the benchmark MLP at 65536 rows: it wins in the two-term mode (141.8 us against 155.5 us for two
          * kernels), ties in the one-term mode where the epilogue's fp32 FMAs become the limit (106.7 / 105.4 us), and
@@ -558,6 +580,56 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
     return SPINGALETT_OK;
 }
 
+/* ---- the three-layer net in one launch ------------------------------------ */
+
+#define SPG_FUSED_MIN_ROWS 1024u     /* below this a handful of 128-row tiles cannot fill the GPU: the per-layer chain spreads better */
+
+/* 16-bit flavour of the one-term pass: the file's own 16-bit type when it has one (exact weights), else fp16 */
+static int fast_type(const spg_net *n)
+{
+    const int prec = n->klayers[0].precision;
+    return prec == PRECISION_BFLOAT16 ? SPGK_T_BF16 : SPGK_T_F16;
+}
+
+static bool fused_eligible(const spg_net *n, const float *d_x, uint32_t N)
+{
+    if (n->dev_layers != 3 || N < SPG_FUSED_MIN_ROWS || ((uintptr_t)d_x & 15u)) return false;
+    if (!spgk_mlp3_supported(&n->klayers[0], &n->klayers[1], &n->klayers[2], n->pub.topology[0])) return false;
+    return weights_keepable(n, fast_type(n), false);
+}
+
+/* one launch over N rows (or over the rows of a device-resident list): the one-term pass, or with pairs the
+ * two-term recomputation of the listed rows written over their one-term results */
+static int fused_pass(spg_net *n, const float *d_x, uint32_t N, float *d_out, bool pairs,
+                      const uint32_t *rows_idx, const uint32_t *rows_limit, uint32_t expected,
+                      float theta, uint32_t *margin_idx, uint32_t *margin_count)
+{
+    const int type = fast_type(n);
+    const spgk_layer *L1 = &n->klayers[0], *L2 = &n->klayers[1], *L3 = &n->klayers[2];
+    int rc;
+    if (!n->d_fused_params) {
+        void *b = NULL;
+        if ((rc = spg_map_kernel_error(spgk_malloc(&b, spgk_mlp3_params_bytes(L1, L2, L3)), "fused MLP parameters"))) return rc;
+        n->d_fused_params = b;
+        if ((rc = spg_map_kernel_error(spgk_mlp3_params(L1, L2, L3, type, n->d_fused_params, n->stream), "fused MLP parameters"))) return rc;
+    }
+    const void *w1 = NULL, *w2 = NULL;
+    uint32_t ld1 = 0, ld2 = 0;
+    uint64_t plane = 0;
+    if ((rc = kept_weight_operand(n, type, 0, 1, true, &w1, &ld1, &plane))) return rc;
+    if ((rc = kept_weight_operand(n, type, 1, 1, true, &w2, &ld2, &plane))) return rc;
+    prof_mark(n);
+    rc = spg_map_kernel_error(spgk_mlp3_forward(L1, w1, ld1, L2, w2, ld2, L3, n->d_fused_params, type,
+                                                d_x, n->pub.topology[0], rows_idx, rows_limit, expected, pairs ? 1 : 0,
+                                                d_out, L3->out, N, theta, margin_idx, margin_count, n->d_status, n->stream),
+                              "three-layer MLP (tcgen05)");
+    prof_mark(n);
+    if (rc) return rc;
+    n->status_pending = true;
+    spg_note_path("tcgen05");
+    return SPINGALETT_OK;
+}
+
 /* Large-batch forward in the selected math mode.  AUTO = the one-term pass, then an exact recomputation of
  * the rows whose top-two softmax outputs are within the margin (their argmax is the only thing the one-term
  * pass could have changed), written over the fast result. */
@@ -567,6 +639,9 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     const SpingalettMathMode mode = spingalett_get_math_mode();
     const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1];
     const bool softmax_out = p->act_func[p->layers - 2] == ACT_SOFTMAX && outw >= 2;
+    /* a three-layer net with a narrow last layer runs its one-term passes as ONE kernel (no activation matrix in HBM) */
+    const bool fused = fused_eligible(n, d_x, N);
+    if (mode == SPINGALETT_MATH_FAST && fused) return fused_pass(n, d_x, N, d_out, false, NULL, NULL, 0, 0.0f, NULL, NULL);
     if (mode != SPINGALETT_MATH_AUTO) return large_chain(n, d_x, N, d_out, mode == SPINGALETT_MATH_EXACT);
     if (!softmax_out) return large_chain(n, d_x, N, d_out, true);
 
@@ -578,12 +653,14 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     /* with the margin known in advance, the softmax epilogue of the last layer picks the rows out itself */
     const spgk_layer *Llast = &n->klayers[n->dev_layers - 1];
     const bool sink = theta > 0.0f && Llast->out <= spgk_gemm_tc_softmax_max();
-    if (sink) {
-        if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
-        spgk_set_margin_sink(theta, n->d_rep_idx, d_count);
+    if (sink && (rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
+    if (fused) {
+        rc = fused_pass(n, d_x, N, d_out, false, NULL, NULL, 0, theta, sink ? n->d_rep_idx : NULL, sink ? d_count : NULL);
+    } else {
+        if (sink) spgk_set_margin_sink(theta, n->d_rep_idx, d_count);
+        rc = large_chain(n, d_x, N, d_out, false);
+        spgk_set_margin_sink(0.0f, NULL, NULL);
     }
-    rc = large_chain(n, d_x, N, d_out, false);
-    spgk_set_margin_sink(0.0f, NULL, NULL);
     if (rc) return rc;
     if (strcmp(spingalett_last_path(), "tcgen05") != 0) return SPINGALETT_OK;      /* the fp32 chain ran: nothing to repair */
     theta = spingalett_get_auto_margin();
@@ -626,6 +703,11 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     if (Llast->act == ACT_SOFTMAX && Llast->out > spgk_gemm_tc_softmax_max()) {
         if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
         if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)N * outw * 4, "repair outputs"))) return rc;
+    }
+    if (fused && n->klayers[0].precision != PRECISION_FLOAT32) {
+        /* files whose weights are exact in 16 bits: the flagged rows again through the same kernel, each as a
+         * hi/lo pair of tile rows, written over their one-term results */
+        return fused_pass(n, d_x, N, d_out, true, n->d_rep_idx, d_count, expected, 0.0f, NULL, NULL);
     }
     spgk_set_dynamic_rows(d_count, expected);
     dynamic_rows = true;

@@ -67,6 +67,7 @@ typedef struct {
     /* 16-bit weight operands kept between calls (nets whose expanded weights are small): [fp16 | bf16][layer] */
     void **d_w16c[2]; uint8_t *w16c_parts[2];
     float *d_head_w;                       /* fp32 weights of a narrow last layer fused into the layer before it */
+    float *d_fused_params;                 /* padded biases + head weights of the one-launch three-layer kernel */
 
     float *h_out; size_t h_out_bytes;       /* library-owned pinned output buffer */
     float *h_stage; size_t h_stage_bytes;   /* pinned staging for forward() */

@@ -36,21 +36,46 @@ def l_net(spg, oracle, has_gpu, tmp_path_factory):
     net.free()
 
 
-def test_wide_bf16_mlp_batch_16384(spg, w_net):
+_W_CACHE = {}
+
+
+def _wide_case(onet):
+    """Inputs of the W configuration and the oracle's outputs on 192 of its rows (computed once per session)."""
+    if not _W_CACHE:
+        n = 16384
+        x = nets.normal_inputs(n, nets.W_TOPO[0], seed=5)
+        rows = np.random.default_rng(1).choice(n, 192, replace=False)
+        _W_CACHE.update(x=x, rows=rows, want=onet.forward_batch(x[rows]))
+    return _W_CACHE["x"], _W_CACHE["rows"], _W_CACHE["want"]
+
+
+@pytest.mark.parametrize("mode", ["exact", "auto", "fast"])
+def test_wide_bf16_mlp_batch_16384(spg, w_net, mode):
+    """All three math modes on the W configuration against the oracle (bar: 99.9 % argmax, 2e-3).  AUTO, the
+    library default, takes the one-term pass plus the exact recomputation of low-margin rows of a 1000-wide softmax."""
     net, onet = w_net
-    n = 16384
-    x = nets.normal_inputs(n, nets.W_TOPO[0], seed=5)
-    spg.set_math_mode(spg.abi.MATH_EXACT)
-    got = net.forward_batch(x)
-    assert spg.last_path() == "tcgen05"
-    rows = np.random.default_rng(1).choice(n, 192, replace=False)
-    want = onet.forward_batch(x[rows])
-    agree, err = nets.parity(got[rows], want)
-    assert agree == 1.0 and err <= 2e-5, (agree, err)           # bar: 99.9 % / 2e-3
-    assert np.all(np.isfinite(got)) and np.allclose(got.sum(1), 1.0, atol=1e-4)
-    # rows are independent: the same rows in a small batch give the same result
-    again = net.forward_batch(x[rows])
-    assert np.abs(again - got[rows]).max() <= 2e-6
+    x, rows, want = _wide_case(onet)
+    spg.set_math_mode({"exact": spg.abi.MATH_EXACT, "auto": spg.abi.MATH_AUTO, "fast": spg.abi.MATH_FAST}[mode])
+    try:
+        got = net.forward_batch(x)
+        assert spg.last_path() == "tcgen05"
+        agree, err = nets.parity(got[rows], want)
+        if mode == "exact":
+            assert agree == 1.0 and err <= 2e-5, (agree, err)
+        elif mode == "auto":
+            assert agree >= 0.999 and err <= 2e-3, (agree, err)
+            assert agree == 1.0, agree                               # 192 rows: one flip would already be 0.5 %
+            assert spg.lib().spingalett_last_repaired(net._h) > 0     # the margin pass found rows to recompute
+        else:
+            # one bf16 term per operand: the stated error bar holds, the argmax bar is not promised in this mode
+            assert err <= 2e-3 and agree >= 0.97, (agree, err)
+        assert np.all(np.isfinite(got)) and np.allclose(got.sum(1), 1.0, atol=1e-4)
+        if mode == "exact":
+            # rows are independent: the same rows in a small batch give the same result
+            again = net.forward_batch(x[rows])
+            assert np.abs(again - got[rows]).max() <= 2e-6
+    finally:
+        spg.set_math_mode(spg.abi.MATH_AUTO)
 
 
 @pytest.mark.parametrize("n", [1, 8, 20, 64, 256])

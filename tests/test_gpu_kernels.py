@@ -388,3 +388,140 @@ def test_encode_array_matches_the_reference_bytes(spg, k, oracle, prec, count):
     got = dst.cpu().numpy()
     assert np.all(got[nbytes:] == 0xAB)
     assert np.array_equal(got[:nbytes], np.frombuffer(want.tobytes(), np.uint8))
+
+
+# ---------------------------------------------------------------------------
+# the three-layer MLP in one launch
+# ---------------------------------------------------------------------------
+def _bind_mlp3(spg, k):
+    vp = C.c_void_p
+    KL = C.POINTER(spg.abi.KLayer)
+    k.spgk_mlp3_supported.argtypes = [KL, KL, KL, C.c_uint32]
+    k.spgk_mlp3_params_bytes.argtypes = [KL, KL, KL]
+    k.spgk_mlp3_params_bytes.restype = C.c_size_t
+    k.spgk_mlp3_params.argtypes = [KL, KL, KL, C.c_int, vp, vp]
+    k.spgk_mlp3_forward.argtypes = [KL, vp, C.c_uint32, KL, vp, C.c_uint32, KL, vp, C.c_int,
+                                    vp, C.c_uint32, vp, vp, C.c_uint32, C.c_int, vp, C.c_uint32, C.c_uint32,
+                                    C.c_float, vp, vp, vp, vp]
+
+
+def _mlp3_case(spg, k, N, K1, N1, N2, HO, acts, t16, seed):
+    """Device operands of a random three-layer net plus everything the float64 restatement needs."""
+    import torch
+    _bind_mlp3(spg, k)
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((N, K1)).astype(np.float32)
+    ws = [(rng.standard_normal((o, i)) * np.sqrt(2.0 / i)).astype(np.float32) for i, o in ((K1, N1), (N1, N2), (N2, HO))]
+    bs = [(rng.standard_normal(o) * 0.1).astype(np.float32) for o in (N1, N2, HO)]
+    scales = [0.75, 1.25, 0.5]
+    dt = torch.float16 if t16 == 0 else torch.bfloat16
+    keep, layers, w16 = [], [], []
+    for (w, b, s, a) in zip(ws, bs, scales, acts):
+        wd, bd = torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda()
+        keep += [wd, bd]
+        layers.append(spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), s, w.shape[1], w.shape[0], 0, a))
+    for L, w in zip(layers[:2], ws[:2]):
+        ld = (w.shape[1] + 7) & ~7
+        t = torch.zeros((w.shape[0], ld), dtype=dt, device="cuda")
+        assert k.spgk_dequant16(C.byref(L), t.data_ptr(), ld, w.shape[0] * ld, 1, t16, None) == 0, k.spgk_error_string()
+        w16.append((t, ld))
+    assert k.spgk_mlp3_supported(C.byref(layers[0]), C.byref(layers[1]), C.byref(layers[2]), K1) == 1
+    pbytes = k.spgk_mlp3_params_bytes(C.byref(layers[0]), C.byref(layers[1]), C.byref(layers[2]))
+    params = torch.zeros(pbytes // 4, dtype=torch.float32, device="cuda")
+    assert k.spgk_mlp3_params(C.byref(layers[0]), C.byref(layers[1]), C.byref(layers[2]), t16, params.data_ptr(), None) == 0
+    return dict(x=x, ws=ws, bs=bs, scales=scales, layers=layers, w16=w16, params=params, keep=keep, xd=torch.from_numpy(x).cuda())
+
+
+def _mlp3_want(case, acts, t16, pairs):
+    """float64 result from the operands the tensor cores see: one 16-bit term per value, or (pairs) the
+    16-bit rounding plus the rounded remainder scaled by 2^11 (fp16) / 2^8 (bf16)."""
+    lo_scale = 2048.0 if t16 == 0 else 256.0
+
+    def operand(v):
+        hi = _round16(v, t16).astype(np.float64)
+        if not pairs:
+            return hi
+        lo = _round16(((v.astype(np.float64) - hi) * lo_scale).astype(np.float32), t16).astype(np.float64)
+        return hi + lo / lo_scale
+    w16 = [t.float().cpu().numpy()[:, :w.shape[1]].astype(np.float64) for (t, _), w in zip(case["w16"], case["ws"][:2])]
+    s, b = case["scales"], case["bs"]
+    h1 = ACT[acts[0]](operand(case["x"]) @ w16[0].T * s[0] + b[0]).astype(np.float32)
+    h2 = ACT[acts[1]](operand(h1) @ w16[1].T * s[1] + b[1]).astype(np.float32)
+    w3 = _round16(case["ws"][2], t16).astype(np.float64)          # the head's weights enter as a 16-bit operand as well
+    z = operand(h2) @ w3.T * s[2] + b[2]
+    return ACT[acts[2]](z), z
+
+
+def _mlp3_run(spg, k, case, t16, N, HO, rows_idx=None, rows_limit=None, pairs=0, out=None, theta=0.0, margin=None):
+    import torch
+    L = case["layers"]
+    if out is None:
+        out = torch.full((case["x"].shape[0] + 1, HO), -3.0, dtype=torch.float32, device="cuda")
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    (w1, ld1), (w2, ld2) = case["w16"]
+    rc = k.spgk_mlp3_forward(C.byref(L[0]), w1.data_ptr(), ld1, C.byref(L[1]), w2.data_ptr(), ld2, C.byref(L[2]),
+                             case["params"].data_ptr(), t16, case["xd"].data_ptr(), case["x"].shape[1],
+                             rows_idx.data_ptr() if rows_idx is not None else None,
+                             rows_limit.data_ptr() if rows_limit is not None else None, 0, pairs,
+                             out.data_ptr(), HO, N, theta,
+                             margin[0].data_ptr() if margin else None, margin[1].data_ptr() if margin else None,
+                             status.data_ptr(), None)
+    assert rc == 0, k.spgk_error_string()
+    assert k.spgk_gemm_tc_status(status.data_ptr(), None) == 0, k.spgk_error_string()
+    return out
+
+
+@pytest.mark.parametrize("N,K1,N1,N2,HO", [(1000, 784, 512, 1000, 10), (128, 64, 64, 64, 3), (300, 100, 256, 300, 16),
+                                           (130, 784, 448, 260, 12), (5000, 20, 16, 16, 1), (257, 132, 200, 1024, 13)])
+@pytest.mark.parametrize("t16", [0, 1])
+@pytest.mark.parametrize("pairs", [0, 1])
+def test_mlp3_fused_against_float64(spg, k, N, K1, N1, N2, HO, t16, pairs):
+    """One-launch MLP vs float64 arithmetic on the same rounded operands (all rows, guard row untouched)."""
+    acts = [[1, 1, 5], [3, 4, 5], [2, 0, 6], [4, 3, 2], [1, 6, 0], [6, 1, 5]][(N + K1 + N1) % 6]
+    case = _mlp3_case(spg, k, N, K1, N1, N2, HO, acts, t16, seed=N + K1 + 31 * HO)
+    got = _mlp3_run(spg, k, case, t16, N, HO, pairs=pairs).cpu().numpy()
+    want, z = _mlp3_want(case, acts, t16, pairs)
+    assert np.all(got[N] == -3.0)
+    # one-term mode: a hidden activation that sits on a 16-bit rounding boundary may round the other way after fp32
+    # accumulation than in the float64 restatement (one unit of 2^-11 / 2^-8 on one of up to 512 terms); the two-term
+    # mode has no such boundary effect above 2^-22 / 2^-16
+    eps = 2.0 ** -11 if t16 == 0 else 2.0 ** -8
+    tol = (3e-5 + (0.25 * eps if not pairs else 0.02 * eps * eps * 2048)) * max(1.0, np.abs(z).max())
+    assert np.abs(got[:N] - want).max() <= tol, (np.abs(got[:N] - want).max(), tol)
+
+
+def test_mlp3_fused_row_list_limit_and_margin(spg, k):
+    """Row list + device-resident row count (only the listed rows are touched), and the margin list of the one-term pass."""
+    import torch
+    N, K1, N1, N2, HO, t16 = 3000, 784, 512, 1000, 10, 0
+    acts = [1, 1, 5]
+    case = _mlp3_case(spg, k, N, K1, N1, N2, HO, acts, t16, seed=11)
+    want1, z1 = _mlp3_want(case, acts, t16, 0)
+    idx = torch.zeros(N, dtype=torch.int32, device="cuda")
+    count = torch.zeros(4, dtype=torch.int32, device="cuda")
+    theta = 0.05
+    fast = _mlp3_run(spg, k, case, t16, N, HO, theta=theta, margin=(idx, count))
+    assert np.abs(fast.cpu().numpy()[:N] - want1).max() < 2e-4      # one fp16 term: a hidden value on a rounding boundary may round the other way
+    n = int(count[0].item())
+    srt = np.sort(z1, axis=1)
+    gap = srt[:, -1] - srt[:, -2]
+    flagged = np.sort(idx.cpu().numpy()[:n])
+    sure = np.nonzero(gap < theta - 2e-3)[0]
+    maybe = np.nonzero(gap < theta + 2e-3)[0]
+    assert set(sure) <= set(flagged) <= set(maybe) and n > 0
+    # exact recomputation of just those rows, in place
+    wantp, _ = _mlp3_want(case, acts, t16, 1)
+    before = fast.clone()
+    _mlp3_run(spg, k, case, t16, N, HO, rows_idx=idx, rows_limit=count, pairs=1, out=fast)
+    after = fast.cpu().numpy()
+    mask = np.zeros(N + 1, bool)
+    mask[flagged] = True
+    assert np.array_equal(after[~mask], before.cpu().numpy()[~mask])
+    assert np.abs(after[:N][mask[:N]] - wantp[mask[:N]]).max() < 1e-5
+    # the two-term rows agree with the full-precision product of the unrounded input far better than the one-term rows
+    x64 = case["x"].astype(np.float64)
+    w = [t.float().cpu().numpy()[:, :ww.shape[1]].astype(np.float64) for (t, _), ww in zip(case["w16"], case["ws"][:2])]
+    s, b = case["scales"], case["bs"]
+    h2 = np.maximum(np.maximum(x64 @ w[0].T * s[0] + b[0], 0) @ w[1].T * s[1] + b[1], 0)
+    full = _softmax(h2 @ _round16(case["ws"][2], t16).astype(np.float64).T * s[2] + b[2])
+    assert np.abs(after[:N][mask[:N]] - full[mask[:N]]).max() < 2e-5
