@@ -15,7 +15,8 @@ LIB = os.path.join(HERE, "lib", "libspingalett.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 GCC = "gcc"
 
-NVCC_FLAGS = [
+# extra -D switches for experiments (e.g. SPG_NVCC_DEFS="-DSPG_DBG_X"); never set in a normal build
+NVCC_FLAGS = os.environ.get("SPG_NVCC_DEFS", "").split() + [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I" + os.path.join(ROOT, "include"),
     "-I" + os.path.join(CSRC, "cuda"),

@@ -32,7 +32,7 @@ constexpr uint32_t UMMA_K = 16;
 constexpr uint32_t A_TILE_BYTES = BM * BK * 2;
 constexpr uint32_t EPI_WARPS = 8;       // two warps per TMEM lane quadrant, each taking half of the tile's columns
 constexpr uint32_t NUM_THREADS = 64 + 32 * EPI_WARPS;   // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2.. epilogue
-constexpr uint32_t WAIT_LIMIT = 1u << 23;
+constexpr uint32_t WAIT_LIMIT = 1u << 16;    // attempts; each may suspend the warp for up to SPG_WAIT_HINT_NS
 constexpr uint32_t MAX_PASSES = 4;
 constexpr uint32_t SOFTMAX_FUSE_MAX = 256;
 constexpr uint32_t STG_PITCH = 80;                        // bytes per staged row: 32 columns x 2 bytes + 16 (bank spread for 16-byte accesses)

@@ -2,15 +2,19 @@
 // persistent tcgen05 kernel for large batches: the layer chain of batch_forward (reference
 // Training.c:313-345) without any activation matrix in HBM.
 //
-// A CTA owns tiles of 128 "slots" (normally 128 batch rows).  Per tile:
-//   * eight converter warps read the fp32 input rows (ld.global, rows prefetched into L2 one tile ahead),
-//     round them to the 16-bit operand type and write [128 x 64] K-major, 128-byte-swizzled A tiles into a
-//     two-slot ring (no separate split pass, no 16-bit copy of the input in HBM);
-//   * one TMA lane streams the 16-bit weight operands of layers 1 and 2 from L2 in [128 x 64] tiles through a
-//     four-slot ring (cp.async.bulk.tensor, no multicast);
-//   * one lane issues tcgen05.mma (kind::f16, M = 128): layer 1 in chunks of 256 output columns over K = in,
-//     then layer 2 in chunks of 256 columns over K = N1, the fp32 accumulators alternating between the two
-//     256-column halves of tensor memory;
+// The grid is made of CTA pairs (clusters of two): a pair owns tiles of 256 "slots" (normally 256 batch rows), 128 per
+// CTA, and runs them as one cta_group::2 MMA stream -- each CTA holds its own rows of the A operands and accumulators
+// and only HALF of every weight tile, which halves the weight bytes per SM that have to come from L2 and sit in shared
+// memory (the budget that the resident hidden layer leaves is small).  Per tile and CTA:
+//   * an input-producer lane streams the fp32 input rows as [128 x 64] tiles (cp.async.bulk.tensor) into a staging ring that
+//     borrows the hidden layer's shared memory while it is idle; four converter warps round them to the 16-bit operand
+//     type and write [128 x 64] K-major, 128-byte-swizzled A tiles into a three-slot ring (no separate split pass, no
+//     16-bit copy of the input in HBM);
+//   * one TMA lane streams this CTA's half of the 16-bit weight tiles of layers 1 and 2 from L2 ([128 x 64] boxes, three-slot
+//     ring; cp.async.bulk.tensor, no multicast, completion counted on the first CTA's barrier);
+//   * one lane of the pair's first CTA issues tcgen05.mma (kind::f16, cta_group::2, M = 256 over the two CTAs): layer 1 in
+//     chunks of 256 output columns over K = in, then layer 2 in chunks of 256 columns over K = N1, the fp32
+//     accumulators alternating between the two 256-column halves of each CTA's tensor memory;
 //   * eight epilogue warps drain the accumulators: a layer-1 chunk becomes act(scale*acc + bias) rounded to 16
 //     bits and written straight into the shared-memory A operand of layer 2 (the hidden matrix never leaves
 //     the SM); a layer-2 chunk stays in registers as fp32 and is multiplied into the head's dot products
@@ -39,13 +43,16 @@ namespace {
 constexpr uint32_t BM = 128;                    // slots per tile (UMMA M)
 constexpr uint32_t BK = 64;                     // K elements per operand tile: one 128-byte swizzle row
 constexpr uint32_t TILE_BYTES = BM * BK * 2;    // every operand tile here is [128 x 64] 16-bit = 16 KB
-constexpr uint32_t W_STAGES = 4, X_STAGES = 2, H1_TILES = 8;
-constexpr uint32_t EPI_WARPS = 8, CVT_WARPS = 8;
+constexpr uint32_t W_STAGES = 3, X_STAGES = 3, H1_TILES = 8;
+constexpr uint32_t EPI_WARPS = 8, CVT_WARPS = 4;
 constexpr uint32_t EPI_WARP0 = 2, CVT_WARP0 = EPI_WARP0 + EPI_WARPS;
-constexpr uint32_t NUM_THREADS = 32 * (CVT_WARP0 + CVT_WARPS);        // 576: TMA, MMA, 8 epilogue, 8 converter warps
+constexpr uint32_t XPROD_WARP = CVT_WARP0 + CVT_WARPS;                // the input producer (TMA of fp32 input tiles)
+constexpr uint32_t NUM_THREADS = 32 * (XPROD_WARP + 1);               // 480: weight TMA, MMA, 8 epilogue, 4 converter warps, input TMA
+constexpr uint32_t XF_STAGES = 3;                                     // fp32 input staging slots ([128 rows x 64 columns] = 32 KB each)
+constexpr uint32_t XF_BYTES = BM * BK * 4;
 constexpr int CVT_ITEMS = 128 * 16 / (32 * CVT_WARPS);                // float4 loads per converter thread and input tile
 constexpr uint32_t SMEM_TILES = (H1_TILES + W_STAGES + X_STAGES) * TILE_BYTES;   // 224 KB
-constexpr uint32_t SMEM_BARS = 256;                                              // the mbarrier table, padded
+constexpr uint32_t SMEM_BARS = 320;                                              // the mbarrier table, padded
 constexpr uint32_t SMEM_BIAS = 2 * 256 * 4;                                      // two chunks' biases (fp32), double-buffered
 constexpr uint32_t SMEM_TOTAL = SMEM_TILES + SMEM_BARS + SMEM_BIAS;
 constexpr uint32_t TMEM_COLS = 512;
@@ -74,6 +81,7 @@ struct FusedParams {
 struct __align__(8) Bars {
     uint64_t w_full[W_STAGES], w_empty[W_STAGES], x_full[X_STAGES], x_empty[X_STAGES];
     uint64_t acc_full[2], acc_empty[2], h1_ready[H1_TILES], xchg_full[4];
+    uint64_t xf_full[XF_STAGES], xf_empty[XF_STAGES], h1_free;
     uint32_t tmem_slot;
     int abort_flag;
 };
@@ -96,10 +104,10 @@ __device__ __forceinline__ void uwait(uint32_t bar, uint32_t parity, uint32_t ab
 {
     if (TRACE && tracing) {
         const long long t0 = clock64();
-        mbar_wait_uniform(bar, parity, abort_addr, status, code);
+        mbar_wait_uniform_cluster(bar, parity, abort_addr, status, code);
         cycles += (unsigned long long)(clock64() - t0);
     } else {
-        mbar_wait_uniform(bar, parity, abort_addr, status, code);
+        mbar_wait_uniform_cluster(bar, parity, abort_addr, status, code);
     }
 }
 
@@ -119,9 +127,14 @@ template <> __device__ __forceinline__ float round16<__half>(float a) { return _
 template <> __device__ __forceinline__ float round16<__nv_bfloat16>(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
 
 // the activation of a whole register block, resolved once per block (the switch is warp-uniform)
-template <int COUNT>
+template <int COUNT, bool RELU = false>
 __device__ __forceinline__ void activate_block(float (&v)[COUNT], int act)
 {
+    if (RELU) {                                      // known at compile time: no switch in the hot loop
+#pragma unroll
+        for (int i = 0; i < COUNT; i++) v[i] = v[i] > 0.0f ? v[i] : 0.0f;
+        return;
+    }
     switch (act) {
         case SPG_ACT_RELU:
 #pragma unroll
@@ -147,80 +160,84 @@ __device__ __forceinline__ void activate_block(float (&v)[COUNT], int act)
     }
 }
 
-// 32 accumulator columns of this thread's row -> scale*acc + bias (bias: this chunk's slice in shared memory, same address in every lane)
-__device__ __forceinline__ void load_block(uint32_t taddr, float scale, const float *bias, float (&v)[32])
+// 16 accumulator columns of this thread's row (already in registers) -> scale*acc + bias, activation, 16-bit, and into the
+// hidden tile (bias: this chunk's slice in shared memory, same address in every lane).  In pair mode the raw accumulators
+// of the hi slot (even lane) and the lo slot (odd lane) first become hi + lo / lo_scale in both lanes.
+template <typename T16, bool PAIRS, bool RELU>
+__device__ __forceinline__ void finish_l1_half(const FusedParams &p, const uint32_t (&r)[16], const float *bias, uint32_t col0, uint32_t lane,
+                                               uint8_t *trow, uint32_t chunk0, uint32_t row)
 {
-    uint32_t r0[16], r1[16];
-    tmem_ld16(taddr, r0);
-    tmem_ld16(taddr + 16, r1);
-    tmem_ld_wait();
+    float v[16];
+    if (PAIRS) {
+        const bool odd = lane & 1u;
 #pragma unroll
-    for (int i = 0; i < 16; i += 4) {
-        const float4 b0 = *reinterpret_cast<const float4 *>(bias + i);
-        const float4 b1 = *reinterpret_cast<const float4 *>(bias + 16 + i);
-        v[i + 0] = fmaf(__uint_as_float(r0[i + 0]), scale, b0.x); v[i + 1] = fmaf(__uint_as_float(r0[i + 1]), scale, b0.y);
-        v[i + 2] = fmaf(__uint_as_float(r0[i + 2]), scale, b0.z); v[i + 3] = fmaf(__uint_as_float(r0[i + 3]), scale, b0.w);
-        v[16 + i + 0] = fmaf(__uint_as_float(r1[i + 0]), scale, b1.x); v[16 + i + 1] = fmaf(__uint_as_float(r1[i + 1]), scale, b1.y);
-        v[16 + i + 2] = fmaf(__uint_as_float(r1[i + 2]), scale, b1.z); v[16 + i + 3] = fmaf(__uint_as_float(r1[i + 3]), scale, b1.w);
+        for (int i = 0; i < 16; i++) {
+            const float mine = __uint_as_float(r[i]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            const float s = odd ? fmaf(mine, p.lo_inv, other) : fmaf(other, p.lo_inv, mine);
+            v[i] = fmaf(s, p.scale1, bias[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+            const float4 b = *reinterpret_cast<const float4 *>(bias + i);
+            v[i + 0] = fmaf(__uint_as_float(r[i + 0]), p.scale1, b.x); v[i + 1] = fmaf(__uint_as_float(r[i + 1]), p.scale1, b.y);
+            v[i + 2] = fmaf(__uint_as_float(r[i + 2]), p.scale1, b.z); v[i + 3] = fmaf(__uint_as_float(r[i + 3]), p.scale1, b.w);
+        }
     }
-}
-// pair mode: the raw accumulators of the hi slot (even lane) and the lo slot (odd lane) become hi + lo / lo_scale in both lanes
-__device__ __forceinline__ void load_block_pairs(uint32_t taddr, float scale, const float *bias, float lo_inv, uint32_t lane, float (&v)[32])
-{
-    uint32_t r0[16], r1[16];
-    tmem_ld16(taddr, r0);
-    tmem_ld16(taddr + 16, r1);
-    tmem_ld_wait();
-    const bool odd = lane & 1u;
+    activate_block<16, RELU>(v, p.act1);
+    if (col0 + 16u > p.N1) {
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-        const float mine = __uint_as_float(i < 16 ? r0[i] : r1[i - 16]);
-        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-        const float s = odd ? fmaf(mine, lo_inv, other) : fmaf(other, lo_inv, mine);
-        v[i] = fmaf(s, scale, bias[i]);
+        for (int i = 0; i < 16; i++) if (col0 + i >= p.N1) v[i] = 0.0f;
+    }
+    if (PAIRS && (lane & 1u)) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = (v[i] - round16<T16>(v[i])) * p.lo_scale;
+    }
+#pragma unroll
+    for (uint32_t g = 0; g < 2; g++) {
+        uint4 qv;
+        qv.x = pack2<T16>(v[8 * g + 0], v[8 * g + 1]); qv.y = pack2<T16>(v[8 * g + 2], v[8 * g + 3]);
+        qv.z = pack2<T16>(v[8 * g + 4], v[8 * g + 5]); qv.w = pack2<T16>(v[8 * g + 6], v[8 * g + 7]);
+        *reinterpret_cast<uint4 *>(trow + (((chunk0 + g) ^ (row & 7u)) << 4)) = qv;
     }
 }
 
 // One layer-1 chunk (256 columns of the hidden layer): this warp's 128 columns -> 16-bit values in the
 // shared-memory A operand of layer 2 (tile kb = column / 64, row = slot, 16-byte pieces XOR-swizzled by row & 7).
-template <typename T16>
+// The columns are walked in halves of 16 with the tensor-memory load of the next half in flight.
+template <typename T16, bool PAIRS, bool RELU>
 __device__ __forceinline__ void epilogue_l1(const FusedParams &p, uint32_t c1, uint32_t taddr, uint32_t q, uint32_t half, uint32_t lane,
                                             uint8_t *h1, uint32_t h1_ready0, const float *cbias)
 {
     const uint32_t row = q * 32u + lane;
+    const uint32_t cbase = c1 * 256u + half * 128u;
+    const uint32_t kb_end = p.kb2;
+    if ((cbase >> 6) >= kb_end) return;                         // beyond the hidden width: no tile to fill
+    const float *bias = cbias + half * 128u;
+    uint32_t ra[16], rb[16];
+    tmem_ld16(taddr, ra);
 #pragma unroll 1
     for (uint32_t pc = 0; pc < 4; pc++) {
-        const uint32_t col0 = c1 * 256u + half * 128u + pc * 32u;
+        const uint32_t col0 = cbase + pc * 32u;
         const uint32_t kb = col0 >> 6;
-        if (kb >= p.kb2) break;                                   // beyond the hidden width: no tile to fill
-        float v[32];
-        if (p.pairs) load_block_pairs(taddr + pc * 32u, p.scale1, cbias + half * 128u + pc * 32u, p.lo_inv, lane, v);
-        else load_block(taddr + pc * 32u, p.scale1, cbias + half * 128u + pc * 32u, v);
-        activate_block<32>(v, p.act1);
-        if (col0 + 32u > p.N1) {
-#pragma unroll
-            for (int i = 0; i < 32; i++) if (col0 + i >= p.N1) v[i] = 0.0f;
-        }
-        if (p.pairs && (lane & 1u)) {
-#pragma unroll
-            for (int i = 0; i < 32; i++) v[i] = (v[i] - round16<T16>(v[i])) * p.lo_scale;
-        }
+        if (kb >= kb_end) break;
         uint8_t *trow = h1 + kb * TILE_BYTES + row * 128u;
-        const uint32_t cbase = (col0 & 63u) >> 3;                 // 0 or 4: which half of the 128-byte row
-#pragma unroll
-        for (uint32_t g = 0; g < 4; g++) {
-            uint4 qv;
-            qv.x = pack2<T16>(v[8 * g + 0], v[8 * g + 1]); qv.y = pack2<T16>(v[8 * g + 2], v[8 * g + 3]);
-            qv.z = pack2<T16>(v[8 * g + 4], v[8 * g + 5]); qv.w = pack2<T16>(v[8 * g + 6], v[8 * g + 7]);
-            *reinterpret_cast<uint4 *>(trow + (((cbase + g) ^ (row & 7u)) << 4)) = qv;
-        }
+        const uint32_t chunk0 = (col0 & 63u) >> 3;              // 0 or 4: which half of the 128-byte row
+        tmem_ld_wait();
+        tmem_ld16(taddr + pc * 32u + 16u, rb);
+        finish_l1_half<T16, PAIRS, RELU>(p, ra, bias + pc * 32u, col0, lane, trow, chunk0, row);
+        tmem_ld_wait();
+        if (pc + 1 < 4 && ((col0 + 32u) >> 6) < kb_end) tmem_ld16(taddr + pc * 32u + 32u, ra);
+        finish_l1_half<T16, PAIRS, RELU>(p, rb, bias + pc * 32u + 16u, col0 + 16u, lane, trow, chunk0 + 2u, row);
         if (pc & 1u) {
             // this warp's 32 rows of tile kb are complete
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(h1_ready0 + 8u * kb);
+            if (lane == 0) mbar_arrive_cluster(h1_ready0 + 8u * kb);       // a barrier of the pair's first CTA
         }
     }
+    tmem_ld_wait();
 }
 
 // 16 rows x 32 columns of the accumulator in the fragment layout of the warp-level MMA: lane (g = lane/4, t = lane%4)
@@ -263,7 +280,7 @@ __device__ __forceinline__ void load_bfrag(const T16 *head, uint32_t ld16, uint3
         }
 }
 
-template <typename T16, int NT>
+template <typename T16, int NT, bool PAIRS, bool RELU>
 __device__ __forceinline__ void epilogue_l2(const FusedParams &p, uint32_t c2, uint32_t taddr, uint32_t half, uint32_t lane,
                                             float (&hd)[2][NT][4], const float *cbias)
 {
@@ -271,73 +288,93 @@ __device__ __forceinline__ void epilogue_l2(const FusedParams &p, uint32_t c2, u
     const uint32_t ld16 = p.nch2 * 256u;
     const T16 *head = reinterpret_cast<const T16 *>(p.head16);
     const uint32_t cbase = c2 * 256u + half * 128u;
-    // B fragments of a 32-column block (two k-steps of 16), fetched one block ahead of their use
+    // B fragments of a 32-column block (two k-steps of 16), fetched one block ahead of their use; the accumulator rows of
+    // a block (two row tiles of 16) likewise come from tensor memory while the block before is worked on
     uint32_t bf[2][NT][2], bf_next[2][NT][2];
-    if (cbase < p.N2) load_bfrag<T16, NT>(head, ld16, cbase, g, t, bf);
+    uint32_t r[2][16];
+    if (cbase >= p.N2) return;
+    load_bfrag<T16, NT>(head, ld16, cbase, g, t, bf);
+    tmem_ld_frag32(taddr, r[0]);
+    tmem_ld_frag32(taddr + (16u << 16), r[1]);
 #pragma unroll 1
     for (uint32_t pc = 0; pc < 4; pc++) {
         const uint32_t col0 = cbase + pc * 32u;
         if (col0 >= p.N2) break;
-        if (pc + 1 < 4 && col0 + 32u < p.N2) load_bfrag<T16, NT>(head, ld16, col0 + 32u, g, t, bf_next);
+        const bool more = pc + 1 < 4 && col0 + 32u < p.N2;
+        if (more) load_bfrag<T16, NT>(head, ld16, col0 + 32u, g, t, bf_next);
         float2 bias[4];
 #pragma unroll
         for (int n = 0; n < 4; n++) bias[n] = *reinterpret_cast<const float2 *>(cbias + half * 128u + pc * 32u + 8 * n + 2 * t);
+        tmem_ld_wait();
+        float v[2][16];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[mt][i] = __uint_as_float(r[mt][i]);
+        if (more) {                                           // the next block's rows: in flight during the arithmetic below
+            tmem_ld_frag32(taddr + pc * 32u + 32u, r[0]);
+            tmem_ld_frag32(taddr + pc * 32u + 32u + (16u << 16), r[1]);
+        }
 #pragma unroll
         for (int mt = 0; mt < 2; mt++) {
-            uint32_t r[16];
-            tmem_ld_frag32(taddr + pc * 32u + ((uint32_t)(16 * mt) << 16), r);      // rows 16*mt .. 16*mt+15 of this warp's quadrant
-            tmem_ld_wait();
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-            if (p.pairs) {
+            if (PAIRS) {
                 // rows 2i (hi) and 2i+1 (lo) sit in lanes that differ by 4: both get hi + lo / lo_scale
                 const bool odd = g & 1u;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[i], 4);
-                    v[i] = odd ? fmaf(v[i], p.lo_inv, other) : fmaf(other, p.lo_inv, v[i]);
+                    const float other = __shfl_xor_sync(0xffffffffu, v[mt][i], 4);
+                    v[mt][i] = odd ? fmaf(v[mt][i], p.lo_inv, other) : fmaf(other, p.lo_inv, v[mt][i]);
                 }
             }
 #pragma unroll
             for (int n = 0; n < 4; n++) {
-                v[4 * n + 0] = fmaf(v[4 * n + 0], p.scale2, bias[n].x); v[4 * n + 1] = fmaf(v[4 * n + 1], p.scale2, bias[n].y);
-                v[4 * n + 2] = fmaf(v[4 * n + 2], p.scale2, bias[n].x); v[4 * n + 3] = fmaf(v[4 * n + 3], p.scale2, bias[n].y);
+                v[mt][4 * n + 0] = fmaf(v[mt][4 * n + 0], p.scale2, bias[n].x); v[mt][4 * n + 1] = fmaf(v[mt][4 * n + 1], p.scale2, bias[n].y);
+                v[mt][4 * n + 2] = fmaf(v[mt][4 * n + 2], p.scale2, bias[n].x); v[mt][4 * n + 3] = fmaf(v[mt][4 * n + 3], p.scale2, bias[n].y);
             }
-            activate_block<16>(v, p.act2);
+            activate_block<16, RELU>(v[mt], p.act2);
             if (col0 + 32u > p.N2) {
                 // columns beyond the layer's width were not written by this chunk's MMAs: keep stale tensor memory out
 #pragma unroll
                 for (int n = 0; n < 4; n++) {
-                    if (col0 + 8 * n + 2 * t >= p.N2) { v[4 * n] = 0.0f; v[4 * n + 2] = 0.0f; }
-                    if (col0 + 8 * n + 2 * t + 1 >= p.N2) { v[4 * n + 1] = 0.0f; v[4 * n + 3] = 0.0f; }
+                    if (col0 + 8 * n + 2 * t >= p.N2) { v[mt][4 * n] = 0.0f; v[mt][4 * n + 2] = 0.0f; }
+                    if (col0 + 8 * n + 2 * t + 1 >= p.N2) { v[mt][4 * n + 1] = 0.0f; v[mt][4 * n + 3] = 0.0f; }
                 }
             }
-            if (p.pairs && (g & 1u)) {
+            if (PAIRS && (g & 1u)) {
 #pragma unroll
-                for (int i = 0; i < 16; i++) v[i] = (v[i] - round16<T16>(v[i])) * p.lo_scale;
+                for (int i = 0; i < 16; i++) v[mt][i] = (v[mt][i] - round16<T16>(v[mt][i])) * p.lo_scale;
+            }
+        }
+        // the warp-level MMAs of the block: k-step by k-step, the (row tile, output tile) accumulators are independent
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+            uint32_t a[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                a[mt][0] = pack2<T16>(v[mt][8 * ks + 0], v[mt][8 * ks + 1]);      // row g,   columns 16ks + 2t, +1
+                a[mt][1] = pack2<T16>(v[mt][8 * ks + 2], v[mt][8 * ks + 3]);      // row g+8
+                a[mt][2] = pack2<T16>(v[mt][8 * ks + 4], v[mt][8 * ks + 5]);      // row g,   columns 16ks + 8 + 2t, +1
+                a[mt][3] = pack2<T16>(v[mt][8 * ks + 6], v[mt][8 * ks + 7]);      // row g+8
             }
 #pragma unroll
-            for (int ks = 0; ks < 2; ks++) {
-                uint32_t a[4];
-                a[0] = pack2<T16>(v[8 * ks + 0], v[8 * ks + 1]);      // row g,   columns 16ks + 2t, +1
-                a[1] = pack2<T16>(v[8 * ks + 2], v[8 * ks + 3]);      // row g+8
-                a[2] = pack2<T16>(v[8 * ks + 4], v[8 * ks + 5]);      // row g,   columns 16ks + 8 + 2t, +1
-                a[3] = pack2<T16>(v[8 * ks + 6], v[8 * ks + 7]);      // row g+8
+            for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) mma_16816<T16>(hd[mt][nt], a, bf[ks][nt][0], bf[ks][nt][1]);
-            }
+                for (int nt = 0; nt < NT; nt++) mma_16816<T16>(hd[mt][nt], a[mt], bf[ks][nt][0], bf[ks][nt][1]);
         }
 #pragma unroll
         for (int ks = 0; ks < 2; ks++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) { bf[ks][nt][0] = bf_next[ks][nt][0]; bf[ks][nt][1] = bf_next[ks][nt][1]; }
     }
+    tmem_ld_wait();
 }
 
-template <typename T16, int NT, bool TRACE>
+// PAIRS: every row as a hi and a lo slot (p.pairs); RELU: both hidden activations are ReLU (known at compile time, the
+// common case); otherwise they are resolved per register block at run time.
+template <typename T16, int NT, bool PAIRS, bool RELU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUtensorMap map_w2, const FusedParams p)
+spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUtensorMap map_w2,
+                      const __grid_constant__ CUtensorMap map_x, const FusedParams p)
 {
     // the whole shared memory of the SM is one dynamic block: operand tiles first (they need 1024-byte alignment
     // for the swizzle atoms, which the start of a CTA's shared window has), then the barrier table and the bias buffers
@@ -358,29 +395,39 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
     const uint32_t x_full0 = smem_u32(bars.x_full), x_empty0 = smem_u32(bars.x_empty);
     const uint32_t acc_full0 = smem_u32(bars.acc_full), acc_empty0 = smem_u32(bars.acc_empty);
     const uint32_t h1_ready0 = smem_u32(bars.h1_ready), xchg_full0 = smem_u32(bars.xchg_full);
+    const uint32_t xf_full0 = smem_u32(bars.xf_full), xf_empty0 = smem_u32(bars.xf_empty), h1_free0 = smem_u32(&bars.h1_free);
     volatile int *abort_flag = &bars.abort_flag;
 
     // the warp index through a shuffle: provably warp-uniform, so role code stays in uniform registers
     const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31u;
     const uint32_t abort_addr = smem_u32(&bars.abort_flag);
 
+    // The two CTAs of a cluster work as a pair: CTA `rank` owns slots 128*rank .. 128*rank+127 of a 256-slot tile.  The MMA
+    // thread of rank 0 issues for both; the barriers it waits on live in ITS shared memory (both CTAs' warps arrive there),
+    // and its commits arrive on the barriers at the same offsets in both CTAs.
+    const uint32_t rank = cluster_rank();
+    const uint32_t lead_x_full0 = mapa(x_full0, 0), lead_acc_empty0 = mapa(acc_empty0, 0), lead_h1_ready0 = mapa(h1_ready0, 0);
+    const uint32_t lead_w_full0 = mapa(w_full0, 0);
+
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < W_STAGES; s++) { mbar_init(w_full0 + 8 * s, 1); mbar_init(w_empty0 + 8 * s, 1); }
-        for (uint32_t s = 0; s < X_STAGES; s++) { mbar_init(x_full0 + 8 * s, CVT_WARPS); mbar_init(x_empty0 + 8 * s, 1); }
-        for (uint32_t a = 0; a < 2; a++) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, EPI_WARPS); }
-        for (uint32_t k = 0; k < H1_TILES; k++) mbar_init(h1_ready0 + 8 * k, 4);
+        for (uint32_t s = 0; s < X_STAGES; s++) { mbar_init(x_full0 + 8 * s, 2 * CVT_WARPS); mbar_init(x_empty0 + 8 * s, 1); }
+        for (uint32_t a = 0; a < 2; a++) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, 2 * EPI_WARPS); }
+        for (uint32_t k = 0; k < H1_TILES; k++) mbar_init(h1_ready0 + 8 * k, 2 * 4);
         for (uint32_t a = 0; a < 4; a++) mbar_init(xchg_full0 + 8 * a, 1);
+        for (uint32_t s = 0; s < XF_STAGES; s++) { mbar_init(xf_full0 + 8 * s, 1); mbar_init(xf_empty0 + 8 * s, CVT_WARPS); }
+        mbar_init(h1_free0, 1);
         bars.abort_flag = 0;
         mbar_fence_init();
         prefetch_map(&map_w1);
         prefetch_map(&map_w2);
     }
-    if (warp == 1) tmem_alloc(smem_u32(&bars.tmem_slot), TMEM_COLS);
+    if (warp == 1) tmem_alloc_pair(smem_u32(&bars.tmem_slot), TMEM_COLS);
     tc_fence_before();
-    __syncthreads();
+    cluster_sync();                                            // both CTAs' barriers exist before anyone arrives on them
     tc_fence_after();
     const uint32_t tmem_base = bars.tmem_slot;
-    // everything above touched only this CTA's own shared and tensor memory: it may overlap the tail of the
+    // everything above touched only this pair's own shared and tensor memory: it may overlap the tail of the
     // kernel in front; from here on earlier results (the row list, the count) are read
     spg_grid_trigger();
     spg_grid_wait();
@@ -390,108 +437,117 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         const uint32_t m = *reinterpret_cast<const volatile uint32_t *>(p.rows_limit);
         rows = m < rows ? m : rows;
     }
-    const uint32_t rpt = p.pairs ? BM / 2 : BM;                // rows per tile
-    const uint32_t tiles = (rows + rpt - 1) / rpt;
-    const uint32_t ntile = tiles > blockIdx.x ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t rpt = PAIRS ? BM / 2 : BM;                // rows per CTA and tile
+    const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const uint32_t tiles = (rows + 2 * rpt - 1) / (2 * rpt);   // 256-slot tiles
+    const uint32_t ntile = tiles > pair ? (tiles - pair + npairs - 1) / npairs : 0;
     const uint32_t nchunks = p.nch1 + p.nch2;
-    const bool tracing = TRACE && p.trace != nullptr && blockIdx.x == 0;
+    constexpr bool TRACE = true;                               // the cycle counters are a run-time switch (p.trace)
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+    // first row of this CTA in the pair's tile number ti
+    auto tile_row0 = [&](uint32_t ti) { return ((pair + ti * npairs) * 2u + rank) * rpt; };
 
     if (warp == 0) {
         // ------------------------------ weight producer (TMA) ------------------------------
-        // the whole warp walks the loops convergently; one elected lane issues
+        // Per k-block each CTA fetches ITS half of the chunk's weight rows ([128 x 64] box starting at row n/2 * rank of the
+        // chunk); both loads complete on the first CTA's barrier.  The whole warp walks the loops convergently; one elected
+        // lane issues.
         uint32_t it = 0;
         unsigned long long w_wait = 0;
         const long long t_begin = TRACE ? clock64() : 0;
+        auto load_w = [&](const CUtensorMap *map, uint32_t kb, uint32_t row) {
+            const uint32_t s = it % W_STAGES, ph = (it / W_STAGES) & 1u;
+            uwait<TRACE>(w_empty0 + 8 * s, ph ^ 1u, abort_addr, p.status, 1, tracing, w_wait);
+            if (elect_one()) {
+                if (rank == 0) mbar_expect_tx(w_full0 + 8 * s, 2 * TILE_BYTES);
+                tma_load_2d_pair(wst_addr + s * TILE_BYTES, map, lead_w_full0 + 8 * s, (int)(kb * BK), (int)row);
+            }
+            __syncwarp();
+            it++;
+        };
         for (uint32_t ti = 0; ti < ntile; ti++) {
-            for (uint32_t ch = 0; ch < nchunks; ch++) {
-                const bool l1 = ch < p.nch1;
-                const uint32_t c = l1 ? ch : ch - p.nch1;
-                const uint32_t width = l1 ? p.N1 : p.N2;
-                const uint32_t ncols = width - c * 256u < 256u ? width - c * 256u : 256u;
-                const uint32_t nh = ncols > 128u ? 2u : 1u;
-                const uint32_t kbs = l1 ? p.kb1 : p.kb2;
-                const CUtensorMap *map = l1 ? &map_w1 : &map_w2;
-                for (uint32_t kb = 0; kb < kbs; kb++) {
-                    for (uint32_t h = 0; h < nh; h++, it++) {
-                        const uint32_t s = it % W_STAGES, ph = (it / W_STAGES) & 1u;
-                        uwait<TRACE>(w_empty0 + 8 * s, ph ^ 1u, abort_addr, p.status, 1, tracing, w_wait);
-                        if (elect_one()) {
-                            mbar_expect_tx(w_full0 + 8 * s, TILE_BYTES);
-                            tma_load_2d(wst_addr + s * TILE_BYTES, map, w_full0 + 8 * s, (int)(kb * BK), (int)(c * 256u + h * 128u));
-                        }
-                        __syncwarp();
-                    }
+            // layer 1: one pass over K with every chunk's tile per k-block (its chunks fill the accumulators side by side)
+            for (uint32_t kb = 0; kb < p.kb1; kb++)
+                for (uint32_t c = 0; c < p.nch1; c++) {
+                    const uint32_t ncols = p.N1 - c * 256u < 256u ? p.N1 - c * 256u : 256u;
+                    load_w(&map_w1, kb, c * 256u + rank * (((ncols + 31u) & ~31u) >> 1));
                 }
+            // layer 2: chunk after chunk
+            for (uint32_t c = 0; c < p.nch2; c++) {
+                const uint32_t ncols = p.N2 - c * 256u < 256u ? p.N2 - c * 256u : 256u;
+                for (uint32_t kb = 0; kb < p.kb2; kb++) load_w(&map_w2, kb, c * 256u + rank * (((ncols + 31u) & ~31u) >> 1));
             }
         }
         if (tracing && lane == 0) { p.trace[24] = (unsigned long long)(clock64() - t_begin); p.trace[25] = w_wait; }
     } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
+        // ------------------------------ MMA issuer (first CTA of the pair only) ------------------------------
         // the whole warp walks the loops convergently (all operands of tcgen05.mma stay warp-uniform); one elected lane issues
-        const uint32_t fmt = std::is_same<T16, __half>::value ? 0u : 1u;
-        uint32_t it = 0, xit = 0, g = 0;
-        unsigned long long t_acc = 0, t_x = 0, t_h1 = 0, t_w = 0, t_issue = 0, t_commit = 0;
-        const long long t_begin = TRACE ? clock64() : 0;
-        for (uint32_t ti = 0; ti < ntile; ti++) {
-            for (uint32_t ch = 0; ch < nchunks; ch++, g++) {
-                const bool l1 = ch < p.nch1;
-                const uint32_t c = l1 ? ch : ch - p.nch1;
-                const uint32_t width = l1 ? p.N1 : p.N2;
-                const uint32_t ncols = width - c * 256u < 256u ? width - c * 256u : 256u;
-                const uint32_t nh = ncols > 128u ? 2u : 1u;
-                const uint32_t kbs = l1 ? p.kb1 : p.kb2;
-                const uint32_t kdim = l1 ? p.K1 : p.N1;
-                const uint32_t acc = g & 1u;
-                uwait<TRACE>(acc_empty0 + 8 * acc, ((g >> 1) & 1u) ^ 1u, abort_addr, p.status, 2, tracing, t_acc);
-                tc_fence_after();
-                for (uint32_t kb = 0; kb < kbs; kb++) {
-                    uint32_t a_addr;
-                    if (l1) {
-                        const uint32_t xs = xit % X_STAGES;
-                        uwait<TRACE>(x_full0 + 8 * xs, (xit / X_STAGES) & 1u, abort_addr, p.status, 3, tracing, t_x);
-                        a_addr = xst_addr + xs * TILE_BYTES;
-                    } else {
-                        if (c == 0) uwait<TRACE>(h1_ready0 + 8 * kb, ti & 1u, abort_addr, p.status, 4, tracing, t_h1);
-                        a_addr = h1_addr + kb * TILE_BYTES;
-                    }
-                    tc_fence_after();
-                    const uint32_t kleft = kdim - kb * BK;
-                    const uint32_t ksteps = kleft >= BK ? BK / 16u : (kleft + 15u) / 16u;
-                    const uint64_t da = smem_desc_sw128(a_addr);
-                    for (uint32_t h = 0; h < nh; h++, it++) {
-                        const uint32_t s = it % W_STAGES;
-                        uwait<TRACE>(w_full0 + 8 * s, (it / W_STAGES) & 1u, abort_addr, p.status, 5, tracing, t_w);
-                        tc_fence_after();
-                        const uint32_t nleft = ncols - h * 128u;
-                        const uint32_t n = nleft >= 128u ? 128u : (nleft + 15u) & ~15u;
-                        const uint32_t idesc = idesc_f16(fmt, fmt, n);
-                        const uint64_t db = smem_desc_sw128(wst_addr + s * TILE_BYTES);
-                        const uint32_t d = tmem_base + acc * 256u + h * 128u;
-                        if (elect_one()) {
-                            const long long t0 = (TRACE && tracing) ? clock64() : 0;
-                            if (ksteps == BK / 16u) {
+        if (rank == 0) {
+            const uint32_t fmt = std::is_same<T16, __half>::value ? 0u : 1u;
+            uint32_t it = 0, xit = 0, g = 0;
+            unsigned long long t_acc = 0, t_x = 0, t_h1 = 0, t_w = 0, t_issue = 0, t_commit = 0;
+            const long long t_begin = TRACE ? clock64() : 0;
+            // one k-block of MMAs: A tile at a_addr, this k-block's weight slot, accumulator `acc`, N = n
+            auto kblock = [&](uint32_t a_addr, uint32_t kdim, uint32_t kb, uint32_t acc, uint32_t n, bool x_done, bool acc_done, bool h1_done) {
+                const uint32_t s = it % W_STAGES;
+                uwait<TRACE>(w_full0 + 8 * s, (it / W_STAGES) & 1u, abort_addr, p.status, 5, tracing, t_w);
+                const uint32_t kleft = kdim - kb * BK;
+                const uint32_t ksteps = kleft >= BK ? BK / 16u : (kleft + 15u) / 16u;
+                const uint64_t da = smem_desc_sw128(a_addr);
+                const uint64_t db = smem_desc_sw128(wst_addr + s * TILE_BYTES);
+                const uint32_t idesc = idesc_f16_pair(fmt, fmt, n);
+                const uint32_t d = tmem_base + acc * 256u;
+                if (elect_one()) {
+                    const long long t0 = (TRACE && tracing) ? clock64() : 0;
+                    if (ksteps == BK / 16u) {
 #pragma unroll
-                                for (uint32_t k = 0; k < BK / 16u; k++) umma_f16(d, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                            } else {
-                                for (uint32_t k = 0; k < ksteps; k++) umma_f16(d, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                            }
-                            const long long t1 = (TRACE && tracing) ? clock64() : 0;
-                            umma_commit(w_empty0 + 8 * s);               // the weight slot is free once these MMAs have read it
-                            if (l1 && h + 1 == nh) umma_commit(x_empty0 + 8 * (xit % X_STAGES));
-                            if (kb + 1 == kbs && h + 1 == nh) umma_commit(acc_full0 + 8 * acc);
-                            if (TRACE && tracing) { t_issue += (unsigned long long)(t1 - t0); t_commit += (unsigned long long)(clock64() - t1); }
-                        }
-                        __syncwarp();
+                        for (uint32_t k = 0; k < BK / 16u; k++) umma_f16_pair(d, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    } else {
+                        for (uint32_t k = 0; k < ksteps; k++) umma_f16_pair(d, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
                     }
-                    if (l1) xit++;
+                    const long long t1 = (TRACE && tracing) ? clock64() : 0;
+                    umma_commit_pair(w_empty0 + 8 * s);              // both CTAs' weight slots are free once these MMAs have read them
+                    if (x_done) umma_commit_pair(x_empty0 + 8 * (xit % X_STAGES));
+                    if (acc_done) umma_commit_pair(acc_full0 + 8 * acc);
+                    if (h1_done) umma_commit_pair(h1_free0);         // the hidden tiles may be overwritten (input staging of the next tile)
+                    if (TRACE && tracing) { t_issue += (unsigned long long)(t1 - t0); t_commit += (unsigned long long)(clock64() - t1); }
+                }
+                __syncwarp();
+                it++;
+            };
+            for (uint32_t ti = 0; ti < ntile; ti++) {
+                // ---- layer 1: ONE pass over the input; chunk c accumulates in accumulator (g + c) & 1 (at most two chunks) ----
+                for (uint32_t c = 0; c < p.nch1; c++)
+                    uwait<TRACE>(acc_empty0 + 8 * ((g + c) & 1u), (((g + c) >> 1) & 1u) ^ 1u, abort_addr, p.status, 2, tracing, t_acc);
+                tc_fence_after();
+                for (uint32_t kb = 0; kb < p.kb1; kb++) {
+                    const uint32_t xs = xit % X_STAGES;
+                    uwait<TRACE>(x_full0 + 8 * xs, (xit / X_STAGES) & 1u, abort_addr, p.status, 3, tracing, t_x);
+                    for (uint32_t c = 0; c < p.nch1; c++) {
+                        const uint32_t ncols = p.N1 - c * 256u < 256u ? p.N1 - c * 256u : 256u;
+                        kblock(xst_addr + xs * TILE_BYTES, p.K1, kb, (g + c) & 1u, (ncols + 31u) & ~31u, c + 1 == p.nch1, kb + 1 == p.kb1, false);
+                    }
+                    xit++;
+                }
+                g += p.nch1;
+                // ---- layer 2: chunk after chunk, the hidden tiles as A operand ----
+                for (uint32_t c = 0; c < p.nch2; c++, g++) {
+                    const uint32_t ncols = p.N2 - c * 256u < 256u ? p.N2 - c * 256u : 256u;
+                    const uint32_t acc = g & 1u;
+                    uwait<TRACE>(acc_empty0 + 8 * acc, ((g >> 1) & 1u) ^ 1u, abort_addr, p.status, 2, tracing, t_acc);
+                    tc_fence_after();
+                    for (uint32_t kb = 0; kb < p.kb2; kb++) {
+                        if (c == 0) uwait<TRACE>(h1_ready0 + 8 * kb, ti & 1u, abort_addr, p.status, 4, tracing, t_h1);
+                        kblock(h1_addr + kb * TILE_BYTES, p.N1, kb, acc, (ncols + 31u) & ~31u, false, kb + 1 == p.kb2, c + 1 == p.nch2 && kb + 1 == p.kb2);
+                    }
                 }
             }
+            if (tracing && lane == 0) {
+                p.trace[0] = (unsigned long long)(clock64() - t_begin);
+                p.trace[1] = t_acc; p.trace[2] = t_x; p.trace[3] = t_h1; p.trace[4] = t_w;
+            }
+            if (tracing && elect_one()) { p.trace[5] = t_issue; p.trace[6] = t_commit; }
         }
-        if (tracing && lane == 0) {
-            p.trace[0] = (unsigned long long)(clock64() - t_begin);
-            p.trace[1] = t_acc; p.trace[2] = t_x; p.trace[3] = t_h1; p.trace[4] = t_w;
-        }
-        if (tracing && elect_one()) { p.trace[5] = t_issue; p.trace[6] = t_commit; }
     } else if (warp < CVT_WARP0) {
         // ------------------------------ epilogue ------------------------------
         const uint32_t q = warp & 3u, half = (warp - EPI_WARP0) >> 2;    // TMEM lane quadrant of this warp; column half of a chunk
@@ -504,13 +560,12 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         float next_bias = __ldg(p.bias1 + et);                               // chunk 0 of the first tile
         uint32_t g = 0;
         bool alive = true;
-        unsigned long long t_full = 0, t_l1 = 0, t_l2 = 0, t_x = 0;
+        unsigned long long t_full = 0, t_l1 = 0, t_l2 = 0, t_x = 0, t_bar = 0;
         const long long t_begin = clock64();
         for (uint32_t ti = 0; ti < ntile; ti++) {
-            const uint32_t tile = blockIdx.x + ti * gridDim.x;
-            const uint32_t r = tile * rpt + (p.pairs ? slot >> 1 : slot);
+            const uint32_t r = tile_row0(ti) + (PAIRS ? slot >> 1 : slot);
             uint32_t orow = ROW_INVALID;
-            if (r < rows && !(p.pairs && (lane & 1u))) orow = p.rows_idx ? p.rows_idx[r] : r;
+            if (r < rows && !(PAIRS && (lane & 1u))) orow = p.rows_idx ? p.rows_idx[r] : r;
             float hd[2][NT][4];
 #pragma unroll
             for (int mt = 0; mt < 2; mt++)
@@ -528,7 +583,9 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
                     const uint32_t nch = ch + 1 < nchunks ? ch + 1 : 0;           // the chunk after this one (of this or the next tile)
                     next_bias = nch < p.nch1 ? __ldg(p.bias1 + nch * 256u + et) : __ldg(p.bias2 + (nch - p.nch1) * 256u + et);
                 }
+                const long long tb0 = tracing ? clock64() : 0;
                 asm volatile("bar.sync 1, %0;" ::"r"(32u * EPI_WARPS) : "memory");   // the epilogue warps only
+                if (tracing) t_bar += (unsigned long long)(clock64() - tb0);
                 // after a wait has given up the warp keeps walking its chunks (the named barrier above needs every epilogue
                 // warp every time) but does no more work: all later waits end at once
                 if (alive && !timed_wait(acc_full0 + 8 * acc, (g >> 1) & 1u, abort_flag, p.status, 6, tracing, t_full)) alive = false;
@@ -537,8 +594,8 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
                 const uint32_t taddr = tmem_base + acc * 256u + half * 128u + ((q * 32u) << 16);
                 const bool last = ch + 1 == nchunks;
                 const long long t_work = tracing ? clock64() : 0;
-                if (ch < p.nch1) epilogue_l1<T16>(p, ch, taddr, q, half, lane, h1, h1_ready0, cbias);
-                else epilogue_l2<T16, NT>(p, ch - p.nch1, taddr, half, lane, hd, cbias);
+                if (ch < p.nch1) epilogue_l1<T16, PAIRS, RELU>(p, ch, taddr, q, half, lane, h1, lead_h1_ready0, cbias);
+                else epilogue_l2<T16, NT, PAIRS, RELU>(p, ch - p.nch1, taddr, half, lane, hd, cbias);
                 if (tracing) { if (ch < p.nch1) t_l1 += (unsigned long long)(clock64() - t_work); else t_l2 += (unsigned long long)(clock64() - t_work); }
                 if (last) {
                     // the rows are complete: both warps of a quadrant lay their fragments out per row; the warp of the upper
@@ -570,9 +627,9 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
                 // memory is a layer-1 epilogue that can only start once this accumulator has been reused)
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
+                if (lane == 0) mbar_arrive_cluster(lead_acc_empty0 + 8 * acc);
                 if (!(last && half == 0)) continue;
-                if (p.pairs) {
+                if (PAIRS) {
                     // the sums of the hi slot (even lane) and the lo slot (odd lane) of a row
 #pragma unroll
                     for (int j = 0; j < HP; j++) {
@@ -607,59 +664,52 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         if (tracing && warp == EPI_WARP0 + 2 && lane == 0) {       // quadrant 0, lower column half
             p.trace[8] = (unsigned long long)(clock64() - t_begin);
             p.trace[9] = t_full; p.trace[10] = t_l1; p.trace[11] = t_l2; p.trace[12] = t_x;
+            p.trace[13] = t_bar;
+        }
+    } else if (warp == XPROD_WARP) {
+        // ------------------------------ input producer (TMA) ------------------------------
+        // While layer 1 of a tile runs, the hidden tiles in shared memory are idle (their next contents only come into being
+        // in layer 1's epilogue): the first 96 KB of that region serve as a three-slot ring of fp32 input tiles, filled by
+        // bulk-tensor copies that need no registers -- up to 96 KB of the input in flight per SM, which is what hides the
+        // latency of HBM at the rate layer 1 consumes it.  Rows addressed through a list take the converters' own loads instead.
+        if (!p.rows_idx) {
+            uint32_t xfit = 0;
+            for (uint32_t ti = 0; ti < ntile; ti++) {
+                // the hidden tiles of the tile before must have been read by its last layer-2 MMA
+                mbar_wait_uniform_cluster(h1_free0, (ti & 1u) ^ 1u, abort_addr, p.status, 10);
+                const uint32_t row0 = tile_row0(ti);
+                for (uint32_t kb = 0; kb < p.kb1; kb++, xfit++) {
+                    const uint32_t s = xfit % XF_STAGES;
+                    mbar_wait_uniform_cluster(xf_empty0 + 8 * s, ((xfit / XF_STAGES) & 1u) ^ 1u, abort_addr, p.status, 11);
+                    if (elect_one()) {
+                        mbar_expect_tx(xf_full0 + 8 * s, XF_BYTES);
+                        tma_load_2d(h1_addr + s * XF_BYTES, &map_x, xf_full0 + 8 * s, (int)(kb * BK), (int)row0);
+                    }
+                    __syncwarp();
+                }
+            }
         }
     } else {
         // ------------------------------ input converters ------------------------------
-        // A step is one [128 slots x 64 columns] tile of the input: thread (cw, lane) handles, for j = 0..7, slot
-        // j*16 + cw*2 + lane/16 and the four columns 4*(lane%16).., so a warp instruction reads two rows x 256 bytes.
+        // A step is one [128 slots x 64 columns] tile of the input: thread (cw, lane) handles, for j = 0..15, slot
+        // j*8 + cw*2 + lane/16 and the four columns 4*(lane%16).., so a warp instruction covers two rows x 256 bytes.
+        // The fp32 values come from the staging ring (rows in order) or, for a row list, from global memory.
         const uint32_t cw = warp - CVT_WARP0;
         const uint32_t sub = lane >> 4, c4 = lane & 15u;
-        const uint32_t steps_per_tile = p.nch1 * p.kb1;
+        const uint32_t steps_per_tile = p.kb1;                  // layer 1 makes one pass over the input per tile
         const uint32_t total = ntile * steps_per_tile;
-        uint32_t srow[CVT_ITEMS];
         unsigned long long t_empty = 0, t_cvt = 0;
         const long long t_begin = clock64();
-        auto prefetch_tile = [&](uint32_t ti) {
-            // the input rows of a whole tile into L2, one bulk prefetch per row
-            if (ti >= ntile) return;
-            const uint32_t t = cw * 32u + lane;
-            if (t >= BM || (p.pairs && (t & 1u))) return;
-            const uint32_t tile = blockIdx.x + ti * gridDim.x;
-            const uint32_t r = tile * rpt + (p.pairs ? t >> 1 : t);
-            if (r >= rows) return;
-            const uint32_t src = p.rows_idx ? p.rows_idx[r] : r;
-            const float *row = p.x + (size_t)src * p.ldx;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(p.K1 * 4u) : "memory");
-        };
-        auto issue = [&](uint32_t step, float4 (&buf)[CVT_ITEMS]) {
-            const uint32_t ti = step / steps_per_tile, kb = (step % steps_per_tile) % p.kb1;
-            if (step % steps_per_tile == 0) {
-                const uint32_t tile = blockIdx.x + ti * gridDim.x;
-#pragma unroll
-                for (int j = 0; j < CVT_ITEMS; j++) {
-                    const uint32_t slot = j * (2u * CVT_WARPS) + cw * 2u + sub;
-                    const uint32_t r = tile * rpt + (p.pairs ? slot >> 1 : slot);
-                    srow[j] = r < rows ? (p.rows_idx ? p.rows_idx[r] : r) : ROW_INVALID;
-                }
-                prefetch_tile(ti + 1);
-            }
-            const uint32_t col = kb * BK + c4 * 4u;
-#pragma unroll
-            for (int j = 0; j < CVT_ITEMS; j++) {
-                buf[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (srow[j] != ROW_INVALID && col < p.K1) buf[j] = __ldg(reinterpret_cast<const float4 *>(p.x + (size_t)srow[j] * p.ldx + col));
-            }
-        };
-        auto convert = [&](uint32_t step, const float4 (&buf)[CVT_ITEMS]) -> bool {
+        // rounds, packs and writes one [128 x 64] A tile; arrives on the first CTA's barrier
+        auto store_tile = [&](uint32_t step, const float4 (&buf)[CVT_ITEMS]) -> bool {
             const uint32_t xs = step % X_STAGES;
             if (!timed_wait(x_empty0 + 8 * xs, ((step / X_STAGES) & 1u) ^ 1u, abort_flag, p.status, 8, tracing, t_empty)) return false;
-            const long long t_work = tracing ? clock64() : 0;
             uint8_t *tile = xst + xs * TILE_BYTES;
 #pragma unroll
             for (int j = 0; j < CVT_ITEMS; j++) {
                 const uint32_t slot = j * (2u * CVT_WARPS) + cw * 2u + sub;
                 float4 v = buf[j];
-                if (p.pairs && (slot & 1u)) {
+                if (PAIRS && (slot & 1u)) {
                     v.x = (v.x - round16<T16>(v.x)) * p.lo_scale; v.y = (v.y - round16<T16>(v.y)) * p.lo_scale;
                     v.z = (v.z - round16<T16>(v.z)) * p.lo_scale; v.w = (v.w - round16<T16>(v.w)) * p.lo_scale;
                 }
@@ -669,21 +719,70 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(x_full0 + 8 * xs);
-            if (tracing) t_cvt += (unsigned long long)(clock64() - t_work);
+            if (lane == 0) mbar_arrive_cluster(lead_x_full0 + 8 * xs);
             return true;
         };
-        if (total) {
-            // two register buffers: the loads of step s+1 are in flight while step s is converted
-            prefetch_tile(0);
-            float4 buf_a[CVT_ITEMS], buf_b[CVT_ITEMS];
-            issue(0, buf_a);
-            for (uint32_t step = 0; step < total; step += 2) {
-                if (step + 1 < total) issue(step + 1, buf_b);
-                if (!convert(step, buf_a)) break;
-                if (step + 1 >= total) break;
-                if (step + 2 < total) issue(step + 2, buf_a);
-                if (!convert(step + 1, buf_b)) break;
+        if (!p.rows_idx) {
+            // ---- rows in order: fp32 tiles arrive in the staging ring ----
+            for (uint32_t step = 0; step < total; step++) {
+                const uint32_t s = step % XF_STAGES;
+                const uint32_t ti = step / steps_per_tile;
+                if (!timed_wait(xf_full0 + 8 * s, (step / XF_STAGES) & 1u, abort_flag, p.status, 12, tracing, t_empty)) break;
+                const long long t_work = tracing ? clock64() : 0;
+                const float4 *stg = reinterpret_cast<const float4 *>(h1 + s * XF_BYTES);
+                const uint32_t row0 = tile_row0(ti);
+                float4 buf[CVT_ITEMS];
+#pragma unroll
+                for (int j = 0; j < CVT_ITEMS; j++) {
+                    const uint32_t slot = j * (2u * CVT_WARPS) + cw * 2u + sub;
+                    const uint32_t rl = PAIRS ? slot >> 1 : slot;                 // staging row of this slot
+                    buf[j] = stg[rl * 16u + c4];
+                    if (row0 + rl >= rows) buf[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+                // the slot can be refilled as soon as every converter warp has its values in registers
+                __syncwarp();
+                if (lane == 0) mbar_arrive(xf_empty0 + 8 * s);
+                if (!store_tile(step, buf)) break;
+                if (tracing) t_cvt += (unsigned long long)(clock64() - t_work);
+            }
+        } else {
+            // ---- a row list: each thread fetches its rows itself, one step ahead of the tile it writes ----
+            uint32_t srow[CVT_ITEMS];
+            float4 buf[CVT_ITEMS];
+            auto issue = [&](uint32_t step) {
+                const uint32_t ti = step / steps_per_tile, kb = step % steps_per_tile;
+                if (kb == 0) {
+                    const uint32_t row0 = tile_row0(ti);
+#pragma unroll
+                    for (int j = 0; j < CVT_ITEMS; j++) {
+                        const uint32_t slot = j * (2u * CVT_WARPS) + cw * 2u + sub;
+                        const uint32_t r = row0 + (PAIRS ? slot >> 1 : slot);
+                        srow[j] = r < rows ? p.rows_idx[r] : ROW_INVALID;
+                    }
+                }
+                const uint32_t col = kb * BK + c4 * 4u;
+#pragma unroll
+                for (int j = 0; j < CVT_ITEMS; j++) {
+                    buf[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (srow[j] != ROW_INVALID && col < p.K1) buf[j] = __ldg(reinterpret_cast<const float4 *>(p.x + (size_t)srow[j] * p.ldx + col));
+                }
+            };
+            // the listed rows of a tile are brought into L2 as a whole (one bulk prefetch per row) before its first loads
+            auto prefetch_rows = [&](uint32_t ti) {
+                const uint32_t t = cw * 32u + lane;                       // 0..127: one slot each
+                if (PAIRS && (t & 1u)) return;
+                const uint32_t r = tile_row0(ti) + (PAIRS ? t >> 1 : t);
+                if (ti >= ntile || r >= rows) return;
+                const float *row = p.x + (size_t)p.rows_idx[r] * p.ldx;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(p.K1 * 4u) : "memory");
+            };
+            if (total) { prefetch_rows(0); prefetch_rows(1); issue(0); }
+            for (uint32_t step = 0; step < total; step++) {
+                if (step % steps_per_tile == 0 && step) prefetch_rows(step / steps_per_tile + 1);
+                const long long t_work = tracing ? clock64() : 0;
+                if (!store_tile(step, buf)) break;
+                if (step + 1 < total) issue(step + 1);
+                if (tracing) t_cvt += (unsigned long long)(clock64() - t_work);
             }
         }
         if (tracing && warp == CVT_WARP0 && lane == 0) {
@@ -699,10 +798,10 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         // a wait gave up: give weight tiles that may still be in flight time to land before the shared memory goes away
         for (int i = 0; i < 256; i++) __nanosleep(1000);
     }
-    __syncthreads();
+    cluster_sync();            // neither CTA leaves while the other may still read its shared memory or arrive on its barriers
     if (warp == 1) {
         tc_fence_after();
-        tmem_free(tmem_base, TMEM_COLS);
+        tmem_free_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -767,26 +866,57 @@ int weight_map(CUtensorMap *map, const void *base, int type16, uint32_t K, uint3
 
 thread_local unsigned long long *tls_trace = nullptr;
 
-template <typename T16, int NT, bool TRACE>
-int launch_fused_t(const CUtensorMap &m1, const CUtensorMap &m2, const FusedParams &p, uint32_t grid, cudaStream_t stream)
+// 2-D map over the fp32 input rows [rows][ld] whose first K columns are valid, boxes of [128 rows x 64 columns], no swizzle
+int input_map(CUtensorMap *map, const float *x, uint32_t K, uint32_t rows, uint32_t ld)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { spgk_set_error("cuTensorMapEncodeTiled", "driver entry point not available"); return SPGK_E_CUDA; }
+    cuuint64_t dims[2] = { K, rows };
+    cuuint64_t strides[1] = { (cuuint64_t)ld * 4 };
+    cuuint32_t box[2] = { BK, BM };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[64];
+        snprintf(msg, sizeof msg, "CUresult %d", (int)r);
+        spgk_set_error("cuTensorMapEncodeTiled (input)", msg);
+        return SPGK_E_CUDA;
+    }
+    return SPGK_OK;
+}
+
+template <typename T16, int NT, bool PAIRS, bool RELU>
+int launch_fused_t(const CUtensorMap &m1, const CUtensorMap &m2, const CUtensorMap &mx, const FusedParams &p, uint32_t grid, cudaStream_t stream)
 {
     static SpgOncePerDevice once;
     int dev = 0;
     SPGK_CUDA(cudaGetDevice(&dev));
     const size_t smem = SMEM_TOTAL;
     int rc = once.run(dev, [&]() -> int {
-        SPGK_CUDA(cudaFuncSetAttribute(spg_mlp3_fused_kernel<T16, NT, TRACE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        SPGK_CUDA(cudaFuncSetAttribute(spg_mlp3_fused_kernel<T16, NT, PAIRS, RELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         return SPGK_OK;
     });
     if (rc) return rc;
-    SPGK_CUDA(spg_launch_chained(spg_mlp3_fused_kernel<T16, NT, TRACE>, dim3(grid), dim3(NUM_THREADS), smem, stream, m1, m2, p));
+    // clusters of two CTAs (one MMA pair per cluster); programmatic stream serialisation as for the other chained kernels
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
+    SPGK_CUDA(cudaLaunchKernelEx(&cfg, spg_mlp3_fused_kernel<T16, NT, PAIRS, RELU>, m1, m2, mx, p));
     return spgk_check_launch("spg_mlp3_fused_kernel");
 }
 
-template <typename T16, int NT>
-int launch_fused(const CUtensorMap &m1, const CUtensorMap &m2, const FusedParams &p, uint32_t grid, cudaStream_t stream)
+template <typename T16>
+int launch_fused(const CUtensorMap &m1, const CUtensorMap &m2, const CUtensorMap &mx, const FusedParams &p, bool relu, uint32_t grid, cudaStream_t stream)
 {
-    return p.trace ? launch_fused_t<T16, NT, true>(m1, m2, p, grid, stream) : launch_fused_t<T16, NT, false>(m1, m2, p, grid, stream);
+    // the warp-level MMA of the head always covers 16 outputs (two tiles of 8)
+    if (p.pairs) return relu ? launch_fused_t<T16, 2, true, true>(m1, m2, mx, p, grid, stream) : launch_fused_t<T16, 2, true, false>(m1, m2, mx, p, grid, stream);
+    return relu ? launch_fused_t<T16, 2, false, true>(m1, m2, mx, p, grid, stream) : launch_fused_t<T16, 2, false, false>(m1, m2, mx, p, grid, stream);
 }
 
 }  // namespace
@@ -868,21 +998,23 @@ int spgk_mlp3_forward(const spgk_layer *L1, const void *w1_16, uint32_t ldw1,
     CUtensorMap m1, m2;
     if ((rc = weight_map(&m1, w1_16, type16, L1->in, L1->out, ldw1))) return rc;
     if ((rc = weight_map(&m2, w2_16, type16, L2->in, L2->out, ldw2))) return rc;
+    CUtensorMap mx = m1;                                         // unused with a row list
+    if (!rows_idx && (rc = input_map(&mx, x, L1->in, N, ldx))) return rc;
 
-    const uint32_t rpt = pairs ? BM / 2 : BM;
+    const uint32_t rpt2 = pairs ? BM : 2 * BM;                  // rows of a 256-slot tile (one per CTA pair)
     uint32_t guess = N;
-    if (rows_limit && rows_expected && rows_expected < N) guess = rows_expected * 2u + rpt;      // a selection: few tiles expected
+    if (rows_limit && rows_expected && rows_expected < N) guess = rows_expected * 2u + rpt2;      // a selection: few tiles expected
     if (guess > N) guess = N;
-    uint32_t tiles = (guess + rpt - 1) / rpt;
-    const uint32_t cap_tiles = (N + rpt - 1) / rpt;
-    // the grid must cover every tile the device-side count can produce: a CTA walks tiles blockIdx.x + i * gridDim.x,
-    // so any grid size is correct; the guess only avoids launching CTAs that would find nothing to do
-    if (tiles > cap_tiles) tiles = cap_tiles;
-    const uint32_t grid = tiles < (uint32_t)dp.sm_count ? (tiles ? tiles : 1u) : (uint32_t)dp.sm_count;
+    uint32_t tiles = (guess + rpt2 - 1) / rpt2;
+    // A pair walks tiles pair + i * pairs, so any grid size covers every tile the device-side count can produce; the guess
+    // only avoids launching pairs that would find nothing to do.
+    const uint32_t max_pairs = (uint32_t)dp.sm_count / 2u;
+    const uint32_t npairs = tiles < max_pairs ? (tiles ? tiles : 1u) : max_pairs;
+    const uint32_t grid = 2u * npairs;
     cudaStream_t st = (cudaStream_t)stream;
-    const bool narrow = L3->out <= 8;        // one or two 8-wide output tiles of the warp-level MMA
-    if (type16 == SPGK_T_F16) return narrow ? launch_fused<__half, 1>(m1, m2, p, grid, st) : launch_fused<__half, 2>(m1, m2, p, grid, st);
-    return narrow ? launch_fused<__nv_bfloat16, 1>(m1, m2, p, grid, st) : launch_fused<__nv_bfloat16, 2>(m1, m2, p, grid, st);
+    const bool relu = L1->act == SPG_ACT_RELU && L2->act == SPG_ACT_RELU;
+    if (type16 == SPGK_T_F16) return launch_fused<__half>(m1, m2, mx, p, relu, grid, st);
+    return launch_fused<__nv_bfloat16>(m1, m2, mx, p, relu, grid, st);
 }
 
 }  // extern "C"

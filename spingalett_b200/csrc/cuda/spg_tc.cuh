@@ -26,19 +26,23 @@ __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier
 
 // Bounded wait on the phase with the given parity.  Once the abort flag is up every wait returns false at
 // once; when the bound is hit the flag is raised and `code` recorded in *status.
+// every try_wait may suspend the warp for up to this long; the iteration limits below count such attempts
+#define SPG_WAIT_HINT_NS 20000u
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *status, int code,
-                                          uint32_t limit = 1u << 22)
+                                          uint32_t limit = 1u << 16)
 {
     if (*abort_flag) return false;
     for (uint32_t i = 0; i < limit; ++i) {
         uint32_t ok;
+        // the time hint lets the hardware suspend the warp until the phase completes (or the time is up) instead of
+        // spinning in the issue slots that the working warps of the same scheduler need
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(SPG_WAIT_HINT_NS) : "memory");
         if (ok) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if ((i & 15u) == 15u && *abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);
@@ -52,7 +56,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // when the abort flag is up (or the bound is hit, which raises it and records `code`) the wait simply ends and the
 // caller carries on; every later wait then ends at once, so the role runs out of its loops quickly.
 __device__ __forceinline__ void mbar_wait_uniform(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem, int32_t *status, int code,
-                                                  uint32_t limit = 1u << 22)
+                                                  uint32_t limit = 1u << 16)
 {
     asm volatile(
         "{\n\t"
@@ -63,10 +67,10 @@ __device__ __forceinline__ void mbar_wait_uniform(uint32_t bar, uint32_t parity,
         "setp.ne.u32 q, a, 0;\n\t"
         "@q bra SPG_WAIT_DONE;\n\t"
         "SPG_WAIT_LOOP:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1, %6;\n\t"
         "@p bra SPG_WAIT_DONE;\n\t"
         "add.u32 n, n, 1;\n\t"
-        "and.b32 a, n, 255;\n\t"
+        "and.b32 a, n, 15;\n\t"
         "setp.ne.u32 q, a, 0;\n\t"
         "@q bra SPG_WAIT_LOOP;\n\t"
         "ld.volatile.shared.u32 a, [%2];\n\t"
@@ -78,7 +82,36 @@ __device__ __forceinline__ void mbar_wait_uniform(uint32_t bar, uint32_t parity,
         "atom.global.cas.b32 a, [%3], 0, %4;\n\t"
         "SPG_WAIT_DONE:\n\t"
         "}"
-        ::"r"(bar), "r"(parity), "r"(abort_flag_smem), "l"(status), "r"(code), "r"(limit) : "memory");
+        ::"r"(bar), "r"(parity), "r"(abort_flag_smem), "l"(status), "r"(code), "r"(limit), "r"(SPG_WAIT_HINT_NS) : "memory");
+}
+
+// The same for a barrier that the other CTA of a pair arrives on (acquire at cluster scope).  The abort flag is only
+// looked at every 16 failed attempts: the common case costs one try_wait.
+__device__ __forceinline__ void mbar_wait_uniform_cluster(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem, int32_t *status, int code,
+                                                          uint32_t limit = 1u << 16)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n, a;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "SPG_WAITC_LOOP:\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%0], %1, %6;\n\t"
+        "@p bra SPG_WAITC_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "and.b32 a, n, 15;\n\t"
+        "setp.ne.u32 q, a, 0;\n\t"
+        "@q bra SPG_WAITC_LOOP;\n\t"
+        "ld.volatile.shared.u32 a, [%2];\n\t"
+        "setp.ne.u32 q, a, 0;\n\t"
+        "@q bra SPG_WAITC_DONE;\n\t"
+        "setp.lt.u32 q, n, %5;\n\t"
+        "@q bra SPG_WAITC_LOOP;\n\t"
+        "st.volatile.shared.u32 [%2], 1;\n\t"
+        "atom.global.cas.b32 a, [%3], 0, %4;\n\t"
+        "SPG_WAITC_DONE:\n\t"
+        "}"
+        ::"r"(bar), "r"(parity), "r"(abort_flag_smem), "l"(status), "r"(code), "r"(limit), "r"(SPG_WAIT_HINT_NS) : "memory");
 }
 
 // one lane of a convergent warp (the same lane every time)
@@ -157,6 +190,72 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
 __host__ __device__ inline uint32_t idesc_f16(uint32_t a_fmt, uint32_t b_fmt, uint32_t n)
 {
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// ---- CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) -----------------------------------------------------
+// One MMA instruction, issued by the pair's first CTA, multiplies a 256-row tile: each CTA's shared memory holds its own
+// 128 rows of A and its half of B's rows (N/2), and each CTA's tensor memory receives its own 128 rows of the accumulator.
+// Per CTA that halves the B bytes that have to be streamed and kept in shared memory.
+
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same location in the shared memory of CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// arrive on a barrier that may live in the other CTA of the cluster (address from mapa)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// all threads of both CTAs
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free_pair(uint32_t taddr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// the barrier at the same shared-memory offset in BOTH CTAs of the pair arrives once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+// Tile load into THIS CTA's shared memory whose completion is counted on a barrier of the pair's first CTA (no multicast:
+// each CTA fetches its own tile).  `leader_bar` is a shared::cluster address (mapa(bar, 0)).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t leader_bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
+}
+// instruction descriptor of the pair MMA: M = 256 over the two CTAs
+__host__ __device__ inline uint32_t idesc_f16_pair(uint32_t a_fmt, uint32_t b_fmt, uint32_t n)
+{
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((256u >> 4) << 24);
 }
 
 }  // namespace spgtc

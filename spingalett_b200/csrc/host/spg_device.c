@@ -697,17 +697,26 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     }
     uint32_t *h_slot = n->h_count + n->count_slot;
     const uint32_t expected = n->count_seen ? *(volatile uint32_t *)h_slot : 0;    /* the count of the call before: a guide to tile shapes only */
-    if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(h_slot, d_count, 4, n->stream), "repair count"))) return rc;
+    /* (the copy is queued behind the repair kernels: nothing sits between the one-term pass and the repair, so the
+     * repair's prologue overlaps the tail of the pass under programmatic dependent launch) */
     if (n->count_slot + 1 > n->count_slots_used) n->count_slots_used = n->count_slot + 1;
-    n->count_pending = true; n->count_seen = true;
     if (Llast->act == ACT_SOFTMAX && Llast->out > spgk_gemm_tc_softmax_max()) {
         if ((rc = reserve((void **)&n->d_rep_in, &n->rep_in_bytes, (size_t)N * in0 * 4, "repair inputs"))) return rc;
         if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)N * outw * 4, "repair outputs"))) return rc;
     }
-    if (fused && n->klayers[0].precision != PRECISION_FLOAT32) {
+    /* The flagged rows are a percent or two of the batch, so either repair is one latency-bound pass over a handful of
+     * tiles.  Measured on the benchmark MLP at 65536 rows: the per-layer exact chain takes 67 us, the one-launch kernel
+     * in pair mode 93 us (a single 128-row tile runs its 13 + 32 k-blocks and six epilogues back to back), so the chain
+     * is the default; SPINGALETT_REPAIR=fused selects the other for comparisons. */
+    static int repair_fused = -1;
+    if (repair_fused < 0) { const char *e = getenv("SPINGALETT_REPAIR"); repair_fused = (e && strcmp(e, "fused") == 0) ? 1 : 0; }
+    if (fused && repair_fused && n->klayers[0].precision != PRECISION_FLOAT32) {
         /* files whose weights are exact in 16 bits: the flagged rows again through the same kernel, each as a
          * hi/lo pair of tile rows, written over their one-term results */
-        return fused_pass(n, d_x, N, d_out, true, n->d_rep_idx, d_count, expected, 0.0f, NULL, NULL);
+        if ((rc = fused_pass(n, d_x, N, d_out, true, n->d_rep_idx, d_count, expected, 0.0f, NULL, NULL))) return rc;
+        if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(h_slot, d_count, 4, n->stream), "repair count"))) return rc;
+        n->count_pending = true; n->count_seen = true;
+        return SPINGALETT_OK;
     }
     spgk_set_dynamic_rows(d_count, expected);
     dynamic_rows = true;
@@ -724,6 +733,8 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     spgk_set_dynamic_rows(NULL, 0);
     dynamic_rows = false;
     if (rc) return rc;
+    if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(h_slot, d_count, 4, n->stream), "repair count"))) return rc;
+    n->count_pending = true; n->count_seen = true;
     spg_note_path("tcgen05");
     return SPINGALETT_OK;
 }
