@@ -4,6 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
                     [--dtype int8] [--batch 65536] [--math exact|fast] [--all-dtypes]
 
+The default line also carries a `train` object: the data-parallel Adam training configuration at the same rank count.
+
 One "step" is one forward pass of the 784-512-1000-10 MLP (weights stored in
 the chosen .nn precision, INT8 by default) over one batch of 65536 synthetic
 U[0,1) rows per GPU.  Ranks are independent (weights replicated, rows sharded,
@@ -77,6 +79,7 @@ def parse():
     ap.add_argument("--all-dtypes", action="store_true", help="also report every stored precision (fewer steps each); on by default for the mlp workload")
     ap.add_argument("--one-dtype", action="store_true", help="skip the per-dtype table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-train", action="store_true", help="skip the training leg of the mlp workload")
     ap.add_argument("--train", action="store_true", help="secondary line: data-parallel Adam training steps (256 rows per GPU per step) instead of inference")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -320,6 +323,15 @@ def measure(spg, net, torch, x_dev, y_dev, x_pin, y_pin, batch, steps, warmup, d
         net.forward_batch_ptr(x_pin.data_ptr(), batch, y_pin.data_ptr())      # returns with the result on the host
     torch.cuda.synchronize()
     e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3) / e2e_steps
+    # the same call on ordinary (pageable) host arrays, which is what a C caller of the reference API passes
+    x_page, y_page = x_pin.numpy().copy(), np.empty_like(y_pin.numpy())
+    net.forward_batch_ptr(x_page.ctypes.data, batch, y_page.ctypes.data)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(2):
+        net.forward_batch_ptr(x_page.ctypes.data, batch, y_page.ctypes.data)
+    torch.cuda.synchronize()
+    measure.pageable_ms = reduce_max((time.perf_counter() - t0) * 1e3) / 2
     return dev_ms, e2e_ms, k_ms, k_cnt, launches, clk.summary()
 
 
@@ -392,6 +404,55 @@ def run_train(args):
     net.free()
 
 
+def train_leg(spg, torch, dist, rank, world, epochs):
+    """The training configuration at this rank count: MLP 784-512-1000-10 from the reference's generator stream, fp32, 256 rows
+    per GPU per step, cross-entropy, Adam lr 1e-3; with more than one rank the gradient is exchanged over NVLink every step.
+    One train() call of `epochs` epochs over 20*256 rows per rank (host arrays in, weights and optimiser state back to the
+    host at the end); device time of the call, max over ranks."""
+    lib = spg.lib()
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            host = np.zeros(128, np.uint8)
+            assert lib.spingalett_dist_unique_id(host.ctypes.data) == 0
+            uid.copy_(torch.from_numpy(host))
+        dist.broadcast(uid, 0)
+        host = uid.cpu().numpy()
+        assert lib.spingalett_dist_init(rank, world, host.ctypes.data) == 0
+    net = spg.Network.build(TOPO, [spg.abi.ACT_RELU, spg.abi.ACT_RELU, spg.abi.ACT_SOFTMAX], spg.abi.WEIGHT_INITIALIZATION_HE, seed=1234)
+    net.set_stream(torch.cuda.current_stream().cuda_stream)
+    steps = epochs * 20
+    rng = np.random.default_rng(100 + rank)
+    rows = 256 * 20
+    x = rng.random((rows, 784), dtype=np.float32)
+    tg = np.zeros((rows, 10), np.float32)
+    tg[np.arange(rows), rng.integers(0, 10, rows)] = 1.0
+    kw = dict(batch_size=256, strategy=spg.abi.STRATEGY_SMALL_BATCH, learning_rate=1e-3)
+    net.train(x[:256 * 8], tg[:256 * 8], epochs=1, **kw)                  # warm-up: allocations, communicator channels
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = spg.kernel_launches()
+    e0.record()
+    net.train(x, tg, epochs=epochs, **kw)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = spg.kernel_launches() - l0
+    if dist is not None:
+        tt = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+        lib.spingalett_dist_shutdown()
+    net.free()
+    return {"metric": "mlp_train_samples_per_sec", "value": 256 * steps * world / (ms * 1e-3), "unit": "samples/s",
+            "ms_per_step": ms / steps, "steps": steps, "world": world, "rows_per_gpu_per_step": 256, "dtype": "f32",
+            "gpu_launches": int(launches),
+            "collective": "gradient exchange of 924930 fp32 values per step over NVLink" if world > 1 else "none",
+            "note": "one train() call: host arrays in, weights and optimiser state back on the host at the end, inside the timed region"}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -453,22 +514,32 @@ def main():
                           else "the stored weights streamed every step (>= 136 MB) exceed the 126 MB L2; no explicit flush"),
                    "sharding": "rows across ranks, weights replicated, no collective"},
         "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": batch * topo[0] * 4, "d2h_bytes_per_step": batch * topo[-1] * 4},
+                "h2d_bytes_per_step": batch * topo[0] * 4, "d2h_bytes_per_step": batch * topo[-1] * 4,
+                "host_buffers": "pinned", "pageable_value": batch * world / (measure.pageable_ms * 1e-3),
+                "pageable_ms_per_step": measure.pageable_ms},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
-    if k_cnt and path_taken == "tcgen05":
+    if k_cnt and path_taken.startswith("tcgen05"):
+        fused = path_taken == "tcgen05-fused"
         flops = flops_per_sample(topo) * batch * args.steps      # algorithmic: 2*N*sum(in*out), one term per product
-        achieved = flops / (k_ms * 1e-3) / 1e12
+        k_ms_eff = min(k_ms, dev_ms * args.steps)                # event pairs around single launches cannot undercut the timed loop
+        achieved = flops / (k_ms_eff * 1e-3) / 1e12
         traffic = None
-        tpath = os.path.join(ROOT, "profiles", "gemm_tc_traffic.json")
+        tpath = os.path.join(ROOT, "profiles", "mlp3_fused_traffic.json" if fused else "gemm_tc_traffic.json")
         if os.path.exists(tpath):
             traffic = json.load(open(tpath)).get(f"{args.workload}_{args.dtype}_{args.math}_{batch}")
         line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                             "frac": achieved / pk["bf16_tflops"], "traffic": traffic,
-                            "kernel": "spg_gemm_tc_kernel", "launches": int(k_cnt), "kernel_ms_per_step": k_ms / args.steps,
+                            "kernel": "spg_mlp3_fused_kernel" if fused else "spg_gemm_tc_kernel",
+                            "launches": int(k_cnt), "kernel_ms_per_step": k_ms_eff / args.steps,
                             "peak_source": pk["source"] + " burst bf16", "tensor_passes_per_product": passes,
-                            "executed_frac": achieved * passes / pk["bf16_tflops"]}
+                            "executed_frac": achieved * passes / pk["bf16_tflops"],
+                            "whole_step_frac": flops / (dev_ms * args.steps * 1e-3) / 1e12 / pk["bf16_tflops"],
+                            "note": ("frac: the one launch per step that computes all three layers of all rows (event pair around it); "
+                                     "whole_step_frac: the same FLOPs over ms_per_step, which in AUTO also holds the exact "
+                                     "recomputation of the low-margin rows (per-layer kernels on a percent or two of the rows)")
+                                    if fused else "frac: summed device time of the layer kernels (event pairs); whole_step_frac: over ms_per_step"}
     elif k_cnt:
         nbytes = algorithmic_bytes(topo, args.dtype, batch)      # per step, all layers (one kernel launch per layer)
         achieved = nbytes * args.steps / (k_ms * 1e-3) / 1e9
@@ -477,7 +548,8 @@ def main():
         if os.path.exists(tpath):
             traffic = json.load(open(tpath)).get(f"{args.workload}_{args.dtype}_{batch}")
         line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                            "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "kernel": "spg_gemv_kernel",
+                            "frac": achieved / pk["hbm_gbs"], "traffic": traffic,
+                            "kernel": "spg_wstream_kernel" if path_taken == "wstream" else "spg_gemv_kernel",
                             "launches": int(k_cnt), "kernel_ms_per_step": k_ms / args.steps,
                             "algorithmic_bytes_per_step": nbytes, "peak_source": pk["source"] + " copy bandwidth",
                             "whole_step_frac": nbytes / (dev_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
@@ -492,6 +564,8 @@ def main():
             per[dt] = {"value": batch * world / (d_ms * 1e-3), "e2e": batch * world / (e_ms * 1e-3),
                        "kernel_tflops": ktf, "roofline_frac": (ktf / pk["bf16_tflops"]) if ktf else None}
         line["per_dtype"] = per
+    if args.workload == "mlp" and not args.no_train:
+        line["train"] = train_leg(spg, torch, dist, rank, world, max(40, args.steps * 2))
     if rank == 0 and world == 1 and not args.no_cpu:
         sample = min(batch, 16384 if args.workload == "mlp" else 64)
         cb = cpu_arm(path, x, 3, 1, sample)

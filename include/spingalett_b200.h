@@ -355,6 +355,16 @@ SPINGALETT_API int spingalett_dist_unique_id(void *id128);
 SPINGALETT_API int spingalett_dist_init(int rank, int world, const void *id128);
 SPINGALETT_API void spingalett_dist_shutdown(void);
 SPINGALETT_API int spingalett_dist_world(void);
+/* A data-parallel train() first makes sure that every rank is about to run the same loop (equal sample_count,
+ * batch_size, epochs, strategy, optimizer, callback / NaN-check intervals): otherwise the ranks would issue different
+ * numbers of gradient exchanges and one of them would wait for ever.  The check is a SUM over ranks of
+ * spingalett_dist_agreement_floats() floats written by spingalett_dist_pack_agreement; a rank whose
+ * spingalett_dist_check_agreement(summed, own, world) returns 0 refuses to train (SPINGALETT_ERR_INVALID).  During
+ * training the epoch's stop decision (callback, non-finite weights) is summed the same way, so all ranks stop together.
+ * The three functions are exported so that the check can be run over any transport. */
+SPINGALETT_API int spingalett_dist_agreement_floats(void);
+SPINGALETT_API void spingalett_dist_pack_agreement(const TrainArgs *args, float *out);
+SPINGALETT_API int spingalett_dist_check_agreement(const float *summed, const float *own, int world);
 
 /* Kernel timing for benchmarks: while enabled, the library brackets each
  * large-batch layer kernel with CUDA events on the net's stream;
@@ -365,7 +375,7 @@ SPINGALETT_API void spingalett_profile_read(NeuralNetwork *net, double *kernel_m
 
 /* Number of kernels this library has launched in the calling process, and the
  * name of the compute path the last batched/forward call took ("gemv",
- * "tcgen05", "simt").  For benchmarks and tests. */
+ * "wstream", "tcgen05", "tcgen05-fused" -- the three-layer net in one launch --, "simt").  For benchmarks and tests. */
 SPINGALETT_API uint64_t spingalett_kernel_launches(void);
 SPINGALETT_API const char *spingalett_last_path(void);
 

@@ -360,6 +360,22 @@ SPGK_API int spgk_train_output(const float *x, uint32_t ldx, const float *w, uin
 SPGK_API int spgk_adam(float *w, float *m, float *v, const float *g, uint64_t n, float lr, float b1, float b2,
                        float mf, float vf, float eps, float gscale, void *stream);
 SPGK_API int spgk_nonfinite(const float *w, uint64_t n, int *flag_dev, void *stream);
+/* spgk_output_delta: the output deltas the direct cross-entropy form does not cover (Training.c:357-376): mse_softmax != 0
+ *   gives delta_j = a_j*((a_j - t_j) - sum_k (a_k - t_k) a_k), otherwise delta_j = (a_j - t_j) * act'(a_j); if loss != NULL the
+ *   batch's summed loss is added to *loss: squared error (loss_ce == 0, SIMD.c:527-531) or -sum t*log(max(a, 1e-9))
+ *   (loss_ce != 0, SIMD.c:543-548).
+ * spgk_sumsq: *out_dev += sum g[i]^2 (global gradient norm, SIMD.c:496-507).
+ * spgk_optimizer_step: one fused pass of SGD (0), MOMENTUM (1), RMSPROP (2), ADAM (3) or ADAMW (4) over the flat buffer
+ *   [weights | biases] exactly as apply_gradients_batch_prescaled does it layer by layer (Training.c:439-507, SIMD.c:279-494):
+ *   weight decay acts on the first n_weights elements only (L2 term for SGD / MOMENTUM / RMSPROP / ADAM, decoupled for
+ *   ADAMW); g is scaled by gscale and, if sumsq_dev != NULL, clipped to max_norm by the global norm sqrt(*sumsq_dev)*gscale
+ *   (SIMD.c:509-518). */
+SPGK_API int spgk_output_delta(const float *a, const float *t, float *delta, uint32_t rows, uint32_t width, int act, int mse_softmax,
+                               int loss_ce, float *loss, void *stream);
+SPGK_API int spgk_sumsq(const float *g, uint64_t n, float *out_dev, void *stream);
+SPGK_API int spgk_optimizer_step(int kind, float *w, float *m, float *v, const float *g, uint64_t n, uint64_t n_weights,
+                                 float lr, float momentum, float b1, float b2, float mf, float vf, float eps, float decay,
+                                 float gscale, const float *sumsq_dev, float max_norm, void *stream);
 
 /* ---- gradient exchange: NCCL, loaded with dlopen at first use -----------------
  * One communicator per process (one process per GPU).  Rank 0 makes a 128-byte id with

@@ -137,7 +137,9 @@ class Network:
 
     def train(self, inputs, targets, *, epochs=1, batch_size=0, strategy=abi.STRATEGY_SMALL_BATCH,
               optimizer=abi.OPTIMIZER_ADAM, learning_rate=0.0, beta1=0.0, beta2=0.0, epsilon=0.0,
-              report_interval=0, reset_optimizer=False, nan_check_interval=0, callback=None, callback_interval=0):
+              report_interval=0, reset_optimizer=False, nan_check_interval=0, callback=None, callback_interval=0,
+              weight_decay=0.0, momentum=0.0, max_grad_norm=0.0, autosave_mode=0, autosave_interval=0, autosave_path=None,
+              autosave_precision=abi.PRECISION_FLOAT32, autosave_with_optimizer=True):
         """reference train(): MODE_ARRAY over host arrays [samples][in] / [samples][out]."""
         x, t = _as_f32(inputs), _as_f32(targets)
         args = abi.TrainArgs()
@@ -152,6 +154,11 @@ class Network:
         args.epochs = epochs
         args.learning_rate = learning_rate
         args.beta1, args.beta2, args.epsilon = beta1, beta2, epsilon
+        args.weight_decay, args.momentum, args.max_grad_norm = weight_decay, momentum, max_grad_norm
+        args.autosave_mode, args.autosave_interval = autosave_mode, autosave_interval
+        args.autosave_path = os.fsencode(autosave_path) if autosave_path else None
+        args.autosave_precision = autosave_precision
+        args.autosave_do_not_save_optimizer = not autosave_with_optimizer
         args.report_interval = report_interval
         args.reset_optimizer = reset_optimizer
         args.nan_check_interval = nan_check_interval

@@ -141,6 +141,7 @@ EXTENSION_SYMBOLS = [
     "spingalett_profile", "spingalett_profile_read", "spingalett_synchronize",
     "spingalett_set_auto_margin", "spingalett_get_auto_margin", "spingalett_last_repaired", "spingalett_net_margin",
     "spingalett_dist_unique_id", "spingalett_dist_init", "spingalett_dist_shutdown", "spingalett_dist_world",
+    "spingalett_dist_agreement_floats", "spingalett_dist_pack_agreement", "spingalett_dist_check_agreement",
 ]
 
 
@@ -174,6 +175,11 @@ def bind_extensions(lib):
     lib.spingalett_dist_init.restype = C.c_int
     lib.spingalett_dist_shutdown.restype = None
     lib.spingalett_dist_world.restype = C.c_int
+    lib.spingalett_dist_agreement_floats.restype = C.c_int
+    lib.spingalett_dist_pack_agreement.argtypes = [C.POINTER(TrainArgs), f32p]
+    lib.spingalett_dist_pack_agreement.restype = None
+    lib.spingalett_dist_check_agreement.argtypes = [f32p, f32p, C.c_int]
+    lib.spingalett_dist_check_agreement.restype = C.c_int
     lib.spingalett_synchronize.argtypes = [NetP]
     lib.spingalett_synchronize.restype = C.c_int
     lib.spingalett_profile.argtypes = [NetP, C.c_bool]

@@ -498,6 +498,96 @@ spg_adam_kernel(float *__restrict__ w, float *__restrict__ m, float *__restrict_
     }
 }
 
+
+// Output-layer delta for the combinations cross-entropy does not cover (reference Training.c:357-376), one warp per row:
+//   mse_softmax: delta_j = a_j * ((a_j - t_j) - sum_k (a_k - t_k) a_k)          (Training.c:357-367)
+//   otherwise:   delta_j = (a_j - t_j) * act'(a_j)                              (Training.c:373-375)
+// and, when loss is not null, the batch's summed loss: squared error (loss_ce == 0, SIMD.c:527-531) or cross-entropy
+// -sum t*log(max(a, 1e-9)) (loss_ce != 0 with an output activation other than softmax / sigmoid, SIMD.c:543-548).
+__global__ void __launch_bounds__(256)
+spg_output_delta_kernel(const float *__restrict__ a, const float *__restrict__ t, float *__restrict__ delta,
+                        uint32_t rows, uint32_t width, int act, int mse_softmax, int loss_ce, float *loss)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    float local = 0.0f;
+    for (uint32_t r = blockIdx.x * 8u + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8u) {
+        const float *ar = a + (uint64_t)r * width, *tr = t + (uint64_t)r * width;
+        float *dr = delta + (uint64_t)r * width;
+        float sum = 0.0f;
+        if (mse_softmax) {
+            for (uint32_t j = lane; j < width; j += 32u) sum += (ar[j] - tr[j]) * ar[j];
+            sum = spg_warp_sum(sum);
+        }
+        for (uint32_t j = lane; j < width; j += 32u) {
+            const float diff = ar[j] - tr[j];
+            dr[j] = mse_softmax ? ar[j] * (diff - sum) : diff * spg_derivative(ar[j], act);
+            if (loss) local += loss_ce ? -tr[j] * logf(fmaxf(ar[j], 1e-9f)) : diff * diff;
+        }
+    }
+    if (loss) {
+        local = spg_warp_sum(local);
+        if (lane == 0 && local != 0.0f) atomicAdd(loss, local);
+    }
+}
+
+// sum of squares of a flat buffer (for the global gradient norm, SIMD.c:496-507), added to *out
+__global__ void __launch_bounds__(256)
+spg_sumsq_kernel(const float *__restrict__ g, uint64_t n, float *out)
+{
+    float local = 0.0f;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) local = fmaf(g[i], g[i], local);
+    local = spg_warp_sum(local);
+    __shared__ float part[8];
+    if ((threadIdx.x & 31u) == 0) part[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        for (int i = 0; i < 8; i++) s += part[i];
+        atomicAdd(out, s);
+    }
+}
+
+// One fused pass of any of the reference's update rules over the flat parameter buffer [weights | biases]
+// (Training.c:439-507, SIMD.c:279-494).  The first n_w elements are weights (weight decay applies to them only),
+// the rest biases.  g is scaled first by gscale (1/ranks after a sum exchange) and, when sumsq is given, by the
+// global-norm clip factor max_norm / norm if norm > max_norm (SIMD.c:509-518; *sumsq holds the sum of squares of
+// the UNSCALED buffer).
+//   kind 0 SGD:      w -= lr * (g + decay*w)
+//   kind 1 MOMENTUM: m = mom*m + decay*w + g ; w -= lr*m
+//   kind 2 RMSPROP:  v = b2*v + (1-b2)*g*g ; w -= lr * (decay*w + g / sqrt(v + eps))
+//   kind 3 ADAM:     g += decay*w (weights) ; m, v as Adam ; w -= lr * (m*mf) / sqrt(v*vf + eps)
+//   kind 4 ADAMW:    m, v as Adam ; w = w*(1 - lr*decay) - lr * (m*mf) / sqrt(v*vf + eps)
+__global__ void __launch_bounds__(256)
+spg_optimizer_kernel(int kind, float *__restrict__ w, float *__restrict__ m, float *__restrict__ v, const float *__restrict__ g,
+                     uint64_t n, uint64_t n_w, float lr, float momentum, float b1, float b2, float mf, float vf, float eps,
+                     float decay, float gscale, const float *sumsq, float max_norm)
+{
+    float gs = gscale;
+    if (sumsq) {
+        const float norm = sqrtf(*sumsq) * gscale;
+        if (norm > max_norm) gs *= max_norm / norm;
+    }
+    const float omb1 = 1.0f - b1, omb2 = 1.0f - b2;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float d = i < n_w ? decay : 0.0f;
+        float gi = g[i] * gs, wi = w[i];
+        switch (kind) {
+            case 0: wi -= lr * fmaf(d, wi, gi); break;
+            case 1: { const float mi = fmaf(momentum, m[i], fmaf(d, wi, gi)); m[i] = mi; wi -= lr * mi; break; }
+            case 2: { const float vi = fmaf(b2, v[i], omb2 * (gi * gi)); v[i] = vi; wi -= lr * fmaf(d, wi, gi / sqrtf(vi + eps)); break; }
+            default: {
+                if (kind == 3) gi = fmaf(d, wi, gi);
+                const float mi = fmaf(b1, m[i], omb1 * gi);
+                const float vi = fmaf(b2, v[i], omb2 * (gi * gi));
+                m[i] = mi; v[i] = vi;
+                const float step = lr * ((mi * mf) / sqrtf(vi * vf + eps));
+                wi = kind == 4 && d > 0.0f ? wi * (1.0f - lr * d) - step : wi - step;
+            }
+        }
+        w[i] = wi;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 spg_nonfinite_kernel(const float *__restrict__ w, uint64_t n, int *flag)
 {
@@ -665,6 +755,40 @@ int spgk_adam(float *w, float *m, float *v, const float *g, uint64_t n, float lr
     if (n == 0) return SPGK_OK;
     spg_adam_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(w, m, v, g, n, lr, b1, b2, mf, vf, eps, gscale);
     return spgk_check_launch("spg_adam_kernel");
+}
+
+
+int spgk_output_delta(const float *a, const float *t, float *delta, uint32_t rows, uint32_t width, int act, int mse_softmax,
+                      int loss_ce, float *loss, void *stream)
+{
+    if (!a || !t || !delta || width == 0) { spgk_set_error("spgk_output_delta", "bad argument"); return SPGK_E_ARG; }
+    if (rows == 0) return SPGK_OK;
+    uint32_t blocks = (rows + 7u) / 8u;
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    spg_output_delta_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(a, t, delta, rows, width, act, mse_softmax, loss_ce, loss);
+    return spgk_check_launch("spg_output_delta_kernel");
+}
+
+int spgk_sumsq(const float *g, uint64_t n, float *out_dev, void *stream)
+{
+    if (!g || !out_dev) { spgk_set_error("spgk_sumsq", "bad argument"); return SPGK_E_ARG; }
+    if (n == 0) return SPGK_OK;
+    spg_sumsq_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(g, n, out_dev);
+    return spgk_check_launch("spg_sumsq_kernel");
+}
+
+int spgk_optimizer_step(int kind, float *w, float *m, float *v, const float *g, uint64_t n, uint64_t n_weights,
+                        float lr, float momentum, float b1, float b2, float mf, float vf, float eps, float decay,
+                        float gscale, const float *sumsq_dev, float max_norm, void *stream)
+{
+    if (!w || !g || kind < 0 || kind > 4 || (kind != 0 && kind != 2 && !m) || (kind >= 2 && !v) || n_weights > n) {
+        spgk_set_error("spgk_optimizer_step", "bad argument");
+        return SPGK_E_ARG;
+    }
+    if (n == 0) return SPGK_OK;
+    spg_optimizer_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(kind, w, m, v, g, n, n_weights, lr, momentum, b1, b2, mf, vf,
+                                                                         eps, decay, gscale, sumsq_dev, max_norm);
+    return spgk_check_launch("spg_optimizer_kernel");
 }
 
 int spgk_nonfinite(const float *w, uint64_t n, int *flag_dev, void *stream)

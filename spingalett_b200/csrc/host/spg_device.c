@@ -563,14 +563,14 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
             if (rc) return rc;
             break;
         }
-        prof_mark(n);
+        if (!dynamic_rows) prof_mark(n);                 /* the timing marks cover the full passes, not the repair of a few rows */
         if (last) spgk_set_output_rows(repair_rows);
         rc = spg_map_kernel_error(spgk_layer_gemm_tc(L, w16, ldw, w_plane, w_parts, type,
                                                      n->d_act16[l & 1], round8(L->in), plane, parts, type,
                                                      o16, round8(L->out), plane, parts, o32, L->out,
                                                      N, (last && fuse_sm) ? 1 : 0, n->d_status, n->stream), "layer (tcgen05)");
         spgk_set_output_rows(NULL);
-        prof_mark(n);
+        if (!dynamic_rows) prof_mark(n);
         if (rc) return rc;
         if (last && L->act == ACT_SOFTMAX && !fuse_sm &&
             (rc = spg_map_kernel_error(spgk_softmax_rows(d_out, L->out, N, L->out, n->stream), "softmax"))) return rc;
@@ -626,7 +626,8 @@ static int fused_pass(spg_net *n, const float *d_x, uint32_t N, float *d_out, bo
     prof_mark(n);
     if (rc) return rc;
     n->status_pending = true;
-    spg_note_path("tcgen05");
+    n->fused_ran = true;
+    spg_note_path("tcgen05-fused");
     return SPINGALETT_OK;
 }
 
@@ -662,7 +663,8 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
         spgk_set_margin_sink(0.0f, NULL, NULL);
     }
     if (rc) return rc;
-    if (strcmp(spingalett_last_path(), "tcgen05") != 0) return SPINGALETT_OK;      /* the fp32 chain ran: nothing to repair */
+    if (strncmp(spingalett_last_path(), "tcgen05", 7) != 0) return SPINGALETT_OK;  /* the fp32 chain ran: nothing to repair */
+    const bool fused_pass_ran = fused;
     theta = spingalett_get_auto_margin();
     if (theta <= 0.0f) {
         /* Self-calibration, once per device image of the net: run both modes on up to 2048 rows, measure the
@@ -735,7 +737,7 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     if (rc) return rc;
     if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(h_slot, d_count, 4, n->stream), "repair count"))) return rc;
     n->count_pending = true; n->count_seen = true;
-    spg_note_path("tcgen05");
+    spg_note_path(fused_pass_ran ? "tcgen05-fused" : "tcgen05");
     return SPINGALETT_OK;
 }
 

@@ -68,6 +68,7 @@ typedef struct {
     void **d_w16c[2]; uint8_t *w16c_parts[2];
     float *d_head_w;                       /* fp32 weights of a narrow last layer fused into the layer before it */
     float *d_fused_params;                 /* padded biases + head weights of the one-launch three-layer kernel */
+    bool fused_ran;                        /* the one-launch kernel has served this net at least once */
 
     float *h_out; size_t h_out_bytes;       /* library-owned pinned output buffer */
     float *h_stage; size_t h_stage_bytes;   /* pinned staging for forward() */
@@ -76,8 +77,11 @@ typedef struct {
     bool prof_on; void **prof_ev; uint32_t prof_cap, prof_used;
     double prof_ms; uint64_t prof_launches;
 
-    /* training state on the device (created by the first train() call) */
+    /* training state on the device (created by the first train() call, kept between calls) */
     void *train;
+    /* while a train() call runs: the flat device buffers [weights | biases] that hold the current parameters and
+     * optimiser moments; save_spingalett encodes from them instead of the (stale) host arrays */
+    const float *live_params, *live_m, *live_v;
 } spg_net;
 
 static inline spg_net *spg_priv(NeuralNetwork *n) { return (spg_net *)(void *)n; }
@@ -113,3 +117,4 @@ SPG_HIDDEN int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, f
 SPG_HIDDEN int spg_map_kernel_error(int rc, const char *where);
 /* train.c */
 SPG_HIDDEN void spg_train_release(spg_net *n);
+SPG_HIDDEN void spg_autosave(spg_net *n, const TrainArgs *a, size_t epoch);

@@ -173,9 +173,23 @@ static void dev_encoder_open(dev_encoder *de, uint32_t max_count)
 
 static void dev_encoder_close(dev_encoder *de) { spgk_free(de->d_src); spgk_free(de->d_dst); de->ok = false; }
 
-static bool write_array(FILE *f, const float *src, uint32_t count, PrecisionMode p, uint8_t *scratch, dev_encoder *de)
+/* dsrc != NULL: the array currently lives on the device (a train() call is running and these are its buffers): it is
+ * encoded there and only the file bytes come back; the host array `src` is stale then and not looked at. */
+static bool write_array(FILE *f, const float *src, const float *dsrc, uint32_t count, PrecisionMode p, uint8_t *scratch, dev_encoder *de)
 {
     size_t n = 0;
+    if (dsrc) {
+        if (p == PRECISION_FLOAT32) {
+            n = (size_t)count * 4;
+            if (spgk_memcpy_d2h(scratch, dsrc, n, NULL) || spgk_stream_sync(NULL)) return false;
+        } else {
+            if (!de || !de->d_dst) return false;
+            n = spgk_encoded_bytes(count, (int)p);
+            if (spgk_encode_array(dsrc, count, (int)p, de->d_dst, NULL) || spgk_memcpy_d2h(scratch, de->d_dst, n, NULL) ||
+                spgk_stream_sync(NULL)) return false;
+        }
+        return fwrite(scratch, 1, n, f) == n;
+    }
     if (de && de->ok && count >= SPG_DEV_ENCODE_MIN && p != PRECISION_FLOAT32) {
         n = spgk_encoded_bytes(count, (int)p);
         if (spgk_memcpy_h2d(de->d_src, src, (size_t)count * 4, NULL) || spgk_encode_array(de->d_src, count, (int)p, de->d_dst, NULL) ||
@@ -244,19 +258,32 @@ void save_spingalett_struct_arguments(SaveArgs a)
         free(scratch); free(zeros); fclose(f); free(path);
         return;
     }
+    /* inside a train() call (autosave, or a save from the caller's callback) the parameters and moments are the flat
+     * device buffers [weights | biases] of the trainer: encode straight from them */
+    spg_net *pn = spg_priv(n);
+    const float *lw = pn->live_params, *lm = pn->live_m, *lv = pn->live_v;
+    const uint64_t tw = n->total_weights;
     dev_encoder de;
     dev_encoder_open(&de, a.precision != PRECISION_FLOAT32 ? maxc : 0);
+    if (lw) {
+        /* the kernels of the step in flight must have finished before their buffers are read on the legacy stream */
+        if (spgk_set_device(pn->device) || spgk_stream_sync(pn->stream)) ok = false;
+        if (ok && a.precision != PRECISION_FLOAT32 && !de.d_dst) {
+            void *b = NULL;
+            if (spgk_malloc(&b, (size_t)maxc * 4 + 16) == 0) de.d_dst = b; else ok = false;
+        }
+    }
     for (uint32_t l = 0; l + 1 < n->layers && ok; l++) {
         uint32_t wc = n->topology[l] * n->topology[l + 1], bc = n->topology[l + 1];
         uint64_t wo = n->weight_offsets[l], bo = n->bias_offsets[l];
-        ok = write_array(f, n->weights + wo, wc, a.precision, scratch, &de);
+        ok = write_array(f, n->weights + wo, lw ? lw + wo : NULL, wc, a.precision, scratch, &de);
         if (ok && has_opt)
-            ok = write_array(f, zeros ? zeros : n->opt_m_weights + wo, wc, a.precision, scratch, &de) &&
-                 write_array(f, zeros ? zeros : n->opt_v_weights + wo, wc, a.precision, scratch, &de);
-        if (ok) ok = write_array(f, n->biases + bo, bc, a.precision, scratch, &de);
+            ok = write_array(f, zeros ? zeros : n->opt_m_weights + wo, lw ? lm + wo : NULL, wc, a.precision, scratch, &de) &&
+                 write_array(f, zeros ? zeros : n->opt_v_weights + wo, lw ? lv + wo : NULL, wc, a.precision, scratch, &de);
+        if (ok) ok = write_array(f, n->biases + bo, lw ? lw + tw + bo : NULL, bc, a.precision, scratch, &de);
         if (ok && has_opt)
-            ok = write_array(f, zeros ? zeros : n->opt_m_biases + bo, bc, a.precision, scratch, &de) &&
-                 write_array(f, zeros ? zeros : n->opt_v_biases + bo, bc, a.precision, scratch, &de);
+            ok = write_array(f, zeros ? zeros : n->opt_m_biases + bo, lw ? lm + tw + bo : NULL, bc, a.precision, scratch, &de) &&
+                 write_array(f, zeros ? zeros : n->opt_v_biases + bo, lw ? lv + tw + bo : NULL, bc, a.precision, scratch, &de);
     }
     dev_encoder_close(&de);
     free(scratch); free(zeros);

@@ -1,19 +1,26 @@
-/* train(): the mini-batch / full-batch training loop on the GPU.
+/* train(): the reference's training loop on the GPU.
  *
- * Control flow and argument handling follow the reference's batched trainer
- * (Src/Spingalett.Training.c:584-817): defaults for unset fields (:593-597), the
+ * Control flow and argument handling follow the reference's trainer
+ * (Src/Spingalett.Training.c:584-920): defaults for unset fields (:593-597), the
  * same validation and messages (:602-626), batch-size defaults (:628-631),
  * optional optimizer reset (:633-640), per-epoch shuffle with the library
  * generator and batches cut from the shuffled order (:748-767), gradients scaled
  * by 1/batch (:753), time_step and the running powers of beta advanced before
  * every update (:777-779; the powers restart at 1 on every call, :687-688), loss
- * reported as summed batch loss / sample_count (:784), NaN scan, callback.
+ * reported as summed batch loss / sample_count (:784), NaN scan (:788-793),
+ * autosave (:795-799, :536-578), callback (:801-806).
  *
- * What runs on the GPU here: MODE_ARRAY with STRATEGY_FULL_BATCH or
- * STRATEGY_SMALL_BATCH, OPTIMIZER_ADAM (no weight decay, no gradient clipping),
- * LOSS_CROSS_ENTROPY over a softmax or sigmoid output layer.  Anything else is
- * refused with SPINGALETT_ERR_INVALID -- there is no CPU trainer behind this
- * library.  Autosave is not implemented.
+ * Every combination the reference trains runs on the GPU: MODE_ARRAY with
+ * STRATEGY_FULL_BATCH, STRATEGY_SMALL_BATCH or STRATEGY_SAMPLE (one sample per
+ * update, in order, :78-250); SGD, MOMENTUM, RMSPROP, ADAM, ADAMW with weight decay
+ * (:439-507); global-norm gradient clipping for the batched strategies (:451-452);
+ * LOSS_MSE and LOSS_CROSS_ENTROPY with any output activation (:347-376).  There
+ * is no CPU trainer behind this library.
+ *
+ * The device buffers (parameters, optimiser moments, workspaces, the caller's
+ * samples) stay allocated between train() calls on the same net; save_spingalett
+ * called from inside a train() call (autosave, or the caller's callback) encodes
+ * straight from those device buffers.
  *
  * Data parallelism: after spingalett_dist_init() every process (one per GPU)
  * trains on its own samples; the flat gradient buffer [gW | gB] is summed across
@@ -21,6 +28,7 @@
  * number of ranks, so replicas stay bit-identical without a broadcast. */
 #include "spg_internal.h"
 #include <stdlib.h>
+#include <stdio.h>
 #include <string.h>
 
 typedef struct {
@@ -29,8 +37,9 @@ typedef struct {
     float *data_x, *data_t;                  /* the caller's samples, resident */
     float *batch_x, *batch_t;                /* gathered mini-batch */
     uint32_t *idx;
-    float *loss; int *flag;
-    uint32_t batch_cap; uint64_t data_rows;
+    float *words;                            /* [0] loss, [1] non-finite flag, [2] sum of squared gradients, [8..] rank agreement */
+    size_t cap[12];                          /* bytes held by each of the buffers above, in declaration order */
+    uint64_t np;                             /* parameters the flat buffers were sized for */
 } train_state;
 
 /* process-wide communicator for the gradient exchange */
@@ -79,27 +88,69 @@ void spingalett_dist_shutdown(void)
 
 int spingalett_dist_world(void) { return s_world; }
 
+/* grow-only device buffer number `slot` of the state */
+static int state_reserve(train_state *t, int slot, void **buf, size_t bytes, const char *what)
+{
+    if (*buf && t->cap[slot] >= bytes) return SPINGALETT_OK;
+    spgk_free(*buf); *buf = NULL; t->cap[slot] = 0;
+    int rc = spg_map_kernel_error(spgk_malloc(buf, bytes ? bytes : 256), what);
+    if (rc == SPINGALETT_OK) t->cap[slot] = bytes;
+    return rc;
+}
+
 static void state_free(train_state *t)
 {
     if (!t) return;
     void *bufs[] = { t->params, t->grads, t->m, t->v, t->acts, t->deltas, t->data_x, t->data_t, t->batch_x, t->batch_t,
-                     t->idx, t->loss, t->flag };
+                     t->idx, t->words };
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) spgk_free(bufs[i]);
     free(t);
 }
 
 void spg_train_release(spg_net *n)
 {
+    n->live_params = n->live_m = n->live_v = NULL;
     if (!n->train) return;
     if (n->device >= 0) spgk_set_device(n->device);
     state_free((train_state *)n->train);
     n->train = NULL;
 }
 
+/* same rule as the reference (Training.c:580-582) */
 static bool should_report(size_t epoch, size_t epochs, size_t interval)
 {
-    if (interval == 0) return false;
-    return epoch == 1 || epoch == epochs || epoch % interval == 0;
+    return interval > 0 && (epoch % interval == 0 || epoch == epochs);
+}
+
+/* ---- agreement between ranks ------------------------------------------------------------------
+ * Before a data-parallel train() every rank must be about to issue the same sequence of exchanges,
+ * or a rank is left waiting in a collective for ever.  Each rank packs what determines that sequence
+ * (sample count, batch size, epochs, strategy / optimiser / loss, intervals) into bytes, one float per
+ * byte plus its square; after a SUM over ranks every byte b must satisfy sum = world*b and sum of
+ * squares = world*b*b (equality holds only if all ranks hold the same byte; exact in fp32 up to 256
+ * ranks).  Exported so that the check can be exercised with any transport (the CPU tests use gloo). */
+#define SPG_AGREE_BYTES 40
+int spingalett_dist_agreement_floats(void) { return 2 * SPG_AGREE_BYTES; }
+
+void spingalett_dist_pack_agreement(const TrainArgs *a, float *out)
+{
+    uint8_t b[SPG_AGREE_BYTES];
+    memset(b, 0, sizeof b);
+    const uint64_t v[4] = { a->sample_count, a->batch_size, (uint64_t)a->epochs,
+                            (uint64_t)a->training_strategy | ((uint64_t)a->optimizer_type << 8) | ((uint64_t)(a->callback ? 1 : 0) << 16) |
+                            ((uint64_t)(a->max_grad_norm > 0.0f ? 1 : 0) << 17) };
+    memcpy(b, v, 32);
+    const uint32_t iv[2] = { (uint32_t)a->nan_check_interval, (uint32_t)(a->callback ? a->callback_interval : 0) };
+    memcpy(b + 32, iv, 8);
+    for (int i = 0; i < SPG_AGREE_BYTES; i++) { out[i] = (float)b[i]; out[SPG_AGREE_BYTES + i] = (float)b[i] * (float)b[i]; }
+}
+
+/* 1 if the summed buffer says every rank packed the same bytes as `mine` */
+int spingalett_dist_check_agreement(const float *summed, const float *mine, int world)
+{
+    for (int i = 0; i < 2 * SPG_AGREE_BYTES; i++)
+        if (summed[i] != mine[i] * (float)world) return 0;
+    return 1;
 }
 
 #define DEV(call, what) do { int rc__ = spg_map_kernel_error((call), what); if (rc__) goto fail; } while (0)
@@ -135,17 +186,13 @@ void train_struct_arguments(TrainArgs a)
             spg_log(LOG_ERROR, "Softmax in hidden layer %u is not supported. Use softmax only in the output layer.", l);
             return;
         }
-    const ActivationFunction out_act = p->act_func[p->layers - 2];
-    if ((a.training_strategy != STRATEGY_FULL_BATCH && a.training_strategy != STRATEGY_SMALL_BATCH) ||
-        a.optimizer_type != OPTIMIZER_ADAM || p->loss_func != LOSS_CROSS_ENTROPY ||
-        (out_act != ACT_SOFTMAX && out_act != ACT_SIGMOID) || a.weight_decay > 0.0f || a.max_grad_norm > 0.0f ||
-        a.autosave_mode != AUTOSAVE_OFF) {
-        spg_set_error(SPINGALETT_ERR_INVALID,
-                      "train: the CUDA trainer takes FULL_BATCH/SMALL_BATCH + ADAM + CROSS_ENTROPY over softmax/sigmoid "
-                      "(no weight decay, clipping or autosave); there is no CPU trainer in this library");
-        spg_log(LOG_ERROR, "train: unsupported combination for the CUDA trainer");
+    if ((unsigned)a.training_strategy > STRATEGY_SMALL_BATCH || (unsigned)a.optimizer_type > OPTIMIZER_ADAMW ||
+        (unsigned)p->loss_func > LOSS_CROSS_ENTROPY) {
+        spg_set_error(SPINGALETT_ERR_INVALID, "train: unknown strategy, optimizer or loss");
+        spg_log(LOG_ERROR, "train: unknown strategy, optimizer or loss");
         return;
     }
+    const ActivationFunction out_act = p->act_func[p->layers - 2];
     if (a.training_strategy == STRATEGY_SMALL_BATCH && a.batch_size == 0) a.batch_size = 32;
     if (a.training_strategy == STRATEGY_SMALL_BATCH && a.batch_size > a.sample_count) a.batch_size = a.sample_count;
 
@@ -161,39 +208,50 @@ void train_struct_arguments(TrainArgs a)
     }
     if (spg_dev_ensure(n) != SPINGALETT_OK) return;          /* binds the device (and validates it exists) */
 
-    const bool mini = a.training_strategy == STRATEGY_SMALL_BATCH;
-    const uint32_t batch = mini ? a.batch_size : a.sample_count;
+    /* STRATEGY_SAMPLE is a batch of one sample per update, in the caller's order (Training.c:894-897, :78-250) */
+    const bool mini = a.training_strategy == STRATEGY_SMALL_BATCH, online = a.training_strategy == STRATEGY_SAMPLE;
+    const uint32_t batch = mini ? a.batch_size : online ? 1u : a.sample_count;
     const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1], last = p->layers - 1;
     const uint64_t tw = p->total_weights, tb = p->total_biases, np = tw + tb, tn = p->total_neurons;
-    spg_log(LOG_INFO, "Starting training: loss=%s, strategy=%s, optimizer=ADAM, compute=CUDA, batch_size=%u, ranks=%d",
-            spg_loss_name(p->loss_func), mini ? "SMALL_BATCH" : "FULL_BATCH", batch, s_world);
+    static const char *const strat_names[] = { "SAMPLE", "FULL_BATCH", "SMALL_BATCH" };
+    static const char *const opt_names[] = { "SGD", "MOMENTUM", "RMSPROP", "ADAM", "ADAMW" };
+    spg_log(LOG_INFO, "Starting training: loss=%s, strategy=%s, optimizer=%s, compute=CUDA, batch_size=%u, ranks=%d",
+            spg_loss_name(p->loss_func), strat_names[a.training_strategy], opt_names[a.optimizer_type], batch, s_world);
 
-    spg_train_release(n);
-    train_state *t = calloc(1, sizeof *t);
-    if (!t) { spg_set_error(SPINGALETT_ERR_ALLOC, "train: state allocation failed"); return; }
-    n->train = t;
+    /* the device state of an earlier call is reused when it was made for the same parameter count */
+    train_state *t = (train_state *)n->train;
+    if (t && t->np != np) { spg_train_release(n); t = NULL; }
+    if (!t) {
+        t = calloc(1, sizeof *t);
+        if (!t) { spg_set_error(SPINGALETT_ERR_ALLOC, "train: state allocation failed"); return; }
+        t->np = np;
+        n->train = t;
+    }
     void *st = n->stream;
     uint32_t *order = NULL;
     float *h_pinned = NULL;
+    bool failed = true;
 
-    DEV(spgk_malloc((void **)&t->params, np * 4), "train: parameters");
-    DEV(spgk_malloc((void **)&t->grads, np * 4), "train: gradients");
-    DEV(spgk_malloc((void **)&t->m, np * 4), "train: adam m");
-    DEV(spgk_malloc((void **)&t->v, np * 4), "train: adam v");
-    DEV(spgk_malloc((void **)&t->acts, (size_t)batch * tn * 4), "train: activations");
-    DEV(spgk_malloc((void **)&t->deltas, (size_t)batch * tn * 4), "train: deltas");
-    DEV(spgk_malloc((void **)&t->data_x, (size_t)a.sample_count * in0 * 4), "train: inputs");
-    DEV(spgk_malloc((void **)&t->data_t, (size_t)a.sample_count * outw * 4), "train: targets");
-    DEV(spgk_malloc((void **)&t->loss, 256), "train: loss word");
-    DEV(spgk_malloc((void **)&t->flag, 256), "train: flag word");
+    if (state_reserve(t, 0, (void **)&t->params, np * 4, "train: parameters") || state_reserve(t, 1, (void **)&t->grads, np * 4, "train: gradients") ||
+        state_reserve(t, 2, (void **)&t->m, np * 4, "train: first moments") || state_reserve(t, 3, (void **)&t->v, np * 4, "train: second moments") ||
+        state_reserve(t, 4, (void **)&t->acts, (size_t)batch * tn * 4, "train: activations") ||
+        state_reserve(t, 5, (void **)&t->deltas, (size_t)batch * tn * 4, "train: deltas") ||
+        state_reserve(t, 6, (void **)&t->data_x, (size_t)a.sample_count * in0 * 4, "train: inputs") ||
+        state_reserve(t, 7, (void **)&t->data_t, (size_t)a.sample_count * outw * 4, "train: targets") ||
+        state_reserve(t, 11, (void **)&t->words, 1024, "train: status words")) goto fail;
     if (mini) {
-        DEV(spgk_malloc((void **)&t->batch_x, (size_t)batch * in0 * 4), "train: batch inputs");
-        DEV(spgk_malloc((void **)&t->batch_t, (size_t)batch * outw * 4), "train: batch targets");
-        DEV(spgk_malloc((void **)&t->idx, (size_t)a.sample_count * 4), "train: shuffle order");
+        if (state_reserve(t, 8, (void **)&t->batch_x, (size_t)batch * in0 * 4, "train: batch inputs") ||
+            state_reserve(t, 9, (void **)&t->batch_t, (size_t)batch * outw * 4, "train: batch targets")) goto fail;
+        if (state_reserve(t, 10, (void **)&t->idx, (size_t)a.sample_count * 4, "train: shuffle order")) goto fail;
         order = malloc((size_t)a.sample_count * sizeof *order);
         if (!order) { spg_set_error(SPINGALETT_ERR_ALLOC, "Mini-batch allocation failed"); goto fail; }
         for (uint32_t i = 0; i < a.sample_count; i++) order[i] = i;
     }
+    float *d_loss = t->words, *d_sumsq = t->words + 2, *d_agree = t->words + 8;
+    int *d_flag = (int *)(t->words + 1);
+    DEV(spgk_host_alloc((void **)&h_pinned, 1024), "train: pinned words");
+
+    /* the host arrays are the truth between calls (callers may edit them): upload them every time */
     DEV(spgk_memcpy_h2d(t->params, p->weights, tw * 4, st), "train: upload weights");
     DEV(spgk_memcpy_h2d(t->params + tw, p->biases, tb * 4, st), "train: upload biases");
     DEV(spgk_memcpy_h2d(t->m, p->opt_m_weights, tw * 4, st), "train: upload m");
@@ -203,13 +261,37 @@ void train_struct_arguments(TrainArgs a)
     DEV(spgk_memcpy_h2d(t->data_x, a.inputs, (size_t)a.sample_count * in0 * 4, st), "train: upload inputs");
     DEV(spgk_memcpy_h2d(t->data_t, a.targets, (size_t)a.sample_count * outw * 4, st), "train: upload targets");
     DEV(spgk_memset(t->grads, 0, np * 4, st), "train: clear gradients");
-    DEV(spgk_host_alloc((void **)&h_pinned, 256), "train: pinned word");
 
+    if (s_world > 1) {
+        /* all ranks must be about to run the same loop, or one of them waits in an exchange for ever */
+        float mine[2 * SPG_AGREE_BYTES];
+        spingalett_dist_pack_agreement(&a, mine);
+        memcpy(h_pinned, mine, sizeof mine);
+        DEV(spgk_memcpy_h2d(d_agree, h_pinned, sizeof mine, st), "train: agreement");
+        DEV(spgk_nccl_allreduce_sum(s_comm, d_agree, 2 * SPG_AGREE_BYTES, st), "train: agreement");
+        DEV(spgk_memcpy_d2h(h_pinned, d_agree, sizeof mine, st), "train: agreement");
+        DEV(spgk_stream_sync(st), "train: agreement");
+        if (!spingalett_dist_check_agreement(h_pinned, mine, s_world)) {
+            spg_set_error(SPINGALETT_ERR_INVALID, "train: the ranks disagree on sample_count, batch_size, epochs, strategy, optimizer or "
+                                                  "callback / check intervals; a data-parallel run needs them equal on every rank");
+            spg_log(LOG_ERROR, "train: ranks disagree on the training arguments");
+            goto fail;
+        }
+    }
+
+    /* save_spingalett called while this call runs (autosave, the callback) reads the device buffers */
+    n->live_params = t->params; n->live_m = t->m; n->live_v = t->v;
+
+    /* which output-layer path: cross-entropy over softmax / sigmoid has delta = a - t (Training.c:368-371) and, for at most
+       16 outputs, a one-launch output end; everything else goes through the general delta kernel */
+    const bool ce_direct = p->loss_func == LOSS_CROSS_ENTROPY && (out_act == ACT_SOFTMAX || out_act == ACT_SIGMOID);
+    const bool fused_out = ce_direct && outw <= 16;
+    const bool clip = a.max_grad_norm > 0.0f && !online;
     float b1pow = 1.0f, b2pow = 1.0f;
     for (size_t epoch = 1; epoch <= a.epochs; epoch++) {
         const bool need_loss = should_report(epoch, a.epochs, a.report_interval) ||
                                (a.callback && should_report(epoch, a.epochs, a.callback_interval));
-        if (need_loss) DEV(spgk_memset(t->loss, 0, 4, st), "train: clear loss");
+        if (need_loss) DEV(spgk_memset(d_loss, 0, 4, st), "train: clear loss");
         if (mini) {
             spg_shuffle(order, a.sample_count);
             DEV(spgk_memcpy_h2d(t->idx, order, (size_t)a.sample_count * 4, st), "train: upload order");
@@ -219,24 +301,21 @@ void train_struct_arguments(TrainArgs a)
         for (uint32_t bi = 0; bi < nb; bi++) {
             const uint32_t start = bi * batch;
             const uint32_t cur = start + batch > a.sample_count ? a.sample_count - start : batch;
-            const float *bx = t->data_x, *bt = t->data_t;
+            const float *bx = t->data_x + (size_t)(mini ? 0 : start) * in0, *bt = t->data_t + (size_t)(mini ? 0 : start) * outw;
             if (mini) {
                 DEV(spgk_gather_rows2(t->data_x, in0, t->batch_x, t->data_t, outw, t->batch_t, t->idx + start, cur, st),
                     "train: gather mini-batch");
                 bx = t->batch_x; bt = t->batch_t;
             }
-            /* forward: activations of layer l live at acts + cur*neuron_offsets[l], [cur][width].  An output layer of at
-               most 16 units is finished in one launch: product, softmax or sigmoid, delta and (when someone will read
-               it) the loss; otherwise product, softmax rows and the delta kernel follow one another */
+            /* forward: activations of layer l live at acts + cur*neuron_offsets[l], [cur][width] */
             float *d_last = t->deltas + (size_t)cur * p->neuron_offsets[last];
-            const bool fused_out = outw <= 16;
             const float *x = bx;
             for (uint32_t l = 0; l < last; l++) {
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 float *y = t->acts + (size_t)cur * p->neuron_offsets[l + 1];
                 if (l + 1 == last && fused_out) {
                     DEV(spgk_train_output(x, fi, t->params + p->weight_offsets[l], fi, t->params + tw + p->bias_offsets[l], y, bt,
-                                          d_last, need_loss ? t->loss : NULL, cur, fo, fi, out_act == ACT_SIGMOID, st),
+                                          d_last, need_loss ? d_loss : NULL, cur, fo, fi, out_act == ACT_SIGMOID, st),
                         "train: output layer");
                     break;
                 }
@@ -245,9 +324,16 @@ void train_struct_arguments(TrainArgs a)
                 if (p->act_func[l] == ACT_SOFTMAX) DEV(spgk_softmax_rows(y, fo, cur, fo, st), "train: softmax");
                 x = y;
             }
-            if (!fused_out)
-                DEV(spgk_ce_delta(t->acts + (size_t)cur * p->neuron_offsets[last], bt, d_last, (uint64_t)cur * outw,
-                                  need_loss ? t->loss : NULL, out_act == ACT_SIGMOID, st), "train: output delta");
+            if (!fused_out) {
+                const float *a_last = t->acts + (size_t)cur * p->neuron_offsets[last];
+                if (ce_direct)
+                    DEV(spgk_ce_delta(a_last, bt, d_last, (uint64_t)cur * outw, need_loss ? d_loss : NULL, out_act == ACT_SIGMOID, st),
+                        "train: output delta");
+                else
+                    DEV(spgk_output_delta(a_last, bt, d_last, cur, outw, (int)out_act,
+                                          p->loss_func == LOSS_MSE && out_act == ACT_SOFTMAX ? 1 : 0,
+                                          p->loss_func == LOSS_MSE ? 0 : 1, need_loss ? d_loss : NULL, st), "train: output delta");
+            }
             /* backwards through the layers: the gradients of layer l (from delta l+1 and activation l) go into the flat
                buffer and, with several replicas, start their all-reduce on the exchange stream at once, so that it runs
                under the delta and gradient products of the layers below */
@@ -281,37 +367,63 @@ void train_struct_arguments(TrainArgs a)
             b1pow *= a.beta1;
             b2pow *= a.beta2;
             const float mf = 1.0f / (1.0f - b1pow), vf = 1.0f / (1.0f - b2pow);
-            DEV(spgk_adam(t->params, t->m, t->v, t->grads, np, a.learning_rate, a.beta1, a.beta2, mf, vf, a.epsilon,
-                          1.0f / (float)s_world, st), "train: adam");
+            if (clip) {
+                DEV(spgk_memset(d_sumsq, 0, 4, st), "train: clear norm");
+                DEV(spgk_sumsq(t->grads, np, d_sumsq, st), "train: gradient norm");
+            }
+            if (a.optimizer_type == OPTIMIZER_ADAM && a.weight_decay <= 0.0f && !clip)
+                DEV(spgk_adam(t->params, t->m, t->v, t->grads, np, a.learning_rate, a.beta1, a.beta2, mf, vf, a.epsilon,
+                              1.0f / (float)s_world, st), "train: adam");
+            else
+                DEV(spgk_optimizer_step((int)a.optimizer_type, t->params, t->m, t->v, t->grads, np, tw, a.learning_rate, a.momentum,
+                                        a.beta1, a.beta2, mf, vf, a.epsilon, a.weight_decay > 0.0f ? a.weight_decay : 0.0f,
+                                        1.0f / (float)s_world, clip ? d_sumsq : NULL, a.max_grad_norm, st), "train: update");
         }
+        /* end of the epoch: loss, NaN scan and the stop decision.  With several ranks the loss is summed and a stop wanted
+           by any rank (its callback, a non-finite weight) stops all of them, so nobody is left in an exchange alone. */
+        const bool nan_now = a.nan_check_interval > 0 && epoch % a.nan_check_interval == 0;
+        const bool cb_now = a.callback && should_report(epoch, a.epochs, a.callback_interval);
         float current_error = 0.0f;
-        if (need_loss) {
-            DEV(spgk_memcpy_d2h(h_pinned, t->loss, 4, st), "train: read loss");
+        bool stop = false, nan_found = false;
+        if (nan_now) {
+            DEV(spgk_memset(d_flag, 0, 4, st), "train: clear flag");
+            DEV(spgk_nonfinite(t->params, np, d_flag, st), "train: nan scan");
+        }
+        if (need_loss || nan_now) {
+            DEV(spgk_memcpy_d2h(h_pinned, t->words, 8, st), "train: read loss");
             DEV(spgk_stream_sync(st), "train: loss sync");
-            current_error = h_pinned[0] / (float)a.sample_count;
+            current_error = need_loss ? h_pinned[0] / (float)a.sample_count : 0.0f;
+            nan_found = nan_now && ((int *)h_pinned)[1] != 0;
         }
         if (should_report(epoch, a.epochs, a.report_interval))
             spg_log(LOG_INFO, "Epoch: %zu/%zu, Error: %f", epoch, a.epochs, (double)current_error);
-        if (a.nan_check_interval > 0 && epoch % a.nan_check_interval == 0) {
-            DEV(spgk_memset(t->flag, 0, 4, st), "train: clear flag");
-            DEV(spgk_nonfinite(t->params, np, t->flag, st), "train: nan scan");
-            DEV(spgk_memcpy_d2h(h_pinned, t->flag, 4, st), "train: read flag");
-            DEV(spgk_stream_sync(st), "train: flag sync");
-            if (*(int *)h_pinned) {
-                spg_log(LOG_ERROR, "NaN/Inf detected in weights at epoch %zu, stopping training", epoch);
-                break;
-            }
+        if (nan_found) {
+            spg_log(LOG_ERROR, "NaN/Inf detected in weights at epoch %zu, stopping training", epoch);
+            stop = true;
         }
-        if (a.callback && should_report(epoch, a.epochs, a.callback_interval)) {
+        if (!stop && a.autosave_mode != AUTOSAVE_OFF && a.autosave_interval > 0 && a.autosave_path &&
+            should_report(epoch, a.epochs, a.autosave_interval) && s_rank == 0)
+            spg_autosave(n, &a, epoch);
+        if (!stop && cb_now) {
             /* the callback may read the net: bring the host mirror up to date first */
             DEV(spgk_memcpy_d2h(p->weights, t->params, tw * 4, st), "train: weights to host");
             DEV(spgk_memcpy_d2h(p->biases, t->params + tw, tb * 4, st), "train: biases to host");
             DEV(spgk_stream_sync(st), "train: callback sync");
             if (a.callback(p, epoch, current_error)) {
                 spg_log(LOG_INFO, "Training interrupted by callback at epoch %zu", epoch);
-                break;
+                stop = true;
             }
         }
+        if (s_world > 1 && (nan_now || cb_now)) {
+            h_pinned[16] = stop ? 1.0f : 0.0f;
+            DEV(spgk_memcpy_h2d(d_agree, h_pinned + 16, 4, st), "train: stop vote");
+            DEV(spgk_nccl_allreduce_sum(s_comm, d_agree, 1, st), "train: stop vote");
+            DEV(spgk_memcpy_d2h(h_pinned + 16, d_agree, 4, st), "train: stop vote");
+            DEV(spgk_stream_sync(st), "train: stop vote");
+            if (h_pinned[16] > 0.0f && !stop) spg_log(LOG_INFO, "Training stopped at epoch %zu because another rank stopped", epoch);
+            stop = h_pinned[16] > 0.0f;
+        }
+        if (stop) break;
     }
     /* host mirrors of everything the reference leaves in the public struct */
     DEV(spgk_memcpy_d2h(p->weights, t->params, tw * 4, st), "train: weights to host");
@@ -324,11 +436,35 @@ void train_struct_arguments(TrainArgs a)
     DEV(spgk_memcpy_d2h(p->opt_v_biases, t->v + tw, tb * 4, st), "train: v to host");
     DEV(spgk_stream_sync(st), "train: final sync");
     spg_log(LOG_INFO, "Training completed.");
+    failed = false;
 fail:
     free(order);
     spgk_host_free(h_pinned);
-    spg_train_release(n);
+    n->live_params = n->live_m = n->live_v = NULL;
+    if (failed) spg_train_release(n);          /* after an error nothing of the device state is trusted */
     /* the inference image on the device (possibly a packed payload) no longer matches the weights */
     spg_dev_invalidate(n);
     spg_net_drop_payload(n);
+}
+
+/* Autosave (Training.c:536-578): the same file naming as the reference -- AUTOSAVE_OVERWRITE writes autosave_path itself,
+ * AUTOSAVE_NEW_FILES inserts "_epoch_<n>" in front of the extension (or appends it when the name has none). */
+void spg_autosave(spg_net *n, const TrainArgs *a, size_t epoch)
+{
+    SaveArgs sa = { .net = &n->pub, .filename = a->autosave_path, .do_not_save_optimizer = a->autosave_do_not_save_optimizer,
+                    .precision = a->autosave_precision };
+    if (a->autosave_mode == AUTOSAVE_OVERWRITE) { save_spingalett_struct_arguments(sa); return; }
+    if (a->autosave_mode != AUTOSAVE_NEW_FILES) return;
+    const char *path = a->autosave_path;
+    const size_t len = strlen(path);
+    const char *dot = strrchr(path, '.'), *slash = strrchr(path, '/'), *back = strrchr(path, '\\');
+    const char *sep = slash && back ? (slash > back ? slash : back) : (slash ? slash : back);
+    const bool has_ext = dot && (!sep || dot > sep);
+    char *buf = malloc(len + 64);
+    if (!buf) return;
+    if (has_ext) snprintf(buf, len + 64, "%.*s_epoch_%zu%s", (int)(dot - path), path, epoch, dot);
+    else snprintf(buf, len + 64, "%s_epoch_%zu", path, epoch);
+    sa.filename = buf;
+    save_spingalett_struct_arguments(sa);
+    free(buf);
 }

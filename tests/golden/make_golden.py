@@ -23,6 +23,57 @@ from spingalett_b200 import abi  # noqa: E402
 PRECS = ["fp32", "fp16", "bf16", "int8", "int4", "int2"]
 
 
+# (name, strategy, optimizer, loss, output activation, weight decay, max_grad_norm, epochs, batch)
+TRAIN_CASES = [
+    ("sgd_decay", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_SGD, abi.LOSS_CROSS_ENTROPY, abi.ACT_SOFTMAX, 1e-3, 0.0, 6, 0),
+    ("momentum_decay", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_MOMENTUM, abi.LOSS_CROSS_ENTROPY, abi.ACT_SOFTMAX, 1e-3, 0.0, 6, 0),
+    ("rmsprop_decay", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_RMSPROP, abi.LOSS_CROSS_ENTROPY, abi.ACT_SOFTMAX, 1e-3, 0.0, 6, 0),
+    ("adam_decay", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_ADAM, abi.LOSS_CROSS_ENTROPY, abi.ACT_SOFTMAX, 1e-3, 0.0, 6, 0),
+    ("adamw_decay", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_ADAMW, abi.LOSS_CROSS_ENTROPY, abi.ACT_SOFTMAX, 1e-2, 0.0, 6, 0),
+    ("sgd_clip", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_SGD, abi.LOSS_CROSS_ENTROPY, abi.ACT_SOFTMAX, 0.0, 0.05, 6, 0),
+    ("mse_sigmoid_adamw", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_ADAMW, abi.LOSS_MSE, abi.ACT_SIGMOID, 1e-4, 0.0, 6, 0),
+    ("mse_softmax_sgd", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_SGD, abi.LOSS_MSE, abi.ACT_SOFTMAX, 0.0, 0.0, 6, 0),
+    ("ce_tanh_out_sgd", abi.STRATEGY_FULL_BATCH, abi.OPTIMIZER_SGD, abi.LOSS_CROSS_ENTROPY, abi.ACT_TANH, 0.0, 0.0, 4, 0),
+    ("sample_momentum", abi.STRATEGY_SAMPLE, abi.OPTIMIZER_MOMENTUM, abi.LOSS_MSE, abi.ACT_SIGMOID, 1e-3, 0.0, 2, 0),
+]
+
+
+def make_train_surface(R, L, rng):
+    """Final weights, biases and reported loss of the reference's train() for every update rule and output-delta form,
+    each starting from tests/golden/train.fp32.nn (output activation and loss overridden in the public struct) on the
+    batch stored in train.npz."""
+    d = np.load(os.path.join(HERE, "train.npz"))
+    x, t = np.ascontiguousarray(d["x"]), np.ascontiguousarray(d["t"])
+    out = {}
+    losses = {}
+
+    def on_epoch(net, epoch, err):
+        on_epoch.last = float(err)
+        return False
+    cb = abi.TrainCallback(on_epoch)
+    for name, strat, opt, loss, out_act, decay, clip, epochs, batch in TRAIN_CASES:
+        net = R.load(os.path.join(HERE, "train.fp32.nn"))
+        c = net.contents
+        c.act_func[c.layers - 2] = out_act
+        c.loss_func = loss
+        L.spingalett_set_compute_mode(abi.COMPUTE_OPENBLAS)
+        a = abi.TrainArgs()
+        a.net = net
+        a.training_strategy, a.optimizer_type = strat, opt
+        a.inputs, a.targets = x.ctypes.data, t.ctypes.data
+        a.sample_count, a.batch_size, a.epochs = x.shape[0], batch, epochs
+        a.learning_rate, a.weight_decay, a.max_grad_norm = 0.01, decay, clip
+        a.callback, a.callback_interval = cb, 1
+        L.train_struct_arguments(a)
+        assert L.spingalett_last_error_code() == 0, name
+        out[name + ".w"] = R.weights(net).copy()
+        out[name + ".b"] = R.biases(net).copy()
+        losses[name] = on_epoch.last
+        R.free(net)
+    L.spingalett_set_compute_mode(abi.COMPUTE_SINGLE_THREADED)
+    np.savez(os.path.join(HERE, "train_surface.npz"), **out, **{k + ".loss": np.float32(v) for k, v in losses.items()})
+
+
 def main():
     assert build_reference() is not None, "reference checkout not found"
     R = Reference
@@ -151,6 +202,10 @@ def main():
                  adam_m=m, adam_v=v, adam_w0=w0)
         L.spingalett_set_compute_mode(abi.COMPUTE_SINGLE_THREADED)
         R.free(net)
+
+    # -- the rest of the train() surface: one short run of the reference's own train() per update rule / loss ----------
+    if L.refh_has_blas():
+        make_train_surface(R, L, rng)
 
     with open(os.path.join(HERE, "golden.json"), "w") as f:
         json.dump(meta, f, indent=1)

@@ -1,6 +1,6 @@
 """Host-side pieces of the multi-process paths, run as two gloo ranks on the CPU: the id exchange
 used to set up the gradient communicator, row sharding of a batch across ranks, and the max-over-ranks
-reduction the benchmark uses for its timing."""
+reduction the benchmark uses for its timing, and the argument agreement a data-parallel train() begins with."""
 import os
 import subprocess
 import sys
@@ -37,6 +37,22 @@ WORKER = textwrap.dedent('''
         assert spg.lib().spingalett_dist_init(rank, world, t.numpy().ctypes.data) != 0
         spg.lib().spingalett_clear_error()
     assert spg.lib().spingalett_dist_init(0, 1, None) == 0 and spg.lib().spingalett_dist_world() == 1
+    # 5. the argument agreement a data-parallel train() starts with: equal arguments pass on every rank, a rank with a
+    #    different sample count makes every rank refuse (the sum over ranks is what NCCL computes on the GPU)
+    import ctypes as C
+    lib, a = spg.lib(), spg.abi
+    def packed(samples):
+        args = a.TrainArgs()
+        args.sample_count, args.batch_size, args.epochs = samples, 256, 10
+        args.training_strategy, args.optimizer_type = a.STRATEGY_SMALL_BATCH, a.OPTIMIZER_ADAM
+        buf = np.zeros(lib.spingalett_dist_agreement_floats(), np.float32)
+        lib.spingalett_dist_pack_agreement(C.byref(args), buf.ctypes.data_as(a.f32p))
+        return buf
+    for samples, agree in ((5120, 1), (5120 + rank, 0)):
+        mine = packed(samples)
+        summed = torch.from_numpy(mine.copy())
+        dist.all_reduce(summed)
+        assert lib.spingalett_dist_check_agreement(summed.numpy().ctypes.data_as(a.f32p), mine.ctypes.data_as(a.f32p), world) == agree
     dist.barrier()
     dist.destroy_process_group()
     print("HOST_DIST_OK", rank)
@@ -48,8 +64,12 @@ def test_two_gloo_ranks_host_logic(tmp_path):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     env = dict(os.environ, SPG_ROOT=root, CUDA_VISIBLE_DEVICES="")
+    import socket
+    with socket.socket() as sk:                     # a port nobody else on this machine is using right now
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29566", str(script)],
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                        capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("HOST_DIST_OK") == 2

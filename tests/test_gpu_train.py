@@ -133,26 +133,92 @@ def test_wide_and_narrow_output_layers_match_oracle_gradients(spg, oracle, outw,
     net.free()
 
 
-def test_unsupported_training_requests_are_refused(spg):
+def test_invalid_training_requests_are_refused(spg):
     lib, a = spg.lib(), spg.abi
     net = spg.Network.build([4, 3, 2], [a.ACT_RELU, a.ACT_SOFTMAX], a.WEIGHT_INITIALIZATION_HE, seed=1)
     x = np.zeros((4, 4), np.float32)
     t = np.zeros((4, 2), np.float32)
-    for kw in (dict(optimizer=a.OPTIMIZER_SGD), dict(strategy=a.STRATEGY_SAMPLE)):
-        with pytest.raises(spg.SpingalettError) as e:
-            net.train(x, t, epochs=1, **kw)
-        assert e.value.code == a.ERR_INVALID
     with pytest.raises(spg.SpingalettError):
         net.train(x, t, epochs=0)
-    mse = spg.Network.build([4, 2], [a.ACT_SIGMOID], a.WEIGHT_INITIALIZATION_HE, loss=a.LOSS_MSE, seed=1)
-    with pytest.raises(spg.SpingalettError):
-        mse.train(x, t, epochs=1, strategy=a.STRATEGY_FULL_BATCH)
+    with pytest.raises(spg.SpingalettError) as e:
+        net.train(x, t, epochs=1, optimizer=17)
+    assert e.value.code == a.ERR_INVALID
     hidden = spg.Network.build([4, 3, 2], [a.ACT_SOFTMAX, a.ACT_SOFTMAX], a.WEIGHT_INITIALIZATION_HE, seed=1)
     with pytest.raises(spg.SpingalettError) as e:                                      # Training.c:620-626
         hidden.train(x, t, epochs=1, strategy=a.STRATEGY_FULL_BATCH)
     assert "hidden" in str(e.value)
-    for n in (net, mse, hidden):
+    for n in (net, hidden):
         n.free()
+
+
+def _train_case_names():
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(os.path.dirname(golden("x")), "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.TRAIN_CASES
+
+
+@pytest.mark.parametrize("case", _train_case_names(), ids=lambda c: c[0])
+def test_every_update_rule_and_output_delta_matches_the_reference_run(spg, case):
+    """SGD / MOMENTUM / RMSPROP / ADAM / ADAMW with weight decay, global-norm clipping, MSE and MSE+softmax deltas, cross-entropy
+    over a non-softmax output, and per-sample training: final parameters and reported loss against the reference's own
+    train() on the same net and batch (tests/golden/train_surface.npz)."""
+    name, strat, opt, loss, out_act, decay, clip, epochs, batch = case
+    g, ref = np.load(golden("train.npz")), np.load(golden("train_surface.npz"))
+    net = spg.Network.load(golden("train.fp32.nn"))
+    c = net.c
+    c.act_func[c.layers - 2] = out_act
+    c.loss_func = loss
+    seen = {}
+
+    def cb(_net, epoch, err):
+        seen["loss"] = float(err)
+        seen["epochs"] = epoch
+        return False
+    net.train(g["x"], g["t"], epochs=epochs, batch_size=batch, strategy=strat, optimizer=opt, learning_rate=0.01,
+              weight_decay=decay, max_grad_norm=clip, callback=cb, callback_interval=1)
+    w, b = net.weights.copy(), net.biases.copy()
+    rw, rb = ref[name + ".w"], ref[name + ".b"]
+    # Adam-like rules move every weight by about lr per step whatever the gradient's size, so where a gradient is ~0 the
+    # summation order decides its sign; those few elements are judged by the norm, the rest element by element
+    tol = 2e-5 if opt in (spg.abi.OPTIMIZER_SGD, spg.abi.OPTIMIZER_MOMENTUM) else 2e-3
+    err = np.abs(np.concatenate([w - rw, b - rb]))
+    assert np.linalg.norm(err) <= 1e-3 * np.linalg.norm(np.concatenate([rw, rb])), (name, err.max())
+    assert np.quantile(err, 0.98) <= tol and err.max() <= 0.05, (name, err.max(), np.quantile(err, 0.98))
+    assert seen["epochs"] == epochs
+    assert abs(seen["loss"] - float(ref[name + ".loss"])) <= 2e-4 * max(1.0, abs(float(ref[name + ".loss"]))), (name, seen["loss"])
+    assert net.c.time_step == (epochs * g["x"].shape[0] if strat == spg.abi.STRATEGY_SAMPLE else epochs)
+    net.free()
+
+
+def test_autosave_writes_the_device_state_and_state_survives_calls(spg, oracle, tmp_path):
+    """AUTOSAVE_NEW_FILES / AUTOSAVE_OVERWRITE (Training.c:536-578): files named like the reference's, written from the
+    trainer's device buffers while train() runs; the last one equals what the net holds afterwards.  A second train() call
+    on the same net reuses the device state of the first."""
+    a = spg.abi
+    g = np.load(golden("train.npz"))
+    net = spg.Network.load(golden("train.fp32.nn"))
+    base = str(tmp_path / "ckpt.nn")
+    net.train(g["x"], g["t"], epochs=4, strategy=a.STRATEGY_FULL_BATCH, learning_rate=0.01, autosave_mode=2, autosave_interval=2,
+              autosave_path=base)                                                       # AUTOSAVE_NEW_FILES
+    names = sorted(p.name for p in tmp_path.iterdir())
+    assert names == ["ckpt_epoch_2.nn", "ckpt_epoch_4.nn"], names
+    last = oracle.OracleNet.from_file(str(tmp_path / "ckpt_epoch_4.nn"))
+    assert last.has_optimizer and last.time_step == 4
+    assert np.array_equal(last.weights, net.weights) and np.array_equal(last.biases, net.biases)
+    mid = oracle.OracleNet.from_file(str(tmp_path / "ckpt_epoch_2.nn"))
+    assert mid.time_step == 2 and not np.array_equal(mid.weights, net.weights)
+    # overwrite mode, quantised, without optimizer sections; then a second call on the same net
+    one = str(tmp_path / "one")
+    net.train(g["x"], g["t"], epochs=3, strategy=a.STRATEGY_FULL_BATCH, learning_rate=0.01, autosave_mode=1, autosave_interval=1,
+              autosave_path=one, autosave_precision=a.PRECISION_INT8, autosave_with_optimizer=False)   # AUTOSAVE_OVERWRITE
+    q = oracle.OracleNet.from_file(one + ".nn")                                          # ".nn" appended as save does
+    assert q.precision == a.PRECISION_INT8 and not q.has_optimizer and net.c.time_step == 7
+    want = oracle.Oracle.decode(oracle.Oracle.encode(net.weights[: 12 * 16], a.PRECISION_INT8), 12 * 16, a.PRECISION_INT8)
+    assert np.array_equal(q.weights[: 12 * 16], want)
+    net.free()
 
 
 def test_two_rank_data_parallel_step(spg, tmp_path):
@@ -166,7 +232,7 @@ def test_two_rank_data_parallel_step(spg, tmp_path):
     worker = os.path.join(os.path.dirname(__file__), "dist_train_worker.py")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29577", worker, str(tmp_path)],
+                        "--master-addr", "127.0.0.1", "--master-port", str(__import__("random").randint(20000, 39999)), worker, str(tmp_path)],
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "DIST_TRAIN_OK" in r.stdout
@@ -245,3 +311,19 @@ def test_training_products_match_float64(spg, rows, fi, fo):
     assert torch.equal(gw0, gw1)
     refb = gs * d.astype(np.float64).sum(axis=0)
     assert np.abs(gb.cpu().numpy() - refb).max() <= tol(refb)
+
+
+def test_a_c_program_written_against_the_public_header_trains_xor(spg, tmp_path):
+    """tests/c/xor_program.c (MSE loss, FOO52 + sigmoid, AdamW with weight decay, callback, save / load / forward through the
+    reference's macros) compiled with gcc against include/ and linked to the library: four OK lines, exit status 0."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "xor_program")
+    libdir = os.path.dirname(spg.LIB_PATH)
+    r = subprocess.run(["gcc", "-std=c2x", "-O1", "-I", os.path.join(root, "include"), os.path.join(root, "tests", "c", "xor_program.c"),
+                        "-o", exe, "-L", libdir, "-lspingalett", "-lm", "-Wl,-rpath," + libdir], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    run = subprocess.run([exe], capture_output=True, text=True, cwd=str(tmp_path), timeout=300)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert run.stdout.count("OK in=") == 4 and "passed 4/4, reloaded 4/4" in run.stdout

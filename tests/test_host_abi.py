@@ -284,3 +284,49 @@ def test_product_does_not_reach_for_the_oracle(spg):
     import subprocess
     deps = subprocess.run(["ldd", spg.LIB_PATH], capture_output=True, text=True).stdout
     assert "oracle" not in deps and "spingalett_ref" not in deps
+
+
+@pytest.mark.parametrize("example", ["XOR.c", "Benchmark.c"])
+def test_reference_examples_compile_unmodified_against_the_header(spg, tmp_path, example):
+    """Where a checkout of the reference is at hand, its example programs compile and link, unmodified, against include/ and
+    the library (they are run on a GPU by hand or by tests/c/xor_program.c's test; here only the build is checked)."""
+    import subprocess
+    src = os.path.join(os.environ.get("SPINGALETT_REFERENCE", "/root/reference"), "Examples", example)
+    if not os.path.exists(src):
+        pytest.skip("no checkout of the reference here")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.dirname(spg.LIB_PATH)
+    r = subprocess.run(["gcc", "-std=c2x", "-O1", "-I", os.path.join(root, "include"), src, "-o", str(tmp_path / "example"),
+                        "-L", libdir, "-lspingalett", "-lm", "-Wl,-rpath," + libdir], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+def test_rank_agreement_check_detects_any_differing_argument(spg):
+    """The data-parallel train() refuses to start unless every rank packed the same arguments: the packed bytes summed over
+    ranks must equal world times the own bytes (and likewise their squares)."""
+    import ctypes as C
+    lib, a = spg.lib(), spg.abi
+    n = lib.spingalett_dist_agreement_floats()
+
+    def pack(**kw):
+        args = a.TrainArgs()
+        args.sample_count, args.batch_size, args.epochs = 5120, 256, 100
+        args.training_strategy, args.optimizer_type = a.STRATEGY_SMALL_BATCH, a.OPTIMIZER_ADAM
+        for k, v in kw.items():
+            setattr(args, k, v)
+        buf = np.zeros(n, np.float32)
+        lib.spingalett_dist_pack_agreement(C.byref(args), buf.ctypes.data_as(a.f32p))
+        return buf
+    base = pack()
+    fp = lambda v: v.ctypes.data_as(a.f32p)
+    for world in (2, 3, 8):
+        assert lib.spingalett_dist_check_agreement(fp(base * world), fp(base), world) == 1
+    for kw in (dict(sample_count=5121), dict(batch_size=128), dict(epochs=101), dict(optimizer_type=a.OPTIMIZER_SGD),
+               dict(training_strategy=a.STRATEGY_FULL_BATCH), dict(nan_check_interval=3), dict(max_grad_norm=1.0)):
+        other = pack(**kw)
+        summed = base + other
+        assert lib.spingalett_dist_check_agreement(fp(summed), fp(base), 2) == 0, kw
+        assert lib.spingalett_dist_check_agreement(fp(summed), fp(other), 2) == 0, kw
+    # three ranks whose values average to the own value still fail (the squares do not)
+    lo, mid, hi = pack(sample_count=5119), pack(sample_count=5120), pack(sample_count=5121)
+    assert lib.spingalett_dist_check_agreement(fp(lo + mid + hi), fp(mid), 3) == 0
