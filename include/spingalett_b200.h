@@ -331,6 +331,14 @@ SPINGALETT_API float spingalett_net_margin(NeuralNetwork *net);
  * (default: the current device).  Returns 0 or an error code. */
 SPINGALETT_API int spingalett_set_device(int device);
 SPINGALETT_API int spingalett_get_device_count(void);
+/* Batch sharding over several GPUs of this process: after spingalett_set_devices(ids, n) with n >= 2, forward_batch
+ * calls with HOST input and output buffers cut the batch into n contiguous row shares (share g = rows
+ * [g*N/n, (g+1)*N/n), sizes differing by at most one: spingalett_split_rows) and run share g on device ids[g] from a
+ * replica of the weights there -- one host thread and one stream per device, weights replicated, no peer access and
+ * no collective.  n <= 1 switches it off; an id may be listed twice.  Device-pointer batches and batches of fewer than
+ * 2n rows run on the net's own device as before.  (No reference counterpart: its forward is CPU code.) */
+SPINGALETT_API int spingalett_set_devices(const int *ids, int n);
+SPINGALETT_API void spingalett_split_rows(uint32_t rows, uint32_t shares, uint32_t share, uint32_t *lo, uint32_t *hi);
 
 /* CUDA stream (a cudaStream_t passed as void*) on which this net's kernels
  * and copies are issued; NULL selects the legacy default stream. */

@@ -387,6 +387,29 @@ SPGK_API int spgk_nccl_allreduce_sum(void *comm, float *buf, uint64_t count, voi
 SPGK_API int spgk_nccl_allreduce_sum2(void *comm, float *buf_a, uint64_t count_a, float *buf_b, uint64_t count_b,
                                      void *stream);
 SPGK_API int spgk_nccl_destroy(void *comm);
+/* Failure handling of the exchange (all on the host; nothing here makes a GPU fault or hang):
+ * spgk_nccl_init waits for the rendezvous at most SPINGALETT_DIST_TIMEOUT_MS milliseconds (environment, default 120000) and
+ * returns SPGK_E_TIMEOUT when a rank never arrives; spgk_stream_sync_bounded waits for a stream by polling with the same
+ * limit, so an exchange whose peer has gone ends in SPGK_E_TIMEOUT instead of a blocked host thread, after which
+ * spgk_nccl_abort (ncclCommAbort) releases the communicator. */
+SPGK_API int spgk_stream_sync_bounded(void *stream);
+SPGK_API int spgk_nccl_abort(void *comm);
+
+/* ---- failure-path hooks (for tests; none of them faults, traps or hangs a GPU) ------------------
+ * spgk_fail_malloc_after(k): the k-th spgk_malloc from now returns SPGK_E_NOMEM (k <= 0 switches it off);
+ *   spgk_mem_info reads the device's free / total bytes, so a test can see that a failed call gave everything back.
+ * spgk_selftest_bounded_wait: launches one small kernel that waits on a barrier nobody arrives on with the kernels' own
+ *   bounded waits and `limit` attempts (<= 4096; each attempt may suspend the warp for 20 us); the kernel returns by itself,
+ *   status3[0] holds the wait's code, and the call returns SPGK_E_TIMEOUT exactly as a GEMM whose wait gave up does.
+ * spgk_selftest_timed_call: host only: a call that answers after answer_ms under the rendezvous timeout wrapper with a
+ *   limit of timeout_ms: 0 or SPGK_E_TIMEOUT.
+ * spgk_selftest_once_per_device: host only: the once-per-device bookkeeping of the launchers over `devices` fake indices and
+ *   `calls` rounds, device `fail_first` failing its first set-up: returns the number of set-ups that ran. */
+SPGK_API void spgk_fail_malloc_after(int k);
+SPGK_API int spgk_mem_info(size_t *free_bytes, size_t *total_bytes);
+SPGK_API int spgk_selftest_bounded_wait(int32_t *status3, uint32_t limit, void *stream);
+SPGK_API int spgk_selftest_timed_call(int answer_ms, int timeout_ms);
+SPGK_API int spgk_selftest_once_per_device(int devices, int calls, int fail_first);
 
 /* ---- K2 without allocations ----------------------------------------------
  * (No counterpart in the reference: it has no GPU code and no scratch memory.)
@@ -403,8 +426,12 @@ SPGK_API int spgk_nccl_destroy(void *comm);
  *     SPGK_NOALLOC_MAX_WEIGHT_BYTES; larger layers are refused with SPGK_E_ARG
  *     and a message naming both sizes.  FP16/BF16 payloads that TMA can read in
  *     place need no weight scratch at all.
- *   - The first call on each device looks up the array's device address; make
- *     that first call before starting any stream capture.
+ *   - The first call on each device looks up the array's device address.  With
+ *     CUDA's lazy module loading the array's memory is reserved when the
+ *     library's device code is first used on a device, not when the library is
+ *     loaded: make one warm-up call per device (or load modules eagerly) BEFORE
+ *     the caller's arena takes the remaining memory.  Every call waits for its
+ *     stream before it returns (it reads the status word back).
  *   - All calls share the one array and it keeps the previous call's contents
  *     (this function clears what has to start at zero), so two calls that
  *     overlap on the GPU -- different streams, different host threads -- race.

@@ -26,8 +26,15 @@ def build_oracle():
     return ORACLE_SO
 
 
-def build_reference(ref_root="/root/reference"):
+def reference_root():
+    """Where the reference checkout is looked for: $SPINGALETT_REFERENCE, else a directory named reference beside this
+    repository."""
+    return os.environ.get("SPINGALETT_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build_reference(ref_root=None):
     """Compile the reference where it lies; returns None when no checkout exists."""
+    ref_root = ref_root or reference_root()
     if not os.path.isdir(os.path.join(ref_root, "Src")):
         return REF_SO if os.path.exists(REF_SO) else None
     subprocess.run(["make", "-C", HERE, "ref", f"REF={ref_root}"], check=True, capture_output=True)

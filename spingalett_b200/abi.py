@@ -141,7 +141,7 @@ EXTENSION_SYMBOLS = [
     "spingalett_profile", "spingalett_profile_read", "spingalett_synchronize",
     "spingalett_set_auto_margin", "spingalett_get_auto_margin", "spingalett_last_repaired", "spingalett_net_margin",
     "spingalett_dist_unique_id", "spingalett_dist_init", "spingalett_dist_shutdown", "spingalett_dist_world",
-    "spingalett_dist_agreement_floats", "spingalett_dist_pack_agreement", "spingalett_dist_check_agreement",
+    "spingalett_set_devices", "spingalett_split_rows", "spingalett_dist_agreement_floats", "spingalett_dist_pack_agreement", "spingalett_dist_check_agreement",
 ]
 
 
@@ -154,6 +154,10 @@ def bind_extensions(lib):
     lib.spingalett_set_device.argtypes = [C.c_int]
     lib.spingalett_set_device.restype = C.c_int
     lib.spingalett_get_device_count.restype = C.c_int
+    lib.spingalett_set_devices.argtypes = [C.POINTER(C.c_int), C.c_int]
+    lib.spingalett_set_devices.restype = C.c_int
+    lib.spingalett_split_rows.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, u32p, u32p]
+    lib.spingalett_split_rows.restype = None
     lib.spingalett_set_stream.argtypes = [NetP, C.c_void_p]
     lib.spingalett_set_stream.restype = None
     lib.spingalett_sync_weights.argtypes = [NetP]

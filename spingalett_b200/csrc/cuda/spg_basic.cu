@@ -86,10 +86,26 @@ int spgk_device_info(int *cc, int *sm_count, size_t *total_mem)
     if (total_mem) *total_mem = p.totalGlobalMem;
     return SPGK_OK;
 }
+// test hook: the k-th device allocation from now fails as if the device were out of memory (k <= 0: off)
+static std::atomic<int> g_fail_malloc_in{0};
+void spgk_fail_malloc_after(int k) { g_fail_malloc_in.store(k > 0 ? k : 0); }
+
 int spgk_malloc(void **dev, size_t bytes)
 {
     *dev = nullptr;
+    if (g_fail_malloc_in.load(std::memory_order_relaxed) > 0 && g_fail_malloc_in.fetch_sub(1) == 1) {
+        spgk_set_error("cudaMalloc", "out of memory (injected by spgk_fail_malloc_after)");
+        return SPGK_E_NOMEM;
+    }
     SPGK_CUDA(cudaMalloc(dev, bytes ? bytes : 256));
+    return SPGK_OK;
+}
+int spgk_mem_info(size_t *free_bytes, size_t *total_bytes)
+{
+    size_t f = 0, t = 0;
+    SPGK_CUDA(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
     return SPGK_OK;
 }
 int spgk_free(void *dev) { if (dev) SPGK_CUDA(cudaFree(dev)); return SPGK_OK; }
@@ -237,8 +253,8 @@ spg_softmax_block_kernel(float *__restrict__ y, uint32_t ldy, uint32_t width)
     }
 }
 
-// Rows whose two largest outputs are closer than `theta` in log space (log p1 - log p2 < theta) are appended
-// to `idx` (order unspecified) and counted in *count.  One warp per row.
+// Rows whose two largest outputs are closer than `theta` in log space (log p1 - log p2 < theta), and rows with a
+// non-finite output, are appended to `idx` (order unspecified) and counted in *count.  One warp per row.
 __global__ void __launch_bounds__(256)
 spg_margin_select_kernel(const float *__restrict__ probs, uint32_t ldp, uint32_t N, uint32_t width, float theta,
                          uint32_t *__restrict__ idx, uint32_t *__restrict__ count)
@@ -247,8 +263,10 @@ spg_margin_select_kernel(const float *__restrict__ probs, uint32_t ldp, uint32_t
     if (row >= N) return;
     const float *r = probs + (uint64_t)row * ldp;
     float a = -FLT_MAX, b = -FLT_MAX;                          // largest, second largest seen by this lane
+    bool bad = false;                                          // a non-finite output: the one-term pass left the 16-bit range
     for (uint32_t i = lane; i < width; i += 32u) {
         const float v = r[i];
+        bad |= !(fabsf(v) <= FLT_MAX);
         if (v > a) { b = a; a = v; } else if (v > b) b = v;
     }
 #pragma unroll
@@ -256,7 +274,8 @@ spg_margin_select_kernel(const float *__restrict__ probs, uint32_t ldp, uint32_t
         const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
         if (oa > a) { b = fmaxf(a, ob); a = oa; } else b = fmaxf(b, oa);
     }
-    if (lane == 0 && b > 0.0f && logf(a) - logf(b) < theta) idx[atomicAdd(count, 1u)] = row;
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0 && (bad || (b > 0.0f && logf(a) - logf(b) < theta))) idx[atomicAdd(count, 1u)] = row;
 }
 
 // Largest change of the top-two log gap between two sets of row outputs: for every row, the two largest entries

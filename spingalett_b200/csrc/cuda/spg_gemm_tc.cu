@@ -342,7 +342,7 @@ __device__ __forceinline__ void epilogue_loop(const GemmParams &p, const RowLimi
                     const float inv = sum > 0.0f ? 1.0f / sum : 1.0f;
 #pragma unroll
                     for (int j = 0; j < HP; j++) z[j] *= inv;
-                    if (p.margin_idx && row < rows && p.head_out >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
+                    if (p.margin_idx && row < rows && p.head_out >= 2 && (!(mx - second >= p.margin_theta) || !(sum < FLT_MAX))) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
                 } else {
 #pragma unroll
                     for (int j = 0; j < HP; j++) z[j] = spg_activate(z[j], p.head_act);
@@ -387,8 +387,6 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, const RowL
                         if (v > mx) { second = mx; mx = v; } else if (v > second) second = v;
                     }
             }
-            // log p1 - log p2 of the softmax equals the gap of the two largest logits
-            if (p.margin_idx && row < rows && p.N >= 2 && mx - second < p.margin_theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
             for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
@@ -397,6 +395,9 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, const RowL
                 for (int i = 0; i < 16; i++)
                     if (c0 + i < p.N) sum += expf(fmaf(__uint_as_float(r[i]), p.scale, p.bias[c0 + i]) - mx);
             }
+            // log p1 - log p2 of the softmax equals the gap of the two largest logits; a row whose one-term pass left the
+            // 16-bit range (non-finite logits or sum) is listed as well
+            if (p.margin_idx && row < rows && p.N >= 2 && (!(mx - second >= p.margin_theta) || !(sum < FLT_MAX))) p.margin_idx[atomicAdd(p.margin_count, 1u)] = row;
             const float inv = sum > 0.0f ? 1.0f / sum : 1.0f;
             for (uint32_t c0 = 0; c0 < p.N; c0 += 16) {
                 uint32_t r[16];
@@ -851,6 +852,44 @@ int spgk_gemm_tc_status(int32_t *status, void *stream)
         return SPGK_E_TIMEOUT;
     }
     return SPGK_OK;
+}
+
+}  // extern "C"
+
+namespace {
+// A barrier nobody ever arrives on, waited for with the same bounded waits the tensor-core kernels use (no copy, no MMA and
+// no tensor memory involved): both give up after `limit` attempts, record their code, raise the abort flag and return.
+__global__ void spg_wait_selftest_kernel(int32_t *status, uint32_t limit)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); abort_flag = 0; spgtc::mbar_fence_init(); }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        // warp 0: the convergent-warp wait; its expiry raises the flag ...
+        mbar_wait_uniform(smem_u32(&bar), 0, smem_u32(&abort_flag), status, 41, limit);
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) {
+        // ... which the per-thread wait of warp 1 then finds up at once (it returns false without recording its own code)
+        const bool ok = spgtc::mbar_wait(smem_u32(&bar), 0, &abort_flag, status + 1, 42, limit);
+        if (threadIdx.x == 32) status[2] = ok ? 1 : 2;
+    }
+}
+}  // namespace
+
+extern "C" {
+
+// Failure-path check: makes a bounded device wait run out on purpose (the kernel returns normally; nothing faults) and
+// reports through the same status word and call the GEMM uses: SPGK_E_TIMEOUT with the wait's code in the message.
+int spgk_selftest_bounded_wait(int32_t *status3, uint32_t limit, void *stream)
+{
+    if (!status3 || limit == 0 || limit > 4096) { spgk_set_error("spgk_selftest_bounded_wait", "bad argument"); return SPGK_E_ARG; }
+    SPGK_CUDA(cudaMemsetAsync(status3, 0, 3 * sizeof(int32_t), (cudaStream_t)stream));
+    spg_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status3, limit);
+    int rc = spgk_check_launch("spg_wait_selftest_kernel");
+    if (rc) return rc;
+    return spgk_gemm_tc_status(status3, stream);
 }
 
 // ---------------------------------------------------------------------------------

@@ -43,18 +43,25 @@ namespace {
 constexpr uint32_t BM = 128;                    // slots per tile (UMMA M)
 constexpr uint32_t BK = 64;                     // K elements per operand tile: one 128-byte swizzle row
 constexpr uint32_t TILE_BYTES = BM * BK * 2;    // every operand tile here is [128 x 64] 16-bit = 16 KB
-constexpr uint32_t W_STAGES = 3, X_STAGES = 3, H1_TILES = 8;
+constexpr uint32_t W_STAGES = 3, H1_TILES = 8;
+constexpr uint32_t XF_STAGES = 2;                                     // fp32 input staging slots ([128 rows x 64 columns] = 32 KB each), in hidden tiles 0..3
+constexpr uint32_t X_PRIV = 2;                                        // 16-bit input tiles with a slot of their own
+constexpr uint32_t X_STAGES = X_PRIV + (H1_TILES - 1 - 2 * XF_STAGES); // plus hidden tiles 4..6, idle while layer 1's MMAs run (tile 7: head-sum exchange)
 constexpr uint32_t EPI_WARPS = 8, CVT_WARPS = 4;
 constexpr uint32_t EPI_WARP0 = 2, CVT_WARP0 = EPI_WARP0 + EPI_WARPS;
 constexpr uint32_t XPROD_WARP = CVT_WARP0 + CVT_WARPS;                // the input producer (TMA of fp32 input tiles)
 constexpr uint32_t NUM_THREADS = 32 * (XPROD_WARP + 1);               // 480: weight TMA, MMA, 8 epilogue, 4 converter warps, input TMA
-constexpr uint32_t XF_STAGES = 3;                                     // fp32 input staging slots ([128 rows x 64 columns] = 32 KB each)
 constexpr uint32_t XF_BYTES = BM * BK * 4;
 constexpr int CVT_ITEMS = 128 * 16 / (32 * CVT_WARPS);                // float4 loads per converter thread and input tile
-constexpr uint32_t SMEM_TILES = (H1_TILES + W_STAGES + X_STAGES) * TILE_BYTES;   // 224 KB
-constexpr uint32_t SMEM_BARS = 320;                                              // the mbarrier table, padded
+constexpr uint32_t SMEM_TILES = (H1_TILES + W_STAGES + X_PRIV) * TILE_BYTES;   // 208 KB
+// the head's 16-bit weights of one layer-2 chunk, [16 outputs][256 columns], rows 16 bytes apart in the banks (pitch 528)
+// so that the B-fragment reads of the warp-level MMA (8 rows x 4 words per instruction) are conflict-free; two buffers
+constexpr uint32_t HEAD_PITCH = 256 * 2 + 16, HEAD_BUF = 16 * HEAD_PITCH;
+constexpr uint32_t SMEM_HEAD = 2 * HEAD_BUF;
+constexpr uint32_t SMEM_BARS = 384;                                              // the mbarrier table, padded
 constexpr uint32_t SMEM_BIAS = 2 * 256 * 4;                                      // two chunks' biases (fp32), double-buffered
-constexpr uint32_t SMEM_TOTAL = SMEM_TILES + SMEM_BARS + SMEM_BIAS;
+constexpr uint32_t SMEM_TOTAL = SMEM_TILES + SMEM_HEAD + SMEM_BARS + SMEM_BIAS;
+static_assert(SMEM_TOTAL <= 232448, "more than the 227 KB a CTA can have");
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t MAX_N1 = H1_TILES * BK;      // the hidden operand of layer 2 must fit its 8 shared-memory tiles
 constexpr uint32_t ROW_INVALID = 0xFFFFFFFFu;
@@ -81,7 +88,7 @@ struct FusedParams {
 struct __align__(8) Bars {
     uint64_t w_full[W_STAGES], w_empty[W_STAGES], x_full[X_STAGES], x_empty[X_STAGES];
     uint64_t acc_full[2], acc_empty[2], h1_ready[H1_TILES], xchg_full[4];
-    uint64_t xf_full[XF_STAGES], xf_empty[XF_STAGES], h1_free;
+    uint64_t xf_full[XF_STAGES], xf_empty[XF_STAGES], h1_free, hb_full[2];
     uint32_t tmem_slot;
     int abort_flag;
 };
@@ -265,35 +272,20 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
 // One layer-2 chunk: this warp's 32 rows x 128 columns of the second hidden layer never leave the registers.  They are
 // read from tensor memory directly in the A-fragment layout of the warp-level MMA (tcgen05.ld 16x256b), get scale, bias
 // and activation, are rounded to 16 bits and multiplied into the head's sums with mma.sync.m16n8k16 against B fragments
-// of the head's weights (16-bit, [output][column], read from L1/L2).  hd[mt][nt][4]: the head's accumulator fragments of
+// of the head's weights (16-bit, [output][column]; this chunk's 256 columns are in shared memory, `hb`).  hd[mt][nt][4]: the head's accumulator fragments of
 // row tile mt (rows 16*mt + g, +8) and output tile nt (outputs 8*nt + 2t, +1).
-template <typename T16, int NT>
-__device__ __forceinline__ void load_bfrag(const T16 *head, uint32_t ld16, uint32_t col0, uint32_t g, uint32_t t, uint32_t (&bf)[2][NT][2])
-{
-#pragma unroll
-    for (int ks = 0; ks < 2; ks++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            const T16 *src = head + (size_t)(nt * 8 + g) * ld16 + col0 + ks * 16 + 2 * t;
-            bf[ks][nt][0] = __ldg(reinterpret_cast<const uint32_t *>(src));
-            bf[ks][nt][1] = __ldg(reinterpret_cast<const uint32_t *>(src + 8));
-        }
-}
-
 template <typename T16, int NT, bool PAIRS, bool RELU>
 __device__ __forceinline__ void epilogue_l2(const FusedParams &p, uint32_t c2, uint32_t taddr, uint32_t half, uint32_t lane,
-                                            float (&hd)[2][NT][4], const float *cbias)
+                                            float (&hd)[2][NT][4], const float *cbias, const uint8_t *hb)
 {
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t ld16 = p.nch2 * 256u;
-    const T16 *head = reinterpret_cast<const T16 *>(p.head16);
     const uint32_t cbase = c2 * 256u + half * 128u;
-    // B fragments of a 32-column block (two k-steps of 16), fetched one block ahead of their use; the accumulator rows of
-    // a block (two row tiles of 16) likewise come from tensor memory while the block before is worked on
-    uint32_t bf[2][NT][2], bf_next[2][NT][2];
+    // this lane's B-fragment words: output row g (+ 8 per output tile), columns half*128 + 2t.. of the chunk
+    const uint8_t *hlane = hb + g * HEAD_PITCH + (half * 128u + 2u * t) * 2u;
+    // the accumulator rows of a 32-column block (two row tiles of 16) come from tensor memory while the block before
+    // is worked on
     uint32_t r[2][16];
     if (cbase >= p.N2) return;
-    load_bfrag<T16, NT>(head, ld16, cbase, g, t, bf);
     tmem_ld_frag32(taddr, r[0]);
     tmem_ld_frag32(taddr + (16u << 16), r[1]);
 #pragma unroll 1
@@ -301,7 +293,6 @@ __device__ __forceinline__ void epilogue_l2(const FusedParams &p, uint32_t c2, u
         const uint32_t col0 = cbase + pc * 32u;
         if (col0 >= p.N2) break;
         const bool more = pc + 1 < 4 && col0 + 32u < p.N2;
-        if (more) load_bfrag<T16, NT>(head, ld16, col0 + 32u, g, t, bf_next);
         float2 bias[4];
 #pragma unroll
         for (int n = 0; n < 4; n++) bias[n] = *reinterpret_cast<const float2 *>(cbias + half * 128u + pc * 32u + 8 * n + 2 * t);
@@ -357,14 +348,13 @@ __device__ __forceinline__ void epilogue_l2(const FusedParams &p, uint32_t c2, u
                 a[mt][3] = pack2<T16>(v[mt][8 * ks + 6], v[mt][8 * ks + 7]);      // row g+8
             }
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+            for (int nt = 0; nt < NT; nt++) {
+                const uint8_t *src = hlane + nt * 8 * HEAD_PITCH + (pc * 32u + ks * 16u) * 2u;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(src), b1 = *reinterpret_cast<const uint32_t *>(src + 16);
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) mma_16816<T16>(hd[mt][nt], a[mt], bf[ks][nt][0], bf[ks][nt][1]);
+                for (int mt = 0; mt < 2; mt++) mma_16816<T16>(hd[mt][nt], a[mt], b0, b1);
+            }
         }
-#pragma unroll
-        for (int ks = 0; ks < 2; ks++)
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) { bf[ks][nt][0] = bf_next[ks][nt][0]; bf[ks][nt][1] = bf_next[ks][nt][1]; }
     }
     tmem_ld_wait();
 }
@@ -385,17 +375,25 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         if (threadIdx.x == 0) atomicCAS(p.status, 0, 9);
         return;
     }
-    Bars &bars = *reinterpret_cast<Bars *>(smem + SMEM_TILES);
-    float *bias_buf = reinterpret_cast<float *>(smem + SMEM_TILES + SMEM_BARS);
+    Bars &bars = *reinterpret_cast<Bars *>(smem + SMEM_TILES + SMEM_HEAD);
+    float *bias_buf = reinterpret_cast<float *>(smem + SMEM_TILES + SMEM_HEAD + SMEM_BARS);
+    uint8_t *head_buf = smem + SMEM_TILES;
     uint8_t *h1 = smem;                                        // [8] layer-2 A operand tiles (hidden layer 1, 16-bit)
-    const uint32_t h1_addr = base, wst_addr = base + H1_TILES * TILE_BYTES, xst_addr = wst_addr + W_STAGES * TILE_BYTES;
-    uint8_t *xst = smem + (H1_TILES + W_STAGES) * TILE_BYTES;
+    const uint32_t h1_addr = base, wst_addr = base + H1_TILES * TILE_BYTES;
+    // The 16-bit input tiles of layer 1: X_PRIV slots of their own, plus -- for rows in order -- the hidden tiles between
+    // the fp32 staging slots and the last one (the head-sum exchange), which hold nothing while layer 1's MMAs run: their
+    // contents come into being in layer 1's epilogue, after the last of those MMAs, and the next tile's input only
+    // arrives once the last layer-2 MMA has read them (h1_free; rows taken through a list are fetched by the converters
+    // ahead of that moment, so they wait for it themselves before a tile's first store).
+    constexpr uint32_t xfn = XF_STAGES, xn = X_STAGES;
+    auto x_stage_off = [&](uint32_t s) { return (s < X_PRIV ? H1_TILES + W_STAGES + s : 2u * XF_STAGES + (s - X_PRIV)) * TILE_BYTES; };
 
     const uint32_t w_full0 = smem_u32(bars.w_full), w_empty0 = smem_u32(bars.w_empty);
     const uint32_t x_full0 = smem_u32(bars.x_full), x_empty0 = smem_u32(bars.x_empty);
     const uint32_t acc_full0 = smem_u32(bars.acc_full), acc_empty0 = smem_u32(bars.acc_empty);
     const uint32_t h1_ready0 = smem_u32(bars.h1_ready), xchg_full0 = smem_u32(bars.xchg_full);
     const uint32_t xf_full0 = smem_u32(bars.xf_full), xf_empty0 = smem_u32(bars.xf_empty), h1_free0 = smem_u32(&bars.h1_free);
+    const uint32_t hb_full0 = smem_u32(bars.hb_full);
     volatile int *abort_flag = &bars.abort_flag;
 
     // the warp index through a shuffle: provably warp-uniform, so role code stays in uniform registers
@@ -417,6 +415,7 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         for (uint32_t a = 0; a < 4; a++) mbar_init(xchg_full0 + 8 * a, 1);
         for (uint32_t s = 0; s < XF_STAGES; s++) { mbar_init(xf_full0 + 8 * s, 1); mbar_init(xf_empty0 + 8 * s, CVT_WARPS); }
         mbar_init(h1_free0, 1);
+        for (uint32_t b = 0; b < 2; b++) mbar_init(hb_full0 + 8 * b, 1);
         bars.abort_flag = 0;
         mbar_fence_init();
         prefetch_map(&map_w1);
@@ -484,18 +483,18 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         // the whole warp walks the loops convergently (all operands of tcgen05.mma stay warp-uniform); one elected lane issues
         if (rank == 0) {
             const uint32_t fmt = std::is_same<T16, __half>::value ? 0u : 1u;
-            uint32_t it = 0, xit = 0, g = 0;
+            uint32_t ws = 0, wph = 0, xs = 0, xph = 0, g = 0;   // weight and input ring positions (slot, phase), chunk counter
+            const uint64_t w_desc0 = smem_desc_sw128(wst_addr);   // a slot further on adds its offset / 16 to the address field
             unsigned long long t_acc = 0, t_x = 0, t_h1 = 0, t_w = 0, t_issue = 0, t_commit = 0;
             const long long t_begin = TRACE ? clock64() : 0;
             // one k-block of MMAs: A tile at a_addr, this k-block's weight slot, accumulator `acc`, N = n
-            auto kblock = [&](uint32_t a_addr, uint32_t kdim, uint32_t kb, uint32_t acc, uint32_t n, bool x_done, bool acc_done, bool h1_done) {
-                const uint32_t s = it % W_STAGES;
-                uwait<TRACE>(w_full0 + 8 * s, (it / W_STAGES) & 1u, abort_addr, p.status, 5, tracing, t_w);
+            auto kblock = [&](uint32_t a_addr, uint32_t kdim, uint32_t kb, uint32_t acc, uint32_t idesc, bool x_done, bool acc_done, bool h1_done) {
+                const uint32_t s = ws;
+                uwait<TRACE>(w_full0 + 8 * s, wph, abort_addr, p.status, 5, tracing, t_w);
                 const uint32_t kleft = kdim - kb * BK;
                 const uint32_t ksteps = kleft >= BK ? BK / 16u : (kleft + 15u) / 16u;
                 const uint64_t da = smem_desc_sw128(a_addr);
-                const uint64_t db = smem_desc_sw128(wst_addr + s * TILE_BYTES);
-                const uint32_t idesc = idesc_f16_pair(fmt, fmt, n);
+                const uint64_t db = w_desc0 + (uint64_t)(s * (TILE_BYTES >> 4));
                 const uint32_t d = tmem_base + acc * 256u;
                 if (elect_one()) {
                     const long long t0 = (TRACE && tracing) ? clock64() : 0;
@@ -507,38 +506,39 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
                     }
                     const long long t1 = (TRACE && tracing) ? clock64() : 0;
                     umma_commit_pair(w_empty0 + 8 * s);              // both CTAs' weight slots are free once these MMAs have read them
-                    if (x_done) umma_commit_pair(x_empty0 + 8 * (xit % X_STAGES));
+                    if (x_done) umma_commit_pair(x_empty0 + 8 * xs);
                     if (acc_done) umma_commit_pair(acc_full0 + 8 * acc);
                     if (h1_done) umma_commit_pair(h1_free0);         // the hidden tiles may be overwritten (input staging of the next tile)
                     if (TRACE && tracing) { t_issue += (unsigned long long)(t1 - t0); t_commit += (unsigned long long)(clock64() - t1); }
                 }
                 __syncwarp();
-                it++;
+                if (++ws == W_STAGES) { ws = 0; wph ^= 1u; }
             };
+            const uint32_t idesc1[2] = {idesc_f16_pair(fmt, fmt, ((p.N1 < 256u ? p.N1 : 256u) + 31u) & ~31u),
+                                        idesc_f16_pair(fmt, fmt, ((p.N1 > 256u ? (p.N1 - 256u < 256u ? p.N1 - 256u : 256u) : 32u) + 31u) & ~31u)};
             for (uint32_t ti = 0; ti < ntile; ti++) {
                 // ---- layer 1: ONE pass over the input; chunk c accumulates in accumulator (g + c) & 1 (at most two chunks) ----
                 for (uint32_t c = 0; c < p.nch1; c++)
                     uwait<TRACE>(acc_empty0 + 8 * ((g + c) & 1u), (((g + c) >> 1) & 1u) ^ 1u, abort_addr, p.status, 2, tracing, t_acc);
                 tc_fence_after();
                 for (uint32_t kb = 0; kb < p.kb1; kb++) {
-                    const uint32_t xs = xit % X_STAGES;
-                    uwait<TRACE>(x_full0 + 8 * xs, (xit / X_STAGES) & 1u, abort_addr, p.status, 3, tracing, t_x);
-                    for (uint32_t c = 0; c < p.nch1; c++) {
-                        const uint32_t ncols = p.N1 - c * 256u < 256u ? p.N1 - c * 256u : 256u;
-                        kblock(xst_addr + xs * TILE_BYTES, p.K1, kb, (g + c) & 1u, (ncols + 31u) & ~31u, c + 1 == p.nch1, kb + 1 == p.kb1, false);
-                    }
-                    xit++;
+                    uwait<TRACE>(x_full0 + 8 * xs, xph, abort_addr, p.status, 3, tracing, t_x);
+                    const uint32_t a_addr = base + x_stage_off(xs);
+                    for (uint32_t c = 0; c < p.nch1; c++)
+                        kblock(a_addr, p.K1, kb, (g + c) & 1u, idesc1[c], c + 1 == p.nch1, kb + 1 == p.kb1, false);
+                    if (++xs == xn) { xs = 0; xph ^= 1u; }
                 }
                 g += p.nch1;
                 // ---- layer 2: chunk after chunk, the hidden tiles as A operand ----
                 for (uint32_t c = 0; c < p.nch2; c++, g++) {
                     const uint32_t ncols = p.N2 - c * 256u < 256u ? p.N2 - c * 256u : 256u;
                     const uint32_t acc = g & 1u;
+                    const uint32_t idesc2 = idesc_f16_pair(fmt, fmt, (ncols + 31u) & ~31u);
                     uwait<TRACE>(acc_empty0 + 8 * acc, ((g >> 1) & 1u) ^ 1u, abort_addr, p.status, 2, tracing, t_acc);
                     tc_fence_after();
                     for (uint32_t kb = 0; kb < p.kb2; kb++) {
                         if (c == 0) uwait<TRACE>(h1_ready0 + 8 * kb, ti & 1u, abort_addr, p.status, 4, tracing, t_h1);
-                        kblock(h1_addr + kb * TILE_BYTES, p.N1, kb, acc, (ncols + 31u) & ~31u, false, kb + 1 == p.kb2, c + 1 == p.nch2 && kb + 1 == p.kb2);
+                        kblock(h1_addr + kb * TILE_BYTES, p.N1, kb, acc, idesc2, false, kb + 1 == p.kb2, c + 1 == p.nch2 && kb + 1 == p.kb2);
                     }
                 }
             }
@@ -586,6 +586,17 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
                 const long long tb0 = tracing ? clock64() : 0;
                 asm volatile("bar.sync 1, %0;" ::"r"(32u * EPI_WARPS) : "memory");   // the epilogue warps only
                 if (tracing) t_bar += (unsigned long long)(clock64() - tb0);
+                // Every epilogue warp is past the chunk before: the head-weight buffer that chunk used is free.  When the
+                // chunk after this one is a layer-2 chunk, its 16 x 256 head weights are asked for now (16 bulk copies of
+                // 512 bytes, one per output row), a whole chunk ahead of their first use.
+                if (alive && warp == EPI_WARP0 && ch + 1 < nchunks && ch + 1 >= p.nch1) {
+                    const uint32_t c2n = ch + 1 - p.nch1, hidx = ti * p.nch2 + c2n, hbuf = hidx & 1u;
+                    if (lane == 0) mbar_expect_tx(hb_full0 + 8 * hbuf, 16u * 512u);
+                    __syncwarp();
+                    if (lane < 16)
+                        bulk_load(smem_u32(head_buf + hbuf * HEAD_BUF + lane * HEAD_PITCH),
+                                  reinterpret_cast<const uint8_t *>(p.head16) + ((size_t)lane * p.nch2 * 256u + c2n * 256u) * 2u, 512u, hb_full0 + 8 * hbuf);
+                }
                 // after a wait has given up the warp keeps walking its chunks (the named barrier above needs every epilogue
                 // warp every time) but does no more work: all later waits end at once
                 if (alive && !timed_wait(acc_full0 + 8 * acc, (g >> 1) & 1u, abort_flag, p.status, 6, tracing, t_full)) alive = false;
@@ -595,7 +606,11 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
                 const bool last = ch + 1 == nchunks;
                 const long long t_work = tracing ? clock64() : 0;
                 if (ch < p.nch1) epilogue_l1<T16, PAIRS, RELU>(p, ch, taddr, q, half, lane, h1, lead_h1_ready0, cbias);
-                else epilogue_l2<T16, NT, PAIRS, RELU>(p, ch - p.nch1, taddr, half, lane, hd, cbias);
+                else {
+                    const uint32_t hidx = ti * p.nch2 + (ch - p.nch1);
+                    if (!timed_wait(hb_full0 + 8 * (hidx & 1u), (hidx >> 1) & 1u, abort_flag, p.status, 13, tracing, t_full)) { alive = false; continue; }
+                    epilogue_l2<T16, NT, PAIRS, RELU>(p, ch - p.nch1, taddr, half, lane, hd, cbias, head_buf + (hidx & 1u) * HEAD_BUF);
+                }
                 if (tracing) { if (ch < p.nch1) t_l1 += (unsigned long long)(clock64() - t_work); else t_l2 += (unsigned long long)(clock64() - t_work); }
                 if (last) {
                     // the rows are complete: both warps of a quadrant lay their fragments out per row; the warp of the upper
@@ -650,7 +665,8 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
 #pragma unroll
                     for (int j = 0; j < HP; j++) z[j] *= inv;
                     // log p1 - log p2 of the softmax equals the gap of the two largest logits
-                    if (p.margin_idx && orow != ROW_INVALID && p.HO >= 2 && mx - second < p.theta) p.margin_idx[atomicAdd(p.margin_count, 1u)] = orow;
+                    // (a row whose one-term pass left the 16-bit range -- non-finite logits or sum -- is listed as well)
+                    if (p.margin_idx && orow != ROW_INVALID && p.HO >= 2 && (!(mx - second >= p.theta) || !(sum < FLT_MAX))) p.margin_idx[atomicAdd(p.margin_count, 1u)] = orow;
                 } else {
                     activate_block<HP>(z, p.act3);
                 }
@@ -669,9 +685,9 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
     } else if (warp == XPROD_WARP) {
         // ------------------------------ input producer (TMA) ------------------------------
         // While layer 1 of a tile runs, the hidden tiles in shared memory are idle (their next contents only come into being
-        // in layer 1's epilogue): the first 96 KB of that region serve as a three-slot ring of fp32 input tiles, filled by
-        // bulk-tensor copies that need no registers -- up to 96 KB of the input in flight per SM, which is what hides the
-        // latency of HBM at the rate layer 1 consumes it.  Rows addressed through a list take the converters' own loads instead.
+        // in layer 1's epilogue): the first 64 KB of that region serve as a two-slot ring of fp32 input tiles, filled by
+        // bulk-tensor copies that need no registers; the converters empty a slot into registers as soon as it lands, so the
+        // next copy is under way while they round and store.  Rows addressed through a list take the converters' own loads instead.
         if (!p.rows_idx) {
             uint32_t xfit = 0;
             for (uint32_t ti = 0; ti < ntile; ti++) {
@@ -679,8 +695,8 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
                 mbar_wait_uniform_cluster(h1_free0, (ti & 1u) ^ 1u, abort_addr, p.status, 10);
                 const uint32_t row0 = tile_row0(ti);
                 for (uint32_t kb = 0; kb < p.kb1; kb++, xfit++) {
-                    const uint32_t s = xfit % XF_STAGES;
-                    mbar_wait_uniform_cluster(xf_empty0 + 8 * s, ((xfit / XF_STAGES) & 1u) ^ 1u, abort_addr, p.status, 11);
+                    const uint32_t s = xfit % xfn;
+                    mbar_wait_uniform_cluster(xf_empty0 + 8 * s, ((xfit / xfn) & 1u) ^ 1u, abort_addr, p.status, 11);
                     if (elect_one()) {
                         mbar_expect_tx(xf_full0 + 8 * s, XF_BYTES);
                         tma_load_2d(h1_addr + s * XF_BYTES, &map_x, xf_full0 + 8 * s, (int)(kb * BK), (int)row0);
@@ -702,9 +718,9 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         const long long t_begin = clock64();
         // rounds, packs and writes one [128 x 64] A tile; arrives on the first CTA's barrier
         auto store_tile = [&](uint32_t step, const float4 (&buf)[CVT_ITEMS]) -> bool {
-            const uint32_t xs = step % X_STAGES;
-            if (!timed_wait(x_empty0 + 8 * xs, ((step / X_STAGES) & 1u) ^ 1u, abort_flag, p.status, 8, tracing, t_empty)) return false;
-            uint8_t *tile = xst + xs * TILE_BYTES;
+            const uint32_t xs = step % xn;
+            if (!timed_wait(x_empty0 + 8 * xs, ((step / xn) & 1u) ^ 1u, abort_flag, p.status, 8, tracing, t_empty)) return false;
+            uint8_t *tile = smem + x_stage_off(xs);
 #pragma unroll
             for (int j = 0; j < CVT_ITEMS; j++) {
                 const uint32_t slot = j * (2u * CVT_WARPS) + cw * 2u + sub;
@@ -725,9 +741,9 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
         if (!p.rows_idx) {
             // ---- rows in order: fp32 tiles arrive in the staging ring ----
             for (uint32_t step = 0; step < total; step++) {
-                const uint32_t s = step % XF_STAGES;
+                const uint32_t s = step % xfn;
                 const uint32_t ti = step / steps_per_tile;
-                if (!timed_wait(xf_full0 + 8 * s, (step / XF_STAGES) & 1u, abort_flag, p.status, 12, tracing, t_empty)) break;
+                if (!timed_wait(xf_full0 + 8 * s, (step / xfn) & 1u, abort_flag, p.status, 12, tracing, t_empty)) break;
                 const long long t_work = tracing ? clock64() : 0;
                 const float4 *stg = reinterpret_cast<const float4 *>(h1 + s * XF_BYTES);
                 const uint32_t row0 = tile_row0(ti);
@@ -778,7 +794,11 @@ spg_mlp3_fused_kernel(const __grid_constant__ CUtensorMap map_w1, const __grid_c
             };
             if (total) { prefetch_rows(0); prefetch_rows(1); issue(0); }
             for (uint32_t step = 0; step < total; step++) {
-                if (step % steps_per_tile == 0 && step) prefetch_rows(step / steps_per_tile + 1);
+                if (step % steps_per_tile == 0) {
+                    if (step) prefetch_rows(step / steps_per_tile + 1);
+                    // some input slots are hidden tiles: the tile before must be through its last layer-2 MMA
+                    if (!timed_wait(h1_free0, ((step / steps_per_tile) & 1u) ^ 1u, abort_flag, p.status, 14, tracing, t_empty)) break;
+                }
                 const long long t_work = tracing ? clock64() : 0;
                 if (!store_tile(step, buf)) break;
                 if (step + 1 < total) issue(step + 1);

@@ -27,10 +27,22 @@ __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier
 // Bounded wait on the phase with the given parity.  Once the abort flag is up every wait returns false at
 // once; when the bound is hit the flag is raised and `code` recorded in *status.
 // every try_wait may suspend the warp for up to this long; the iteration limits below count such attempts
+#ifndef SPG_WAIT_HINT_NS
 #define SPG_WAIT_HINT_NS 20000u
+#endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *status, int code,
                                           uint32_t limit = 1u << 16)
 {
+    {
+        // the common case: the phase is already complete (one plain attempt, no abort check, no time hint)
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
     if (*abort_flag) return false;
     for (uint32_t i = 0; i < limit; ++i) {
         uint32_t ok;
@@ -62,6 +74,8 @@ __device__ __forceinline__ void mbar_wait_uniform(uint32_t bar, uint32_t parity,
         "{\n\t"
         ".reg .pred p, q;\n\t"
         ".reg .u32 n, a;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "@p bra SPG_WAIT_DONE;\n\t"
         "mov.u32 n, 0;\n\t"
         "ld.volatile.shared.u32 a, [%2];\n\t"
         "setp.ne.u32 q, a, 0;\n\t"
@@ -85,8 +99,11 @@ __device__ __forceinline__ void mbar_wait_uniform(uint32_t bar, uint32_t parity,
         ::"r"(bar), "r"(parity), "r"(abort_flag_smem), "l"(status), "r"(code), "r"(limit), "r"(SPG_WAIT_HINT_NS) : "memory");
 }
 
-// The same for a barrier that the other CTA of a pair arrives on (acquire at cluster scope).  The abort flag is only
-// looked at every 16 failed attempts: the common case costs one try_wait.
+// The same for a barrier that the other CTA of a pair arrives on.  No thread reads what the other CTA's threads wrote:
+// the waiter only issues tensor-core or bulk-copy work that reads each CTA's own shared memory through the async
+// proxy, behind the writers' proxy fence and this barrier, so the default (CTA-scope) acquire is used, which measured
+// 30 cycles cheaper per call than the cluster-scope form.  The first attempt is a plain try_wait (21 cycles when the
+// phase is complete); the abort flag is only looked at every 16 failed attempts.
 __device__ __forceinline__ void mbar_wait_uniform_cluster(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem, int32_t *status, int code,
                                                           uint32_t limit = 1u << 16)
 {
@@ -94,9 +111,11 @@ __device__ __forceinline__ void mbar_wait_uniform_cluster(uint32_t bar, uint32_t
         "{\n\t"
         ".reg .pred p, q;\n\t"
         ".reg .u32 n, a;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n\t"
+        "@p bra SPG_WAITC_DONE;\n\t"
         "mov.u32 n, 0;\n\t"
         "SPG_WAITC_LOOP:\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%0], %1, %6;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1, %6;\n\t"
         "@p bra SPG_WAITC_DONE;\n\t"
         "add.u32 n, n, 1;\n\t"
         "and.b32 a, n, 15;\n\t"
@@ -131,6 +150,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// untiled bulk copy global -> this CTA's shared memory, completing on an mbarrier (16-byte aligned addresses and size)
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap *map) { asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory"); }
 
@@ -210,10 +235,13 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank)
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
     return r;
 }
-// arrive on a barrier that may live in the other CTA of the cluster (address from mapa)
+// arrive on a barrier that may live in the other CTA of the cluster (address from mapa).  Default semantics (release at
+// CTA scope): the arriving warp's shared-memory writes are in its own CTA's shared memory, fenced for the async proxy,
+// before the arrive leaves; the waiter reads them only through tensor-core instructions.  The cluster-scope release
+// measured 1300 cycles per arrive in this kernel, the default form 60.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // all threads of both CTAs
 __device__ __forceinline__ void cluster_sync()

@@ -13,8 +13,14 @@
 // needs and the elementwise work fused into its epilogue.
 #include "spg_common.cuh"
 #include <dlfcn.h>
+#include <chrono>
+#include <condition_variable>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <memory>
+#include <mutex>
+#include <thread>
 
 namespace {
 
@@ -606,6 +612,7 @@ struct NcclApi {
     int (*CommInitRank)(nccl_comm *, int, nccl_uid, int);
     int (*AllReduce)(const void *, void *, size_t, int, int, nccl_comm, cudaStream_t);
     int (*CommDestroy)(nccl_comm);
+    int (*CommAbort)(nccl_comm);
     int (*GroupStart)(void);
     int (*GroupEnd)(void);
     const char *(*GetErrorString)(int);
@@ -623,6 +630,7 @@ int nccl_load()
     g_nccl.CommInitRank = (int (*)(nccl_comm *, int, nccl_uid, int))dlsym(h, "ncclCommInitRank");
     g_nccl.AllReduce = (int (*)(const void *, void *, size_t, int, int, nccl_comm, cudaStream_t))dlsym(h, "ncclAllReduce");
     g_nccl.CommDestroy = (int (*)(nccl_comm))dlsym(h, "ncclCommDestroy");
+    g_nccl.CommAbort = (int (*)(nccl_comm))dlsym(h, "ncclCommAbort");
     g_nccl.GetErrorString = (const char *(*)(int))dlsym(h, "ncclGetErrorString");
     g_nccl.GroupStart = (int (*)(void))dlsym(h, "ncclGroupStart");
     g_nccl.GroupEnd = (int (*)(void))dlsym(h, "ncclGroupEnd");
@@ -810,17 +818,96 @@ int spgk_nccl_unique_id(void *id128)
     return SPGK_OK;
 }
 
+}  // extern "C"
+
+namespace {
+
+// Runs `fn` on a helper thread and waits for it at most timeout_ms.  A rendezvous that never completes (a rank that died
+// before it joined) must not hold the caller for ever: on expiry the caller gets SPGK_E_TIMEOUT and carries on; the
+// helper thread stays parked inside the call it cannot leave and is abandoned (it owns only its own heap block).
+struct TimedCall { std::mutex m; std::condition_variable cv; bool done = false; int rc = 0; };
+
+template <typename Fn>
+int run_with_timeout(Fn fn, int timeout_ms, const char *what)
+{
+    auto st = std::make_shared<TimedCall>();
+    std::thread([st, fn]() {
+        const int rc = fn();
+        std::lock_guard<std::mutex> g(st->m);
+        st->rc = rc; st->done = true;
+        st->cv.notify_all();
+    }).detach();
+    std::unique_lock<std::mutex> g(st->m);
+    if (!st->cv.wait_for(g, std::chrono::milliseconds(timeout_ms), [&] { return st->done; })) {
+        char msg[96];
+        snprintf(msg, sizeof msg, "no answer within %d ms (a rank that never joined?)", timeout_ms);
+        spgk_set_error(what, msg);
+        return SPGK_E_TIMEOUT;
+    }
+    return st->rc;
+}
+
+int dist_timeout_ms()
+{
+    const char *e = getenv("SPINGALETT_DIST_TIMEOUT_MS");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 ? v : 120000;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Host-only check of the timeout wrapper (no NCCL, no CUDA): a call that answers after answer_ms against a limit of
+// timeout_ms.  Returns what the wrapper returned (0, or SPGK_E_TIMEOUT).
+int spgk_selftest_timed_call(int answer_ms, int timeout_ms)
+{
+    return run_with_timeout([answer_ms]() -> int { std::this_thread::sleep_for(std::chrono::milliseconds(answer_ms)); return 0; },
+                            timeout_ms, "selftest");
+}
+
 int spgk_nccl_init(void **comm, int rank, int world, const void *id128)
 {
     int rc = nccl_load();
     if (rc) return rc;
     nccl_uid id;
     memcpy(&id, id128, sizeof id);
-    nccl_comm c = nullptr;
-    rc = nccl_check(g_nccl.CommInitRank(&c, world, id, rank), "ncclCommInitRank");
-    if (rc) return rc;
-    *comm = c;
+    int dev = 0;
+    SPGK_CUDA(cudaGetDevice(&dev));
+    auto slot = std::make_shared<nccl_comm>(nullptr);
+    // ncclCommInitRank blocks until every rank has arrived: bounded by SPINGALETT_DIST_TIMEOUT_MS (default 120 s)
+    rc = run_with_timeout([slot, world, id, rank, dev]() -> int {
+        if (cudaSetDevice(dev) != cudaSuccess) return -1;
+        return g_nccl.CommInitRank(slot.get(), world, id, rank);
+    }, dist_timeout_ms(), "ncclCommInitRank");
+    if (rc == SPGK_E_TIMEOUT) return rc;
+    if ((rc = nccl_check(rc, "ncclCommInitRank"))) return rc;
+    *comm = *slot;
     return SPGK_OK;
+}
+
+// Waits for the stream at most SPINGALETT_DIST_TIMEOUT_MS (polling, no blocking call): an exchange whose peer has gone
+// never finishes, and the caller then aborts the communicator instead of hanging.
+int spgk_stream_sync_bounded(void *stream)
+{
+    const auto t0 = std::chrono::steady_clock::now();
+    const int limit = dist_timeout_ms();
+    for (;;) {
+        const cudaError_t e = cudaStreamQuery((cudaStream_t)stream);
+        if (e == cudaSuccess) return SPGK_OK;
+        if (e != cudaErrorNotReady) { spgk_set_error("cudaStreamQuery", cudaGetErrorString(e)); return SPGK_E_CUDA; }
+        if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > limit) {
+            spgk_set_error("stream wait", "the gradient exchange did not finish in time (a rank has gone?)");
+            return SPGK_E_TIMEOUT;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+int spgk_nccl_abort(void *comm)
+{
+    if (!comm || !g_nccl.handle || !g_nccl.CommAbort) return SPGK_OK;
+    return nccl_check(g_nccl.CommAbort(comm), "ncclCommAbort");
 }
 
 int spgk_nccl_allreduce_sum(void *comm, float *buf, uint64_t count, void *stream)

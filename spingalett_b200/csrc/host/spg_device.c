@@ -8,6 +8,7 @@
  * on the general SIMT kernel -- still on the GPU; nothing here computes on
  * the CPU. */
 #include "spg_internal.h"
+#include <pthread.h>
 #include <stdlib.h>
 #include <math.h>
 #include <string.h>
@@ -39,12 +40,55 @@ int spingalett_get_device_count(void)
     return n;
 }
 
+/* ---- batch sharding over several GPUs of one process ------------------------------------------------
+ * spingalett_set_devices(ids, n): host-pointer batches of forward_batch are cut into n contiguous row shares
+ * ([g*N/n, (g+1)*N/n), sizes differing by at most one) and share g runs on device ids[g] from a replica of the
+ * net's weights there, one host thread per device, no peer access and no collective.  n <= 1 (or ids == NULL)
+ * switches it off.  An id may appear more than once (two replicas on one GPU). */
+#define SPG_MAX_FANOUT 16
+static int g_fan_ids[SPG_MAX_FANOUT];
+static int g_fan_n = 0;
+static pthread_mutex_t g_fan_lock = PTHREAD_MUTEX_INITIALIZER;
+
+int spingalett_set_devices(const int *ids, int n)
+{
+    int count = spingalett_get_device_count();
+    if (n < 0 || n > SPG_MAX_FANOUT || (n > 0 && !ids)) { spg_set_error(SPINGALETT_ERR_INVALID, "set_devices: bad list"); return SPINGALETT_ERR_INVALID; }
+    for (int i = 0; i < n; i++)
+        if (ids[i] < 0 || ids[i] >= count) { spg_set_errorf(SPINGALETT_ERR_INVALID, "set_devices: no device %d", ids[i]); return SPINGALETT_ERR_INVALID; }
+    pthread_mutex_lock(&g_fan_lock);
+    g_fan_n = n > 1 ? n : 0;
+    for (int i = 0; i < g_fan_n; i++) g_fan_ids[i] = ids[i];
+    pthread_mutex_unlock(&g_fan_lock);
+    return SPINGALETT_OK;
+}
+
+void spingalett_split_rows(uint32_t rows, uint32_t shares, uint32_t share, uint32_t *lo, uint32_t *hi)
+{
+    const uint32_t base = shares ? rows / shares : 0, extra = shares ? rows % shares : 0;
+    const uint32_t b = share * base + (share < extra ? share : extra);
+    if (lo) *lo = b;
+    if (hi) *hi = b + base + (share < extra ? 1u : 0u);
+}
+
 void spingalett_set_stream(NeuralNetwork *net, void *cuda_stream)
 {
     if (net) spg_priv(net)->stream = cuda_stream;
 }
 
-void spg_dev_invalidate(spg_net *n) { if (n->dev_ready) spg_dev_release(n); }
+static void shadows_release(spg_net *n)
+{
+    for (int g = 0; g < SPG_MAX_FANOUT; g++) {
+        spg_net *sh = n->shadow[g];
+        if (!sh) continue;
+        spg_dev_release(sh);
+        spgk_host_free(sh->h_out);
+        free(sh);
+        n->shadow[g] = NULL;
+    }
+}
+
+void spg_dev_invalidate(spg_net *n) { shadows_release(n); if (n->dev_ready) spg_dev_release(n); }
 
 static int bind_device(spg_net *n)
 {
@@ -65,6 +109,7 @@ static int bind_device(spg_net *n)
 
 void spg_dev_release(spg_net *n)
 {
+    if (!n->is_shadow) shadows_release(n);
     if (n->device >= 0) spgk_set_device(n->device);
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         if (n->d_w) spgk_free(n->d_w[l]);
@@ -745,12 +790,102 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
 /* batched inference entry point                                             */
 /* ------------------------------------------------------------------------ */
 
+static float *forward_batch_on(spg_net *n, ForwardBatchArgs a);
+
+/* a replica record for device `dev`: shares the host arrays and the packed payload of `n`, owns its device image */
+static spg_net *shadow_for(spg_net *n, int slot, int dev)
+{
+    spg_net *sh = n->shadow[slot];
+    if (sh && sh->device == dev) return sh;
+    if (sh) { spg_dev_release(sh); spgk_host_free(sh->h_out); free(sh); n->shadow[slot] = NULL; }
+    sh = calloc(1, sizeof *sh);
+    if (!sh) return NULL;
+    sh->pub = n->pub;
+    sh->magic = n->magic;
+    sh->is_shadow = true;
+    sh->store_precision = n->store_precision;
+    sh->payload_w = n->payload_w; sh->payload_w_bytes = n->payload_w_bytes; sh->amax_w = n->amax_w; sh->payload_layers = n->payload_layers;
+    sh->device = dev;
+    sh->auto_calibrated = n->auto_calibrated; sh->auto_theta = n->auto_theta;
+    n->shadow[slot] = sh;
+    return sh;
+}
+
+typedef struct { spg_net *net; ForwardBatchArgs args; int rc; char msg[SPG_ERRMSG_MAX]; } fan_job;
+
+static void *fan_worker(void *arg)
+{
+    fan_job *j = arg;
+    spingalett_clear_error();
+    j->rc = forward_batch_on(j->net, j->args) ? SPINGALETT_OK : spingalett_last_error_code();
+    if (j->rc) {                                  /* the error state is per thread: hand the text to the caller */
+        const char *m = spingalett_last_error_message();
+        strncpy(j->msg, m ? m : "", sizeof j->msg - 1);
+        if (j->rc == SPINGALETT_OK) j->rc = SPINGALETT_ERR_DEVICE;
+    }
+    return NULL;
+}
+
 float *forward_batch_struct_arguments(ForwardBatchArgs a)
 {
     NeuralNetwork *p = a.net;
     if (!p || !a.inputs) { spg_set_error(SPINGALETT_ERR_INVALID, "forward_batch: net or inputs is NULL"); return NULL; }
     if (p->layers < 2) { spg_set_error(SPINGALETT_ERR_INVALID, "Network must have at least 2 layers for forward pass"); return NULL; }
     spg_net *n = spg_priv(p);
+    int ids[SPG_MAX_FANOUT], G;
+    pthread_mutex_lock(&g_fan_lock);
+    G = g_fan_n;
+    memcpy(ids, g_fan_ids, sizeof ids);
+    pthread_mutex_unlock(&g_fan_lock);
+    const bool host_in = spgk_is_device_pointer(a.inputs) != 1, host_out = !a.outputs || spgk_is_device_pointer(a.outputs) != 1;
+    if (G < 2 || !host_in || !host_out || a.sample_count < 2u * (uint32_t)G) return forward_batch_on(n, a);
+
+    /* fan-out: one host thread per device, each on its own contiguous share of the rows */
+    const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1];
+    float *result = a.outputs;
+    if (!result) {
+        const size_t out_bytes = (size_t)a.sample_count * outw * sizeof(float);
+        if (n->h_out_bytes < out_bytes || !n->h_out) {
+            spgk_host_free(n->h_out); n->h_out = NULL; n->h_out_bytes = 0;
+            void *h = NULL;
+            if (spg_map_kernel_error(spgk_host_alloc(&h, out_bytes), "forward_batch: output buffer")) return NULL;
+            n->h_out = h; n->h_out_bytes = out_bytes;
+        }
+        result = n->h_out;
+    }
+    fan_job jobs[SPG_MAX_FANOUT];
+    pthread_t th[SPG_MAX_FANOUT];
+    bool started[SPG_MAX_FANOUT] = { false };
+    int failed = SPINGALETT_OK;
+    const char *why = NULL;
+    for (int g = 0; g < G; g++) {
+        uint32_t lo, hi;
+        spingalett_split_rows(a.sample_count, (uint32_t)G, (uint32_t)g, &lo, &hi);
+        /* share 0 runs on the net's own record when that is (or can be) bound to the first device of the list */
+        spg_net *target = (g == 0 && (n->device < 0 || n->device == ids[0])) ? n : shadow_for(n, g, ids[g]);
+        if (!target) { failed = SPINGALETT_ERR_ALLOC; why = "forward_batch: replica allocation failed"; break; }
+        if (target == n && n->device < 0) n->device = ids[0];
+        jobs[g] = (fan_job){ .net = target, .rc = 0,
+                             .args = { .net = &target->pub, .inputs = a.inputs + (size_t)lo * in0, .sample_count = hi - lo,
+                                       .outputs = result + (size_t)lo * outw } };
+        jobs[g].msg[0] = 0;
+        if (pthread_create(&th[g], NULL, fan_worker, &jobs[g]) != 0) { failed = SPINGALETT_ERR_ALLOC; why = "forward_batch: thread creation failed"; break; }
+        started[g] = true;
+    }
+    for (int g = 0; g < G; g++) {
+        if (!started[g]) continue;
+        pthread_join(th[g], NULL);
+        if (jobs[g].rc && !failed) { failed = jobs[g].rc; why = jobs[g].msg; }
+    }
+    if (n->device >= 0) spgk_set_device(n->device);
+    if (failed) { spg_set_errorf(failed, "forward_batch (device fan-out): %s", why ? why : "failed"); return NULL; }
+    spg_note_path("fan-out");
+    return result;
+}
+
+static float *forward_batch_on(spg_net *n, ForwardBatchArgs a)
+{
+    NeuralNetwork *p = &n->pub;
     const uint32_t N = a.sample_count;
     const uint32_t in0 = p->topology[0], outw = p->topology[p->layers - 1];
     if (spg_dev_ensure(n) != SPINGALETT_OK) return NULL;

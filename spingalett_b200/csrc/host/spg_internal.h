@@ -20,7 +20,7 @@
 #define SPG_NET_MAGIC 0x4E475053u /* "SPGN" */
 #define SPG_HIDDEN __attribute__((visibility("hidden")))
 
-typedef struct {
+typedef struct spg_net_s {
     NeuralNetwork pub;          /* MUST stay first: &net->pub == (NeuralNetwork *)net */
     uint32_t magic;
 
@@ -76,6 +76,11 @@ typedef struct {
     /* optional kernel timing (spingalett_profile): event pairs around the layer kernels */
     bool prof_on; void **prof_ev; uint32_t prof_cap, prof_used;
     double prof_ms; uint64_t prof_launches;
+
+    /* replicas of the device image on other GPUs (spingalett_set_devices): records that share this net's host arrays and
+     * packed payload and own only their device side; slot g serves share g of a batch */
+    struct spg_net_s *shadow[16];
+    bool is_shadow;
 
     /* training state on the device (created by the first train() call, kept between calls) */
     void *train;

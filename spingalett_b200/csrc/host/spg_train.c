@@ -153,6 +153,23 @@ int spingalett_dist_check_agreement(const float *summed, const float *mine, int 
     return 1;
 }
 
+/* Waiting for the stream inside train(): with several ranks the wait is bounded (SPINGALETT_DIST_TIMEOUT_MS), because an
+ * exchange whose peer has left never finishes; when the limit is hit the communicator is aborted, so that this rank's
+ * process can go on (and report the error) instead of hanging. */
+static int train_sync(void *st)
+{
+    if (s_world <= 1) return spgk_stream_sync(st);
+    const int rc = spgk_stream_sync_bounded(st);
+    if (rc == SPGK_E_TIMEOUT && s_comm) {
+        spg_log(LOG_ERROR, "train: the gradient exchange timed out; aborting the communicator");
+        spgk_nccl_abort(s_comm);
+        s_comm = NULL;
+        dist_release();
+        s_rank = 0; s_world = 1;
+    }
+    return rc;
+}
+
 #define DEV(call, what) do { int rc__ = spg_map_kernel_error((call), what); if (rc__) goto fail; } while (0)
 
 void train_struct_arguments(TrainArgs a)
@@ -270,7 +287,7 @@ void train_struct_arguments(TrainArgs a)
         DEV(spgk_memcpy_h2d(d_agree, h_pinned, sizeof mine, st), "train: agreement");
         DEV(spgk_nccl_allreduce_sum(s_comm, d_agree, 2 * SPG_AGREE_BYTES, st), "train: agreement");
         DEV(spgk_memcpy_d2h(h_pinned, d_agree, sizeof mine, st), "train: agreement");
-        DEV(spgk_stream_sync(st), "train: agreement");
+        DEV(train_sync(st), "train: agreement");
         if (!spingalett_dist_check_agreement(h_pinned, mine, s_world)) {
             spg_set_error(SPINGALETT_ERR_INVALID, "train: the ranks disagree on sample_count, batch_size, epochs, strategy, optimizer or "
                                                   "callback / check intervals; a data-parallel run needs them equal on every rank");
@@ -295,7 +312,7 @@ void train_struct_arguments(TrainArgs a)
         if (mini) {
             spg_shuffle(order, a.sample_count);
             DEV(spgk_memcpy_h2d(t->idx, order, (size_t)a.sample_count * 4, st), "train: upload order");
-            DEV(spgk_stream_sync(st), "train: order sync");        /* `order` is reshuffled next epoch */
+            DEV(train_sync(st), "train: order sync");        /* `order` is reshuffled next epoch */
         }
         const uint32_t nb = (a.sample_count + batch - 1) / batch;
         for (uint32_t bi = 0; bi < nb; bi++) {
@@ -391,7 +408,7 @@ void train_struct_arguments(TrainArgs a)
         }
         if (need_loss || nan_now) {
             DEV(spgk_memcpy_d2h(h_pinned, t->words, 8, st), "train: read loss");
-            DEV(spgk_stream_sync(st), "train: loss sync");
+            DEV(train_sync(st), "train: loss sync");
             current_error = need_loss ? h_pinned[0] / (float)a.sample_count : 0.0f;
             nan_found = nan_now && ((int *)h_pinned)[1] != 0;
         }
@@ -408,7 +425,7 @@ void train_struct_arguments(TrainArgs a)
             /* the callback may read the net: bring the host mirror up to date first */
             DEV(spgk_memcpy_d2h(p->weights, t->params, tw * 4, st), "train: weights to host");
             DEV(spgk_memcpy_d2h(p->biases, t->params + tw, tb * 4, st), "train: biases to host");
-            DEV(spgk_stream_sync(st), "train: callback sync");
+            DEV(train_sync(st), "train: callback sync");
             if (a.callback(p, epoch, current_error)) {
                 spg_log(LOG_INFO, "Training interrupted by callback at epoch %zu", epoch);
                 stop = true;
@@ -419,7 +436,7 @@ void train_struct_arguments(TrainArgs a)
             DEV(spgk_memcpy_h2d(d_agree, h_pinned + 16, 4, st), "train: stop vote");
             DEV(spgk_nccl_allreduce_sum(s_comm, d_agree, 1, st), "train: stop vote");
             DEV(spgk_memcpy_d2h(h_pinned + 16, d_agree, 4, st), "train: stop vote");
-            DEV(spgk_stream_sync(st), "train: stop vote");
+            DEV(train_sync(st), "train: stop vote");
             if (h_pinned[16] > 0.0f && !stop) spg_log(LOG_INFO, "Training stopped at epoch %zu because another rank stopped", epoch);
             stop = h_pinned[16] > 0.0f;
         }
@@ -434,7 +451,7 @@ void train_struct_arguments(TrainArgs a)
     DEV(spgk_memcpy_d2h(p->opt_m_biases, t->m + tw, tb * 4, st), "train: m to host");
     DEV(spgk_memcpy_d2h(p->opt_v_weights, t->v, tw * 4, st), "train: v to host");
     DEV(spgk_memcpy_d2h(p->opt_v_biases, t->v + tw, tb * 4, st), "train: v to host");
-    DEV(spgk_stream_sync(st), "train: final sync");
+    DEV(train_sync(st), "train: final sync");
     spg_log(LOG_INFO, "Training completed.");
     failed = false;
 fail:

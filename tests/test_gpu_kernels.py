@@ -525,3 +525,204 @@ def test_mlp3_fused_row_list_limit_and_margin(spg, k):
     h2 = np.maximum(np.maximum(x64 @ w[0].T * s[0] + b[0], 0) @ w[1].T * s[1] + b[1], 0)
     full = _softmax(h2 @ _round16(case["ws"][2], t16).astype(np.float64).T * s[2] + b[2])
     assert np.abs(after[:N][mask[:N]] - full[mask[:N]]).max() < 2e-5
+
+
+# ---------------------------------------------------------------------------
+# the reference-made edge tables on the device kernels
+# ---------------------------------------------------------------------------
+def _edge_check(got, want, x, exact_inf, of_nan=None):
+    """Element-wise comparison with the reference's table: NaN where it has NaN, the same infinity, else 1e-5 relative.
+    Kernels that carry activations as 16-bit terms cannot split an infinite input (inf - inf is NaN), so for +-inf inputs
+    their pre-activation is NaN and they may answer what the activation makes of a NaN (of_nan: NaN itself, or 0 for
+    ReLU, whose comparison `x > 0 ? x : 0` is false for NaN in the reference as well) instead of the table's value
+    (exact_inf = False); they never answer any other number."""
+    for g, w, xi in zip(got, want, x):
+        if np.isnan(w):
+            assert np.isnan(g), (xi, g, w)
+        elif np.isinf(xi) and not exact_inf:
+            assert np.isnan(g) or g == w or (of_nan is not None and g == of_nan), (xi, g, w)
+        elif np.isinf(w):
+            assert g == w, (xi, g, w)
+        else:
+            assert abs(g - w) <= 1e-5 * max(1.0, abs(w)) + 1e-30, (xi, g, w)
+
+
+@pytest.mark.parametrize("act", [0, 1, 2, 3, 4, 6])
+def test_activation_edge_table_on_every_layer_kernel(spg, k, act):
+    """+-0, 1 +- 1 ulp (FOO52's knee), +-88, +-1e30, +-inf ... (tests/golden/activations.npz, written by the reference's own
+    activate()) through a layer with identity weights and zero bias on each layer kernel: the general SIMT layer, the GEMV,
+    the weight-streaming kernel, the tcgen05 GEMM and the one-launch MLP."""
+    import torch
+    g = np.load(__import__("conftest").golden("activations.npz"))
+    x, want = g["x"], g["activate"][act]
+    of_nan = float(__import__("oracle").Oracle.activate([np.nan], act)[0])     # Activation.c:23-38 on a NaN: 0 for ReLU, else NaN
+    n, W = len(x), 64
+    X = np.zeros((n, W), np.float32)
+    X[:, 0] = x
+    xd = torch.from_numpy(X).cuda()
+    eye = np.eye(W, dtype=np.float32)
+    wd, bd = torch.from_numpy(eye).cuda(), torch.zeros(W, device="cuda")
+    L = spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), 1.0, W, W, 0, act)
+    vp = C.c_void_p
+    # 1. general SIMT layer (fp32): exact class behaviour, infinities included
+    y = torch.zeros((n, W), device="cuda")
+    assert k.spgk_layer_simt(C.byref(L), xd.data_ptr(), W, y.data_ptr(), W, n, None) == 0, k.spgk_error_string()
+    _edge_check(y.cpu().numpy()[:, 0], want, x, exact_inf=True)
+    # 2. GEMV (up to 8 rows a call)
+    k.spgk_gemv_status.argtypes = [vp, vp]
+    nb = k.spgk_gemv_scratch_bytes(C.byref(L), 8)
+    if nb:
+        scratch = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+        y.zero_()
+        for r0 in range(0, n, 8):
+            rows = min(8, n - r0)
+            assert k.spgk_layer_gemv(C.byref(L), xd[r0:].data_ptr(), W, y[r0:].data_ptr(), W, rows, scratch.data_ptr(), None) == 0, k.spgk_error_string()
+            assert k.spgk_gemv_status(scratch.data_ptr(), None) == 0
+        _edge_check(y.cpu().numpy()[:, 0], want, x, exact_inf=False, of_nan=of_nan)
+    # 3. weight streaming through the tensor core (bf16 identity weights)
+    k.spgk_wstream_scratch_bytes.argtypes = [C.POINTER(spg.abi.KLayer), C.c_uint32]
+    k.spgk_wstream_scratch_bytes.restype = C.c_size_t
+    k.spgk_layer_wstream.argtypes = [C.POINTER(spg.abi.KLayer), vp, vp, vp, vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, vp, vp]
+    k.spgk_wstream_status.argtypes = [vp, vp]
+    wb = torch.from_numpy(eye).to(torch.bfloat16).cuda()
+    Lb = spg.abi.KLayer(wb.data_ptr(), bd.data_ptr(), 1.0, W, W, 2, act)
+    nb = k.spgk_wstream_scratch_bytes(C.byref(Lb), n)
+    if nb:
+        scratch = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+        y.zero_()
+        assert k.spgk_layer_wstream(C.byref(Lb), None, None, None, xd.data_ptr(), W, y.data_ptr(), W, n, scratch.data_ptr(), None) == 0, k.spgk_error_string()
+        assert k.spgk_wstream_status(scratch.data_ptr(), None) == 0
+        _edge_check(y.cpu().numpy()[:, 0], want, x, exact_inf=False, of_nan=of_nan)
+    # 4. tcgen05 GEMM, two bf16 terms per activation
+    a16 = torch.zeros((2, n, W), dtype=torch.bfloat16, device="cuda")
+    assert k.spgk_split16(xd.data_ptr(), W, n, W, a16.data_ptr(), W, n * W, 2, 1, None) == 0
+    w16 = torch.zeros((1, W, W), dtype=torch.bfloat16, device="cuda")
+    assert k.spgk_dequant16(C.byref(L), w16.data_ptr(), W, W * W, 1, 1, None) == 0
+    o32 = torch.zeros((n, W), device="cuda")
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    assert k.spgk_layer_gemm_tc(C.byref(L), w16.data_ptr(), W, W * W, 1, 1, a16.data_ptr(), W, n * W, 2, 1,
+                                None, 0, 0, 1, o32.data_ptr(), W, n, 0, status.data_ptr(), None) == 0, k.spgk_error_string()
+    assert k.spgk_gemm_tc_status(status.data_ptr(), None) == 0
+    _edge_check(o32.cpu().numpy()[:, 0], want, x, exact_inf=False, of_nan=of_nan)
+    # 5. the one-launch MLP in pair mode (two fp16 terms): the activation under test is layer 1's, layer 2 and the head
+    #    pass the value on (identity weights, no activation); fp16 terms reach |x| <= 65504 only
+    if act != 6:
+        _bind_mlp3(spg, k)
+        L1 = spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), 1.0, W, W, 0, act)
+        L2 = spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), 1.0, W, W, 0, 6)
+        eye16 = torch.from_numpy(np.eye(16, W, dtype=np.float32)).cuda()
+        L3 = spg.abi.KLayer(eye16.data_ptr(), bd.data_ptr(), 1.0, W, 16, 0, 6)
+        w16h = torch.from_numpy(eye).to(torch.float16).cuda()
+        assert k.spgk_mlp3_supported(C.byref(L1), C.byref(L2), C.byref(L3), W) == 1
+        params = torch.zeros(k.spgk_mlp3_params_bytes(C.byref(L1), C.byref(L2), C.byref(L3)) // 4, device="cuda")
+        assert k.spgk_mlp3_params(C.byref(L1), C.byref(L2), C.byref(L3), 0, params.data_ptr(), None) == 0
+        out = torch.zeros((n, 16), device="cuda")
+        assert k.spgk_mlp3_forward(C.byref(L1), w16h.data_ptr(), W, C.byref(L2), w16h.data_ptr(), W, C.byref(L3), params.data_ptr(), 0,
+                                   xd.data_ptr(), W, None, None, 0, 1, out.data_ptr(), 16, n, 0.0, None, None, status.data_ptr(), None) == 0, k.spgk_error_string()
+        assert k.spgk_gemm_tc_status(status.data_ptr(), None) == 0
+        got = out.cpu().numpy()[:, 0]
+        small = np.abs(x) <= 60000
+        _edge_check(got[small], want[small], x[small], exact_inf=False, of_nan=of_nan)
+
+
+def test_softmax_edge_table_on_the_row_block_and_fused_kernels(spg, k):
+    """Rows of tests/golden/softmax.npz (all -1e30, one +1e30, a single element, 88 / 89 / -90, 1000 wide ...) through the
+    warp-per-row kernel, the CTA-per-row kernel (few rows wider than 64) and the softmax fused into the GEMM epilogue
+    (identity weights), against the reference's apply_softmax outputs (Activation.c:5-21)."""
+    import torch
+    g = np.load(__import__("conftest").golden("softmax.npz"))
+    nrows = len(g.files) // 2
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    for i in range(nrows):
+        row, want = g[f"in{i}"], g[f"out{i}"]
+        w = len(row)
+        # many copies -> the warp-per-row kernel; one copy of a wide row -> the CTA-per-row kernel
+        for copies in (70, 1):
+            y = torch.from_numpy(np.tile(row, (copies, 1)).astype(np.float32)).cuda()
+            assert k.spgk_softmax_rows(y.data_ptr(), w, copies, w, None) == 0, k.spgk_error_string()
+            got = y.cpu().numpy()
+            assert np.abs(got - want).max() <= 1e-6, (i, copies, np.abs(got - want).max())
+        if w <= 256 and w >= 2:
+            W = (w + 7) & ~7
+            eye = np.eye(w, W, dtype=np.float32)
+            wd, bd = torch.from_numpy(eye).cuda(), torch.zeros(w, device="cuda")
+            L = spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), 1.0, W, w, 0, 5)
+            X = np.zeros((3, W), np.float32)
+            X[:, :w] = row
+            xd = torch.from_numpy(X).cuda()
+            a16 = torch.zeros((2, 3, W), dtype=torch.bfloat16, device="cuda")
+            assert k.spgk_split16(xd.data_ptr(), W, 3, W, a16.data_ptr(), W, 3 * W, 2, 1, None) == 0
+            w16 = torch.zeros((1, w, W), dtype=torch.bfloat16, device="cuda")
+            assert k.spgk_dequant16(C.byref(L), w16.data_ptr(), W, w * W, 1, 1, None) == 0
+            o32 = torch.zeros((3, w), device="cuda")
+            assert k.spgk_layer_gemm_tc(C.byref(L), w16.data_ptr(), W, w * W, 1, 1, a16.data_ptr(), W, 3 * W, 2, 1,
+                                        None, 0, 0, 1, o32.data_ptr(), w, 3, 1, status.data_ptr(), None) == 0, k.spgk_error_string()
+            assert k.spgk_gemm_tc_status(status.data_ptr(), None) == 0
+            got = o32.cpu().numpy()
+            # the logits pass through two bf16 terms (16 significant bits): 2^-16 relative on a logit of 88 moves e^x by 1e-3
+            tol = 1e-6 if np.abs(row).max() < 20 or np.abs(row).max() > 1e20 else 3e-3
+            assert np.abs(got - want).max() <= tol, (i, np.abs(got - want).max())
+
+
+def test_a_bounded_device_wait_that_runs_out_is_reported_not_hung(spg, k):
+    """A barrier nobody arrives on, waited for with the tensor-core kernels' own bounded waits and a small limit: the kernel
+    returns by itself, the status word carries the wait's code, the host call answers SPGK_E_TIMEOUT (which the library
+    maps to SPINGALETT_ERR_DEVICE), and the context is as usable afterwards as before."""
+    import torch
+    k.spgk_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
+    st = torch.zeros(16, dtype=torch.int32, device="cuda")
+    rc = k.spgk_selftest_bounded_wait(st.data_ptr(), 32, None)
+    assert rc == -4, (rc, k.spgk_error_string())                     # SPGK_E_TIMEOUT
+    assert b"bounded wait 41" in k.spgk_error_string()
+    host = st.cpu().numpy()
+    assert host[0] == 0 and host[1] == 0 and host[2] == 2            # word cleared by the status call; warp 1 saw the abort flag
+    # the context still works: any other kernel runs
+    y = torch.ones((4, 8), device="cuda")
+    assert k.spgk_softmax_rows(y.data_ptr(), 8, 4, 8, None) == 0
+    assert abs(float(y.sum()) - 4.0) < 1e-5
+
+
+def test_injected_allocation_failures_are_reported_and_leak_nothing(spg, k):
+    """The k-th device allocation fails (host-side injection): upload, batched forward and train() each answer ERR_ALLOC and
+    give back what they had taken -- free device memory returns to its level."""
+    import torch
+    lib, a = spg.lib(), spg.abi
+    lib.spgk_mem_info.argtypes = [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+
+    def free_bytes():
+        torch.cuda.synchronize()
+        f = C.c_size_t(0)
+        assert lib.spgk_mem_info(C.byref(f), None) == 0
+        return f.value
+    x = np.random.default_rng(0).random((2048, 20), dtype=np.float32)
+    t = np.zeros((2048, 10), np.float32)
+    t[:, 3] = 1.0
+    # one clean pass first: the driver loads each kernel's module on first use and takes device memory for it
+    warm = spg.Network.build([20, 33, 17, 10], [a.ACT_RELU, a.ACT_FOO52, a.ACT_SOFTMAX], a.WEIGHT_INITIALIZATION_HE, seed=5)
+    warm.forward_batch(x)
+    warm.train(x, t, epochs=1, batch_size=256)
+    warm.free()
+    seen_fail = 0
+    for kth in range(1, 40):
+        net = spg.Network.build([20, 33, 17, 10], [a.ACT_RELU, a.ACT_FOO52, a.ACT_SOFTMAX], a.WEIGHT_INITIALIZATION_HE, seed=5)
+        before = free_bytes()
+        lib.spgk_fail_malloc_after(kth)
+        try:
+            try:
+                net.forward_batch(x)
+                net.train(x, t, epochs=1, batch_size=256)
+                worked = True
+            except spg.SpingalettError as e:
+                worked = False
+                assert e.code == a.ERR_ALLOC, (kth, e)
+                seen_fail += 1
+        finally:
+            lib.spgk_fail_malloc_after(0)
+        if not worked:
+            # a failed call must have released its own buffers; what an earlier successful call of this net holds is freed with the net
+            net.free()
+            assert free_bytes() >= before, (kth, before, free_bytes())
+        else:
+            net.free()
+            break
+    assert seen_fail >= 10 and worked                                  # every allocation site was hit once, then the sweep ran through

@@ -154,3 +154,71 @@ def test_config_mlp_784_512_1000_10(spg, oracle, tmp_path_factory, prec, n, math
         again = net.forward_batch(x[rows[:512]])
         assert np.abs(again - got[rows[:512]]).max() <= nets.tolerance(p)
     net.free()
+
+
+@pytest.mark.parametrize("n", [512, 4096])
+def test_auto_mode_recomputes_rows_that_leave_the_fp16_range(spg, oracle, tmp_path_factory, n):
+    """The one-term pass of a non-bf16 file runs on fp16 operands: an input beyond 65504 (or a hidden value that overflows)
+    gives non-finite logits there.  AUTO lists such rows with the low-margin ones and recomputes them with two bf16 terms
+    (fp32 range), so its result for them is the exact mode's; every other row is untouched by their presence.  n = 512 takes
+    the per-layer chain, n = 4096 the one-launch kernel."""
+    d = tmp_path_factory.getbasetemp()
+    path = nets.make_net_file(spg, str(d / "A_range_int8.nn"), nets.A_TOPO, nets.A_ACTS, 3, seed=1234, reference_rng=True)
+    net = spg.Network.load(path)
+    onet = oracle.OracleNet.from_file(path)
+    x = nets.uniform_inputs(n, 784, seed=99)
+    big = [3, n // 2, n - 1]
+    x[big[0]] *= 1.0e6                       # every input of the row beyond the fp16 range
+    x[big[1], 17] = 3.0e5                    # a single large input
+    x[big[2]] *= 4.0e3                       # inputs fit, the hidden layers overflow fp16
+    try:
+        spg.set_math_mode(spg.abi.MATH_AUTO)
+        got = net.forward_batch(x)
+        want = onet.forward_batch(x[big])
+        assert np.all(np.isfinite(got)), np.nonzero(~np.isfinite(got).all(1))[0]
+        assert np.abs(got[big] - want).max() <= 5e-5, (spg.last_path(), got[big], want)
+        assert spg.lib().spingalett_last_repaired(net._h) >= 2
+        clean = x.copy()
+        clean[big] = 0.5
+        other = net.forward_batch(clean)
+        keep = np.ones(n, bool)
+        keep[big] = False
+        assert np.abs(other[keep] - got[keep]).max() <= 2e-6
+    finally:
+        spg.set_math_mode(spg.abi.MATH_AUTO)
+        net.free()
+
+
+def test_batch_fan_out_over_device_replicas(spg, oracle, has_gpu):
+    """spingalett_set_devices: a host batch cut into row shares, one replica and one host thread per listed device.  On a
+    one-GPU machine the list names device 0 twice (two replicas, two threads, two streams); with more GPUs it names
+    the first two as well, which also exercises the per-device launcher set-up of every kernel on a second device."""
+    import ctypes as C
+    assert has_gpu
+    lib = spg.lib()
+    count = lib.spingalett_get_device_count()
+    lists = [[0, 0], [0, 0, 0]] + ([[0, 1], [1, 0, 1]] if count >= 2 else [])
+    path = golden("small.int4.nn")
+    onet = oracle.OracleNet.from_file(path)
+    rng = np.random.default_rng(3)
+    for ids in lists:
+        net = spg.Network.load(path)
+        arr = (C.c_int * len(ids))(*ids)
+        assert lib.spingalett_set_devices(arr, len(ids)) == 0
+        try:
+            for n in (5, 37, 3000, 40000):
+                x = rng.random((n, onet.topology[0]), dtype=np.float32)
+                got = net.forward_batch(x)
+                want = onet.forward_batch(x)
+                agree, err = nets.parity(got, want)
+                assert err <= 5e-3 and agree >= 0.999, (ids, n, agree, err)
+                assert spg.last_path() == ("fan-out" if n >= 2 * len(ids) else spg.last_path())
+            assert spg.last_path() == "fan-out"
+        finally:
+            assert lib.spingalett_set_devices(None, 0) == 0
+        again = net.forward_batch(x)                                 # back on one device: the same answer, up to the one-term error
+        assert np.abs(again - got).max() <= 6e-4                     # of rows that one replica's margin calibration recomputes and another's not
+        net.free()
+    bad = (C.c_int * 2)(0, count)
+    assert lib.spingalett_set_devices(bad, 2) == spg.abi.ERR_INVALID
+    lib.spingalett_clear_error()

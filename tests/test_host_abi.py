@@ -291,7 +291,8 @@ def test_reference_examples_compile_unmodified_against_the_header(spg, tmp_path,
     """Where a checkout of the reference is at hand, its example programs compile and link, unmodified, against include/ and
     the library (they are run on a GPU by hand or by tests/c/xor_program.c's test; here only the build is checked)."""
     import subprocess
-    src = os.path.join(os.environ.get("SPINGALETT_REFERENCE", "/root/reference"), "Examples", example)
+    from oracle import reference_root
+    src = os.path.join(reference_root(), "Examples", example)
     if not os.path.exists(src):
         pytest.skip("no checkout of the reference here")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -330,3 +331,43 @@ def test_rank_agreement_check_detects_any_differing_argument(spg):
     # three ranks whose values average to the own value still fail (the squares do not)
     lo, mid, hi = pack(sample_count=5119), pack(sample_count=5120), pack(sample_count=5121)
     assert lib.spingalett_dist_check_agreement(fp(lo + mid + hi), fp(mid), 3) == 0
+
+
+def test_once_per_device_bookkeeping_of_the_launchers(spg):
+    """cudaFuncSetAttribute is per device: the launchers run their set-up once per device index, retry a set-up that failed,
+    and refuse indices outside the table (host-only check of that bookkeeping)."""
+    lib = spg.lib()
+    assert lib.spgk_selftest_once_per_device(1, 5, -1) == 1
+    assert lib.spgk_selftest_once_per_device(8, 3, -1) == 8          # eight devices, three rounds of calls: eight set-ups
+    assert lib.spgk_selftest_once_per_device(4, 3, 2) == 5           # device 2 failed once and was set up again
+
+
+def test_rendezvous_timeout_wrapper(spg):
+    """The communicator rendezvous runs under a host timeout: a call that answers in time passes its result through, one
+    that does not (a rank that never joined) ends with SPGK_E_TIMEOUT after the limit instead of blocking for ever."""
+    import time
+    lib = spg.lib()
+    assert lib.spgk_selftest_timed_call(5, 2000) == 0
+    t0 = time.time()
+    assert lib.spgk_selftest_timed_call(5000, 150) == -4             # SPGK_E_TIMEOUT
+    assert time.time() - t0 < 2.0
+
+
+def test_row_shares_of_the_device_fan_out_cover_the_batch_once(spg):
+    """spingalett_split_rows: contiguous shares, sizes within one row of each other, every row exactly once -- also when
+    there are fewer rows than shares."""
+    import ctypes as C
+    lib = spg.lib()
+    for rows in (0, 1, 7, 8, 65536, 65537, 1000003):
+        for shares in (1, 2, 3, 4, 8, 16):
+            spans = []
+            for g in range(shares):
+                lo, hi = C.c_uint32(), C.c_uint32()
+                lib.spingalett_split_rows(rows, shares, g, C.byref(lo), C.byref(hi))
+                spans.append((lo.value, hi.value))
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(shares - 1))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+            assert spans == [spg.shard_rows(rows, shares, g) for g in range(shares)]
+    assert lib.spingalett_set_devices(None, 0) == 0

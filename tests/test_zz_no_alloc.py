@@ -6,10 +6,10 @@ process handed all of HBM to its own arena at start-up, or they cannot afford th
 device-wide synchronisation inside cudaMalloc -- so this variant keeps its scratch
 (the expanded 16-bit weight operand and the kernel's status word) in a fixed array
 of the library's device image.  Both entry points run the same kernels on the same
-operands, so their outputs must be identical; two calls in a row with different
-layers check that nothing left in the shared array by the first call leaks into
-the second.  The file sorts last so that a run stopping at the first failure has
-already run every other test; it also passes on its own in a fresh process.
+operands, so their outputs must be identical (and both are held to a float64
+product of the same operands); two calls in a row with different layers check that
+nothing left in the shared array by the first call leaks into the second.  The file
+sorts last so that a run stopping at the first failure has already run every other test; it also passes on its own in a fresh process.
 """
 import ctypes as C
 
@@ -74,6 +74,20 @@ def _one_layer(spg, lib, oracle, torch, M, N, K, prec, act, parts, seed):
     rc = lib.spgk_layer_gemm_tc_noalloc(C.byref(L), a16.data_ptr(), ld, M * ld, parts, t16,
                                         got16.data_ptr(), ldo, M * ldo, parts, got32.data_ptr(), N, M, 0, None)
     assert rc == 0, lib.spgk_error_string()
+    # Both results are also held to a float64 product of the operands the tensor cores saw (the rounded activation terms
+    # and the decoded weights), so the two entry points cannot agree on a wrong answer.
+    if prec == 0:
+        dec = w16.float().cpu().numpy()[:, :, :K].astype(np.float64).sum(0)   # the bf16 terms of the fp32 weights
+    else:
+        dec = oracle.Oracle.decode(raw, N * K, prec).astype(np.float64).reshape(N, K)
+    xs = a16.float().cpu().numpy()[:, :, :K].astype(np.float64).sum(0)
+    z = xs @ dec.T + bias.cpu().numpy().astype(np.float64)
+    want = {1: lambda v: np.maximum(v, 0), 3: lambda v: np.where(v > 0, v, 0.01 * v),
+            4: lambda v: np.where(v > 1, 1 + 0.01 * (v - 1), np.where(v < 0, 0.01 * v, v))}[act](z)
+    tol = (2e-5 * np.sqrt(K) + 1e-5) * max(1.0, np.abs(want).max())
+    for name, res in (("regular", ref32), ("no-alloc", got32)):
+        err = np.abs(res.cpu().numpy() - want).max()
+        assert err <= tol, (name, err, tol)
     return ref32.cpu().numpy(), got32.cpu().numpy(), ref16.float().cpu().numpy(), got16.float().cpu().numpy()
 
 
