@@ -219,7 +219,7 @@ spg_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (tid == 0) {
         for (uint32_t s = 0; s < p.RS; s++) { mbar_init(rfull0 + 8 * s, 1); mbar_init(rempty0 + 8 * s, p.direct ? 1 : CONV_WARPS); }
-        for (uint32_t s = 0; s < p.AS; s++) { mbar_init(afull0 + 8 * s, CONV_WARPS); mbar_init(aempty0 + 8 * s, 1); }
+        for (uint32_t s = 0; s < p.AS; s++) { mbar_init(afull0 + 8 * s, CONV_WARPS / p.AS); mbar_init(aempty0 + 8 * s, 1); }
         for (uint32_t s = 0; s < p.BS; s++) { mbar_init(bfull0 + 8 * s, 1); mbar_init(bempty0 + 8 * s, 1); }
         for (uint32_t a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 128); }
         *abort_flag = 0;
@@ -240,148 +240,210 @@ spg_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t kb1 = min(kb0 + p.kb_per_split, p.kb_total);                          \
     const uint32_t nraw = (kb1 - kb0 + p.kbr - 1) / p.kbr;
 
+    const uint32_t abort_addr = smem_u32(const_cast<int *>(abort_flag));
     if (warp == 0) {
         // ------------------------------ producer ----------------------------------
-        if (lane == 0) {
-            uint32_t rc = 0, bc = 0;
-            bool alive = true;
-            for (uint32_t item = blockIdx.x; item < p.items && alive; item += gridDim.x) {
-                WS_ITEM_RANGE(item)
-                for (uint32_t r = 0; r < nraw && alive; r++, rc++) {
-                    const uint32_t rs = rc % p.RS;
-                    if (!mbar_wait(rempty0 + 8 * rs, ((rc / p.RS) & 1u) ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
+        // The whole warp walks the loops convergently (ring positions are counted up, never divided out), one elected
+        // lane issues the copies.  After an abort the waits end at once; the flag is looked at once per raw box so that
+        // no copy is started into shared memory that is about to be given up.
+        uint32_t rs = 0, rph = 0, bs = 0, bph = 0;
+        for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
+            WS_ITEM_RANGE(item)
+            for (uint32_t r = 0; r < nraw; r++) {
+                if (*abort_flag) goto ws_role_done;
+                mbar_wait_uniform(rempty0 + 8 * rs, rph ^ 1u, abort_addr, p.status, 1);
+                if (elect_one()) {
                     mbar_expect_tx(rfull0 + 8 * rs, RAW_BYTES);
                     tma_load_2d(base + rs * RAW_BYTES, &map_w, rfull0 + 8 * rs, (int)((kb0 / p.kbr + r) * 128u), (int)(mt * TILE_ROWS));
-                    const uint32_t kbs = min(p.kbr, kb1 - kb0 - r * p.kbr);
-                    for (uint32_t j = 0; j < kbs; j++, bc++) {
-                        const uint32_t bs = bc % p.BS;
-                        if (!mbar_wait(bempty0 + 8 * bs, ((bc / p.BS) & 1u) ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
+                }
+                __syncwarp();
+                const uint32_t kbs = min(p.kbr, kb1 - kb0 - r * p.kbr);
+                for (uint32_t j = 0; j < kbs; j++) {
+                    mbar_wait_uniform(bempty0 + 8 * bs, bph ^ 1u, abort_addr, p.status, 2);
+                    if (*abort_flag) goto ws_role_done;
+                    if (elect_one()) {
                         mbar_expect_tx(bfull0 + 8 * bs, p.b_slot_bytes);
                         tma_load_2d(base + b_off + bs * p.b_slot_bytes, &map_x, bfull0 + 8 * bs, (int)((kb0 + r * p.kbr + j) * 64u), 0);
                     }
+                    __syncwarp();
+                    if (++bs == p.BS) { bs = 0; bph ^= 1u; }
                 }
+                if (++rs == p.RS) { rs = 0; rph ^= 1u; }
             }
         }
-        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            uint32_t rc = 0, ac = 0, bc = 0, tcount = 0;
-            bool alive = true;
-            const uint32_t terms = p.prec == SPG_P_I8 ? 2u : 1u;       // INT8: low-nibble tile + high-nibble tile
-            for (uint32_t item = blockIdx.x; item < p.items && alive; item += gridDim.x, tcount++) {
-                WS_ITEM_RANGE(item)
-                const uint32_t acc = tcount & 1u;
-                if (!mbar_wait(tempty0 + 8 * acc, ((tcount >> 1) & 1u) ^ 1u, abort_flag, p.status, 3)) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * p.NC;
-                uint32_t first = 1;
-                for (uint32_t r = 0; r < nraw && alive; r++, rc++) {
-                    const uint32_t kbs = min(p.kbr, kb1 - kb0 - r * p.kbr);
-                    if (p.direct && !mbar_wait(rfull0 + 8 * (rc % p.RS), (rc / p.RS) & 1u, abort_flag, p.status, 4)) { alive = false; break; }
-                    for (uint32_t j = 0; j < kbs; j++, bc++) {
-                        uint32_t a_addr;
-                        if (p.direct) {
-                            a_addr = base + (rc % p.RS) * RAW_BYTES;
-                        } else {
-                            if (!mbar_wait(afull0 + 8 * (ac % p.AS), (ac / p.AS) & 1u, abort_flag, p.status, 5)) { alive = false; break; }
-                            a_addr = base + a_off + (ac % p.AS) * p.a_slot_bytes;
-                        }
-                        const uint32_t bs = bc % p.BS;
-                        if (!mbar_wait(bfull0 + 8 * bs, (bc / p.BS) & 1u, abort_flag, p.status, 6)) { alive = false; break; }
-                        tc_fence_after();
-                        const uint64_t db = smem_desc_sw128(base + b_off + bs * p.b_slot_bytes);
+        // Convergent as well: descriptors, ring positions and the accumulator address stay warp-uniform (tcgen05.mma takes
+        // them from uniform registers), the waits are single try_waits when the data is already there.
+        uint32_t rs = 0, rph = 0, as = 0, aph = 0, bs = 0, bph = 0, tcount = 0;
+        const uint32_t terms = p.prec == SPG_P_I8 ? 2u : 1u;           // INT8: low-nibble tile + high-nibble tile
+        const uint64_t r_desc0 = smem_desc_sw128(base), a_desc0 = smem_desc_sw128(base + a_off), b_desc0 = smem_desc_sw128(base + b_off);
+        const uint32_t a_step = p.a_slot_bytes >> 4, b_step = p.b_slot_bytes >> 4;
+        for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, tcount++) {
+            WS_ITEM_RANGE(item)
+            (void)mt;
+            const uint32_t acc = tcount & 1u;
+            mbar_wait_uniform(tempty0 + 8 * acc, ((tcount >> 1) & 1u) ^ 1u, abort_addr, p.status, 3);
+            if (*abort_flag) goto ws_role_done;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * p.NC;
+            uint32_t accum = 0;
+            for (uint32_t r = 0; r < nraw; r++) {
+                const uint32_t kbs = min(p.kbr, kb1 - kb0 - r * p.kbr);
+                if (p.direct) mbar_wait_uniform(rfull0 + 8 * rs, rph, abort_addr, p.status, 4);
+                for (uint32_t j = 0; j < kbs; j++) {
+                    uint64_t da;
+                    if (p.direct) {
+                        da = r_desc0 + (uint64_t)(rs * (RAW_BYTES >> 4));
+                    } else {
+                        mbar_wait_uniform(afull0 + 8 * as, aph, abort_addr, p.status, 5);
+                        da = a_desc0 + (uint64_t)(as * a_step);
+                    }
+                    mbar_wait_uniform(bfull0 + 8 * bs, bph, abort_addr, p.status, 6);
+                    tc_fence_after();
+                    const uint64_t db = b_desc0 + (uint64_t)(bs * b_step);
+                    if (elect_one()) {
                         for (uint32_t tm = 0; tm < terms; tm++) {
-                            const uint64_t da = smem_desc_sw128(a_addr + tm * A_TILE);
 #pragma unroll
-                            for (uint32_t k = 0; k < 4; k++) { umma_f16(d_tmem, da + 2 * k, db + 2 * k, p.idesc, first ? 0u : 1u); first = 0; }
+                            for (uint32_t k = 0; k < 4; k++) { umma_f16(d_tmem, da + tm * (A_TILE >> 4) + 2 * k, db + 2 * k, p.idesc, accum); accum = 1; }
                         }
                         umma_commit(bempty0 + 8 * bs);
-                        if (!p.direct) { umma_commit(aempty0 + 8 * (ac % p.AS)); ac++; }
+                        if (!p.direct) umma_commit(aempty0 + 8 * as);
                     }
-                    if (p.direct && alive) umma_commit(rempty0 + 8 * (rc % p.RS));
+                    __syncwarp();
+                    accum = 1;
+                    if (++bs == p.BS) { bs = 0; bph ^= 1u; }
+                    if (!p.direct && ++as == p.AS) { as = 0; aph ^= 1u; }
                 }
-                if (alive) umma_commit(tfull0 + 8 * acc);
+                if (p.direct) {
+                    if (elect_one()) umma_commit(rempty0 + 8 * rs);
+                    __syncwarp();
+                }
+                if (++rs == p.RS) { rs = 0; rph ^= 1u; }
+                if (*abort_flag) goto ws_role_done;
             }
+            if (elect_one()) umma_commit(tfull0 + 8 * acc);
+            __syncwarp();
         }
-        __syncwarp();
     } else if (warp >= CONV_WARP0) {
         // ------------------------------ converters --------------------------------
+        // G groups of 8/G warps, G = slots of the operand ring (4 or 2); group g takes the k-blocks whose running number
+        // is g mod G -- always ring slot g, so a group only ever waits for its own previous tile to be consumed -- and G
+        // operand tiles are being written at any time: the latency of one (load, unpack, store, proxy fence, arrive) is
+        // hidden behind the others.  A thread handles G (row, half k-block) units of its group's k-block: all raw words
+        // are loaded first, then unpacked and stored.  Every warp waits for every raw box and arrives on its "empty"
+        // barrier once it is through it, whether or not one of its k-blocks was in it.
         if (!p.direct) {
-            const uint32_t ct = tid - CONV_WARP0 * 32;                 // 0..255: one (row, half k-block) unit per k-block
-            const uint32_t r7 = ct & 7u, h = (ct >> 3) & 1u, row = (ct >> 4) * 8u + r7;
-            uint32_t rc = 0, ac = 0;
+            const uint32_t G = p.AS, wpg = CONV_WARPS / G, TG = 32u * wpg;
+            const uint32_t cw = warp - CONV_WARP0, grp = cw / wpg;
+            const uint32_t ctg = (cw % wpg) * 32u + lane;              // 0..TG-1 inside the group
+            uint32_t rs = 0, rph = 0, as = 0, aph = 0;
             for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
                 WS_ITEM_RANGE(item)
                 (void)mt;
-                for (uint32_t r = 0; r < nraw; r++, rc++) {
-                    const uint32_t rs = rc % p.RS;
-                    const bool okr = mbar_wait(rfull0 + 8 * rs, (rc / p.RS) & 1u, abort_flag, p.status, 7);
-                    const uint8_t *rawrow = smem + rs * RAW_BYTES + row * 128u;
+                for (uint32_t r = 0; r < nraw; r++) {
+                    const bool okr = mbar_wait(rfull0 + 8 * rs, rph, abort_flag, p.status, 7);
+                    const uint8_t *rawbox = smem + rs * RAW_BYTES;
                     const uint32_t kbs = min(p.kbr, kb1 - kb0 - r * p.kbr);
-                    for (uint32_t j = 0; j < kbs; j++, ac++) {
-                        const uint32_t as = ac % p.AS;
-                        const bool ok = okr && mbar_wait(aempty0 + 8 * as, ((ac / p.AS) & 1u) ^ 1u, abort_flag, p.status, 8);
-                        if (ok) {
-                            uint8_t *arow = smem + a_off + as * p.a_slot_bytes + row * 128u;
-                            if (p.prec == SPG_P_I4) {
-                                // 32 nibbles = one 16-byte piece (piece j*2+h of the raw row) -> chunks h*4 .. h*4+3
-                                const uint4 w = *reinterpret_cast<const uint4 *>(rawrow + (((j * 2u + h) ^ r7) << 4));
-                                const uint32_t ws[4] = { w.x, w.y, w.z, w.w };
+                    for (uint32_t j = 0; j < kbs; j++) {
+                        if (as == grp) {
+                            const bool ok = okr && mbar_wait(aempty0 + 8 * as, aph ^ 1u, abort_flag, p.status, 8);
+                            if (ok) {
+                                uint8_t *atile = smem + a_off + as * p.a_slot_bytes;
+                                if (p.prec == SPG_P_I4) {
+                                    // 32 nibbles = one 16-byte piece (piece j*2+h of the raw row) -> chunks h*4 .. h*4+3
+                                    uint4 w[4];
 #pragma unroll
-                                for (uint32_t q = 0; q < 4; q++) {
-                                    const uint32_t v = ws[q] ^ 0x88888888u;
-                                    uint4 o;
-                                    o.x = field_pair(v, 0x000F000Fu, 0x43084308u);
-                                    o.y = field_pair(v >> 4, 0x000F000Fu, 0x43084308u);
-                                    o.z = field_pair(v >> 8, 0x000F000Fu, 0x43084308u);
-                                    o.w = field_pair(v >> 12, 0x000F000Fu, 0x43084308u);
-                                    *reinterpret_cast<uint4 *>(arow + (((h * 4u + q) ^ r7) << 4)) = o;
-                                }
-                            } else if (p.prec == SPG_P_I2) {
-                                // 32 crumbs = 8 bytes (half of piece j) -> chunks h*4 .. h*4+3
-                                const uint2 w = *reinterpret_cast<const uint2 *>(rawrow + ((j ^ r7) << 4) + h * 8u);
-                                const uint32_t ws[2] = { w.x, w.y };
-#pragma unroll
-                                for (uint32_t q = 0; q < 2; q++) {
-                                    const uint32_t v = ws[q] ^ 0xAAAAAAAAu;
-#pragma unroll
-                                    for (uint32_t c2 = 0; c2 < 2; c2++) {
-                                        uint4 o;
-                                        o.x = field_pair(v >> (8 * c2), 0x00030003u, 0x43024302u);
-                                        o.y = field_pair(v >> (8 * c2 + 2), 0x00030003u, 0x43024302u);
-                                        o.z = field_pair(v >> (8 * c2 + 4), 0x00030003u, 0x43024302u);
-                                        o.w = field_pair(v >> (8 * c2 + 6), 0x00030003u, 0x43024302u);
-                                        *reinterpret_cast<uint4 *>(arow + (((h * 4u + q * 2u + c2) ^ r7) << 4)) = o;
+                                    for (uint32_t u = 0; u < 4; u++) {
+                                        if (u >= G) break;
+                                        const uint32_t ct = u * TG + ctg, r7 = ct & 7u, h = (ct >> 3) & 1u, row = (ct >> 4) * 8u + r7;
+                                        w[u] = *reinterpret_cast<const uint4 *>(rawbox + row * 128u + (((j * 2u + h) ^ r7) << 4));
                                     }
-                                }
-                            } else {
-                                // INT8: 32 bytes = pieces j*4 + h*2 + {0,1}; low nibbles -> tile 0, high nibbles * 16 -> tile 1
 #pragma unroll
-                                for (uint32_t pc = 0; pc < 2; pc++) {
-                                    const uint4 w = *reinterpret_cast<const uint4 *>(rawrow + (((j * 4u + h * 2u + pc) ^ r7) << 4));
-                                    const uint32_t ws[4] = { w.x, w.y, w.z, w.w };
+                                    for (uint32_t u = 0; u < 4; u++) {
+                                        if (u >= G) break;
+                                        const uint32_t ct = u * TG + ctg, r7 = ct & 7u, h = (ct >> 3) & 1u, row = (ct >> 4) * 8u + r7;
+                                        uint8_t *arow = atile + row * 128u;
+                                        const uint32_t ws[4] = { w[u].x, w[u].y, w[u].z, w[u].w };
 #pragma unroll
-                                    for (uint32_t q = 0; q < 2; q++) {
-                                        const uint32_t v0 = ws[2 * q] ^ 0x80808080u, v1 = ws[2 * q + 1] ^ 0x80808080u;
-                                        uint4 lo, hi;
-                                        lo.x = field_pair(v0, 0x000F000Fu, 0x43004300u); lo.y = field_pair(v0 >> 8, 0x000F000Fu, 0x43004300u);
-                                        lo.z = field_pair(v1, 0x000F000Fu, 0x43004300u); lo.w = field_pair(v1 >> 8, 0x000F000Fu, 0x43004300u);
-                                        hi.x = high_nibble_pair(v0 >> 4); hi.y = high_nibble_pair(v0 >> 12);
-                                        hi.z = high_nibble_pair(v1 >> 4); hi.w = high_nibble_pair(v1 >> 12);
-                                        const uint32_t chunk = ((h * 4u + pc * 2u + q) ^ r7) << 4;
-                                        *reinterpret_cast<uint4 *>(arow + chunk) = lo;
-                                        *reinterpret_cast<uint4 *>(arow + A_TILE + chunk) = hi;
+                                        for (uint32_t q = 0; q < 4; q++) {
+                                            const uint32_t v = ws[q] ^ 0x88888888u;
+                                            uint4 o;
+                                            o.x = field_pair(v, 0x000F000Fu, 0x43084308u);
+                                            o.y = field_pair(v >> 4, 0x000F000Fu, 0x43084308u);
+                                            o.z = field_pair(v >> 8, 0x000F000Fu, 0x43084308u);
+                                            o.w = field_pair(v >> 12, 0x000F000Fu, 0x43084308u);
+                                            *reinterpret_cast<uint4 *>(arow + (((h * 4u + q) ^ r7) << 4)) = o;
+                                        }
+                                    }
+                                } else if (p.prec == SPG_P_I2) {
+                                    // 32 crumbs = 8 bytes (half of piece j) -> chunks h*4 .. h*4+3
+                                    uint2 w[4];
+#pragma unroll
+                                    for (uint32_t u = 0; u < 4; u++) {
+                                        if (u >= G) break;
+                                        const uint32_t ct = u * TG + ctg, r7 = ct & 7u, h = (ct >> 3) & 1u, row = (ct >> 4) * 8u + r7;
+                                        w[u] = *reinterpret_cast<const uint2 *>(rawbox + row * 128u + ((j ^ r7) << 4) + h * 8u);
+                                    }
+#pragma unroll
+                                    for (uint32_t u = 0; u < 4; u++) {
+                                        if (u >= G) break;
+                                        const uint32_t ct = u * TG + ctg, r7 = ct & 7u, h = (ct >> 3) & 1u, row = (ct >> 4) * 8u + r7;
+                                        uint8_t *arow = atile + row * 128u;
+                                        const uint32_t ws[2] = { w[u].x, w[u].y };
+#pragma unroll
+                                        for (uint32_t q = 0; q < 2; q++) {
+                                            const uint32_t v = ws[q] ^ 0xAAAAAAAAu;
+#pragma unroll
+                                            for (uint32_t c2 = 0; c2 < 2; c2++) {
+                                                uint4 o;
+                                                o.x = field_pair(v >> (8 * c2), 0x00030003u, 0x43024302u);
+                                                o.y = field_pair(v >> (8 * c2 + 2), 0x00030003u, 0x43024302u);
+                                                o.z = field_pair(v >> (8 * c2 + 4), 0x00030003u, 0x43024302u);
+                                                o.w = field_pair(v >> (8 * c2 + 6), 0x00030003u, 0x43024302u);
+                                                *reinterpret_cast<uint4 *>(arow + (((h * 4u + q * 2u + c2) ^ r7) << 4)) = o;
+                                            }
+                                        }
+                                    }
+                                } else {
+                                    // INT8: 32 bytes = pieces j*4 + h*2 + {0,1}; low nibbles -> tile 0, high nibbles * 16 -> tile 1
+#pragma unroll
+                                    for (uint32_t u = 0; u < 4; u++) {
+                                        if (u >= G) break;
+                                        const uint32_t ct = u * TG + ctg, r7 = ct & 7u, h = (ct >> 3) & 1u, row = (ct >> 4) * 8u + r7;
+                                        const uint8_t *rawrow = rawbox + row * 128u;
+                                        uint8_t *arow = atile + row * 128u;
+                                        uint4 w2[2];
+#pragma unroll
+                                        for (uint32_t pc = 0; pc < 2; pc++) w2[pc] = *reinterpret_cast<const uint4 *>(rawrow + (((j * 4u + h * 2u + pc) ^ r7) << 4));
+#pragma unroll
+                                        for (uint32_t pc = 0; pc < 2; pc++) {
+                                            const uint32_t ws[4] = { w2[pc].x, w2[pc].y, w2[pc].z, w2[pc].w };
+#pragma unroll
+                                            for (uint32_t q = 0; q < 2; q++) {
+                                                const uint32_t v0 = ws[2 * q] ^ 0x80808080u, v1 = ws[2 * q + 1] ^ 0x80808080u;
+                                                uint4 lo, hi;
+                                                lo.x = field_pair(v0, 0x000F000Fu, 0x43004300u); lo.y = field_pair(v0 >> 8, 0x000F000Fu, 0x43004300u);
+                                                lo.z = field_pair(v1, 0x000F000Fu, 0x43004300u); lo.w = field_pair(v1 >> 8, 0x000F000Fu, 0x43004300u);
+                                                hi.x = high_nibble_pair(v0 >> 4); hi.y = high_nibble_pair(v0 >> 12);
+                                                hi.z = high_nibble_pair(v1 >> 4); hi.w = high_nibble_pair(v1 >> 12);
+                                                const uint32_t chunk = ((h * 4u + pc * 2u + q) ^ r7) << 4;
+                                                *reinterpret_cast<uint4 *>(arow + chunk) = lo;
+                                                *reinterpret_cast<uint4 *>(arow + A_TILE + chunk) = hi;
+                                            }
+                                        }
                                     }
                                 }
                             }
+                            fence_async_smem();                        // make the tile visible to the tensor core's reads
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(afull0 + 8 * as);
                         }
-                        fence_async_smem();                            // make the tile visible to the tensor core's reads
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(afull0 + 8 * as);
+                        if (++as == p.AS) { as = 0; aph ^= 1u; }
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(rempty0 + 8 * rs);
+                    if (++rs == p.RS) { rs = 0; rph ^= 1u; }
                 }
             }
         }
@@ -389,9 +451,14 @@ spg_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         ws_epilogue(p, tmem_base, tfull0, tempty0, abort_flag, s_last, warp, lane);
     }
 #undef WS_ITEM_RANGE
-
+ws_role_done:
     tc_fence_before();
     __syncthreads();
+    if (*abort_flag) {
+        // a wait gave up: give copies that may still be in flight time to land before the shared memory goes away
+        if (tid == 0) for (int i = 0; i < 256; i++) __nanosleep(1000);
+        __syncthreads();
+    }
     if (warp == 1) { tc_fence_after(); tmem_free(tmem_base, tmem_cols); }
 }
 
@@ -435,11 +502,13 @@ WsPlan ws_plan(const spgk_layer *L, uint32_t N)
     pl.a_slot = prec == SPG_P_I8 ? 2 * A_TILE : A_TILE;
     pl.b_slot = pl.NC * 128u;
     // ring depths: as deep as shared memory allows, never less than two slots each
+    // (the operand ring has 4 or 2 slots: one per converter group)
     bool fits = false;
     size_t a_bytes = 0;
-    for (uint32_t depth = 4; depth >= 2 && !fits; depth--) {
-        pl.AS = pl.direct ? 1 : depth;
-        pl.BS = depth;
+    static const uint32_t depths[5][2] = { {4, 4}, {4, 3}, {4, 2}, {2, 3}, {2, 2} };
+    for (int d = 0; d < 5 && !fits; d++) {
+        pl.AS = pl.direct ? 1 : depths[d][0];
+        pl.BS = depths[d][1];
         a_bytes = pl.direct ? 0 : (size_t)pl.AS * pl.a_slot;
         const size_t fixed = 1024 + a_bytes + (size_t)pl.BS * pl.b_slot + 1024;
         if (fixed + 2 * RAW_BYTES <= 225u * 1024) {

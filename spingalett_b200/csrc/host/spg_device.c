@@ -453,7 +453,19 @@ int spg_dev_forward_small(spg_net *n, const float *d_x, uint32_t ldx, uint32_t N
 
 static uint32_t round8(uint32_t v) { return (v + 7u) & ~7u; }
 
-#define SPG_W16_KEEP_MAX ((size_t)256 << 20)    /* keep expanded 16-bit weight operands between calls up to this many bytes per net and type */
+/* Expanded 16-bit weight operands are kept between calls up to this many bytes per net and type (4 GiB unless
+ * SPINGALETT_W16_KEEP_MB says otherwise; 0 = expand per call).  A quantised file costs up to 4x (INT4) or 8x (INT2) its
+ * packed size per kept type; nets beyond the budget are expanded into a scratch buffer on every call. */
+static size_t w16_keep_max(void)
+{
+    static size_t cached = (size_t)-1;
+    if (cached == (size_t)-1) {
+        const char *e = getenv("SPINGALETT_W16_KEEP_MB");
+        cached = (e && *e) ? (size_t)strtoull(e, NULL, 10) << 20 : (size_t)4096 << 20;
+    }
+    return cached;
+}
+#define SPG_W16_KEEP_MAX w16_keep_max()    /* keep expanded 16-bit weight operands between calls up to this many bytes per net and type */
 
 static int large_simt(spg_net *n, const float *d_x, uint32_t N, float *d_out)
 {
@@ -933,7 +945,10 @@ static float *forward_batch_on(spg_net *n, ForwardBatchArgs a)
     for (uint32_t l = 0; l < n->dev_layers && gemv_groups; l++)
         if (!spgk_gemv_scratch_bytes(&n->klayers[l], SPGK_GEMV_MAX_BATCH)) gemv_groups = false;
     const uint32_t group = N <= SPGK_GEMV_MAX_BATCH ? N : (gemv_groups ? SPGK_GEMV_MAX_BATCH : 128u);
-    if (N <= SPGK_GEMV_MAX_BATCH || gemv_groups || (N <= 512 && all_wstream(n, N < group ? N : group))) {
+    /* more than one group of 128 rows: the GEMM chain on kept 16-bit operands (1.06 ms at 256 rows of the large INT4
+     * net) beats two or more passes of the streaming kernel (1.77 ms) whenever those operands fit the keep budget */
+    const bool chain_kept = N > 128 && weights_keepable(n, fast_type(n), false) && weights_keepable(n, SPGK_T_BF16, true);
+    if (N <= SPGK_GEMV_MAX_BATCH || gemv_groups || (N <= 512 && !chain_kept && all_wstream(n, N < group ? N : group))) {
         for (uint32_t r0 = 0; r0 < N; r0 += group) {
             const uint32_t rows = N - r0 < group ? N - r0 : group;
             float *d_last = NULL;

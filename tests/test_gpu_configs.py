@@ -78,13 +78,14 @@ def test_wide_bf16_mlp_batch_16384(spg, w_net, mode):
         spg.set_math_mode(spg.abi.MATH_AUTO)
 
 
-@pytest.mark.parametrize("n", [1, 8, 20, 64, 256])
+@pytest.mark.parametrize("n", [1, 8, 20, 64, 128, 256])
 def test_large_int4_mlp_batch_sweep(spg, l_net, n):
     net, onet = l_net
     x = nets.normal_inputs(n, nets.L_TOPO[0], seed=100 + n)
     spg.set_math_mode(spg.abi.MATH_EXACT)
     got = net.forward_batch(x)
-    assert spg.last_path() == ("gemv" if n <= 24 else "wstream")      # 9..24 rows: GEMV in groups of 8
+    # 9..24 rows: GEMV in groups of 8; up to 128 rows: one pass of the streaming kernel; beyond: the GEMM chain on kept operands
+    assert spg.last_path() == ("gemv" if n <= 24 else "wstream" if n <= 128 else "tcgen05")
     rows = np.arange(n) if n <= 64 else np.random.default_rng(2).choice(n, 64, replace=False)
     want = onet.forward_batch(x[rows])
     agree, err = nets.parity(got[rows], want)
