@@ -387,6 +387,29 @@ SPGK_API int spgk_nccl_allreduce_sum(void *comm, float *buf, uint64_t count, voi
 SPGK_API int spgk_nccl_allreduce_sum2(void *comm, float *buf_a, uint64_t count_a, float *buf_b, uint64_t count_b,
                                      void *stream);
 SPGK_API int spgk_nccl_destroy(void *comm);
+
+/* ---- K5: the gradient exchange of data-parallel training in one kernel over peer memory ---------------------------
+ * (no counterpart in the reference, whose data parallelism is OpenMP threads adding into one gradient buffer,
+ * Training.c:396-419; the update rules are those of Training.c:439-507 / SIMD.c:279-494.)
+ * spgk_xchg_create is collective over the ranks of `comm` (2..8, one process and one GPU each, all on one node): every
+ * rank allocates an arena [flags | G | W | M | V] for np parameters, the IPC handles travel through a sum all-reduce
+ * and the peers' arenas are mapped.  spgk_xchg_buffer gives this rank's own G (0), W (1), M (2), V (3): the training
+ * kernels write gradients into G and read parameters from W.  spgk_xchg_step then does, in one launch on every rank:
+ * sum of shard r of all ranks' G in rank order (peer loads), update rule `kind` (0 SGD, 1 MOMENTUM, 2 RMSPROP, 3 ADAM,
+ * 4 ADAMW; arguments as spgk_optimizer_step) on shard r of W / M / V, new weights of the shard into every rank's W
+ * (peer stores).  Afterwards all W are identical bit for bit; M and V are current in the owner's shard only, and
+ * spgk_xchg_gather (collective as well) brings the shards of G (the summed gradients), M and V to every rank.
+ * The ranks' kernels wait for one another through flags in peer memory, every wait bounded (about half a second):
+ * spgk_xchg_status, called after a stream synchronisation, returns SPGK_E_TIMEOUT when one gave up.  All ranks must
+ * issue the same sequence of step / gather calls.  No TMA, multicast or NVLS is involved. */
+SPGK_API int spgk_xchg_create(void **xchg, int rank, int world, uint64_t np, void *comm, void *stream);
+SPGK_API void spgk_xchg_destroy(void *xchg);
+SPGK_API uint64_t spgk_xchg_capacity(const void *xchg);
+SPGK_API float *spgk_xchg_buffer(void *xchg, int which);
+SPGK_API int spgk_xchg_step(void *xchg, int kind, uint64_t n_weights, float lr, float momentum, float b1, float b2, float mf, float vf,
+                            float eps, float decay, float gscale, void *stream);
+SPGK_API int spgk_xchg_gather(void *xchg, void *stream);
+SPGK_API int spgk_xchg_status(void *xchg, void *stream);
 /* Failure handling of the exchange (all on the host; nothing here makes a GPU fault or hang):
  * spgk_nccl_init waits for the rendezvous at most SPINGALETT_DIST_TIMEOUT_MS milliseconds (environment, default 120000) and
  * returns SPGK_E_TIMEOUT when a rank never arrives; spgk_stream_sync_bounded waits for a stream by polling with the same

@@ -30,6 +30,7 @@
 #include <stdlib.h>
 #include <stdio.h>
 #include <string.h>
+#include <time.h>
 
 typedef struct {
     float *params, *grads, *m, *v;          /* flat device buffers: [weights | biases] */
@@ -48,9 +49,14 @@ static int s_rank = 0, s_world = 1;
 /* the exchange runs on a stream of its own so that one layer's gradients cross NVLink while the next layer's are computed:
    s_ev_ready orders it after the gradient kernels, s_ev_done orders the optimiser after it */
 static void *s_ar_stream = NULL, *s_ev_ready = NULL, *s_ev_done = NULL;
+/* the one-kernel exchange over peer memory (spgk_xchg_*): created by the first data-parallel train() call for its
+   parameter count, kept for later calls; NULL = the NCCL exchange */
+static void *s_xchg = NULL;
 
 static void dist_release(void)
 {
+    if (s_xchg) spgk_xchg_destroy(s_xchg);
+    s_xchg = NULL;
     if (s_ev_ready) spgk_event_destroy(s_ev_ready);
     if (s_ev_done) spgk_event_destroy(s_ev_done);
     if (s_ar_stream) spgk_stream_destroy(s_ar_stream);
@@ -296,14 +302,58 @@ void train_struct_arguments(TrainArgs a)
         }
     }
 
+    /* Several ranks: the exchange of a step is one kernel over peer memory (sum of the gradient shards by peer loads, the
+       update on the own shard, the new weights stored into every replica) unless gradient clipping needs the global norm
+       first or SPINGALETT_EXCHANGE=nccl asks for the NCCL all-reduce.  Its buffers live in an arena the peers can map:
+       the step's kernels write gradients there and read parameters from there.  Setting it up is collective, and a rank
+       on which it fails takes all of them to the NCCL path. */
+    float *P = t->params, *G = t->grads, *M = t->m, *V = t->v;
+    const bool clip = a.max_grad_norm > 0.0f && a.training_strategy != STRATEGY_SAMPLE;
+    bool fused_x = false;
+    if (s_world > 1) {
+        const char *mode = getenv("SPINGALETT_EXCHANGE");
+        const bool want = !clip && !(mode && strcmp(mode, "nccl") == 0);
+        /* first vote: does every rank want it, and does every rank still hold an arena of this size from an earlier call? */
+        h_pinned[32] = want ? 1.0f : 0.0f;
+        h_pinned[33] = want && s_xchg && spgk_xchg_capacity(s_xchg) == np ? 1.0f : 0.0f;
+        DEV(spgk_memcpy_h2d(d_agree, h_pinned + 32, 8, st), "train: exchange vote");
+        DEV(spgk_nccl_allreduce_sum(s_comm, d_agree, 2, st), "train: exchange vote");
+        DEV(spgk_memcpy_d2h(h_pinned + 32, d_agree, 8, st), "train: exchange vote");
+        DEV(train_sync(st), "train: exchange vote");
+        const bool all_want = h_pinned[32] == (float)s_world, all_have = h_pinned[33] == (float)s_world;
+        if (s_xchg && !(all_want && all_have)) { spgk_xchg_destroy(s_xchg); s_xchg = NULL; }
+        if (all_want) {
+            bool mine_ok = true;
+            if (!s_xchg && spgk_xchg_create(&s_xchg, s_rank, s_world, np, s_comm, st) != SPGK_OK) {
+                spg_log(LOG_INFO, "train: no peer-memory exchange here (%s); NCCL all-reduce instead", spgk_error_string());
+                s_xchg = NULL; mine_ok = false;
+            }
+            /* second vote: did the set-up work everywhere? */
+            h_pinned[32] = mine_ok ? 0.0f : 1.0f;
+            DEV(spgk_memcpy_h2d(d_agree, h_pinned + 32, 4, st), "train: exchange vote");
+            DEV(spgk_nccl_allreduce_sum(s_comm, d_agree, 1, st), "train: exchange vote");
+            DEV(spgk_memcpy_d2h(h_pinned + 32, d_agree, 4, st), "train: exchange vote");
+            DEV(train_sync(st), "train: exchange vote");
+            fused_x = h_pinned[32] == 0.0f;
+            if (!fused_x && s_xchg) { spgk_xchg_destroy(s_xchg); s_xchg = NULL; }
+        }
+        if (fused_x) {
+            P = spgk_xchg_buffer(s_xchg, 1); G = spgk_xchg_buffer(s_xchg, 0); M = spgk_xchg_buffer(s_xchg, 2); V = spgk_xchg_buffer(s_xchg, 3);
+            DEV(spgk_memcpy_d2d(P, t->params, np * 4, st), "train: parameters into the exchange arena");
+            DEV(spgk_memcpy_d2d(M, t->m, np * 4, st), "train: moments into the exchange arena");
+            DEV(spgk_memcpy_d2d(V, t->v, np * 4, st), "train: moments into the exchange arena");
+            DEV(spgk_memset(G, 0, np * 4, st), "train: clear gradients");
+        }
+        spg_log(LOG_INFO, "train: gradient exchange over %s", fused_x ? "peer memory (one kernel per step)" : "NCCL all-reduce");
+    }
+
     /* save_spingalett called while this call runs (autosave, the callback) reads the device buffers */
-    n->live_params = t->params; n->live_m = t->m; n->live_v = t->v;
+    n->live_params = P; n->live_m = M; n->live_v = V;
 
     /* which output-layer path: cross-entropy over softmax / sigmoid has delta = a - t (Training.c:368-371) and, for at most
        16 outputs, a one-launch output end; everything else goes through the general delta kernel */
     const bool ce_direct = p->loss_func == LOSS_CROSS_ENTROPY && (out_act == ACT_SOFTMAX || out_act == ACT_SIGMOID);
     const bool fused_out = ce_direct && outw <= 16;
-    const bool clip = a.max_grad_norm > 0.0f && !online;
     float b1pow = 1.0f, b2pow = 1.0f;
     for (size_t epoch = 1; epoch <= a.epochs; epoch++) {
         const bool need_loss = should_report(epoch, a.epochs, a.report_interval) ||
@@ -331,13 +381,13 @@ void train_struct_arguments(TrainArgs a)
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 float *y = t->acts + (size_t)cur * p->neuron_offsets[l + 1];
                 if (l + 1 == last && fused_out) {
-                    DEV(spgk_train_output(x, fi, t->params + p->weight_offsets[l], fi, t->params + tw + p->bias_offsets[l], y, bt,
+                    DEV(spgk_train_output(x, fi, P + p->weight_offsets[l], fi, P + tw + p->bias_offsets[l], y, bt,
                                           d_last, need_loss ? d_loss : NULL, cur, fo, fi, out_act == ACT_SIGMOID, st),
                         "train: output layer");
                     break;
                 }
-                DEV(spgk_train_gemm(0, x, fi, t->params + p->weight_offsets[l], fi, y, fo, cur, fo, fi, 1.0f,
-                                    t->params + tw + p->bias_offsets[l], NULL, 0, (int)p->act_func[l], st), "train: forward");
+                DEV(spgk_train_gemm(0, x, fi, P + p->weight_offsets[l], fi, y, fo, cur, fo, fi, 1.0f,
+                                    P + tw + p->bias_offsets[l], NULL, 0, (int)p->act_func[l], st), "train: forward");
                 if (p->act_func[l] == ACT_SOFTMAX) DEV(spgk_softmax_rows(y, fo, cur, fo, st), "train: softmax");
                 x = y;
             }
@@ -359,24 +409,24 @@ void train_struct_arguments(TrainArgs a)
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 const float *dl = t->deltas + (size_t)cur * p->neuron_offsets[l + 1];
                 const float *al = l == 0 ? bx : t->acts + (size_t)cur * p->neuron_offsets[l];
-                DEV(spgk_train_grad(dl, fo, al, fi, t->grads + p->weight_offsets[l], fi, t->grads + tw + p->bias_offsets[l],
+                DEV(spgk_train_grad(dl, fo, al, fi, G + p->weight_offsets[l], fi, G + tw + p->bias_offsets[l],
                                     fo, fi, cur, gs, st), "train: gradients");
-                if (s_world > 1) {
+                if (s_world > 1 && !fused_x) {
                     DEV(spgk_event_record(s_ev_ready, st), "train: exchange order");
                     DEV(spgk_stream_wait_event(s_ar_stream, s_ev_ready), "train: exchange order");
                     if (l == 0)             /* the bias gradients of every layer are complete now: one launch for both */
-                        DEV(spgk_nccl_allreduce_sum2(s_comm, t->grads + p->weight_offsets[l], (uint64_t)fi * fo, t->grads + tw, tb,
+                        DEV(spgk_nccl_allreduce_sum2(s_comm, G + p->weight_offsets[l], (uint64_t)fi * fo, G + tw, tb,
                                                      s_ar_stream), "train: all-reduce");
                     else
-                        DEV(spgk_nccl_allreduce_sum(s_comm, t->grads + p->weight_offsets[l], (uint64_t)fi * fo, s_ar_stream),
+                        DEV(spgk_nccl_allreduce_sum(s_comm, G + p->weight_offsets[l], (uint64_t)fi * fo, s_ar_stream),
                             "train: all-reduce");
                 }
                 if (l > 0)
-                    DEV(spgk_train_gemm(1, dl, fo, t->params + p->weight_offsets[l], fi,
+                    DEV(spgk_train_gemm(1, dl, fo, P + p->weight_offsets[l], fi,
                                         t->deltas + (size_t)cur * p->neuron_offsets[l], fi, cur, fi, fo, 1.0f, NULL,
                                         t->acts + (size_t)cur * p->neuron_offsets[l], fi, (int)p->act_func[l - 1], st), "train: delta");
             }
-            if (s_world > 1) {
+            if (s_world > 1 && !fused_x) {
                 DEV(spgk_event_record(s_ev_done, s_ar_stream), "train: exchange order");
                 DEV(spgk_stream_wait_event(st, s_ev_done), "train: exchange order");
             }
@@ -386,13 +436,16 @@ void train_struct_arguments(TrainArgs a)
             const float mf = 1.0f / (1.0f - b1pow), vf = 1.0f / (1.0f - b2pow);
             if (clip) {
                 DEV(spgk_memset(d_sumsq, 0, 4, st), "train: clear norm");
-                DEV(spgk_sumsq(t->grads, np, d_sumsq, st), "train: gradient norm");
+                DEV(spgk_sumsq(G, np, d_sumsq, st), "train: gradient norm");
             }
-            if (a.optimizer_type == OPTIMIZER_ADAM && a.weight_decay <= 0.0f && !clip)
-                DEV(spgk_adam(t->params, t->m, t->v, t->grads, np, a.learning_rate, a.beta1, a.beta2, mf, vf, a.epsilon,
+            if (fused_x)
+                DEV(spgk_xchg_step(s_xchg, (int)a.optimizer_type, tw, a.learning_rate, a.momentum, a.beta1, a.beta2, mf, vf, a.epsilon,
+                                   a.weight_decay > 0.0f ? a.weight_decay : 0.0f, 1.0f / (float)s_world, st), "train: exchange and update");
+            else if (a.optimizer_type == OPTIMIZER_ADAM && a.weight_decay <= 0.0f && !clip)
+                DEV(spgk_adam(P, M, V, G, np, a.learning_rate, a.beta1, a.beta2, mf, vf, a.epsilon,
                               1.0f / (float)s_world, st), "train: adam");
             else
-                DEV(spgk_optimizer_step((int)a.optimizer_type, t->params, t->m, t->v, t->grads, np, tw, a.learning_rate, a.momentum,
+                DEV(spgk_optimizer_step((int)a.optimizer_type, P, M, V, G, np, tw, a.learning_rate, a.momentum,
                                         a.beta1, a.beta2, mf, vf, a.epsilon, a.weight_decay > 0.0f ? a.weight_decay : 0.0f,
                                         1.0f / (float)s_world, clip ? d_sumsq : NULL, a.max_grad_norm, st), "train: update");
         }
@@ -404,7 +457,7 @@ void train_struct_arguments(TrainArgs a)
         bool stop = false, nan_found = false;
         if (nan_now) {
             DEV(spgk_memset(d_flag, 0, 4, st), "train: clear flag");
-            DEV(spgk_nonfinite(t->params, np, d_flag, st), "train: nan scan");
+            DEV(spgk_nonfinite(P, np, d_flag, st), "train: nan scan");
         }
         if (need_loss || nan_now) {
             DEV(spgk_memcpy_d2h(h_pinned, t->words, 8, st), "train: read loss");
@@ -419,12 +472,15 @@ void train_struct_arguments(TrainArgs a)
             stop = true;
         }
         if (!stop && a.autosave_mode != AUTOSAVE_OFF && a.autosave_interval > 0 && a.autosave_path &&
-            should_report(epoch, a.epochs, a.autosave_interval) && s_rank == 0)
-            spg_autosave(n, &a, epoch);
+            should_report(epoch, a.epochs, a.autosave_interval)) {
+            /* the moments are current in their owners' shards only: collect them (every rank takes part) before rank 0 writes */
+            if (fused_x && !a.autosave_do_not_save_optimizer) DEV(spgk_xchg_gather(s_xchg, st), "train: gather optimiser state");
+            if (s_rank == 0) spg_autosave(n, &a, epoch);
+        }
         if (!stop && cb_now) {
             /* the callback may read the net: bring the host mirror up to date first */
-            DEV(spgk_memcpy_d2h(p->weights, t->params, tw * 4, st), "train: weights to host");
-            DEV(spgk_memcpy_d2h(p->biases, t->params + tw, tb * 4, st), "train: biases to host");
+            DEV(spgk_memcpy_d2h(p->weights, P, tw * 4, st), "train: weights to host");
+            DEV(spgk_memcpy_d2h(p->biases, P + tw, tb * 4, st), "train: biases to host");
             DEV(train_sync(st), "train: callback sync");
             if (a.callback(p, epoch, current_error)) {
                 spg_log(LOG_INFO, "Training interrupted by callback at epoch %zu", epoch);
@@ -442,16 +498,18 @@ void train_struct_arguments(TrainArgs a)
         }
         if (stop) break;
     }
+    if (fused_x) DEV(spgk_xchg_gather(s_xchg, st), "train: gather gradients and optimiser state");
     /* host mirrors of everything the reference leaves in the public struct */
-    DEV(spgk_memcpy_d2h(p->weights, t->params, tw * 4, st), "train: weights to host");
-    DEV(spgk_memcpy_d2h(p->biases, t->params + tw, tb * 4, st), "train: biases to host");
-    DEV(spgk_memcpy_d2h(p->grad_weights, t->grads, tw * 4, st), "train: gradients to host");
-    DEV(spgk_memcpy_d2h(p->grad_biases, t->grads + tw, tb * 4, st), "train: gradients to host");
-    DEV(spgk_memcpy_d2h(p->opt_m_weights, t->m, tw * 4, st), "train: m to host");
-    DEV(spgk_memcpy_d2h(p->opt_m_biases, t->m + tw, tb * 4, st), "train: m to host");
-    DEV(spgk_memcpy_d2h(p->opt_v_weights, t->v, tw * 4, st), "train: v to host");
-    DEV(spgk_memcpy_d2h(p->opt_v_biases, t->v + tw, tb * 4, st), "train: v to host");
+    DEV(spgk_memcpy_d2h(p->weights, P, tw * 4, st), "train: weights to host");
+    DEV(spgk_memcpy_d2h(p->biases, P + tw, tb * 4, st), "train: biases to host");
+    DEV(spgk_memcpy_d2h(p->grad_weights, G, tw * 4, st), "train: gradients to host");
+    DEV(spgk_memcpy_d2h(p->grad_biases, G + tw, tb * 4, st), "train: gradients to host");
+    DEV(spgk_memcpy_d2h(p->opt_m_weights, M, tw * 4, st), "train: m to host");
+    DEV(spgk_memcpy_d2h(p->opt_m_biases, M + tw, tb * 4, st), "train: m to host");
+    DEV(spgk_memcpy_d2h(p->opt_v_weights, V, tw * 4, st), "train: v to host");
+    DEV(spgk_memcpy_d2h(p->opt_v_biases, V + tw, tb * 4, st), "train: v to host");
     DEV(train_sync(st), "train: final sync");
+    if (fused_x) DEV(spgk_xchg_status(s_xchg, st), "train: gradient exchange");
     spg_log(LOG_INFO, "Training completed.");
     failed = false;
 fail:
@@ -459,6 +517,7 @@ fail:
     spgk_host_free(h_pinned);
     n->live_params = n->live_m = n->live_v = NULL;
     if (failed) spg_train_release(n);          /* after an error nothing of the device state is trusted */
+    if (failed && s_xchg) { spgk_xchg_destroy(s_xchg); s_xchg = NULL; }
     /* the inference image on the device (possibly a packed payload) no longer matches the weights */
     spg_dev_invalidate(n);
     spg_net_drop_payload(n);

@@ -1,8 +1,8 @@
 """Worker of the two-rank data-parallel training test (launched by torchrun, one process per GPU).
 
-Each rank trains one full-batch step on its own 256 rows; the library all-reduces the flat
-gradient with NCCL.  Rank 0 then checks the summed gradient against the oracle's gradient of the
-concatenated 512-row batch and that both replicas hold identical weights."""
+Each rank trains on its own 256 rows, once with the one-kernel exchange over peer memory and once with the NCCL
+all-reduce: the summed gradient of a full-batch step against the oracle's gradient of the concatenated batch, and
+weights, gradients and optimiser moments bit-identical on every rank after full-batch and mini-batch steps."""
 import os
 import sys
 
@@ -33,30 +33,56 @@ def main():
     assert lib.spingalett_dist_world() == world
 
     topo, acts = [784, 512, 1000, 10], [spg.abi.ACT_RELU, spg.abi.ACT_RELU, spg.abi.ACT_SOFTMAX]
-    net = spg.Network.build(topo, acts, spg.abi.WEIGHT_INITIALIZATION_HE, seed=1234)      # same seed: same replica
-    onet = OracleNet.from_arrays(net.topology, net.acts, net.weights, net.biases)
     rng = np.random.default_rng(7)
     x = rng.random((256 * world, 784), dtype=np.float32)
     tg = np.zeros((256 * world, 10), np.float32)
     tg[np.arange(256 * world), rng.integers(0, 10, 256 * world)] = 1.0
     mine = slice(256 * rank, 256 * (rank + 1))
-    net.train(x[mine], tg[mine], epochs=1, strategy=spg.abi.STRATEGY_FULL_BATCH, learning_rate=1e-3)
-    c = net.c
-    g = np.concatenate([np.ctypeslib.as_array(c.grad_weights, shape=(c.total_weights,)),
-                        np.ctypeslib.as_array(c.grad_biases, shape=(c.total_biases,))]).copy()
-    w = np.concatenate([net.weights, net.biases]).copy()
-    gathered = [torch.zeros(w.size) for _ in range(world)]
-    dist.all_gather(gathered, torch.from_numpy(w))
-    if rank == 0:
-        for other in gathered[1:]:
-            assert np.array_equal(other.numpy(), w), "replicas diverged"
+
+    def flat(c, a, b, na, nb):
+        return np.concatenate([np.ctypeslib.as_array(getattr(c, a), shape=(na,)), np.ctypeslib.as_array(getattr(c, b), shape=(nb,))]).copy()
+
+    def same_everywhere(v, what):
+        gathered = [torch.zeros(v.size) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(v))
+        for other in gathered:
+            assert np.array_equal(other.numpy(), v), what + ": replicas diverged"
+
+    results = {}
+    # the one-kernel exchange over peer memory (default) and the NCCL all-reduce
+    for mode in ("p2p", "nccl"):
+        os.environ["SPINGALETT_EXCHANGE"] = mode
+        net = spg.Network.build(topo, acts, spg.abi.WEIGHT_INITIALIZATION_HE, seed=1234)      # same seed: same replica
+        onet = OracleNet.from_arrays(net.topology, net.acts, net.weights, net.biases)
+        # one full-batch step: the summed gradient against the oracle's gradient of the concatenated batch
+        net.train(x[mine], tg[mine], epochs=1, strategy=spg.abi.STRATEGY_FULL_BATCH, learning_rate=1e-3)
+        c = net.c
+        nw, nb = int(c.total_weights), int(c.total_biases)
+        g = flat(c, "grad_weights", "grad_biases", nw, nb)
+        w = np.concatenate([net.weights, net.biases]).copy()
+        same_everywhere(w, mode + " weights")
+        same_everywhere(g, mode + " summed gradients")
         # summed per-rank gradients (each scaled 1/256) = world * gradient of the whole batch scaled 1/(256*world)
         og = onet.gradients(x, tg, 1.0 / (256 * world)) * world
         rel = np.linalg.norm(g - og) / np.linalg.norm(og)
-        assert rel <= 1e-4, rel
+        assert rel <= 1e-4, (mode, rel)
+        # several mini-batch steps with decay (AdamW): weights and both moments identical on every rank afterwards
+        net.train(x[mine], tg[mine], epochs=3, batch_size=64, learning_rate=1e-3, optimizer=spg.abi.OPTIMIZER_ADAMW, weight_decay=1e-2)
+        w2 = np.concatenate([net.weights, net.biases]).copy()
+        m2 = flat(net.c, "opt_m_weights", "opt_m_biases", nw, nb)
+        v2 = flat(net.c, "opt_v_weights", "opt_v_biases", nw, nb)
+        same_everywhere(w2, mode + " weights after mini-batch steps")
+        same_everywhere(m2, mode + " first moments")
+        same_everywhere(v2, mode + " second moments")
+        assert np.all(np.isfinite(w2)) and np.any(m2 != 0) and np.any(v2 != 0) and not np.array_equal(w2, w)
+        results[mode] = (g, w, w2, m2, v2)
+        net.free()
+    # the two exchanges add the ranks' gradients in different orders: equal up to fp32 rounding of the sums
+    for a_, b_ in zip(results["p2p"], results["nccl"]):
+        assert np.abs(a_ - b_).max() <= 1e-5 * max(1.0, float(np.abs(b_).max())), np.abs(a_ - b_).max()
+    if rank == 0:
         print("DIST_TRAIN_OK rel", rel, flush=True)
     lib.spingalett_dist_shutdown()
-    net.free()
     dist.barrier()
     dist.destroy_process_group()
 
