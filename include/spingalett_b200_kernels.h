@@ -410,6 +410,9 @@ SPGK_API int spgk_xchg_step(void *xchg, int kind, uint64_t n_weights, float lr, 
                             float eps, float decay, float gscale, void *stream);
 SPGK_API int spgk_xchg_gather(void *xchg, void *stream);
 SPGK_API int spgk_xchg_status(void *xchg, void *stream);
+/* the exchange's bounded wait on a flag nobody writes (16 uint32 of device scratch): leaves {1, 42, 7} in the first
+ * three words -- timed out, status code recorded, thread carried on; limit = polls (at most 2^20) */
+SPGK_API int spgk_selftest_xchg_wait(uint32_t *words16_dev, uint32_t limit, int sys_scope, void *stream);
 /* Failure handling of the exchange (all on the host; nothing here makes a GPU fault or hang):
  * spgk_nccl_init waits for the rendezvous at most SPINGALETT_DIST_TIMEOUT_MS milliseconds (environment, default 120000) and
  * returns SPGK_E_TIMEOUT when a rank never arrives; spgk_stream_sync_bounded waits for a stream by polling with the same

@@ -95,11 +95,11 @@ __device__ __forceinline__ uint32_t ld_flag_sys(const uint32_t *p)
 
 // polls until *p has reached `want` (wrap-safe); false when the bound was hit (status word set, caller carries on)
 template <bool SYS>
-__device__ __forceinline__ bool xg_wait(const uint32_t *p, uint32_t want, uint32_t *status, uint32_t code)
+__device__ __forceinline__ bool xg_wait(const uint32_t *p, uint32_t want, uint32_t *status, uint32_t code, uint32_t limit = XG_WAIT_LIMIT)
 {
     uint32_t polls = 0;
     while ((int32_t)((SYS ? ld_flag_sys(p) : ld_acquire_gpu(p)) - want) < 0) {
-        if (++polls > XG_WAIT_LIMIT) { atomicExch(status, code); return false; }
+        if (++polls > limit) { atomicExch(status, code); return false; }
         if (polls > 64) __nanosleep(50);
     }
     return true;
@@ -218,6 +218,15 @@ spg_xchg_gather_kernel(const XchgParams p)
     xg_barrier(p, 1, false);                             // nobody reads this rank's shards any more
 }
 
+// the exchange's wait on a flag that nobody sets, with a small bound: out[0] = 1 when the wait reported the time-out,
+// out[1] = the status word it left, out[2] = 7 once the thread has carried on past it
+__global__ void spg_xchg_wait_selftest_kernel(uint32_t *words, uint32_t limit, int sys_scope)
+{
+    const bool ok = sys_scope ? xg_wait<true>(words + 8, 1u, words + 1, 42u, limit) : xg_wait<false>(words + 8, 1u, words + 1, 42u, limit);
+    words[0] = ok ? 0u : 1u;
+    words[2] = 7u;
+}
+
 void xg_fill(const Xchg *x, XchgParams *p)
 {
     memset(p, 0, sizeof *p);
@@ -318,6 +327,16 @@ void spgk_xchg_destroy(void *xv)
     for (int q = 0; q < x->world; q++) if (x->peer[q]) cudaIpcCloseMemHandle(x->peer[q]);
     cudaFree(x->arena);
     delete x;
+}
+
+// Failure-path check without a failure: runs the exchange's bounded wait on a flag that is never written.  words3
+// (device, 3 x uint32 of the caller) receives {1, 42, 7}: timed out, status code recorded, thread carried on.
+int spgk_selftest_xchg_wait(uint32_t *words16_dev, uint32_t limit, int sys_scope, void *stream)
+{
+    if (!words16_dev || limit == 0 || limit > (1u << 20)) { spgk_set_error("spgk_selftest_xchg_wait", "bad argument"); return SPGK_E_ARG; }
+    if (cudaMemsetAsync(words16_dev, 0, 64, (cudaStream_t)stream) != cudaSuccess) { spgk_set_error("spgk_selftest_xchg_wait", cudaGetErrorString(cudaGetLastError())); return SPGK_E_CUDA; }
+    spg_xchg_wait_selftest_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(words16_dev, limit, sys_scope);
+    return spgk_check_launch("spg_xchg_wait_selftest_kernel");
 }
 
 uint64_t spgk_xchg_capacity(const void *xv) { return xv ? static_cast<const Xchg *>(xv)->np : 0; }

@@ -726,3 +726,17 @@ def test_injected_allocation_failures_are_reported_and_leak_nothing(spg, k):
             net.free()
             break
     assert seen_fail >= 10 and worked                                  # every allocation site was hit once, then the sweep ran through
+
+
+@pytest.mark.parametrize("sys_scope", [0, 1])
+def test_exchange_wait_times_out_and_carries_on(spg, k, sys_scope):
+    """The peer-memory exchange's wait (device and system scope flavours) on a flag that nothing sets: after its bound the
+    wait reports the time-out, records its code in the status word and the thread carries on -- no hang, the context stays
+    usable (a kernel launched afterwards runs)."""
+    import torch
+    words = torch.full((16,), 99, dtype=torch.int32, device="cuda")
+    k.spgk_selftest_xchg_wait.argtypes = [C.c_void_p, C.c_uint32, C.c_int, C.c_void_p]
+    assert k.spgk_selftest_xchg_wait(words.data_ptr(), 2000, sys_scope, None) == 0, k.spgk_error_string()
+    torch.cuda.synchronize()
+    assert words[:3].tolist() == [1, 42, 7]
+    assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
