@@ -41,7 +41,7 @@ constexpr uint32_t XG_THREADS = 256;
 // then per phase the local CTA counter and the local release flag, then the status word
 constexpr uint32_t XG_LINE = 32;
 constexpr uint32_t XG_FLAG0 = 0, XG_CNT0 = 2 * XG_MAX_WORLD * XG_LINE, XG_GO0 = XG_CNT0 + 2 * XG_LINE, XG_STATUS_WORD = XG_GO0 + 2 * XG_LINE;
-constexpr int XG_UNROLL = 4;                            // elements of 4 floats a thread has in flight: all peer loads of a batch are issued before the first is used
+constexpr int XG_UNROLL = 2;                            // elements of 4 floats a thread works on at a time: the loads of every rank's copy of them (up to 16 x 16 bytes) are issued before the first is used -- a warp issues in order, so a sum placed between two loads would make the second wait for the first's round trip over NVLink
 constexpr size_t XG_HEAD_BYTES = 16384;                 // flags + status, padded (keeps the buffers 256-byte aligned)
 constexpr uint32_t XG_WAIT_LIMIT = 1u << 23;            // polls of 50 ns or more each before a wait gives up (about half a second)
 
@@ -162,19 +162,27 @@ spg_xchg_step_kernel(const XchgParams p)
     float *M = xg_buf(p.arena[p.rank], 2, p.np_pad), *V = xg_buf(p.arena[p.rank], 3, p.np_pad);
     const float omb1 = 1.0f - p.b1, omb2 = 1.0f - p.b2;
     for (uint64_t i0 = lo + 4ull * threadIdx.x; i0 < hi; i0 += 4ull * XG_THREADS * XG_UNROLL) {
+        float4 g[XG_MAX_WORLD][XG_UNROLL];
+#pragma unroll
+        for (uint32_t q = 0; q < XG_MAX_WORLD; q++) {
+            if (q < p.world) {
+                const float *Gq = q == p.rank ? G : xg_buf(p.arena[q], 0, p.np_pad);
+#pragma unroll
+                for (int u = 0; u < XG_UNROLL; u++) {
+                    const uint64_t i = i0 + 4ull * XG_THREADS * u;
+                    g[q][u] = i < hi ? ld_peer(Gq + base + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+        }
         float4 s[XG_UNROLL];
 #pragma unroll
         for (int u = 0; u < XG_UNROLL; u++) s[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (uint32_t q = 0; q < p.world; q++) {         // rank order: the sum is the same whoever computes it
-            const float *Gq = q == p.rank ? G : xg_buf(p.arena[q], 0, p.np_pad);
-            float4 g[XG_UNROLL];
 #pragma unroll
-            for (int u = 0; u < XG_UNROLL; u++) {
-                const uint64_t i = i0 + 4ull * XG_THREADS * u;
-                g[u] = i < hi ? ld_peer(Gq + base + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t q = 0; q < XG_MAX_WORLD; q++) {     // rank order: the sum is the same whoever computes it
+            if (q < p.world) {
+#pragma unroll
+                for (int u = 0; u < XG_UNROLL; u++) { s[u].x += g[q][u].x; s[u].y += g[q][u].y; s[u].z += g[q][u].z; s[u].w += g[q][u].w; }
             }
-#pragma unroll
-            for (int u = 0; u < XG_UNROLL; u++) { s[u].x += g[u].x; s[u].y += g[u].y; s[u].z += g[u].z; s[u].w += g[u].w; }
         }
 #pragma unroll
         for (int u = 0; u < XG_UNROLL; u++) {
