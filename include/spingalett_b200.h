@@ -306,9 +306,11 @@ SPINGALETT_API int spingalett_synchronize(NeuralNetwork *net);
  *         99.9 % parity bar.
  * AUTO (default): the FAST pass, then every row whose two largest softmax
  *         outputs are within a margin (log p1 - log p2 < margin) is recomputed
- *         in EXACT mode and written over the fast result, so every argmax is the
- *         EXACT one at close to FAST cost; the probabilities of the other rows
- *         keep the FAST error (<= 3e-4 measured with fp16, against a 2e-3 bar).
+ *         in EXACT mode and written over the fast result (so is a row whose
+ *         FAST result is not finite: an input or hidden value beyond the fp16
+ *         range); the argmax is then expected to be the EXACT one at close to
+ *         FAST cost, and the probabilities of the other rows keep the FAST
+ *         error (<= 3e-4 measured with fp16, against a 2e-3 bar).
  *         The margin is measured, not guessed: on the first AUTO call after a
  *         net's weights reach the GPU both modes run on up to 2048 rows of the
  *         batch and the margin becomes four times the largest change of the
@@ -316,6 +318,11 @@ SPINGALETT_API int spingalett_synchronize(NeuralNetwork *net);
  *         change is below 0.002 with fp16 operands, 0.013 with bf16).
  *         spingalett_set_auto_margin(m > 0) fixes the margin instead; 0 returns
  *         to calibration.  Networks that do not end in softmax run EXACT.
+ *         LIMIT: the calibration runs once per net, on the first large batch it
+ *         sees, and is not repeated when the inputs change character; AUTO's
+ *         agreement with EXACT is that measurement's expectation (the parity
+ *         tests allow 3 differing rows in 16384), not a guarantee.  Callers
+ *         that need the guarantee use SPINGALETT_MATH_EXACT.
  * The small-batch paths always use exact products (they are memory-bound). */
 typedef enum { SPINGALETT_MATH_FAST = 0, SPINGALETT_MATH_EXACT = 1, SPINGALETT_MATH_AUTO = 2 } SpingalettMathMode;
 SPINGALETT_API void spingalett_set_math_mode(SpingalettMathMode mode);
@@ -355,9 +362,14 @@ SPINGALETT_API void spingalett_seed(uint64_t seed);
 /* Data-parallel training, one process per GPU.  Rank 0 creates a 128-byte id
  * (spingalett_dist_unique_id) and passes it to the other ranks over any host
  * channel; every rank then calls spingalett_dist_init(rank, world, id).  From
- * then on train() sums the flat gradient buffer [gW | gB] across ranks with one
- * NCCL all-reduce per step and Adam divides by `world`, which keeps replicas
- * bit-identical.  The reference has no multi-process mode; single-rank train()
+ * then on every step of train() sums the flat gradient buffer [gW | gB] across
+ * ranks and applies the update with the 1/world average folded in: by default in
+ * one kernel per rank over peer memory (CUDA IPC between the processes of one
+ * node; shard r is summed in rank order and updated by rank r, the new weights
+ * are stored into every replica), else with NCCL all-reduces (when a rank cannot
+ * map its peers, with gradient clipping, or with SPINGALETT_EXCHANGE=nccl in the
+ * environment; the ranks vote, so all take the same way).  Either way the
+ * replicas stay bit-identical.  The reference has no multi-process mode; single-rank train()
  * behaves like its batched trainer (Training.c:691-817). */
 SPINGALETT_API int spingalett_dist_unique_id(void *id128);
 SPINGALETT_API int spingalett_dist_init(int rank, int world, const void *id128);
