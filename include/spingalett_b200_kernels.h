@@ -250,6 +250,10 @@ SPGK_API int spgk_wstream_status(void *scratch, void *stream);
  * Does batch_forward()'s layer step, reference Training.c:318-343. */
 SPGK_API int spgk_gemm_tc_supported(const spgk_layer *L);
 SPGK_API uint32_t spgk_gemm_tc_softmax_max(void);
+/* whether spgk_layer_gemm_tc finishes a softmax layer of `width` columns in its own epilogue for `rows` rows: rows that fit one
+ * tile (256 columns) always; up to 1024 columns when the batch has at least 64 row tiles and its row count is known on the
+ * host (the CTA then owns whole row tiles: logits written, then normalised row by row; Activation.c:5-21) */
+SPGK_API int spgk_gemm_tc_softmax_fusable(uint32_t width, uint32_t rows, int dynamic_rows);
 SPGK_API int spgk_weights16_direct(const spgk_layer *L, int type16);
 SPGK_API size_t spgk_weights16_bytes(const spgk_layer *L, int parts);
 SPGK_API int spgk_dequant16(const spgk_layer *L, void *dst, uint32_t ldw, uint64_t plane, int parts,

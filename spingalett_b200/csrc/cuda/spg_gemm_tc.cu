@@ -34,7 +34,8 @@ constexpr uint32_t EPI_WARPS = 8;       // two warps per TMEM lane quadrant, eac
 constexpr uint32_t NUM_THREADS = 64 + 32 * EPI_WARPS;   // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2.. epilogue
 constexpr uint32_t WAIT_LIMIT = 1u << 16;    // attempts; each may suspend the warp for up to SPG_WAIT_HINT_NS
 constexpr uint32_t MAX_PASSES = 4;
-constexpr uint32_t SOFTMAX_FUSE_MAX = 256;
+constexpr uint32_t SOFTMAX_FUSE_MAX = 256;       // a row that fits one tile
+constexpr uint32_t SOFTMAX_WIDE_MAX = 1024;      // a row over up to four column tiles of a CTA that owns the row tile
 constexpr uint32_t STG_PITCH = 80;                        // bytes per staged row: 32 columns x 2 bytes + 16 (bank spread for 16-byte accesses)
 constexpr uint32_t PATCH_BYTES = 32 * 128;                 // TMA-store patch: 32 rows x 64 columns, 128-byte swizzled rows
 constexpr uint32_t STG_BYTES = EPI_WARPS * PATCH_BYTES;    // per epilogue warp: one patch (the register-store path uses 32 x STG_PITCH of it)
@@ -54,6 +55,7 @@ struct GemmParams {
     float *out32; uint32_t ldo32;
     int32_t *status;
     // optional narrow last layer ("head") finished inside this layer's epilogue: out = head_act(head_bias + head_scale * Wh * act(...))
+    uint32_t own_rows;            // a CTA owns whole row tiles and walks their column tiles in order (fused head, wide fused softmax)
     const float *head_w;          // [round_up(N, 32)][HP] fp32, unscaled, rows beyond N zero (staged into shared memory)
     const float *head_bias; float head_scale; uint32_t head_out, head_hp; int head_act, head_softmax;
     uint32_t stg_bytes;           // bytes of the epilogue's shared-memory region (patches, or head weights + exchange)
@@ -102,7 +104,7 @@ __device__ __forceinline__ void tile_coords(const GemmParams &p, const RowLimit 
 // a CTA owns whole row tiles (all their column tiles in a row), because the head sums over every column of a row.
 __device__ __forceinline__ uint32_t my_tile_count(const GemmParams &p, const RowLimit &rl)
 {
-    if (p.head_w) {
+    if (p.own_rows) {
         const uint32_t rt = rl.m_tiles > blockIdx.x ? (rl.m_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         return rt * p.n_tiles;
     }
@@ -111,7 +113,7 @@ __device__ __forceinline__ uint32_t my_tile_count(const GemmParams &p, const Row
 }
 __device__ __forceinline__ void my_tile(const GemmParams &p, const RowLimit &rl, uint32_t i, uint32_t &m_tile, uint32_t &n_tile)
 {
-    if (p.head_w) { m_tile = blockIdx.x + (i / p.n_tiles) * gridDim.x; n_tile = i % p.n_tiles; }
+    if (p.own_rows) { m_tile = blockIdx.x + (i / p.n_tiles) * gridDim.x; n_tile = i % p.n_tiles; }
     else tile_coords(p, rl, blockIdx.x + i * gridDim.x, m_tile, n_tile);
 }
 
@@ -418,6 +420,97 @@ __device__ __forceinline__ void epilogue_softmax(const GemmParams &p, const RowL
     }
 }
 
+// Fused row softmax for rows wider than one tile (up to SOFTMAX_WIDE_MAX columns; the CTA owns the row tile and walks its
+// column tiles in order).  Per column tile the row's thread (lower column-half warps, one thread per TMEM lane) adds
+// scale and bias, keeps the two largest logits seen so far and writes the raw logits to the output.  After the last
+// column tile both warps of a quadrant share the tile's rows: a row at a time, lanes across the columns (coalesced),
+// they read the row's logits once into registers, sum expf(v - max), apply the margin test and write expf(v - max) / sum
+// -- the arithmetic of the reference's three sweeps (Activation.c:5-21), the division only when the sum is positive.
+__device__ __forceinline__ void epilogue_softmax_wide(const GemmParams &p, const RowLimit &rl, uint32_t rows, uint32_t tmem_base, uint32_t tfull0,
+                                                      uint32_t tempty0, uint32_t hx0, volatile int *abort_flag, uint32_t warp, uint32_t lane,
+                                                      uint8_t *stage)
+{
+    const uint32_t q = warp & 3u, half = (warp - 2u) >> 2;
+    const uint32_t ntile = my_tile_count(p, rl);
+    float4 *slots = reinterpret_cast<float4 *>(stage);           // [2 row-tile parities][128 rows] {max, second, output row, row}
+    float mx = -FLT_MAX, second = -FLT_MAX;
+    for (uint32_t tcount = 0; tcount < ntile; tcount++) {
+        uint32_t mt, nt;
+        my_tile(p, rl, tcount, mt, nt);
+        const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(tfull0 + 8 * acc, acc_ph, abort_flag, p.status, 4)) break;
+        tc_fence_after();
+        const uint32_t row = mt * BM + q * 32u + lane;
+        const uint32_t orow = row < rows ? (p.out_rows ? p.out_rows[row] : row) : 0xFFFFFFFFu;
+        if (half == 0) {
+            if (nt == 0) { mx = -FLT_MAX; second = -FLT_MAX; }
+            const uint32_t col0 = nt * p.BN, cols = p.N - col0 < p.BN ? p.N - col0 : p.BN;
+            const uint32_t taddr = tmem_base + acc * p.BN + ((q * 32u) << 16);
+            float *orow_ptr = p.out32 + (uint64_t)orow * p.ldo32 + col0;
+            const bool vec = (p.ldo32 & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.out32) & 15u) == 0;      // 16-byte stores (BN is a multiple of 4)
+            for (uint32_t c0 = 0; c0 < cols; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    v[i] = c0 + i < cols ? fmaf(__uint_as_float(r[i]), p.scale, p.bias[col0 + c0 + i]) : -FLT_MAX;
+                    if (v[i] > mx) { second = mx; mx = v[i]; } else if (v[i] > second) second = v[i];
+                }
+                if (orow != 0xFFFFFFFFu) {
+                    if (vec && c0 + 16 <= cols) {
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4 *>(orow_ptr + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) if (c0 + i < cols) orow_ptr[c0 + i] = v[i];
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        mbar_arrive(tempty0 + 8 * acc);
+        if (nt + 1 != p.n_tiles) continue;
+        // ---- the row tile is complete ----
+        const uint32_t rt = tcount / p.n_tiles;                   // this CTA's row-tile counter: slot and barrier parity
+        float4 *slot = slots + (rt & 1u) * BM + q * 32u;
+        if (half == 0) {
+            slot[lane] = make_float4(mx, second, __uint_as_float(orow), __uint_as_float(row));
+            __threadfence_block();                               // the raw logits and the slot, before the other warp is told
+            mbar_arrive(hx0 + 8 * q);                            // (the barrier counts 32 arrivals: every lane)
+            __syncwarp();
+        } else if (!mbar_wait(hx0 + 8 * q, rt & 1u, abort_flag, p.status, 5)) break;
+        for (uint32_t rr = 0; rr < 16; rr++) {
+            const float4 st = slot[half * 16u + rr];
+            const uint32_t o = __float_as_uint(st.z);
+            if (o == 0xFFFFFFFFu) continue;                      // a row beyond the batch (the same for the whole warp)
+            float *out = p.out32 + (uint64_t)o * p.ldo32;
+            // the whole row in registers (32 values per lane, all loads in flight at once), each value through expf once
+            float e[SOFTMAX_WIDE_MAX / 32];
+#pragma unroll
+            for (uint32_t j = 0; j < SOFTMAX_WIDE_MAX / 32; j++) {
+                const uint32_t c = lane + 32u * j;
+                e[j] = c < p.N ? out[c] : 0.0f;
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (uint32_t j = 0; j < SOFTMAX_WIDE_MAX / 32; j++)
+                if (lane + 32u * j < p.N) { e[j] = expf(e[j] - st.x); sum += e[j]; }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            // log p1 - log p2 of the softmax equals the gap of the two largest logits; a row whose one-term pass left the
+            // 16-bit range (non-finite logits or sum) is listed as well
+            if (lane == 0 && p.margin_idx && p.N >= 2 && (!(st.x - st.y >= p.margin_theta) || !(sum < FLT_MAX)))
+                p.margin_idx[atomicAdd(p.margin_count, 1u)] = __float_as_uint(st.w);
+            const float inv = sum > 0.0f ? 1.0f / sum : 1.0f;
+#pragma unroll
+            for (uint32_t j = 0; j < SOFTMAX_WIDE_MAX / 32; j++)
+                if (lane + 32u * j < p.N) out[lane + 32u * j] = e[j] * inv;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_o, const GemmParams p)
@@ -547,7 +640,10 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         else if (p.head_hp == 12) epilogue_loop<ACTV, 12>(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0); \
         else epilogue_loop<ACTV, 16>(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane, stage, &map_o, hx0)
         switch (p.softmax ? -1 : p.act) {
-            case -1:               epilogue_softmax(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane); break;
+            case -1:
+                if (p.n_tiles == 1) epilogue_softmax(p, rl, rows, tmem_base, tfull0, tempty0, abort_flag, warp, lane);
+                else epilogue_softmax_wide(p, rl, rows, tmem_base, tfull0, tempty0, hx0, abort_flag, warp, lane, stage);
+                break;
             case SPG_ACT_RELU:     SPG_EPI(SPG_ACT_RELU); break;
             case SPG_ACT_LEAKY:    SPG_EPI(SPG_ACT_LEAKY); break;
             case SPG_ACT_FOO52:    SPG_EPI(SPG_ACT_FOO52); break;
@@ -664,6 +760,15 @@ extern "C" {
 
 uint32_t spgk_gemm_tc_softmax_max(void) { return SOFTMAX_FUSE_MAX; }
 
+// Whether a softmax layer of this width is finished inside the GEMM's epilogue for a batch of `rows`: always when the row
+// fits one tile; up to SOFTMAX_WIDE_MAX columns when there are enough row tiles to give most SMs one (a CTA then owns
+// whole row tiles), and not for a device-resident row count (a handful of rows would leave the layer to a few CTAs).
+int spgk_gemm_tc_softmax_fusable(uint32_t width, uint32_t rows, int dynamic_rows)
+{
+    if (width <= SOFTMAX_FUSE_MAX) return 1;
+    return (width <= SOFTMAX_WIDE_MAX && !dynamic_rows && rows >= 64u * BM) ? 1 : 0;
+}
+
 int spgk_gemm_tc_supported(const spgk_layer *L)
 {
     if (!L || L->in == 0 || L->out == 0) return 0;
@@ -730,7 +835,7 @@ static int gemm_launch(const spgk_layer *L,
                        const spgk_layer *head, const float *head_w)
 {
     if (!L || !w16 || !a16 || !L->bias || (!out16 && !out32) || !status || a_parts < 1 || a_parts > 2 || w_parts < 1 || w_parts > 2 ||
-        (out16 && (ldo16 & 7u)) || (softmax_fused && (!out32 || L->out > SOFTMAX_FUSE_MAX))) {
+        (out16 && (ldo16 & 7u)) || (softmax_fused && (!out32 || L->out > SOFTMAX_WIDE_MAX))) {
         spgk_set_error("spgk_layer_gemm_tc", "bad argument");
         return SPGK_E_ARG;
     }
@@ -787,7 +892,8 @@ static int gemm_launch(const spgk_layer *L,
     p.scale = L->w_scale; p.bias = L->bias;
     p.act = L->act == SPG_ACT_SOFTMAX ? SPG_ACT_NONE : L->act;
     p.softmax = softmax_fused ? 1 : 0;
-    if (softmax_fused && p.n_tiles != 1) { spgk_set_error("spgk_layer_gemm_tc", "softmax row does not fit one tile"); return SPGK_E_ARG; }
+    if (softmax_fused && p.n_tiles != 1 && L->out > SOFTMAX_WIDE_MAX) { spgk_set_error("spgk_layer_gemm_tc", "softmax row wider than the fused epilogue takes"); return SPGK_E_ARG; }
+    p.own_rows = (head || (softmax_fused && p.n_tiles != 1)) ? 1u : 0u;
     p.out16 = out16; p.ldo16 = ldo16; p.o_plane = o_plane; p.out_parts = out_parts; p.type16 = type16;
     p.out32 = out32; p.ldo32 = ldo32;
     p.status = status;
@@ -808,7 +914,7 @@ static int gemm_launch(const spgk_layer *L,
         rc = make_map(&map_o, out16, type16, ldo16, N, ldo16, o_plane, 1, 32);
         if (rc) return rc;
     }
-    const uint32_t tiles = head ? p.m_tiles : p.m_tiles * p.n_tiles;       // with a head a CTA owns whole row tiles
+    const uint32_t tiles = p.own_rows ? p.m_tiles : p.m_tiles * p.n_tiles;   // with a head or a wide softmax a CTA owns whole row tiles
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
     const size_t smem = 1024 + (size_t)stages * stage_bytes + p.stg_bytes + 8 * (2 * stages + 8) + 64;
     SPGK_CUDA(spg_launch_chained(spg_gemm_tc_kernel, dim3(grid), dim3(NUM_THREADS), smem, (cudaStream_t)stream, map_a, map_w, map_o, p));

@@ -588,7 +588,7 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
     for (uint32_t l = 0; l < n->dev_layers; l++) {
         const spgk_layer *L = &n->klayers[l];
         bool last = l + 1 == n->dev_layers;
-        bool fuse_sm = L->act == ACT_SOFTMAX && L->out <= spgk_gemm_tc_softmax_max();
+        bool fuse_sm = L->act == ACT_SOFTMAX && spgk_gemm_tc_softmax_fusable(L->out, N, dynamic_rows ? 1 : 0);
         void *o16 = last ? NULL : n->d_act16[(l + 1) & 1];
         float *o32 = last ? d_out : NULL;
         const void *w16 = NULL;
@@ -710,7 +710,7 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     if (theta <= 0.0f && n->auto_calibrated) theta = n->auto_theta;
     /* with the margin known in advance, the softmax epilogue of the last layer picks the rows out itself */
     const spgk_layer *Llast = &n->klayers[n->dev_layers - 1];
-    const bool sink = theta > 0.0f && Llast->out <= spgk_gemm_tc_softmax_max();
+    const bool sink = theta > 0.0f && (fused || spgk_gemm_tc_softmax_fusable(Llast->out, N, 0));
     if (sink && (rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "repair count clear"))) return rc;
     if (fused) {
         rc = fused_pass(n, d_x, N, d_out, false, NULL, NULL, 0, theta, sink ? n->d_rep_idx : NULL, sink ? d_count : NULL);

@@ -77,9 +77,14 @@ def main():
         assert np.all(np.isfinite(w2)) and np.any(m2 != 0) and np.any(v2 != 0) and not np.array_equal(w2, w)
         results[mode] = (g, w, w2, m2, v2)
         net.free()
-    # the two exchanges add the ranks' gradients in different orders: equal up to fp32 rounding of the sums
-    for a_, b_ in zip(results["p2p"], results["nccl"]):
-        assert np.abs(a_ - b_).max() <= 1e-5 * max(1.0, float(np.abs(b_).max())), np.abs(a_ - b_).max()
+    # the two exchanges add the ranks' gradients in different orders: the summed gradients agree to fp32 rounding of the
+    # sums; weights and moments after Adam steps agree loosely (an element whose gradient is rounding noise may step the
+    # other way), which is a sanity check, not a parity claim -- the claims are the per-mode checks above
+    names = ("summed gradient", "weights after one step", "weights after mini-batch steps", "first moments", "second moments")
+    for name, a_, b_ in zip(names, results["p2p"], results["nccl"]):
+        diff = float(np.abs(a_ - b_).max())
+        bound = (1e-5 if name == "summed gradient" else 5e-3) * max(1.0, float(np.abs(b_).max()))
+        assert diff <= bound, (name, diff, bound)
     if rank == 0:
         print("DIST_TRAIN_OK rel", rel, flush=True)
     lib.spingalett_dist_shutdown()
@@ -88,4 +93,11 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        # torchrun's own summary buries the rank's traceback: leave it where the test can find it
+        import traceback
+        with open(os.path.join(sys.argv[1], f"rank{os.environ.get('RANK', '0')}.err"), "w") as f:
+            traceback.print_exc(file=f)
+        raise

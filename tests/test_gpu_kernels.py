@@ -664,6 +664,57 @@ def test_softmax_edge_table_on_the_row_block_and_fused_kernels(spg, k):
             assert np.abs(got - want).max() <= tol, (i, np.abs(got - want).max())
 
 
+@pytest.mark.parametrize("rows,width,K", [(8192, 1000, 64), (8300, 1024, 136), (9000, 513, 72)])
+def test_wide_softmax_fused_in_the_gemm_epilogue(spg, k, rows, width, K):
+    """A softmax layer wider than one 256-column tile, finished inside the GEMM kernel (the CTA owns the row tile: raw logits
+    per column tile, then sum and normalisation row by row) against float64 on the same two-term operands, with the margin
+    list it writes on the way; the last row tile is ragged."""
+    import torch
+    k.spgk_gemm_tc_softmax_fusable.argtypes = [C.c_uint32, C.c_uint32, C.c_int]
+    assert k.spgk_gemm_tc_softmax_fusable(width, rows, 0) == 1
+    assert k.spgk_gemm_tc_softmax_fusable(width, rows, 1) == 0 and k.spgk_gemm_tc_softmax_fusable(width, 4096, 0) == 0
+    assert k.spgk_gemm_tc_softmax_fusable(200, 5, 1) == 1 and k.spgk_gemm_tc_softmax_fusable(1025, rows, 0) == 0
+    rng = np.random.default_rng(rows + width)
+    w = (rng.standard_normal((width, K)) * 2.0 / np.sqrt(K)).astype(np.float32)
+    b = (rng.standard_normal(width) * 0.3).astype(np.float32)
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    ld = (K + 7) & ~7
+    wd, bd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda(), torch.from_numpy(x).cuda()
+    L = spg.abi.KLayer(wd.data_ptr(), bd.data_ptr(), 1.0, K, width, 0, 5)
+    a16 = torch.zeros((2, rows, ld), dtype=torch.bfloat16, device="cuda")
+    assert k.spgk_split16(xd.data_ptr(), K, rows, K, a16.data_ptr(), ld, rows * ld, 2, 1, None) == 0
+    w16 = torch.zeros((2, width, ld), dtype=torch.bfloat16, device="cuda")
+    assert k.spgk_dequant16(C.byref(L), w16.data_ptr(), ld, width * ld, 2, 1, None) == 0
+    out = torch.full((rows + 1, width), -7.0, device="cuda")
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    idx = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    count = torch.zeros(4, dtype=torch.int32, device="cuda")
+    theta = 0.02
+    k.spgk_set_margin_sink.argtypes = [C.c_float, C.c_void_p, C.c_void_p]
+    k.spgk_set_margin_sink(theta, idx.data_ptr(), count.data_ptr())
+    try:
+        rc = k.spgk_layer_gemm_tc(C.byref(L), w16.data_ptr(), ld, width * ld, 2, 1, a16.data_ptr(), ld, rows * ld, 2, 1,
+                                  None, 0, 0, 1, out.data_ptr(), width, rows, 1, status.data_ptr(), None)
+    finally:
+        k.spgk_set_margin_sink(0.0, None, None)
+    assert rc == 0, k.spgk_error_string()
+    assert k.spgk_gemm_tc_status(status.data_ptr(), None) == 0, k.spgk_error_string()
+    got = out.cpu().numpy()
+    assert np.all(got[rows] == -7.0)                                     # nothing written past the batch
+    xs = a16.float().cpu().numpy()[:, :, :K].astype(np.float64).sum(0)
+    ws = w16.float().cpu().numpy()[:, :, :K].astype(np.float64).sum(0)
+    z = xs @ ws.T + b.astype(np.float64)
+    want = _softmax(z)
+    assert np.abs(got[:rows] - want).max() <= 2e-5, np.abs(got[:rows] - want).max()      # fp32 accumulation of logits up to about 8
+    assert np.allclose(got[:rows].sum(1), 1.0, atol=1e-5)
+    srt = np.sort(z, axis=1)
+    gap = srt[:, -1] - srt[:, -2]
+    n = int(count[0].item())
+    flagged = set(idx.cpu().numpy()[:n].tolist())
+    assert len(flagged) == n and n > 0
+    assert set(np.nonzero(gap < theta - 1e-4)[0].tolist()) <= flagged <= set(np.nonzero(gap < theta + 1e-4)[0].tolist())
+
+
 def test_a_bounded_device_wait_that_runs_out_is_reported_not_hung(spg, k):
     """A barrier nobody arrives on, waited for with the tensor-core kernels' own bounded waits and a small limit: the kernel
     returns by itself, the status word carries the wait's code, the host call answers SPGK_E_TIMEOUT (which the library

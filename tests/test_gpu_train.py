@@ -221,20 +221,23 @@ def test_autosave_writes_the_device_state_and_state_survives_calls(spg, oracle, 
     net.free()
 
 
-def test_two_rank_data_parallel_step(spg, tmp_path):
-    """Two processes, one GPU each: the all-reduced gradient equals the gradient of the concatenated
-    batch and both replicas end bit-identical.  Needs two GPUs."""
-    if spg.lib().spingalett_get_device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_two_rank_data_parallel_step(spg, tmp_path, world):
+    """`world` processes, one GPU each, through both gradient exchanges (the one-kernel exchange over peer memory and the
+    NCCL all-reduce): the summed gradient equals the gradient of the concatenated batch, and weights, gradients and
+    optimiser moments end bit-identical on every rank.  Needs `world` GPUs."""
+    if spg.lib().spingalett_get_device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import os
     import subprocess
     import sys
     worker = os.path.join(os.path.dirname(__file__), "dist_train_worker.py")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", str(__import__("random").randint(20000, 39999)), worker, str(tmp_path)],
                        capture_output=True, text=True, env=env, timeout=600)
-    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    notes = "".join(open(os.path.join(str(tmp_path), f)).read()[-1500:] for f in sorted(os.listdir(str(tmp_path))) if f.endswith(".err"))
+    assert r.returncode == 0, notes + r.stdout[-1000:] + r.stderr[-1000:]
     assert "DIST_TRAIN_OK" in r.stdout
 
 
