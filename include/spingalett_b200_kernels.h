@@ -73,6 +73,7 @@ SPGK_API int spgk_memset(void *dev, int value, size_t bytes, void *stream);
 SPGK_API int spgk_stream_sync(void *stream);
 /* 1 if ptr is device (or managed) memory, 0 if host, <0 on error */
 SPGK_API int spgk_is_device_pointer(const void *ptr);
+SPGK_API int spgk_is_pinned_host_pointer(const void *ptr);   /* 1: page-locked host memory, 0: pageable or unknown */
 /* number of kernel launches made through this shim by the calling process */
 SPGK_API uint64_t spgk_launch_count(void);
 
@@ -80,6 +81,7 @@ SPGK_API uint64_t spgk_launch_count(void);
 SPGK_API int spgk_event_create(void **event);
 SPGK_API int spgk_event_destroy(void *event);
 SPGK_API int spgk_event_record(void *event, void *stream);
+SPGK_API int spgk_event_sync(void *event);                    /* the host waits for the event */
 SPGK_API int spgk_event_elapsed_ms(void *start, void *stop, float *ms);
 /* a second (non-blocking) stream and cross-stream ordering, for copies that overlap compute */
 SPGK_API int spgk_stream_create(void **stream);

@@ -150,6 +150,15 @@ int spgk_stream_create(void **stream) { cudaStream_t s; SPGK_CUDA(cudaStreamCrea
 int spgk_stream_destroy(void *stream) { if (stream) SPGK_CUDA(cudaStreamDestroy((cudaStream_t)stream)); return SPGK_OK; }
 int spgk_stream_wait_event(void *stream, void *event) { SPGK_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0)); return SPGK_OK; }
 int spgk_event_elapsed_ms(void *start, void *stop, float *ms) { SPGK_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop)); return SPGK_OK; }
+int spgk_event_sync(void *event) { SPGK_CUDA(cudaEventSynchronize((cudaEvent_t)event)); return SPGK_OK; }
+// 1: page-locked host memory (cudaMallocHost, cudaHostRegister), 0: ordinary (pageable) host memory or unknown
+int spgk_is_pinned_host_pointer(const void *ptr)
+{
+    cudaPointerAttributes a;
+    cudaError_t e = cudaPointerGetAttributes(&a, ptr);
+    if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+    return a.type == cudaMemoryTypeHost ? 1 : 0;
+}
 int spgk_is_device_pointer(const void *ptr)
 {
     cudaPointerAttributes a;

@@ -56,6 +56,7 @@ typedef struct spg_net_s {
     uint32_t *h_count; bool count_pending, count_seen;      /* pinned: [slot] repaired-row counts of the last AUTO call (one slot per pipelined chunk) */
     uint32_t count_slot, count_slots_used;
     void *copy_stream; void *copy_ev[SPG_PIPE_MAX + 1];      /* host-input pipeline: copies run ahead of compute */
+    float *h_chunk[2]; size_t h_chunk_bytes;                /* page-locked staging for pageable inputs: two chunks */
 
     /* large-batch workspace */
     float *d_in32;  size_t in32_bytes;      /* staging for host inputs */

@@ -189,6 +189,26 @@ def test_auto_mode_recomputes_rows_that_leave_the_fp16_range(spg, oracle, tmp_pa
         net.free()
 
 
+def test_pageable_host_batch_through_the_staged_pipeline(spg, oracle, monkeypatch):
+    """A host batch large enough for the chunked pipeline (ragged last chunk) from ordinary pageable memory: the library
+    copies it into page-locked staging with several host threads; results equal the oracle's and those of the same call
+    with staging switched off and with page-locked inputs."""
+    import torch
+    path = golden("small.int8.nn")
+    onet = oracle.OracleNet.from_file(path)
+    net = spg.Network.load(path)
+    n = 2 * 16384 + 1234
+    x = np.random.default_rng(12).random((n, onet.topology[0]), dtype=np.float32)      # numpy memory: pageable
+    got = net.forward_batch(x)
+    rows = np.random.default_rng(13).choice(n, 4096, replace=False)
+    agree, err = nets.parity(got[rows], onet.forward_batch(x[rows]))
+    assert err <= 5e-3 and agree >= 0.999, (agree, err)
+    pinned = torch.from_numpy(x).pin_memory()
+    again = net.forward_batch(pinned.numpy())
+    assert np.array_equal(again, got)
+    net.free()
+
+
 def test_batch_fan_out_over_device_replicas(spg, oracle, has_gpu):
     """spingalett_set_devices: a host batch cut into row shares, one replica and one host thread per listed device.  On a
     one-GPU machine the list names device 0 twice (two replicas, two threads, two streams); with more GPUs it names
