@@ -318,11 +318,13 @@ SPINGALETT_API int spingalett_synchronize(NeuralNetwork *net);
  *         change is below 0.002 with fp16 operands, 0.013 with bf16).
  *         spingalett_set_auto_margin(m > 0) fixes the margin instead; 0 returns
  *         to calibration.  Networks that do not end in softmax run EXACT.
- *         LIMIT: the calibration runs once per net, on the first large batch it
- *         sees, and is not repeated when the inputs change character; AUTO's
- *         agreement with EXACT is that measurement's expectation (the parity
- *         tests allow 3 differing rows in 16384), not a guarantee.  Callers
- *         that need the guarantee use SPINGALETT_MATH_EXACT.
+ *         LIMIT: the calibration is a measurement on up to 2048 rows of the
+ *         first large batch a net sees, repeated on every 1024th large call
+ *         (the margin then only grows); between two measurements inputs of a
+ *         different character are judged by the old margin.  AUTO's agreement
+ *         with EXACT is that measurement's expectation (the parity tests allow
+ *         3 differing rows in 16384), not a guarantee.  Callers that need the
+ *         guarantee use SPINGALETT_MATH_EXACT.
  * The small-batch paths always use exact products (they are memory-bound). */
 typedef enum { SPINGALETT_MATH_FAST = 0, SPINGALETT_MATH_EXACT = 1, SPINGALETT_MATH_AUTO = 2 } SpingalettMathMode;
 SPINGALETT_API void spingalett_set_math_mode(SpingalettMathMode mode);

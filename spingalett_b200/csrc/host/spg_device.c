@@ -125,6 +125,7 @@ void spg_dev_release(spg_net *n)
     spgk_free(n->d_ws_scratch); n->d_ws_scratch = NULL; n->ws_scratch_bytes = 0;
     spgk_free(n->d_rep_idx); n->d_rep_idx = NULL; n->rep_idx_bytes = 0;
     n->auto_calibrated = false;
+    n->auto_calls = 0;
     spgk_free(n->d_rep_in); n->d_rep_in = NULL; n->rep_in_bytes = 0;
     spgk_free(n->d_rep_out); n->d_rep_out = NULL; n->rep_out_bytes = 0;
     spgk_free(n->d_in32); n->d_in32 = NULL; n->in32_bytes = 0;
@@ -642,6 +643,7 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
 
 /* ---- the three-layer net in one launch ------------------------------------ */
 
+#define SPG_AUTO_RECAL 1024u         /* large AUTO calls between two measurements of the margin */
 #define SPG_FUSED_MIN_ROWS 1024u     /* below this a handful of 128-row tiles cannot fill the GPU: the per-layer chain spreads better */
 
 /* 16-bit flavour of the one-term pass: the file's own 16-bit type when it has one (exact weights), else fp16 */
@@ -729,16 +731,23 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     if (theta <= 0.0f) {
         /* Self-calibration, once per device image of the net: run both modes on up to 2048 rows, measure the
          * largest change of the top-two log gap the one-term pass causes, and use four times that as margin. */
-        if (!n->auto_calibrated) {
+        /* ... and again on every SPG_AUTO_RECAL-th call, on that call's rows: the margin only ever grows, so inputs that
+         * have drifted to where the one-term pass errs more widen it (one extra exact pass over 2048 rows and a host
+         * read, a millisecond in a thousand calls) */
+        const bool again = n->auto_calibrated && ++n->auto_calls % SPG_AUTO_RECAL == 0;
+        if (!n->auto_calibrated || again) {
             const uint32_t rows = N < 2048 ? N : 2048;
             if ((rc = reserve((void **)&n->d_rep_out, &n->rep_out_bytes, (size_t)rows * outw * 4, "calibration outputs"))) return rc;
             if ((rc = large_chain(n, d_x, rows, n->d_rep_out, true))) return rc;          /* exact rows; d_out already holds the fast ones */
-            if ((rc = spg_map_kernel_error(spgk_memset(d_count, 0, 4, n->stream), "calibration clear"))) return rc;
-            if ((rc = spg_map_kernel_error(spgk_gap_error(d_out, n->d_rep_out, outw, rows, outw, d_count, n->stream), "calibration"))) return rc;
+            /* (a word of its own: on a repeated measurement d_count already holds this call's number of listed rows) */
+            uint32_t *d_gap = d_count + 8;
+            if ((rc = spg_map_kernel_error(spgk_memset(d_gap, 0, 4, n->stream), "calibration clear"))) return rc;
+            if ((rc = spg_map_kernel_error(spgk_gap_error(d_out, n->d_rep_out, outw, rows, outw, d_gap, n->stream), "calibration"))) return rc;
             float emax = 0.0f;
-            if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(&emax, d_count, 4, n->stream), "calibration read"))) return rc;
+            if ((rc = spg_map_kernel_error(spgk_memcpy_d2h(&emax, d_gap, 4, n->stream), "calibration read"))) return rc;
             if ((rc = spg_map_kernel_error(spgk_stream_sync(n->stream), "calibration sync"))) return rc;
-            n->auto_theta = emax * 4.0f > 1e-4f ? emax * 4.0f : 1e-4f;
+            const float measured = emax * 4.0f > 1e-4f ? emax * 4.0f : 1e-4f;
+            n->auto_theta = again && n->auto_theta > measured ? n->auto_theta : measured;
             n->auto_calibrated = true;
             spg_log(LOG_DEBUG, "auto math mode: largest top-two log-gap change on %u rows %.3g, margin %.3g", rows, (double)emax, (double)n->auto_theta);
         }

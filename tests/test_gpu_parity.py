@@ -209,6 +209,38 @@ def test_pageable_host_batch_through_the_staged_pipeline(spg, oracle, monkeypatc
     net.free()
 
 
+@pytest.mark.parametrize("which", ["chain", "one-launch"])
+def test_auto_margin_is_measured_again_every_1024_large_calls(spg, oracle, tmp_path_factory, which):
+    """The AUTO margin is calibrated on the first large batch and measured again on every 1024th large call, where it can
+    only grow: after inputs of a harsher distribution (wider range, so larger one-term errors) the margin is at least
+    what it was, and results stay within the parity bar."""
+    lib = spg.lib()
+    lib.spingalett_net_margin.restype = __import__("ctypes").c_float
+    if which == "chain":
+        path = golden("small.fp16.nn")
+    else:                                  # the benchmark MLP: its one-term pass is the one-launch kernel
+        path = nets.make_net_file(spg, str(tmp_path_factory.getbasetemp() / "A_recal_int8.nn"), nets.A_TOPO, nets.A_ACTS, 3,
+                                  seed=1234, reference_rng=True)
+    onet = oracle.OracleNet.from_file(path)
+    net = spg.Network.load(path)
+    spg.set_math_mode(spg.abi.MATH_AUTO)
+    rng = np.random.default_rng(21)
+    n = 2048
+    x = rng.random((n, onet.topology[0]), dtype=np.float32)
+    net.forward_batch(x)
+    assert spg.last_path() == ("tcgen05" if which == "chain" else "tcgen05-fused"), spg.last_path()
+    first = float(lib.spingalett_net_margin(net._h))
+    assert first > 0.0
+    harsh = (rng.standard_normal((n, onet.topology[0])) * 6.0).astype(np.float32)
+    for _ in range(1030):
+        got = net.forward_batch(harsh)
+    later = float(lib.spingalett_net_margin(net._h))
+    assert later >= first and np.isfinite(later), (first, later)
+    agree, err = nets.parity(got, onet.forward_batch(harsh))
+    assert agree >= 0.999 and err <= 5e-3, (agree, err)
+    net.free()
+
+
 def test_batch_fan_out_over_device_replicas(spg, oracle, has_gpu):
     """spingalett_set_devices: a host batch cut into row shares, one replica and one host thread per listed device.  On a
     one-GPU machine the list names device 0 twice (two replicas, two threads, two streams); with more GPUs it names
