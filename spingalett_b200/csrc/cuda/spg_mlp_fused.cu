@@ -6,21 +6,25 @@
 // CTA, and runs them as one cta_group::2 MMA stream -- each CTA holds its own rows of the A operands and accumulators
 // and only HALF of every weight tile, which halves the weight bytes per SM that have to come from L2 and sit in shared
 // memory (the budget that the resident hidden layer leaves is small).  Per tile and CTA:
-//   * an input-producer lane streams the fp32 input rows as [128 x 64] tiles (cp.async.bulk.tensor) into a staging ring that
-//     borrows the hidden layer's shared memory while it is idle; four converter warps round them to the 16-bit operand
-//     type and write [128 x 64] K-major, 128-byte-swizzled A tiles into a three-slot ring (no separate split pass, no
-//     16-bit copy of the input in HBM);
-//   * one TMA lane streams this CTA's half of the 16-bit weight tiles of layers 1 and 2 from L2 ([128 x 64] boxes, three-slot
+//   * an input-producer warp streams the fp32 input rows as [128 x 64] tiles (cp.async.bulk.tensor) into a two-slot staging
+//     ring that borrows the hidden layer's shared memory while it is idle; four converter warps round them to the 16-bit
+//     operand type and write [128 x 64] K-major, 128-byte-swizzled A tiles into a five-slot ring (two slots of its own,
+//     three more in idle hidden tiles; no separate split pass, no 16-bit copy of the input in HBM);
+//   * one TMA warp streams this CTA's half of the 16-bit weight tiles of layers 1 and 2 from L2 ([128 x 64] boxes, three-slot
 //     ring; cp.async.bulk.tensor, no multicast, completion counted on the first CTA's barrier);
-//   * one lane of the pair's first CTA issues tcgen05.mma (kind::f16, cta_group::2, M = 256 over the two CTAs): layer 1 in
-//     chunks of 256 output columns over K = in, then layer 2 in chunks of 256 columns over K = N1, the fp32
-//     accumulators alternating between the two 256-column halves of each CTA's tensor memory;
+//   * one warp of the pair's first CTA issues tcgen05.mma (kind::f16, cta_group::2, M = 256 over the two CTAs), whole-warp
+//     convergent with one elected lane: layer 1 as ONE pass over K = in whose two chunks of 256 output columns fill the two
+//     256-column halves of each CTA's tensor memory side by side, then layer 2 in chunks of 256 columns over K = N1, the
+//     fp32 accumulators alternating between the halves;
 //   * eight epilogue warps drain the accumulators: a layer-1 chunk becomes act(scale*acc + bias) rounded to 16
 //     bits and written straight into the shared-memory A operand of layer 2 (the hidden matrix never leaves
-//     the SM); a layer-2 chunk stays in registers as fp32 and is multiplied into the head's dot products
-//     (fp32 FMAs), so the wide second hidden matrix is never stored anywhere; after the last chunk the row's
+//     the SM); a layer-2 chunk is read from tensor memory in the fragment layout of the warp-level MMA, gets scale,
+//     bias and activation in registers, is rounded to 16 bits and multiplied into the head's dot products with
+//     mma.sync.m16n8k16 against the head's weights of the chunk (brought into shared memory a chunk ahead by bulk
+//     copies), so the wide second hidden matrix is never stored anywhere; after the last chunk the row's
 //     head sums get bias, softmax (Activation.c:5-21) or the head's activation, and the <= 16 outputs are
-//     written.  Rows whose two largest logits are within `theta` are appended to a list (AUTO math mode).
+//     written.  Rows whose two largest logits are within `theta`, or whose logits are not finite, are appended to a
+//     list (AUTO math mode).
 //
 // "Pair" mode computes rows exactly on the same one-term tensor-core pass: a row occupies two adjacent slots,
 // one carrying the 16-bit rounding of each value and one the rounding error scaled by 2^11 (fp16) or 2^8
@@ -28,6 +32,9 @@
 // activations are split the same way.  With integer, fp16 or bf16 weight files (exact 16-bit weights) every
 // product is then exact and only the fp32 accumulation order differs from the reference.
 //
+// Waits and arrives are the cheap forms: a first plain try_wait (21 cycles when the phase is complete), CTA-scope
+// semantics on barriers the other CTA of the pair arrives on (the waiter reads peer-written shared memory only through
+// the tensor core, behind the writer's proxy fence; the cluster-scope release cost 1300 cycles per arrive here).
 // Every mbarrier wait is bounded; on expiry the CTA records a code in `status`, raises a shared abort flag
 // that all roles poll, lets its copies land, frees its tensor memory and returns.
 #include "spg_common.cuh"
