@@ -15,9 +15,12 @@ no collective), so scaling is weak: `value` is all ranks' rows per second.
             with CUDA events on the launching stream, max over ranks
   e2e       the same call with HOST (pinned) buffers: H2D of the batch and D2H
             of the result inside the timed region
-  roofline  the tcgen05 GEMM kernel: algorithmic FLOPs of the launches in the
-            timed region / their summed device time (event pairs recorded by
-            the library around each launch), against the measured bf16 peak
+  roofline  the dominant kernel of the path that ran (config.path): the one-launch
+            three-layer kernel or the per-layer tcgen05 GEMM -- algorithmic FLOPs of
+            its launches / their summed device time (event pairs recorded by the
+            library around each launch), against the measured bf16 peak; the GEMV or
+            weight-streaming kernel for small batches -- packed weight bytes / time,
+            against the measured HBM bandwidth
   cpu_baseline  the reference's own CPU forward (built from its sources into
             oracle/_ref) or, if that is absent, the C restatement in oracle/,
             timed on this host's cores on a bounded sample of the same batch
