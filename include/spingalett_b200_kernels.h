@@ -386,6 +386,22 @@ SPGK_API int spgk_optimizer_step(int kind, float *w, float *m, float *v, const f
 /* ---- gradient exchange: NCCL, loaded with dlopen at first use -----------------
  * One communicator per process (one process per GPU).  Rank 0 makes a 128-byte id with
  * spgk_nccl_unique_id and hands it to the other ranks by any host channel. */
+/* A training step whose launches have the same arguments every time, so that it can be replayed as a CUDA graph: what
+ * changes from step to step -- the first row of the step in the shuffled order, Adam's bias corrections -- lives in a small
+ * device record (spgk_train_state_bytes) that spgk_train_state_step advances as the first launch of every step, with
+ * the host's own fp32 operations (Training.c:480-500).  After spgk_train_use_state(state) this thread's
+ * spgk_gather_rows2 offsets its index list by the record's position and spgk_adam / spgk_optimizer_step take mf and vf
+ * from it; NULL switches back.  spgk_graph_begin / _end capture the launches issued on `stream` in between
+ * (relaxed capture mode) and return an executable graph; _launch replays it; a capture that fails returns an error and
+ * leaves the stream usable. */
+SPGK_API size_t spgk_train_state_bytes(void);
+SPGK_API int spgk_train_state_reset(void *state, void *stream);
+SPGK_API int spgk_train_state_step(void *state, uint32_t steps_per_epoch, uint32_t batch, float b1, float b2, void *stream);
+SPGK_API void spgk_train_use_state(const void *state);
+SPGK_API int spgk_graph_begin(void *stream);
+SPGK_API int spgk_graph_end(void *stream, void **exec);
+SPGK_API int spgk_graph_launch(void *exec, void *stream);
+SPGK_API void spgk_graph_destroy(void *exec);
 SPGK_API int spgk_nccl_unique_id(void *id128);
 SPGK_API int spgk_nccl_init(void **comm, int rank, int world, const void *id128);
 SPGK_API int spgk_nccl_allreduce_sum(void *comm, float *buf, uint64_t count, void *stream);
@@ -407,13 +423,15 @@ SPGK_API int spgk_nccl_destroy(void *comm);
  * spgk_xchg_gather (collective as well) brings the shards of G (the summed gradients), M and V to every rank.
  * The ranks' kernels wait for one another through flags in peer memory, every wait bounded (about half a second):
  * spgk_xchg_status, called after a stream synchronisation, returns SPGK_E_TIMEOUT when one gave up.  All ranks must
- * issue the same sequence of step / gather calls.  No TMA, multicast or NVLS is involved. */
+ * issue the same sequence of step / gather calls (the running number of the collective lives in the arena and is advanced
+ * by the kernels, and mfvf_dev -- two floats on the device, optional -- overrides mf and vf: a step's launch then has
+ * the same arguments every time and can be part of a replayed graph).  No TMA, multicast or NVLS is involved. */
 SPGK_API int spgk_xchg_create(void **xchg, int rank, int world, uint64_t np, void *comm, void *stream);
 SPGK_API void spgk_xchg_destroy(void *xchg);
 SPGK_API uint64_t spgk_xchg_capacity(const void *xchg);
 SPGK_API float *spgk_xchg_buffer(void *xchg, int which);
 SPGK_API int spgk_xchg_step(void *xchg, int kind, uint64_t n_weights, float lr, float momentum, float b1, float b2, float mf, float vf,
-                            float eps, float decay, float gscale, void *stream);
+                            float eps, float decay, float gscale, const float *mfvf_dev, void *stream);
 SPGK_API int spgk_xchg_gather(void *xchg, void *stream);
 SPGK_API int spgk_xchg_status(void *xchg, void *stream);
 /* the exchange's bounded wait on a flag nobody writes (16 uint32 of device scratch): leaves {1, 42, 7} in the first

@@ -41,13 +41,15 @@ constexpr uint32_t XG_THREADS = 256;
 // then per phase the local CTA counter and the local release flag, then the status word
 constexpr uint32_t XG_LINE = 32;
 constexpr uint32_t XG_FLAG0 = 0, XG_CNT0 = 2 * XG_MAX_WORLD * XG_LINE, XG_GO0 = XG_CNT0 + 2 * XG_LINE, XG_STATUS_WORD = XG_GO0 + 2 * XG_LINE;
+constexpr uint32_t XG_SEQ_WORD = XG_STATUS_WORD + XG_LINE;   // running number of this rank's collectives (advanced by the kernels themselves)
 constexpr int XG_UNROLL = 2;                            // elements of 4 floats a thread works on at a time: the loads of every rank's copy of them (up to 16 x 16 bytes) are issued before the first is used -- a warp issues in order, so a sum placed between two loads would make the second wait for the first's round trip over NVLink
 constexpr size_t XG_HEAD_BYTES = 16384;                 // flags + status, padded (keeps the buffers 256-byte aligned)
 constexpr uint32_t XG_WAIT_LIMIT = 1u << 23;            // polls of 50 ns or more each before a wait gives up (about half a second)
 
 struct XchgParams {
     float *arena[XG_MAX_WORLD];                         // every rank's arena (own: the local pointer)
-    uint32_t rank, world, seq;                          // seq: running number of this collective, >= 1
+    uint32_t rank, world, seq;                          // seq: running number of this collective, >= 1 (filled in by the kernel from the arena)
+    const float *mfvf;                                  // optional: the step's Adam bias corrections {mf, vf} on the device
     uint64_t shard, np_pad, n_w;                        // n_w: the first n_w elements are weights (decay applies to them)
     int kind;
     float lr, momentum, b1, b2, mf, vf, eps, decay, gscale;
@@ -58,7 +60,6 @@ struct Xchg {
     void *peer[XG_MAX_WORLD];
     int rank, world;
     uint64_t np, shard, np_pad;
-    uint32_t seq;
     uint32_t grid;                                      // CTAs per launch: all resident at once (cooperative launch)
 };
 
@@ -152,8 +153,14 @@ __device__ __forceinline__ void xg_update(const XchgParams &p, float &w, float &
 }
 
 __global__ void __launch_bounds__(XG_THREADS)
-spg_xchg_step_kernel(const XchgParams p)
+spg_xchg_step_kernel(const XchgParams p0)
 {
+    // the collective's number comes from the arena and is advanced at the end, so that every launch has the same
+    // arguments (the step can be replayed as a graph); every CTA has read it before any CTA passes the first barrier
+    XchgParams p = p0;
+    uint32_t *seq_word = reinterpret_cast<uint32_t *>(p.arena[p.rank]) + XG_SEQ_WORD;
+    p.seq = *reinterpret_cast<volatile uint32_t *>(seq_word) + 1u;
+    if (p.mfvf) { p.mf = p.mfvf[0]; p.vf = p.mfvf[1]; }
     xg_barrier(p, 0, false);                             // every rank's gradients are complete
     const uint64_t base = (uint64_t)p.rank * p.shard;
     const uint64_t per = ((p.shard + gridDim.x - 1) / gridDim.x + 3) & ~(uint64_t)3;
@@ -204,12 +211,16 @@ spg_xchg_step_kernel(const XchgParams p)
         }
     }
     xg_barrier(p, 1, true);                              // every rank's weight stores have landed
+    if (blockIdx.x == 0 && threadIdx.x == 0) *seq_word = p.seq;
 }
 
 // Shards of G (summed gradients), M and V from their owners into this rank's arena.
 __global__ void __launch_bounds__(XG_THREADS)
-spg_xchg_gather_kernel(const XchgParams p)
+spg_xchg_gather_kernel(const XchgParams p0)
 {
+    XchgParams p = p0;
+    uint32_t *seq_word = reinterpret_cast<uint32_t *>(p.arena[p.rank]) + XG_SEQ_WORD;
+    p.seq = *reinterpret_cast<volatile uint32_t *>(seq_word) + 1u;
     xg_barrier(p, 0, false);
     const uint64_t per = ((p.shard + gridDim.x - 1) / gridDim.x + 3) & ~(uint64_t)3;
     const uint64_t lo = (uint64_t)blockIdx.x * per, hi = lo + per < p.shard ? lo + per : p.shard;
@@ -224,6 +235,7 @@ spg_xchg_gather_kernel(const XchgParams p)
         }
     }
     xg_barrier(p, 1, false);                             // nobody reads this rank's shards any more
+    if (blockIdx.x == 0 && threadIdx.x == 0) *seq_word = p.seq;
 }
 
 // the exchange's wait on a flag that nobody sets, with a small bound: out[0] = 1 when the wait reported the time-out,
@@ -358,15 +370,14 @@ float *spgk_xchg_buffer(void *xv, int which)
 }
 
 int spgk_xchg_step(void *xv, int kind, uint64_t n_weights, float lr, float momentum, float b1, float b2, float mf, float vf, float eps,
-                   float decay, float gscale, void *stream)
+                   float decay, float gscale, const float *mfvf_dev, void *stream)
 {
     Xchg *x = static_cast<Xchg *>(xv);
     if (!x || kind < 0 || kind > 4) { spgk_set_error("spgk_xchg_step", "bad argument"); return SPGK_E_ARG; }
     XchgParams p;
     xg_fill(x, &p);
-    p.seq = ++x->seq;
     p.n_w = n_weights; p.kind = kind; p.lr = lr; p.momentum = momentum; p.b1 = b1; p.b2 = b2; p.mf = mf; p.vf = vf; p.eps = eps;
-    p.decay = decay; p.gscale = gscale;
+    p.decay = decay; p.gscale = gscale; p.mfvf = mfvf_dev;
     return xg_launch(reinterpret_cast<const void *>(spg_xchg_step_kernel), x, &p, stream, "spg_xchg_step_kernel");
 }
 
@@ -376,7 +387,6 @@ int spgk_xchg_gather(void *xv, void *stream)
     if (!x) { spgk_set_error("spgk_xchg_gather", "bad argument"); return SPGK_E_ARG; }
     XchgParams p;
     xg_fill(x, &p);
-    p.seq = ++x->seq;
     return xg_launch(reinterpret_cast<const void *>(spg_xchg_gather_kernel), x, &p, stream, "spg_xchg_gather_kernel");
 }
 

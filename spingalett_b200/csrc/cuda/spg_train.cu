@@ -471,11 +471,35 @@ spg_gather_rows_kernel(const float *__restrict__ src, const uint32_t *__restrict
     }
 }
 
+// What changes from one optimiser step to the next, kept on the device so that a step's launches have the same
+// arguments every time and can be replayed as a CUDA graph: the position in the epoch (first row of the step in the
+// shuffled order) and Adam's running powers of beta1 / beta2 with the bias corrections made of them.  The host
+// computes the same values with the same fp32 operations (Training.c:480-500), so both ways give the same bits.
+struct SpgStepState { uint32_t step, start; float b1pow, b2pow, mf, vf; };
+
+// first launch of a step: this step's values, then the position moves on
+__global__ void spg_train_state_kernel(SpgStepState *st, uint32_t steps_per_epoch, uint32_t batch, float b1, float b2)
+{
+    st->start = st->step * batch;
+    st->step = st->step + 1 == steps_per_epoch ? 0u : st->step + 1;
+    st->b1pow *= b1;
+    st->b2pow *= b2;
+    st->mf = 1.0f / (1.0f - st->b1pow);
+    st->vf = 1.0f / (1.0f - st->b2pow);
+}
+
+struct SpgGraph { cudaGraphExec_t exec; uint32_t nodes; };
+
+// the device step state that the launchers below hand to their kernels (NULL: arguments come from the host)
+thread_local const SpgStepState *tls_step_state = nullptr;
+
 // gather the same rows of two tables (a mini-batch's inputs and targets) in one launch
 __global__ void __launch_bounds__(256)
 spg_gather_rows2_kernel(const float *__restrict__ src_a, uint32_t wa, float *__restrict__ dst_a, const float *__restrict__ src_b,
-                        uint32_t wb, float *__restrict__ dst_b, const uint32_t *__restrict__ idx, uint32_t rows)
+                        uint32_t wb, float *__restrict__ dst_b, const uint32_t *__restrict__ idx, uint32_t rows,
+                        const SpgStepState *__restrict__ state)
 {
+    if (state) idx += state->start;                    // the step's first row of the shuffled order, kept on the device
     const uint32_t w = wa + wb;
     const uint64_t total = (uint64_t)rows * w;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -491,8 +515,9 @@ spg_gather_rows2_kernel(const float *__restrict__ src_a, uint32_t wa, float *__r
 // m = b1*m + (1-b1)*g ; v = b2*v + (1-b2)*g*g ; w -= lr * (m*mf) / sqrt(v*vf + eps).
 __global__ void __launch_bounds__(256)
 spg_adam_kernel(float *__restrict__ w, float *__restrict__ m, float *__restrict__ v, const float *__restrict__ g, uint64_t n,
-                float lr, float b1, float b2, float mf, float vf, float eps, float gscale)
+                float lr, float b1, float b2, float mf, float vf, float eps, float gscale, const SpgStepState *__restrict__ state)
 {
+    if (state) { mf = state->mf; vf = state->vf; }     // bias corrections of this step, advanced on the device
     const float omb1 = 1.0f - b1, omb2 = 1.0f - b2;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         const float gi = g[i] * gscale;
@@ -566,8 +591,9 @@ spg_sumsq_kernel(const float *__restrict__ g, uint64_t n, float *out)
 __global__ void __launch_bounds__(256)
 spg_optimizer_kernel(int kind, float *__restrict__ w, float *__restrict__ m, float *__restrict__ v, const float *__restrict__ g,
                      uint64_t n, uint64_t n_w, float lr, float momentum, float b1, float b2, float mf, float vf, float eps,
-                     float decay, float gscale, const float *sumsq, float max_norm)
+                     float decay, float gscale, const float *sumsq, float max_norm, const SpgStepState *__restrict__ state)
 {
+    if (state) { mf = state->mf; vf = state->vf; }
     float gs = gscale;
     if (sumsq) {
         const float norm = sqrtf(*sumsq) * gscale;
@@ -723,13 +749,77 @@ int spgk_train_output(const float *x, uint32_t ldx, const float *w, uint32_t ldw
     return spgk_check_launch("spg_train_fwd_narrow_kernel");
 }
 
+// ---- device step state and graph replay of a training step --------------------------------------------------------------
+size_t spgk_train_state_bytes(void) { return sizeof(SpgStepState); }
+
+// starts a run of steps: position 0, beta powers 1 (Training.c:480-500 starts them there at every train() call)
+int spgk_train_state_reset(void *state, void *stream)
+{
+    if (!state) { spgk_set_error("spgk_train_state_reset", "bad argument"); return SPGK_E_ARG; }
+    const SpgStepState init = { 0u, 0u, 1.0f, 1.0f, 0.0f, 0.0f };
+    SPGK_CUDA(cudaMemcpyAsync(state, &init, sizeof init, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    SPGK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));      // `init` is on this stack
+    return SPGK_OK;
+}
+
+// first launch of a step: sets the step's first row and bias corrections in `state` and moves the position on
+int spgk_train_state_step(void *state, uint32_t steps_per_epoch, uint32_t batch, float b1, float b2, void *stream)
+{
+    if (!state || steps_per_epoch == 0) { spgk_set_error("spgk_train_state_step", "bad argument"); return SPGK_E_ARG; }
+    spg_train_state_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(static_cast<SpgStepState *>(state), steps_per_epoch, batch, b1, b2);
+    return spgk_check_launch("spg_train_state_kernel");
+}
+
+// from now on spgk_gather_rows2 (row offset), spgk_adam and spgk_optimizer_step (bias corrections) of this thread take
+// those values from `state` instead of their arguments; NULL switches back
+void spgk_train_use_state(const void *state) { tls_step_state = static_cast<const SpgStepState *>(state); }
+
+// Stream capture of a step's launches into a graph, and its replay.  begin .. end must enclose only launches and
+// memsets on `stream`; end returns the executable graph (NULL and an error code if the capture did not come off).
+int spgk_graph_begin(void *stream)
+{
+    SPGK_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeRelaxed));
+    return SPGK_OK;
+}
+int spgk_graph_end(void *stream, void **exec_out)
+{
+    if (!exec_out) return SPGK_E_ARG;
+    *exec_out = nullptr;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture((cudaStream_t)stream, &g);
+    if (e != cudaSuccess || !g) { spgk_set_error("cudaStreamEndCapture", cudaGetErrorString(e)); cudaGetLastError(); return SPGK_E_CUDA; }
+    size_t nodes = 0;
+    cudaGraphGetNodes(g, nullptr, &nodes);
+    cudaGraphExec_t x = nullptr;
+    e = cudaGraphInstantiate(&x, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) { spgk_set_error("cudaGraphInstantiate", cudaGetErrorString(e)); cudaGetLastError(); return SPGK_E_CUDA; }
+    *exec_out = new SpgGraph{ x, (uint32_t)nodes };
+    return SPGK_OK;
+}
+int spgk_graph_launch(void *exec, void *stream)
+{
+    SpgGraph *gr = static_cast<SpgGraph *>(exec);
+    if (!gr) return SPGK_E_ARG;
+    SPGK_CUDA(cudaGraphLaunch(gr->exec, (cudaStream_t)stream));
+    for (uint32_t i = 0; i < gr->nodes; i++) spgk_count_launch();      // the launch counter counts kernels, replayed or not
+    return SPGK_OK;
+}
+void spgk_graph_destroy(void *exec)
+{
+    SpgGraph *gr = static_cast<SpgGraph *>(exec);
+    if (!gr) return;
+    cudaGraphExecDestroy(gr->exec);
+    delete gr;
+}
+
 int spgk_gather_rows2(const float *src_a, uint32_t width_a, float *dst_a, const float *src_b, uint32_t width_b, float *dst_b,
                       const uint32_t *idx, uint32_t rows, void *stream)
 {
     if (!src_a || !dst_a || !src_b || !dst_b || !idx) { spgk_set_error("spgk_gather_rows2", "bad argument"); return SPGK_E_ARG; }
     if (rows == 0 || width_a + width_b == 0) return SPGK_OK;
     spg_gather_rows2_kernel<<<blocks_for((uint64_t)rows * (width_a + width_b)), 256, 0, (cudaStream_t)stream>>>(
-        src_a, width_a, dst_a, src_b, width_b, dst_b, idx, rows);
+        src_a, width_a, dst_a, src_b, width_b, dst_b, idx, rows, tls_step_state);
     return spgk_check_launch("spg_gather_rows2_kernel");
 }
 
@@ -761,7 +851,7 @@ int spgk_adam(float *w, float *m, float *v, const float *g, uint64_t n, float lr
 {
     if (!w || !m || !v || !g) { spgk_set_error("spgk_adam", "bad argument"); return SPGK_E_ARG; }
     if (n == 0) return SPGK_OK;
-    spg_adam_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(w, m, v, g, n, lr, b1, b2, mf, vf, eps, gscale);
+    spg_adam_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(w, m, v, g, n, lr, b1, b2, mf, vf, eps, gscale, tls_step_state);
     return spgk_check_launch("spg_adam_kernel");
 }
 
@@ -795,7 +885,7 @@ int spgk_optimizer_step(int kind, float *w, float *m, float *v, const float *g, 
     }
     if (n == 0) return SPGK_OK;
     spg_optimizer_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(kind, w, m, v, g, n, n_weights, lr, momentum, b1, b2, mf, vf,
-                                                                         eps, decay, gscale, sumsq_dev, max_norm);
+                                                                         eps, decay, gscale, sumsq_dev, max_norm, tls_step_state);
     return spgk_check_launch("spg_optimizer_kernel");
 }
 

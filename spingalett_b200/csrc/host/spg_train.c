@@ -52,6 +52,8 @@ static void *s_ar_stream = NULL, *s_ev_ready = NULL, *s_ev_done = NULL;
 /* the one-kernel exchange over peer memory (spgk_xchg_*): created by the first data-parallel train() call for its
    parameter count, kept for later calls; NULL = the NCCL exchange */
 static void *s_xchg = NULL;
+/* a stream of the library's own for train() calls of nets that sit on the legacy default stream (one per process) */
+static void *s_train_stream = NULL;
 
 static void dist_release(void)
 {
@@ -177,6 +179,8 @@ static int train_sync(void *st)
 }
 
 #define DEV(call, what) do { int rc__ = spg_map_kernel_error((call), what); if (rc__) goto fail; } while (0)
+/* inside the step: a failure while the step is being captured into a graph only ends the capture */
+#define SDEV(call, what) do { int rc__ = spg_map_kernel_error((call), what); if (rc__) { if (in_capture) goto capture_abort; goto fail; } } while (0)
 
 void train_struct_arguments(TrainArgs a)
 {
@@ -250,10 +254,21 @@ void train_struct_arguments(TrainArgs a)
         t->np = np;
         n->train = t;
     }
+    /* The legacy default stream cannot be captured into a graph: a net that runs on it trains on a stream of the
+       library's own for the length of this call (everything the call touches, autosave and the callback's saves
+       included, follows n->stream, so it is switched and put back at the end).  Earlier work of the net is awaited first;
+       the call itself ends with a synchronisation, so later work on the caller's stream is ordered behind it. */
+    void *const caller_stream = n->stream;
+    if ((uintptr_t)n->stream <= 2) {
+        if (!s_train_stream && spgk_stream_create(&s_train_stream) != SPGK_OK) { spingalett_clear_error(); s_train_stream = NULL; }
+        if (s_train_stream && spgk_stream_sync(n->stream) == SPGK_OK) n->stream = s_train_stream;
+    }
     void *st = n->stream;
     uint32_t *order = NULL;
     float *h_pinned = NULL;
     bool failed = true;
+    void *graph_exec = NULL;                 /* the step as an executable CUDA graph, once captured */
+    bool graph_failed = false, in_capture = false;
 
     if (state_reserve(t, 0, (void **)&t->params, np * 4, "train: parameters") || state_reserve(t, 1, (void **)&t->grads, np * 4, "train: gradients") ||
         state_reserve(t, 2, (void **)&t->m, np * 4, "train: first moments") || state_reserve(t, 3, (void **)&t->v, np * 4, "train: second moments") ||
@@ -355,10 +370,26 @@ void train_struct_arguments(TrainArgs a)
     const bool ce_direct = p->loss_func == LOSS_CROSS_ENTROPY && (out_act == ACT_SOFTMAX || out_act == ACT_SIGMOID);
     const bool fused_out = ce_direct && outw <= 16;
     float b1pow = 1.0f, b2pow = 1.0f;
+    /* Replay of the step as a CUDA graph: with one rank or the peer-memory exchange, a strategy whose steps are all the same size and more than a
+       handful of steps, the launches of a step take what changes between steps (position in the epoch, Adam's bias
+       corrections) from a small device record, so the first step runs directly, the second is captured, and every later
+       one is a single graph launch -- the host thread is then out of the step's critical path (ten launches per 0.12 ms
+       step otherwise: two identical train() calls differed by 20 % with the host's load).  SPINGALETT_TRAIN_GRAPH=0
+       keeps the direct launches. */
+    const uint32_t steps_per_epoch = (a.sample_count + batch - 1) / batch;
+    bool graph_mode = (s_world == 1 || fused_x) && !online && a.sample_count % batch == 0 && (uint64_t)steps_per_epoch * a.epochs >= 4;
+    { const char *e = getenv("SPINGALETT_TRAIN_GRAPH"); if (e && *e == '0') graph_mode = false; }
+    void *step_state = (void *)(t->words + 128);      /* clear of the loss / flag / norm words and of the rank-agreement floats */
+    uint64_t steps_done = 0;
+    if (graph_mode) {
+        DEV(spgk_train_state_reset(step_state, st), "train: step state");
+        spgk_train_use_state(step_state);
+    }
     for (size_t epoch = 1; epoch <= a.epochs; epoch++) {
         const bool need_loss = should_report(epoch, a.epochs, a.report_interval) ||
                                (a.callback && should_report(epoch, a.epochs, a.callback_interval));
-        if (need_loss) DEV(spgk_memset(d_loss, 0, 4, st), "train: clear loss");
+        if (need_loss || graph_mode) DEV(spgk_memset(d_loss, 0, 4, st), "train: clear loss");
+        float *const loss_ptr = (need_loss || graph_mode) ? d_loss : NULL;      /* a replayed step always adds to the loss word */
         if (mini) {
             spg_shuffle(order, a.sample_count);
             DEV(spgk_memcpy_h2d(t->idx, order, (size_t)a.sample_count * 4, st), "train: upload order");
@@ -369,8 +400,25 @@ void train_struct_arguments(TrainArgs a)
             const uint32_t start = bi * batch;
             const uint32_t cur = start + batch > a.sample_count ? a.sample_count - start : batch;
             const float *bx = t->data_x + (size_t)(mini ? 0 : start) * in0, *bt = t->data_t + (size_t)(mini ? 0 : start) * outw;
+            p->time_step++;
+            b1pow *= a.beta1;
+            b2pow *= a.beta2;
+            const float mf = 1.0f / (1.0f - b1pow), vf = 1.0f / (1.0f - b2pow);
+            steps_done++;
+            if (graph_exec) {                                        /* every step after the second */
+                DEV(spgk_graph_launch(graph_exec, st), "train: step (graph)");
+                continue;
+            }
+            bool capture = graph_mode && !graph_failed && steps_done == 2;
+          for (;;) {
+            if (capture) {
+                if (spgk_graph_begin(st) == SPGK_OK) in_capture = true;
+                else { spingalett_clear_error(); graph_failed = true; capture = false; }
+            }
+            if (graph_mode) SDEV(spgk_train_state_step(step_state, steps_per_epoch, batch, a.beta1, a.beta2, st), "train: step state");
             if (mini) {
-                DEV(spgk_gather_rows2(t->data_x, in0, t->batch_x, t->data_t, outw, t->batch_t, t->idx + start, cur, st),
+                /* (with the device record the kernel adds the step's first row itself) */
+                SDEV(spgk_gather_rows2(t->data_x, in0, t->batch_x, t->data_t, outw, t->batch_t, graph_mode ? t->idx : t->idx + start, cur, st),
                     "train: gather mini-batch");
                 bx = t->batch_x; bt = t->batch_t;
             }
@@ -381,25 +429,25 @@ void train_struct_arguments(TrainArgs a)
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 float *y = t->acts + (size_t)cur * p->neuron_offsets[l + 1];
                 if (l + 1 == last && fused_out) {
-                    DEV(spgk_train_output(x, fi, P + p->weight_offsets[l], fi, P + tw + p->bias_offsets[l], y, bt,
-                                          d_last, need_loss ? d_loss : NULL, cur, fo, fi, out_act == ACT_SIGMOID, st),
+                    SDEV(spgk_train_output(x, fi, P + p->weight_offsets[l], fi, P + tw + p->bias_offsets[l], y, bt,
+                                          d_last, loss_ptr, cur, fo, fi, out_act == ACT_SIGMOID, st),
                         "train: output layer");
                     break;
                 }
-                DEV(spgk_train_gemm(0, x, fi, P + p->weight_offsets[l], fi, y, fo, cur, fo, fi, 1.0f,
+                SDEV(spgk_train_gemm(0, x, fi, P + p->weight_offsets[l], fi, y, fo, cur, fo, fi, 1.0f,
                                     P + tw + p->bias_offsets[l], NULL, 0, (int)p->act_func[l], st), "train: forward");
-                if (p->act_func[l] == ACT_SOFTMAX) DEV(spgk_softmax_rows(y, fo, cur, fo, st), "train: softmax");
+                if (p->act_func[l] == ACT_SOFTMAX) SDEV(spgk_softmax_rows(y, fo, cur, fo, st), "train: softmax");
                 x = y;
             }
             if (!fused_out) {
                 const float *a_last = t->acts + (size_t)cur * p->neuron_offsets[last];
                 if (ce_direct)
-                    DEV(spgk_ce_delta(a_last, bt, d_last, (uint64_t)cur * outw, need_loss ? d_loss : NULL, out_act == ACT_SIGMOID, st),
+                    SDEV(spgk_ce_delta(a_last, bt, d_last, (uint64_t)cur * outw, loss_ptr, out_act == ACT_SIGMOID, st),
                         "train: output delta");
                 else
-                    DEV(spgk_output_delta(a_last, bt, d_last, cur, outw, (int)out_act,
+                    SDEV(spgk_output_delta(a_last, bt, d_last, cur, outw, (int)out_act,
                                           p->loss_func == LOSS_MSE && out_act == ACT_SOFTMAX ? 1 : 0,
-                                          p->loss_func == LOSS_MSE ? 0 : 1, need_loss ? d_loss : NULL, st), "train: output delta");
+                                          p->loss_func == LOSS_MSE ? 0 : 1, loss_ptr, st), "train: output delta");
             }
             /* backwards through the layers: the gradients of layer l (from delta l+1 and activation l) go into the flat
                buffer and, with several replicas, start their all-reduce on the exchange stream at once, so that it runs
@@ -409,45 +457,54 @@ void train_struct_arguments(TrainArgs a)
                 const uint32_t fi = p->topology[l], fo = p->topology[l + 1];
                 const float *dl = t->deltas + (size_t)cur * p->neuron_offsets[l + 1];
                 const float *al = l == 0 ? bx : t->acts + (size_t)cur * p->neuron_offsets[l];
-                DEV(spgk_train_grad(dl, fo, al, fi, G + p->weight_offsets[l], fi, G + tw + p->bias_offsets[l],
+                SDEV(spgk_train_grad(dl, fo, al, fi, G + p->weight_offsets[l], fi, G + tw + p->bias_offsets[l],
                                     fo, fi, cur, gs, st), "train: gradients");
                 if (s_world > 1 && !fused_x) {
-                    DEV(spgk_event_record(s_ev_ready, st), "train: exchange order");
-                    DEV(spgk_stream_wait_event(s_ar_stream, s_ev_ready), "train: exchange order");
+                    SDEV(spgk_event_record(s_ev_ready, st), "train: exchange order");
+                    SDEV(spgk_stream_wait_event(s_ar_stream, s_ev_ready), "train: exchange order");
                     if (l == 0)             /* the bias gradients of every layer are complete now: one launch for both */
-                        DEV(spgk_nccl_allreduce_sum2(s_comm, G + p->weight_offsets[l], (uint64_t)fi * fo, G + tw, tb,
+                        SDEV(spgk_nccl_allreduce_sum2(s_comm, G + p->weight_offsets[l], (uint64_t)fi * fo, G + tw, tb,
                                                      s_ar_stream), "train: all-reduce");
                     else
-                        DEV(spgk_nccl_allreduce_sum(s_comm, G + p->weight_offsets[l], (uint64_t)fi * fo, s_ar_stream),
+                        SDEV(spgk_nccl_allreduce_sum(s_comm, G + p->weight_offsets[l], (uint64_t)fi * fo, s_ar_stream),
                             "train: all-reduce");
                 }
                 if (l > 0)
-                    DEV(spgk_train_gemm(1, dl, fo, P + p->weight_offsets[l], fi,
+                    SDEV(spgk_train_gemm(1, dl, fo, P + p->weight_offsets[l], fi,
                                         t->deltas + (size_t)cur * p->neuron_offsets[l], fi, cur, fi, fo, 1.0f, NULL,
                                         t->acts + (size_t)cur * p->neuron_offsets[l], fi, (int)p->act_func[l - 1], st), "train: delta");
             }
             if (s_world > 1 && !fused_x) {
-                DEV(spgk_event_record(s_ev_done, s_ar_stream), "train: exchange order");
-                DEV(spgk_stream_wait_event(st, s_ev_done), "train: exchange order");
+                SDEV(spgk_event_record(s_ev_done, s_ar_stream), "train: exchange order");
+                SDEV(spgk_stream_wait_event(st, s_ev_done), "train: exchange order");
             }
-            p->time_step++;
-            b1pow *= a.beta1;
-            b2pow *= a.beta2;
-            const float mf = 1.0f / (1.0f - b1pow), vf = 1.0f / (1.0f - b2pow);
             if (clip) {
-                DEV(spgk_memset(d_sumsq, 0, 4, st), "train: clear norm");
-                DEV(spgk_sumsq(G, np, d_sumsq, st), "train: gradient norm");
+                SDEV(spgk_memset(d_sumsq, 0, 4, st), "train: clear norm");
+                SDEV(spgk_sumsq(G, np, d_sumsq, st), "train: gradient norm");
             }
             if (fused_x)
-                DEV(spgk_xchg_step(s_xchg, (int)a.optimizer_type, tw, a.learning_rate, a.momentum, a.beta1, a.beta2, mf, vf, a.epsilon,
-                                   a.weight_decay > 0.0f ? a.weight_decay : 0.0f, 1.0f / (float)s_world, st), "train: exchange and update");
+                SDEV(spgk_xchg_step(s_xchg, (int)a.optimizer_type, tw, a.learning_rate, a.momentum, a.beta1, a.beta2, mf, vf, a.epsilon,
+                                   a.weight_decay > 0.0f ? a.weight_decay : 0.0f, 1.0f / (float)s_world,
+                                   graph_mode ? (const float *)step_state + 4 : NULL, st), "train: exchange and update");
             else if (a.optimizer_type == OPTIMIZER_ADAM && a.weight_decay <= 0.0f && !clip)
-                DEV(spgk_adam(P, M, V, G, np, a.learning_rate, a.beta1, a.beta2, mf, vf, a.epsilon,
+                SDEV(spgk_adam(P, M, V, G, np, a.learning_rate, a.beta1, a.beta2, mf, vf, a.epsilon,
                               1.0f / (float)s_world, st), "train: adam");
             else
-                DEV(spgk_optimizer_step((int)a.optimizer_type, P, M, V, G, np, tw, a.learning_rate, a.momentum,
+                SDEV(spgk_optimizer_step((int)a.optimizer_type, P, M, V, G, np, tw, a.learning_rate, a.momentum,
                                         a.beta1, a.beta2, mf, vf, a.epsilon, a.weight_decay > 0.0f ? a.weight_decay : 0.0f,
                                         1.0f / (float)s_world, clip ? d_sumsq : NULL, a.max_grad_norm, st), "train: update");
+            if (!capture) break;
+            /* the launches above were recorded, not run: make the graph and run it, or -- if that fails -- issue them again */
+            in_capture = false;
+            if (spgk_graph_end(st, &graph_exec) == SPGK_OK) { DEV(spgk_graph_launch(graph_exec, st), "train: step (graph)"); break; }
+          capture_abort:
+            /* a launch that cannot be recorded, or a graph that cannot be made: give the capture up for good and issue the
+               step's launches directly (nothing of the step has run yet) */
+            if (in_capture) { void *x = NULL; spgk_graph_end(st, &x); spgk_graph_destroy(x); in_capture = false; }
+            spg_log(LOG_DEBUG, "train: no graph replay (%s)", spgk_error_string());
+            spingalett_clear_error();
+            graph_exec = NULL; graph_failed = true; capture = false;
+          }
         }
         /* end of the epoch: loss, NaN scan and the stop decision.  With several ranks the loss is summed and a stop wanted
            by any rank (its callback, a non-finite weight) stops all of them, so nobody is left in an exchange alone. */
@@ -513,6 +570,10 @@ void train_struct_arguments(TrainArgs a)
     spg_log(LOG_INFO, "Training completed.");
     failed = false;
 fail:
+    n->stream = caller_stream;
+    if (in_capture) { void *x = NULL; spgk_graph_end(st, &x); spgk_graph_destroy(x); }      /* never leave the stream capturing */
+    spgk_graph_destroy(graph_exec);
+    spgk_train_use_state(NULL);
     free(order);
     spgk_host_free(h_pinned);
     n->live_params = n->live_m = n->live_v = NULL;
