@@ -300,10 +300,11 @@ SPINGALETT_API int spingalett_synchronize(NeuralNetwork *net);
  * EXACT : two 16-bit terms hi+lo (>= 16 significant bits) at twice the tensor
  *         work; products with 16-bit or integer weights are exact and only the
  *         fp32 accumulation order differs from the reference.
- * FAST  : one 16-bit term (fp16, 11 significant bits; bf16 for BF16 files, 8
- *         bits).  Measured on the 784-512-1000-10 MLP: ~99.95 % argmax agreement
- *         with the reference with fp16, ~99.7 % with bf16, i.e. at or below the
- *         99.9 % parity bar.
+ * FAST  : one fp16 term per operand (11 significant bits; a BF16 file's weights
+ *         are exact in fp16 while they lie within its range -- checked once per
+ *         upload -- else bf16 terms, 8 bits, are used).  Measured on the
+ *         784-512-1000-10 MLP: ~99.95 % argmax agreement with the reference with
+ *         fp16, ~99.7 % with bf16, i.e. at or below the 99.9 % parity bar.
  * AUTO (default): the FAST pass, then every row whose two largest softmax
  *         outputs are within a margin (log p1 - log p2 < margin) is recomputed
  *         in EXACT mode and written over the fast result (so is a row whose

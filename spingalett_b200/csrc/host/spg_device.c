@@ -126,6 +126,7 @@ void spg_dev_release(spg_net *n)
     spgk_free(n->d_rep_idx); n->d_rep_idx = NULL; n->rep_idx_bytes = 0;
     n->auto_calibrated = false;
     n->auto_calls = 0;
+    n->bf16_fits_f16 = 0;
     spgk_free(n->d_rep_in); n->d_rep_in = NULL; n->rep_in_bytes = 0;
     spgk_free(n->d_rep_out); n->d_rep_out = NULL; n->rep_out_bytes = 0;
     spgk_free(n->d_in32); n->d_in32 = NULL; n->in32_bytes = 0;
@@ -541,6 +542,27 @@ static bool weights_keepable(const spg_net *n, int type, bool exact)
     return wtotal <= SPG_W16_KEEP_MAX;
 }
 
+/* The one-term pass of a BF16 file takes fp16 operands when every weight is within fp16's range (any trained or
+ * initialised net: the check is one pass over the host mirror, once per upload): fp16 carries 11 significant bits of an
+ * activation against bf16's 8, an eighth of the rounding error, so AUTO lists about an eighth of the rows for the exact
+ * recomputation (which keeps bf16: two terms, fp32 range).  bf16 weights are exact in fp16 down to 6.1e-5; smaller
+ * ones keep an absolute error below 6e-8. */
+static bool bf16_file_as_f16(spg_net *n)
+{
+    if (!n->bf16_fits_f16) {
+        const NeuralNetwork *p = &n->pub;
+        float mx = 0.0f;
+        bool finite = true;
+        for (uint64_t i = 0; i < p->total_weights; i++) {
+            const float a = fabsf(p->weights[i]);
+            if (!(a <= 3.0e38f)) finite = false;
+            if (a > mx) mx = a;
+        }
+        n->bf16_fits_f16 = (finite && mx < 60000.0f) ? 1 : 2;
+    }
+    return n->bf16_fits_f16 == 1;
+}
+
 static _Thread_local bool dynamic_rows = false;      /* true around the repair chain of the AUTO mode */
 static _Thread_local const uint32_t *repair_rows = NULL;   /* repair chain: input row i is row repair_rows[i] of d_x, and its result goes back there */
 
@@ -556,7 +578,8 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
     /* 16-bit flavour: the file's own 16-bit type when it has one (exact
      * weights); otherwise fp16 for the one-term mode (11 significant bits) and
      * bf16 for the two-term mode (fp32 range, 16 bits over two terms). */
-    const int type = prec == PRECISION_FP16 ? SPGK_T_F16 : prec == PRECISION_BFLOAT16 ? SPGK_T_BF16
+    const int type = prec == PRECISION_FP16 ? SPGK_T_F16
+                   : prec == PRECISION_BFLOAT16 ? ((exact || !bf16_file_as_f16(n)) ? SPGK_T_BF16 : SPGK_T_F16)
                    : exact ? SPGK_T_BF16 : SPGK_T_F16;
     const int parts = exact ? 2 : 1;
     uint32_t maxld = 0;
@@ -646,14 +669,14 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
 #define SPG_AUTO_RECAL 1024u         /* large AUTO calls between two measurements of the margin */
 #define SPG_FUSED_MIN_ROWS 1024u     /* below this a handful of 128-row tiles cannot fill the GPU: the per-layer chain spreads better */
 
-/* 16-bit flavour of the one-term pass: the file's own 16-bit type when it has one (exact weights), else fp16 */
-static int fast_type(const spg_net *n)
+/* 16-bit flavour of the one-term pass: fp16, except for a BF16 file with weights beyond fp16's range */
+static int fast_type(spg_net *n)
 {
     const int prec = n->klayers[0].precision;
-    return prec == PRECISION_BFLOAT16 ? SPGK_T_BF16 : SPGK_T_F16;
+    return prec == PRECISION_BFLOAT16 && !bf16_file_as_f16(n) ? SPGK_T_BF16 : SPGK_T_F16;
 }
 
-static bool fused_eligible(const spg_net *n, const float *d_x, uint32_t N)
+static bool fused_eligible(spg_net *n, const float *d_x, uint32_t N)
 {
     if (n->dev_layers != 3 || N < SPG_FUSED_MIN_ROWS || ((uintptr_t)d_x & 15u)) return false;
     if (!spgk_mlp3_supported(&n->klayers[0], &n->klayers[1], &n->klayers[2], n->pub.topology[0])) return false;

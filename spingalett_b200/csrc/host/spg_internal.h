@@ -53,6 +53,7 @@ typedef struct spg_net_s {
     /* AUTO math mode: rows recomputed exactly after the one-term pass */
     uint32_t *d_rep_idx; size_t rep_idx_bytes; float *d_rep_in; size_t rep_in_bytes; float *d_rep_out; size_t rep_out_bytes;
     uint32_t last_repaired; bool auto_calibrated; float auto_theta;
+    uint8_t bf16_fits_f16;                /* BF16 file: 0 not looked at yet, 1 every weight is within fp16's range, 2 not */
     uint32_t auto_calls;                  /* large AUTO calls since the calibration: every SPG_AUTO_RECAL-th one measures again */
     uint32_t *h_count; bool count_pending, count_seen;      /* pinned: [slot] repaired-row counts of the last AUTO call (one slot per pipelined chunk) */
     uint32_t count_slot, count_slots_used;
