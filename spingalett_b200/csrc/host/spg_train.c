@@ -41,6 +41,7 @@ typedef struct {
     float *words;                            /* [0] loss, [1] non-finite flag, [2] sum of squared gradients, [8..] rank agreement */
     size_t cap[12];                          /* bytes held by each of the buffers above, in declaration order */
     uint64_t np;                             /* parameters the flat buffers were sized for */
+    void *stream;                            /* a stream of the library's own for nets that sit on the legacy default stream */
 } train_state;
 
 /* process-wide communicator for the gradient exchange */
@@ -52,8 +53,6 @@ static void *s_ar_stream = NULL, *s_ev_ready = NULL, *s_ev_done = NULL;
 /* the one-kernel exchange over peer memory (spgk_xchg_*): created by the first data-parallel train() call for its
    parameter count, kept for later calls; NULL = the NCCL exchange */
 static void *s_xchg = NULL;
-/* a stream of the library's own for train() calls of nets that sit on the legacy default stream (one per process) */
-static void *s_train_stream = NULL;
 
 static void dist_release(void)
 {
@@ -112,6 +111,7 @@ static void state_free(train_state *t)
     void *bufs[] = { t->params, t->grads, t->m, t->v, t->acts, t->deltas, t->data_x, t->data_t, t->batch_x, t->batch_t,
                      t->idx, t->words };
     for (size_t i = 0; i < sizeof bufs / sizeof bufs[0]; i++) spgk_free(bufs[i]);
+    spgk_stream_destroy(t->stream);
     free(t);
 }
 
@@ -260,8 +260,8 @@ void train_struct_arguments(TrainArgs a)
        the call itself ends with a synchronisation, so later work on the caller's stream is ordered behind it. */
     void *const caller_stream = n->stream;
     if ((uintptr_t)n->stream <= 2) {
-        if (!s_train_stream && spgk_stream_create(&s_train_stream) != SPGK_OK) { spingalett_clear_error(); s_train_stream = NULL; }
-        if (s_train_stream && spgk_stream_sync(n->stream) == SPGK_OK) n->stream = s_train_stream;
+        if (!t->stream && spgk_stream_create(&t->stream) != SPGK_OK) { spingalett_clear_error(); t->stream = NULL; }
+        if (t->stream && spgk_stream_sync(n->stream) == SPGK_OK) n->stream = t->stream;
     }
     void *st = n->stream;
     uint32_t *order = NULL;
