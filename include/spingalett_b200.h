@@ -326,7 +326,9 @@ SPINGALETT_API int spingalett_synchronize(NeuralNetwork *net);
  *         with EXACT is that measurement's expectation (the parity tests allow
  *         3 differing rows in 16384), not a guarantee.  Callers that need the
  *         guarantee use SPINGALETT_MATH_EXACT.
- * The small-batch paths always use exact products (they are memory-bound). */
+ * The small-batch paths always use exact products (they are memory-bound), and
+ * AUTO runs batches of up to 512 rows in EXACT: a chain that is bound by
+ * streaming the weights pays next to nothing for the second term. */
 typedef enum { SPINGALETT_MATH_FAST = 0, SPINGALETT_MATH_EXACT = 1, SPINGALETT_MATH_AUTO = 2 } SpingalettMathMode;
 SPINGALETT_API void spingalett_set_math_mode(SpingalettMathMode mode);
 SPINGALETT_API SpingalettMathMode spingalett_get_math_mode(void);

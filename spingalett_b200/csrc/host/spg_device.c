@@ -666,6 +666,7 @@ static int large_chain(spg_net *n, const float *d_x, uint32_t N, float *d_out, b
 
 /* ---- the three-layer net in one launch ------------------------------------ */
 
+#define SPG_AUTO_EXACT_ROWS 512u     /* AUTO runs batches of up to this many rows in EXACT */
 #define SPG_AUTO_RECAL 1024u         /* large AUTO calls between two measurements of the margin */
 #define SPG_FUSED_MIN_ROWS 1024u     /* below this a handful of 128-row tiles cannot fill the GPU: the per-layer chain spreads better */
 
@@ -730,6 +731,10 @@ int spg_dev_forward_large(spg_net *n, const float *d_x, uint32_t N, float *d_out
     if (mode == SPINGALETT_MATH_FAST && fused) return fused_pass(n, d_x, N, d_out, false, NULL, NULL, 0, 0.0f, NULL, NULL);
     if (mode != SPINGALETT_MATH_AUTO) return large_chain(n, d_x, N, d_out, mode == SPINGALETT_MATH_EXACT);
     if (!softmax_out) return large_chain(n, d_x, N, d_out, true);
+    /* Few rows: the chain is bound by streaming the weights (or by latency), where the exact chain's second pass over K
+     * is nearly free, while the one-term pass plus the recomputation chain costs two chains: 0.70 ms against 1.05 ms at
+     * 256 rows of the large INT4 net, 1.00 against 1.20 at 512 (the curves cross near 700 rows). */
+    if (N <= SPG_AUTO_EXACT_ROWS) return large_chain(n, d_x, N, d_out, true);
 
     int rc;
     if ((rc = reserve((void **)&n->d_rep_idx, &n->rep_idx_bytes, (size_t)N * 4 + 256, "repair index"))) return rc;

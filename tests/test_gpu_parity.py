@@ -156,12 +156,12 @@ def test_config_mlp_784_512_1000_10(spg, oracle, tmp_path_factory, prec, n, math
     net.free()
 
 
-@pytest.mark.parametrize("n", [512, 4096])
+@pytest.mark.parametrize("n", [768, 4096])
 def test_auto_mode_recomputes_rows_that_leave_the_fp16_range(spg, oracle, tmp_path_factory, n):
     """The one-term pass of a non-bf16 file runs on fp16 operands: an input beyond 65504 (or a hidden value that overflows)
     gives non-finite logits there.  AUTO lists such rows with the low-margin ones and recomputes them with two bf16 terms
-    (fp32 range), so its result for them is the exact mode's; every other row is untouched by their presence.  n = 512 takes
-    the per-layer chain, n = 4096 the one-launch kernel."""
+    (fp32 range), so its result for them is the exact mode's; every other row is untouched by their presence.  n = 768 takes
+    the per-layer chain, n = 4096 the one-launch kernel (up to 512 rows AUTO runs EXACT outright)."""
     d = tmp_path_factory.getbasetemp()
     path = nets.make_net_file(spg, str(d / "A_range_int8.nn"), nets.A_TOPO, nets.A_ACTS, 3, seed=1234, reference_rng=True)
     net = spg.Network.load(path)
