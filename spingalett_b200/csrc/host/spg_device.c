@@ -1043,9 +1043,10 @@ static float *forward_batch_on(spg_net *n, ForwardBatchArgs a)
     for (uint32_t l = 0; l < n->dev_layers && gemv_groups; l++)
         if (!spgk_gemv_scratch_bytes(&n->klayers[l], SPGK_GEMV_MAX_BATCH)) gemv_groups = false;
     const uint32_t group = N <= SPGK_GEMV_MAX_BATCH ? N : (gemv_groups ? SPGK_GEMV_MAX_BATCH : 128u);
-    /* more than one group of 128 rows: the GEMM chain on kept 16-bit operands (1.06 ms at 256 rows of the large INT4
-     * net) beats two or more passes of the streaming kernel (1.77 ms) whenever those operands fit the keep budget */
-    const bool chain_kept = N > 128 && weights_keepable(n, fast_type(n), false) && weights_keepable(n, SPGK_T_BF16, true);
+    /* from about a hundred rows on the GEMM chain on kept 16-bit operands (0.70 ms at 128 and at 256 rows of the large
+     * INT4 net, two-term) beats the streaming kernel (0.58 ms at 64 rows, 0.88 ms at 128, 1.77 ms for the two passes of
+     * 256) whenever those operands fit the keep budget */
+    const bool chain_kept = N > 96 && weights_keepable(n, fast_type(n), false) && weights_keepable(n, SPGK_T_BF16, true);
     if (N <= SPGK_GEMV_MAX_BATCH || gemv_groups || (N <= 512 && !chain_kept && all_wstream(n, N < group ? N : group))) {
         for (uint32_t r0 = 0; r0 < N; r0 += group) {
             const uint32_t rows = N - r0 < group ? N - r0 : group;

@@ -84,8 +84,8 @@ def test_large_int4_mlp_batch_sweep(spg, l_net, n):
     x = nets.normal_inputs(n, nets.L_TOPO[0], seed=100 + n)
     spg.set_math_mode(spg.abi.MATH_EXACT)
     got = net.forward_batch(x)
-    # 9..24 rows: GEMV in groups of 8; up to 128 rows: one pass of the streaming kernel; beyond: the GEMM chain on kept operands
-    assert spg.last_path() == ("gemv" if n <= 24 else "wstream" if n <= 128 else "tcgen05")
+    # 9..24 rows: GEMV in groups of 8; up to 96 rows: one pass of the streaming kernel; beyond: the GEMM chain on kept operands
+    assert spg.last_path() == ("gemv" if n <= 24 else "wstream" if n <= 96 else "tcgen05")
     rows = np.arange(n) if n <= 64 else np.random.default_rng(2).choice(n, 64, replace=False)
     want = onet.forward_batch(x[rows])
     agree, err = nets.parity(got[rows], want)
