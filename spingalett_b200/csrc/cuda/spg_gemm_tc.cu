@@ -589,8 +589,11 @@ spg_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         for (uint32_t ti = 0; ti < ntile; ti++) {
             uint32_t mt, nt;
             my_tile(p, rl, ti, mt, nt);
-            for (uint32_t ps = 0; ps < p.npass; ps++) {
-                for (uint32_t kb = 0; kb < p.kblocks; kb++, it++) {
+            // k-block outermost, the passes of a multi-term product inside: the weight tile of a k-block is fetched for every
+            // pass, and fetched back to back the second fetch is an L2 hit -- with the passes outermost a small batch on a
+            // large layer (weight panel of a tile beyond L2) streamed the weights from HBM once per pass
+            for (uint32_t kb = 0; kb < p.kblocks; kb++) {
+                for (uint32_t ps = 0; ps < p.npass; ps++, it++) {
                     const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
                     mbar_wait_uniform(empty0 + 8 * s, ph ^ 1u, abort_addr, p.status, 1, WAIT_LIMIT);
                     if (elect_one()) {
