@@ -4,7 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
                     [--dtype int8] [--batch 65536] [--math exact|fast] [--all-dtypes]
 
-The default line also carries a `train` object: the data-parallel Adam training configuration at the same rank count.
+The default line also carries a `train` object: the data-parallel Adam training configuration at the same rank count,
+and, on one GPU, an `other_configs` object: the wide BF16 net at 16384 rows and the large INT4 net at 1 and 64 rows,
+each measured by this script in a child process (`--workload wide|large`), so that every configuration is in one run.
 
 One "step" is one forward pass of the 784-512-1000-10 MLP (weights stored in
 the chosen .nn precision, INT8 by default) over one batch of 65536 synthetic
@@ -83,6 +85,7 @@ def parse():
     ap.add_argument("--one-dtype", action="store_true", help="skip the per-dtype table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-train", action="store_true", help="skip the training leg of the mlp workload")
+    ap.add_argument("--no-others", action="store_true", help="skip the other configurations (wide, large) of the default line")
     ap.add_argument("--train", action="store_true", help="secondary line: data-parallel Adam training steps (256 rows per GPU per step) instead of inference")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -463,6 +466,29 @@ def train_leg(spg, torch, dist, rank, world, epochs):
             "note": "one train() call: host arrays in, weights and optimiser state back on the host at the end, inside the timed region; the faster of two identical calls (calls_ms)"}
 
 
+def other_configs():
+    """The wide BF16 net (16384 rows, AUTO) and the large INT4 net (1 row: GEMV; 64 rows: weight streaming), each run by
+    this script in a child process once the parent's measurement is over; a short form of each child's line is kept.
+    A child that fails leaves its error text in its place: the parent's line does not depend on it."""
+    out = {}
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT")}
+    for key, extra in (("wide_bf16_b16384_auto", ["--workload", "wide", "--steps", "5"]),
+                       ("large_int4_b1", ["--workload", "large", "--batch", "1"]),
+                       ("large_int4_b64", ["--workload", "large", "--batch", "64"])):
+        cmd = [sys.executable, os.path.abspath(__file__), *extra, "--one-dtype", "--no-cpu"]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env)
+            d = json.loads(r.stdout.strip().splitlines()[-1])
+            rf = d.get("roofline") or {}
+            out[key] = {"value": d["value"], "unit": d["unit"], "ms_per_step": d["ms_per_step"], "steps": d["steps"],
+                        "workload": d["config"]["workload"], "path": d["config"]["path"], "dtype": d["dtype"],
+                        "e2e": d["e2e"]["value"], "gpu_launches": d["gpu_launches"], "clocks": d.get("clocks"),
+                        "roofline": {k: rf.get(k) for k in ("bound", "achieved", "peak", "unit", "frac", "whole_step_frac", "kernel")}}
+        except Exception as e:                      # noqa: BLE001 - reported, not fatal
+            out[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    return out
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -580,6 +606,11 @@ def main():
         sample = min(batch, 16384 if args.workload == "mlp" else 64)
         cb = cpu_arm(path, x, 3, 1, sample)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if args.workload == "mlp" and world == 1 and not args.no_others and not args.one_dtype:
+        torch.cuda.synchronize()
+        del x_dev, y_dev, x_pin, y_pin
+        torch.cuda.empty_cache()
+        line["other_configs"] = other_configs()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
