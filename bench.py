@@ -30,9 +30,11 @@ no collective), so scaling is weak: `value` is all ranks' rows per second.
 `--impl reference` runs only that CPU arm and prints the same JSON shape.
 """
 import argparse
+import atexit
 import ctypes
 import json
 import os
+import shutil
 import subprocess
 import sys
 import tempfile
@@ -262,6 +264,7 @@ def run_reference(args):
         return
     from oracle import Reference
     tmpdir = tempfile.mkdtemp(prefix="spg_bench_")
+    atexit.register(shutil.rmtree, tmpdir, ignore_errors=True)      # the .nn files of the large nets are hundreds of MB
     if Reference.available():
         path = reference_net_file(args.dtype, tmpdir, args.workload)
     else:
@@ -514,6 +517,7 @@ def main():
     spg.set_math_mode({"exact": spg.abi.MATH_EXACT, "fast": spg.abi.MATH_FAST, "auto": spg.abi.MATH_AUTO}[args.math])
     pk = peaks()
     tmpdir = tempfile.mkdtemp(prefix=f"spg_bench_r{rank}_")
+    atexit.register(shutil.rmtree, tmpdir, ignore_errors=True)      # the .nn files of the large nets are hundreds of MB
     batch = args.batch
 
     topo = args.topo
